@@ -1,0 +1,177 @@
+"""CPU checks that pin the oracle to the reference's own known answers."""
+
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from oracle import beam_oracle as bo
+from multigpubeamsearch_b200 import puzzles
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def _golden_state(case):
+    if case["kind"] == "arange":
+        return np.arange(120, dtype=np.uint8)
+    hi = int(case["kind"][len("uniform"):])
+    return np.random.default_rng(case["seed"]).integers(0, hi, size=120, dtype=np.uint8)
+
+
+def test_hash64_matches_reference_cpu_helper():
+    data = json.loads((GOLDEN / "hash64_reference.json").read_text())
+    assert data["state_size"] == 120
+    states = np.stack([_golden_state(c) for c in data["cases"]])
+    h = bo.hash64(states)
+    assert [int(x) for x in h] == [c["hash64"] for c in data["cases"]]
+    # the reference documents this value for the identity arrangement
+    assert int(h[0]) == 0x64F5E55CD40D3123
+    for w in (2, 3, 8):
+        assert bo.owner_rank(h, w).tolist() == [c[f"owner_w{w}"] for c in data["cases"]]
+
+
+def test_hash64_scalar_definition():
+    # independent scalar restatement with Python ints
+    rng = np.random.default_rng(5)
+    for n in (16, 54, 96, 120):
+        s = rng.integers(0, 8, size=(7, n), dtype=np.uint8)
+        for row, got_h, got_f in zip(s, bo.hash64(s), bo.fingerprint64(s)):
+            h = bo.FNV_OFFSET
+            f = bo.GOLDEN
+            for v in row.tolist():
+                h = ((h ^ v) * bo.FNV_PRIME) & bo.MASK64
+                f ^= (v + bo.GOLDEN + (f << 6) + (f >> 2)) & bo.MASK64
+                f &= bo.MASK64
+
+            def mix(x):
+                x ^= x >> 33
+                x = (x * 0xFF51AFD7ED558CCD) & bo.MASK64
+                x ^= x >> 33
+                x = (x * 0xC4CEB9FE1A85EC53) & bo.MASK64
+                x ^= x >> 33
+                return x
+
+            h = mix(h)
+            if h in (0, 1, 2):
+                h += 4
+            f = mix(f ^ bo.FP_XOR)
+            if f == 0:
+                f = 4
+            assert int(got_h) == h and int(got_f) == f
+
+
+def test_dedup_known_answers_stream3():
+    # tests/stream3_dedup_smoke.py:73-147: duplicates resolve to the min (score, payload)
+    a, b, c = (0x101, 0xAAA), (0x202, 0xBBB), (0x303, 0xCCC)
+    keys = [a, a, b, b, c]
+    vals = [(50, 0), (40, 1), (40, 2), (40, 3), (10, 24)]
+    best = bo.dedup_by_key(keys, vals)
+    assert best == {a: (40, 1), b: (40, 2), c: (10, 24)}
+
+
+def test_dedup_known_answers_stream4():
+    # tests/stream4_shard_smoke.py:45-105: score beats parent beats route; threshold 100 drops score 200
+    a, b, c, d = (0x101, 0xAAA), (0x202, 0xBBB), (0x303, 0xCCC), (0x404, 0xDDD)
+    metas = [(a, 10, 80, 0x010101), (b, 20, 90, 0x020202), (a, 9, 70, 0x030303),
+             (b, 19, 90, 0x040404), (c, 30, 200, 0x050505), (d, 40, 10, 0x060606)]
+    kept = [(k, (score, parent, route)) for k, parent, score, route in metas if score <= 100]
+    best = bo.dedup_by_key([k for k, _ in kept], [v for _, v in kept])
+    assert best[a] == (70, 9, 0x030303)
+    assert best[b] == (90, 19, 0x040404)
+    assert best[d] == (10, 40, 0x060606)
+    assert c not in best and len(best) == 3
+
+
+def test_threshold_rules():
+    # beam_engine.py:1662-1759: six survivors [10,20,40 | 30,50,60], beam 6 -> T = 60
+    assert bo.v6_histogram_threshold([10, 20, 40, 30, 50, 60], 6) == 60
+    assert bo.v6_histogram_threshold([10, 20, 40, 30, 50, 60], 3) == 30
+    assert bo.v6_histogram_threshold([], 3) == bo.UINT32_MAX
+    assert bo.v6_histogram_threshold([1, 2], 3) == bo.UINT32_MAX
+    # beam_types.hpp:125-134: unset until enough survivors, then monotone
+    assert bo.v6_threshold_update(bo.UINT32_MAX, False, 5, 6, 77) == (bo.UINT32_MAX, False)
+    assert bo.v6_threshold_update(bo.UINT32_MAX, False, 6, 6, 60) == (60, True)
+    assert bo.v6_threshold_update(60, True, 9, 6, 80) == (60, True)
+    assert bo.v6_threshold_update(60, True, 9, 6, 40) == (40, True)
+    assert bo.v6_threshold_update(60, True, 2, 6, 10) == (60, True)
+    # beam_kernels.cu:657-680
+    assert bo.legacy_threshold([5, 5, 7, 9], 2) == (True, 7)
+    assert bo.legacy_threshold([5, 5, 7, 9], 5) == (False, 0)
+    # tests/test_architecture_v6_static.py:69-114 score constants
+    assert bo.SCORE_BIN_COUNT == 76801
+    assert int(bo.q_to_score_key(np.float32(300.0))) == 76800
+    assert int(bo.q_to_score_key(np.float32(1e9))) == 76800
+    assert int(bo.q_to_score_key(np.float32(-3.0))) == 0
+
+
+def test_balance_targets():
+    # production_v6_dispatcher.py:584-588
+    rank, local = bo.balance_targets(10, 4)
+    assert rank.tolist() == [0, 0, 0, 1, 1, 2, 2, 2, 3, 3]
+    assert local.tolist() == [0, 1, 2, 0, 1, 0, 1, 2, 0, 1]
+
+
+def test_legacy_hamming_q():
+    # beam_kernels.cu:133-143
+    assert bo.legacy_hamming_q([0, 1, 2, 127, 200]).tolist() == [65535, 65023, 64511, 511, 1]
+
+
+def test_select_mode_nesting():
+    pz = puzzles.puzzle54()
+    f = np.stack([pz.scramble(j, 12) for j in range(40)])
+    c = bo.expand(f, pz.generators)
+    k = bo.hamming(c, pz.solved)
+    payload = np.arange(c.shape[0], dtype=np.uint32)
+    u = bo.dedup_exact(c, k, payload)
+    for beam in (1, 17, 100, 10 ** 6):
+        legacy = set(bo.select(u, beam, "legacy_strict").tolist())
+        exact = set(bo.select(u, beam, "exact_k").tolist())
+        incl = set(bo.select(u, beam, "v6_inclusive").tolist())
+        assert len(exact) == min(beam, u.score.size)
+        assert legacy <= exact <= incl
+
+
+def test_expand_inverse_pairs_and_identity_generators():
+    pz = puzzles.puzzle54()
+    g = pz.fanout // 2
+    s = pz.scramble(3, 20)[None, :]
+    c = bo.expand(s, pz.generators)
+    for m in range(g):
+        back = bo.expand(c[m:m + 1], pz.generators)[m + g]
+        assert np.array_equal(back, s[0])  # data_loader.validate_inverse_pairs
+    # tests/dispatcher_skeleton_smoke.py:11-46: identity generators collapse 2 parents x 24 moves to 2 unique
+    ident = np.tile(np.arange(20, dtype=np.uint8), (24, 1))
+    f = np.stack([np.arange(20, dtype=np.uint8), np.arange(20, dtype=np.uint8)[::-1].copy()])
+    ch = bo.expand(f, ident)
+    u = bo.dedup_exact(ch, np.zeros(48, np.uint32), np.arange(48, dtype=np.uint32))
+    assert ch.shape[0] == 48 and u.score.size == 2
+    assert sorted(u.payload.tolist()) == [0, 24]
+
+
+def test_search_known_shallow_scrambles():
+    # scripts/kaggle_correctness_check.py:154-179: scrambles of length 0/1/2 are found at depth 0/1/2
+    pz = puzzles.puzzle54()
+    sc = bo.hamming_scorer(pz.solved)
+    g = pz.generators.astype(np.int64)
+    s0 = pz.solved
+    s1 = s0[g[0]]
+    s2 = s1[g[1]]
+    for start, depth in ((s0, 0), (s1, 1), (s2, 2)):
+        r = bo.search(start, pz.generators, pz.solved, sc, beam=64, max_depth=4)
+        assert r.found and r.depth == depth
+        assert np.array_equal(bo.replay(start, pz.generators, r.path), pz.solved)
+
+
+@pytest.mark.parametrize("world", [1, 2, 3])
+def test_search_lrx_world_invariance(world):
+    pz = puzzles.lrx(8)
+    sc = bo.hamming_scorer(pz.solved)
+    start = pz.scramble(1, 14)
+    base = bo.search(start, pz.generators, pz.solved, sc, beam=64, max_depth=30, keep_frontiers=True)
+    r = bo.search(start, pz.generators, pz.solved, sc, beam=64, max_depth=30, world=world, keep_frontiers=True)
+    assert (r.found, r.depth, r.frontier_sizes) == (base.found, base.depth, base.frontier_sizes)
+    for a, b in zip(base.frontiers, r.frontiers):
+        assert np.array_equal(a, b)
+    if r.found:
+        assert np.array_equal(bo.replay(start, pz.generators, r.path), pz.solved)
