@@ -1,0 +1,518 @@
+"""Python control plane of the B200 beam-search engine.
+
+Mirror of the reference's beam_engine.py: the same entry points (make_default_config, build_extension,
+init_distributed_if_needed, allocate_buffers, create_nccl_id, configure_engine, run_one_search) and the same
+``BeamEngine(cfg, buffers, backend)`` object with the method names of the reference's pybind class
+(beam_engine.cpp:2114-2148).  Python owns all device memory as torch tensors; the engine underneath is
+libmgbs_b200.so, reached through its C ABI (include/mgbs.h).  There is no CPU fallback.
+
+Differences that a caller of the reference will notice:
+  * state length, fan-out and value range are run-time config keys (state_len, fanout, num_values) instead of
+    the compile-time 120 / 24;
+  * scores are "lower is better" integer keys (the v6 orientation, beam_types.hpp:22-27);
+  * selection keeps exactly GLOBAL_BEAM_WIDTH states, ties broken on (score, hash, fingerprint); the reference's
+    two threshold rules are available as select_mode "v6_inclusive" and "legacy_strict".
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Any, Dict, List, Optional
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from . import build as _build
+from .puzzles import Puzzle
+
+HISTORY_NONE = 0xFFFFFFFF
+
+
+def _flag_enabled(name: str, default: str = "0") -> bool:
+    return os.environ.get(name, default).strip().lower() not in {"", "0", "false", "no", "off"}
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+def make_default_config() -> Dict[str, Any]:
+    """Config dict from the environment; reference keys and env names (beam_engine.py:68-109) plus the shape keys."""
+    world_size = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    state_len = int(os.environ.get("STATE_LEN", "54"))
+    return {
+        "world_size": world_size,
+        "rank": rank,
+        "global_beam_width": int(os.environ.get("GLOBAL_BEAM_WIDTH", str(1 << 16))),
+        "fanout": int(os.environ.get("FANOUT", "12")),
+        "state_len": state_len,
+        "state_size_bytes": _round_up(state_len, 16),
+        "num_values": int(os.environ.get("NUM_VALUES", "6")),
+        "b_micro": int(os.environ.get("B_MICRO", "32768")),
+        "probe_limit": int(os.environ.get("PROBE_LIMIT", "64")),
+        "bucket_cap_per_peer": int(os.environ.get("BUCKET_CAP_PER_PEER", "0")),
+        "gamma": float(os.environ.get("GAMMA", "1.05")),
+        "beta": float(os.environ.get("BETA", "1.15")),
+        "hash_load_factor": float(os.environ.get("HASH_LOAD_FACTOR", "0.55")),
+        "inference_backend": os.environ.get("INFERENCE_BACKEND", "central_hamming"),
+        "max_depth": int(os.environ.get("MAX_DEPTH", "4")),
+        "select_mode": os.environ.get("SELECT_MODE", "exact_k"),
+        "band_rounds": int(os.environ.get("BAND_ROUNDS", "6")),
+        "band_levels": int(os.environ.get("BAND_LEVELS", "3")),
+        "hash_bits": int(os.environ.get("ORDER_KEY_HASH_BITS", "44")),
+        "materialize_children": _flag_enabled("MATERIALIZE_CHILDREN"),
+        "use_cuda_graphs": _flag_enabled("USE_CUDA_GRAPHS", "1"),
+        "score_offset": float(os.environ.get("NN_SCORE_BIAS", "0.0")),
+    }
+
+
+def config_for_puzzle(puzzle: Puzzle, **overrides: Any) -> Dict[str, Any]:
+    cfg = make_default_config()
+    cfg.update({
+        "state_len": puzzle.state_len,
+        "state_size_bytes": _round_up(puzzle.state_len, 16),
+        "fanout": puzzle.fanout,
+        "num_values": puzzle.num_values,
+    })
+    cfg.update(overrides)
+    return cfg
+
+
+class _Ext:
+    """What build_extension returns: the reference's module surface (BeamEngine, derive_sizes, get_nccl_unique_id)."""
+
+    def __init__(self, lib: C.CDLL):
+        self.lib = lib
+        self.BeamEngine = BeamEngine
+
+    def derive_sizes(self, cfg: Dict[str, Any]) -> Dict[str, int]:
+        """Derived sizes (ext.derive_sizes, beam_engine.cpp:1692-1748)."""
+        out = (C.c_int64 * 6)()
+        _lib.check(self.lib.mgbs_derive_sizes(int(cfg["global_beam_width"]), int(cfg["world_size"]),
+                                              float(cfg["gamma"]), float(cfg["beta"]),
+                                              float(cfg["hash_load_factor"]), int(cfg["band_rounds"]),
+                                              int(cfg["band_levels"]), out), "derive_sizes")
+        n_local, k_keep, k_work, hash_capacity, pool_target, hist_words = (int(x) for x in out)
+        world = int(cfg["world_size"])
+        fanout = int(cfg["fanout"])
+        cand_cap = k_work * fanout
+        bucket = int(cfg.get("bucket_cap_per_peer", 0))
+        if world > 1 and bucket <= 0:
+            # every rank sends about cand/world records to each peer; 25 % head-room plus a constant
+            bucket = int(cand_cap / world * 1.25) + 1024
+        return {
+            "n_local": n_local, "k_keep": k_keep, "k_work": k_work, "hash_capacity": hash_capacity,
+            "pool_target": pool_target, "hist_words": hist_words, "cand_cap": cand_cap,
+            "bucket_cap_per_peer": bucket if world > 1 else 0,
+            "hash_slot_bytes": 32, "candidate_record_bytes": 24 + int(cfg["state_size_bytes"]),
+            "history_records": int(cfg["max_depth"]) * k_work,
+            "ctrl_bytes": C.sizeof(_lib.MgbsCtrl),
+        }
+
+    def get_nccl_unique_id(self) -> bytes:
+        buf = (C.c_uint8 * 128)()
+        _lib.check(self.lib.mgbs_nccl_unique_id(_build.nccl_library_path().encode(), C.addressof(buf)),
+                   "get_nccl_unique_id")
+        return bytes(buf)
+
+
+def build_extension(verbose: bool = False) -> _Ext:
+    """Build (if needed) and load the native library; raises when it cannot (beam_engine.py:112-157)."""
+    if _build.needs_build():
+        _build.build(verbose=verbose)
+    return _Ext(_lib.load())
+
+
+def init_distributed_if_needed(cfg: Dict[str, Any]) -> None:
+    """beam_engine.py:160-168."""
+    if not torch.cuda.is_available():
+        raise RuntimeError("a CUDA device is required")
+    local_rank = int(os.environ.get("LOCAL_RANK", str(cfg["rank"] % torch.cuda.device_count())))
+    torch.cuda.set_device(local_rank)
+    if cfg["world_size"] > 1 and not dist.is_initialized():
+        dist.init_process_group(backend="nccl", rank=cfg["rank"], world_size=cfg["world_size"],
+                                device_id=torch.device("cuda", local_rank))
+
+
+def allocate_buffers(ext: _Ext, cfg: Dict[str, Any]) -> Dict[str, torch.Tensor]:
+    """Every device buffer of one engine, zeroed (allocate_buffers, beam_engine.py:171-234)."""
+    sizes = ext.derive_sizes(cfg)
+    device = torch.device("cuda", torch.cuda.current_device())
+    k_work = sizes["k_work"]
+    stride = int(cfg["state_size_bytes"])
+    cand_cap = sizes["cand_cap"]
+    world = int(cfg["world_size"])
+    need_children = bool(cfg.get("materialize_children")) or world > 1 or \
+        str(cfg.get("inference_backend", "")).lower() not in {"dummy", "central_hamming", "uniform"}
+
+    def z(shape, dtype):
+        return torch.zeros(shape, dtype=dtype, device=device)
+
+    buffers = {
+        "beam_current": z((k_work, stride), torch.uint8),
+        "beam_next": z((k_work, stride), torch.uint8),
+        "action_table": z((int(cfg["fanout"]), int(cfg["state_len"])), torch.uint8),
+        "central_state": z((int(cfg["state_len"]),), torch.uint8),
+        "cand_hash": z((cand_cap,), torch.int64),
+        "cand_fingerprint": z((cand_cap,), torch.int64),
+        "cand_score": z((cand_cap,), torch.int32),
+        "cand_payload": z((cand_cap,), torch.int32),
+        "hash_table": z((sizes["hash_capacity"] * 32,), torch.uint8),
+        "hist": z((sizes["hist_words"],), torch.int32),
+        "tie_buf": z((world * _lib.TIE_SEG_WORDS,), torch.int64),
+        "history_payload": z((max(1, int(cfg["max_depth"])), k_work), torch.int32),
+        "score_current": z((k_work,), torch.int32),
+        "score_next": z((k_work,), torch.int32),
+        "ctrl": z((C.sizeof(_lib.MgbsCtrl),), torch.uint8),
+    }
+    if need_children:
+        buffers["next_state_pool"] = z((cand_cap, stride), torch.uint8)
+    if world > 1:
+        cap = sizes["bucket_cap_per_peer"]
+        for side in ("send", "recv"):
+            buffers[f"{side}_hash"] = z((world * cap,), torch.int64)
+            buffers[f"{side}_fingerprint"] = z((world * cap,), torch.int64)
+            buffers[f"{side}_score"] = z((world * cap,), torch.int32)
+            buffers[f"{side}_payload"] = z((world * cap,), torch.int32)
+            buffers[f"{side}_states"] = z((world * cap, stride), torch.uint8)
+            buffers[f"{side}_counts"] = z((world,), torch.int32)
+    return buffers
+
+
+class BeamEngine:
+    """The reference's BeamEngine surface (beam_engine.cpp:2114-2148) over the C ABI."""
+
+    def __init__(self, cfg: Dict[str, Any], buffers: Dict[str, torch.Tensor], backend: str = "dummy"):
+        self.lib = _lib.load()
+        self.cfg = dict(cfg)
+        self.buffers = buffers
+        backend = (backend or "dummy").strip().lower()
+        if backend not in {"dummy", "central_hamming", "uniform", "mlp"}:
+            # the reference throws for backends it cannot build (beam_engine.cpp:700-703)
+            raise RuntimeError(f"unknown inference backend: {backend}")
+        self.backend = backend
+        self._sizes = _Ext(self.lib).derive_sizes(cfg)
+        self._stream = torch.cuda.current_stream()
+        self._use_graph = bool(cfg.get("use_cuda_graphs", True))
+        self._graph_used = False
+        self._scorer = None
+        self._uniform: Optional[int] = None
+        self._events = None
+        self._timing: Dict[str, float] = {}
+        c = _lib.MgbsConfig()
+        c.state_len = int(cfg["state_len"])
+        c.state_stride = int(cfg["state_size_bytes"])
+        c.fanout = int(cfg["fanout"])
+        c.world_size = int(cfg["world_size"])
+        c.rank = int(cfg["rank"])
+        mode = str(cfg.get("select_mode", "exact_k"))
+        if mode not in _lib.SELECT_MODES:
+            raise RuntimeError(f"unknown select_mode {mode!r}")
+        c.select_mode = _lib.SELECT_MODES[mode]
+        c.hash_bits = int(cfg.get("hash_bits", 44)) if mode == "exact_k" else 0
+        c.score_mode = {"dummy": _lib.SCORE_HAMMING, "central_hamming": _lib.SCORE_HAMMING,
+                        "uniform": _lib.SCORE_UNIFORM, "mlp": _lib.SCORE_EXTERNAL}[backend]
+        c.band_levels = int(cfg["band_levels"])
+        c.band_rounds = int(cfg["band_rounds"])
+        c.probe_limit = int(cfg["probe_limit"])
+        c.uniform_score = 0
+        c.global_beam_width = int(cfg["global_beam_width"])
+        c.frontier_cap = self._sizes["k_work"]
+        c.pool_target = self._sizes["pool_target"]
+        c.hash_capacity = self._sizes["hash_capacity"]
+        c.cand_cap = self._sizes["cand_cap"]
+        c.bucket_cap = self._sizes["bucket_cap_per_peer"]
+        c.history_depths = int(buffers["history_payload"].shape[0])
+        b = buffers
+
+        def p(name):
+            t = b.get(name)
+            if t is None:
+                return None
+            if not t.is_cuda or not t.is_contiguous():
+                raise RuntimeError(f"buffer {name} must be a contiguous CUDA tensor")  # check_cuda_*_tensor
+            return t.data_ptr()
+
+        c.frontier[0], c.frontier[1] = p("beam_current"), p("beam_next")
+        c.gens, c.solved = p("action_table"), p("central_state")
+        c.children = p("next_state_pool")
+        c.cand_hash, c.cand_fp = p("cand_hash"), p("cand_fingerprint")
+        c.cand_score, c.cand_payload = p("cand_score"), p("cand_payload")
+        c.table, c.hist, c.tie_buf = p("hash_table"), p("hist"), p("tie_buf")
+        c.history = p("history_payload")
+        c.frontier_score[0], c.frontier_score[1] = p("score_current"), p("score_next")
+        c.ctrl = p("ctrl")
+        for side in ("send", "recv"):
+            setattr(c, f"{side}_hash", p(f"{side}_hash"))
+            setattr(c, f"{side}_fp", p(f"{side}_fingerprint"))
+            setattr(c, f"{side}_score", p(f"{side}_score"))
+            setattr(c, f"{side}_payload", p(f"{side}_payload"))
+            setattr(c, f"{side}_states", p(f"{side}_states"))
+            setattr(c, f"{side}_counts", p(f"{side}_counts"))
+        if c.score_mode == _lib.SCORE_EXTERNAL and not c.children:
+            raise RuntimeError("a neural backend needs the next_state_pool buffer (materialised children)")
+        self._c = c
+        handle = C.c_void_p()
+        _lib.check(self.lib.mgbs_engine_create(C.byref(c), C.byref(handle)), "BeamEngine")
+        self._h = handle
+        self._ctrl = _lib.MgbsCtrl()
+        self._central: Optional[np.ndarray] = None
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            self.lib.mgbs_engine_destroy(h)
+            self._h = None
+
+    # -- set-up ---------------------------------------------------------------------------------
+    def _sp(self):
+        return C.c_void_p(self._stream.cuda_stream)
+
+    def init_nccl(self, unique_id: bytes) -> None:
+        if len(unique_id) != 128:
+            raise RuntimeError("NCCL unique id must be 128 bytes")
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        _lib.check(self.lib.mgbs_engine_init_nccl(self._h, _build.nccl_library_path().encode(), C.addressof(buf)),
+                   "init_nccl")
+
+    def set_action_permutation_table(self, table: bytes) -> None:
+        """fanout x state_len bytes, row-major gather tables (beam_engine.cpp:979-985)."""
+        n, g = int(self.cfg["state_len"]), int(self.cfg["fanout"])
+        if len(table) != n * g:
+            raise RuntimeError(f"action table must be {g}x{n} bytes, got {len(table)}")
+        arr = np.frombuffer(table, dtype=np.uint8).reshape(g, n)
+        if arr.max(initial=0) >= n:
+            raise RuntimeError("action table entry out of range")
+        self.buffers["action_table"].copy_(torch.from_numpy(arr.copy()))
+
+    def set_central_state(self, state: bytes) -> None:
+        n = int(self.cfg["state_len"])
+        if len(state) != n:
+            raise RuntimeError(f"central state must be {n} bytes, got {len(state)}")
+        self._central = np.frombuffer(state, dtype=np.uint8).copy()
+        self.buffers["central_state"].copy_(torch.from_numpy(self._central))
+
+    def set_scorer(self, scorer) -> None:
+        """Attach a device scorer object (see scorers.MLPValueScorer): it supplies a C callback and its handle."""
+        self._scorer = scorer
+        fn, user = scorer.c_callback()
+        _lib.check(self.lib.mgbs_engine_set_scorer(self._h, fn, user), "set_scorer")
+
+    def begin_uniform_score(self, score: int) -> None:
+        """Prepass fill: every child gets the same score (beam_engine.cpp:893-915)."""
+        self._uniform = int(score)
+        _lib.check(self.lib.mgbs_engine_set_score_mode(self._h, _lib.SCORE_UNIFORM, int(score)), "begin_uniform_score")
+
+    def set_uniform_score(self, score: int) -> None:
+        self.begin_uniform_score(score)
+
+    def end_uniform_score(self) -> None:
+        self._uniform = None
+        _lib.check(self.lib.mgbs_engine_set_score_mode(self._h, self._c.score_mode, 0), "end_uniform_score")
+
+    def enable_cuda_graphs(self, on: bool) -> None:
+        self._use_graph = bool(on)
+
+    def cuda_graph_captured(self) -> bool:
+        return self._graph_used
+
+    def enable_step_timers(self, on: bool) -> None:
+        self._events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) if on else None
+
+    def step_timing(self) -> Dict[str, float]:
+        return dict(self._timing)
+
+    # -- search ---------------------------------------------------------------------------------
+    def reset_search(self, state: bytes, active_on_this_rank: bool = True) -> None:
+        n = int(self.cfg["state_len"])
+        if len(state) != n:
+            raise RuntimeError(f"state must be {n} bytes, got {len(state)}")
+        solved = self._central is not None and bytes(self._central) == bytes(state)
+        buf = (C.c_uint8 * n).from_buffer_copy(state)
+        # every rank is given the start state, so every rank agrees on "found at depth 0"
+        _lib.check(self.lib.mgbs_engine_reset(self._h, C.addressof(buf), int(bool(active_on_this_rank)),
+                                              int(solved), self._sp()), "reset_search")
+        self._read_ctrl()
+
+    def clear_runtime_state(self) -> None:
+        zero = bytes(int(self.cfg["state_len"]))
+        _lib.check(self.lib.mgbs_engine_reset(self._h, zero, 0, 0, self._sp()), "clear_runtime_state")
+        self._read_ctrl()
+
+    def load_frontier(self, rows: np.ndarray, depth: int = 0) -> None:
+        """Make ``rows`` ([K, state_len] uint8) the current frontier at ``depth`` (test and benchmark entry)."""
+        rows = np.ascontiguousarray(rows, dtype=np.uint8)
+        if rows.ndim != 2 or rows.shape[1] != int(self.cfg["state_len"]):
+            raise RuntimeError("frontier rows must be [K, state_len] uint8")
+        _lib.check(self.lib.mgbs_engine_load_frontier(self._h, rows.ctypes.data_as(C.c_void_p), rows.shape[0],
+                                                      depth & 1, int(depth), self._sp()), "load_frontier")
+        self._read_ctrl()
+
+    def _read_ctrl(self) -> _lib.MgbsCtrl:
+        _lib.check(self.lib.mgbs_engine_read_ctrl(self._h, C.byref(self._ctrl), self._sp()), "status")
+        return self._ctrl
+
+    def step(self, histogram_period_micro: int = 8) -> None:
+        """One depth step (BeamEngine::step, beam_engine.cpp:1104-1116); asynchronous on the engine's stream."""
+        parity = self._ctrl.depth & 1
+        if self._events:
+            self._events[0].record(self._stream)
+        if self._use_graph:
+            _lib.check(self.lib.mgbs_engine_step_graph(self._h, parity, self._sp()), "step")
+            self._graph_used = True
+        else:
+            _lib.check(self.lib.mgbs_engine_enqueue_depth(self._h, parity, 0, self._sp()), "step")
+        if self._events:
+            self._events[1].record(self._stream)
+            self._events[1].synchronize()
+            self._timing = {"total_cuda_event_ms": self._events[0].elapsed_time(self._events[1])}
+        self._ctrl.depth += 1  # host shadow; status() refreshes it from the device
+
+    def step_current(self, histogram_period_micro: int = 8) -> None:
+        """Eager step without the graph (beam_engine.cpp:1118-1134)."""
+        parity = self._ctrl.depth & 1
+        _lib.check(self.lib.mgbs_engine_enqueue_depth(self._h, parity, 0, self._sp()), "step_current")
+        self._ctrl.depth += 1
+
+    def search(self, max_depth: int, histogram_period_micro: int = 8) -> Dict[str, Any]:
+        """Depth loop until found / max_depth / empty frontier (beam_engine.cpp:1147-1171)."""
+        _lib.check(self.lib.mgbs_engine_search(self._h, int(max_depth), int(self._use_graph), C.byref(self._ctrl),
+                                               self._sp()), "search")
+        self._graph_used = self._graph_used or self._use_graph
+        st = self.status()
+        return {"found": bool(st["found"]), "depth": int(st["found_depth"] if st["found"] else st["depth"]),
+                "status": st}
+
+    def status(self) -> Dict[str, Any]:
+        """Keys of the reference's status() (beam_engine.cpp:1173-1198) plus this engine's own counters."""
+        c = self._read_ctrl()
+        parity = c.depth & 1
+        from .records import unpack_payload
+        fp, fr, fm = unpack_payload(c.found_payload)
+        bits = int(c.status)
+        return {
+            "current_size": int(c.frontier_count[parity]),
+            "compacted_size": int(c.next_count),
+            "found": int(c.found),
+            "local_found": int(c.found and c.found_payload != 0xFFFFFFFF),
+            "found_local_index": int(fp) if c.found_payload != 0xFFFFFFFF else -1,
+            "found_action": int(fm) if c.found_payload != 0xFFFFFFFF else -1,
+            "found_depth": int(c.found_depth),
+            "cuda_graph_captured": self._graph_used,
+            "threshold_valid": int(c.threshold_key != 0xFFFFFFFFFFFFFFFF),
+            "threshold_q": int(c.threshold_key >> self._c.hash_bits) if c.threshold_key != 0xFFFFFFFFFFFFFFFF else 0,
+            "threshold_key": int(c.threshold_key),
+            "depth": int(c.depth),
+            "counters": [int(c.table_count), int(c.inserted_total), int(c.cand_count), int(c.unique_total),
+                         int(c.hash_overflow), int(c.rounds_used), int(c.bands_done), bits],
+            "status_bits": bits,
+            "status_names": [n for b, n in _lib.STATUS_NAMES.items() if bits & b],
+            "total_candidates": int(c.total_candidates),
+        }
+
+    def sizes(self) -> Dict[str, int]:
+        return dict(self._sizes)
+
+    # -- results --------------------------------------------------------------------------------
+    def _frontier_tensor(self, parity: int) -> torch.Tensor:
+        return self.buffers["beam_current" if parity == 0 else "beam_next"]
+
+    def frontier(self) -> np.ndarray:
+        """Current frontier rows [K, state_len] (host copy)."""
+        c = self._read_ctrl()
+        parity = c.depth & 1
+        k = int(c.frontier_count[parity])
+        n = int(self.cfg["state_len"])
+        return self._frontier_tensor(parity)[:k, :n].cpu().numpy()
+
+    def frontier_scores(self) -> np.ndarray:
+        c = self._read_ctrl()
+        parity = c.depth & 1
+        k = int(c.frontier_count[parity])
+        t = self.buffers["score_current" if parity == 0 else "score_next"]
+        return t[:k].cpu().numpy().astype(np.uint32)
+
+    def frontier_payloads(self) -> np.ndarray:
+        """Back-pointers (parent, rank, move packed) of the current frontier rows; depth must be >= 1."""
+        c = self._read_ctrl()
+        k = int(c.frontier_count[c.depth & 1])
+        return self.buffers["history_payload"][c.depth - 1, :k].cpu().numpy().astype(np.uint32)
+
+    def current_state_bytes(self, i: int) -> bytes:
+        c = self._read_ctrl()
+        parity = c.depth & 1
+        if i < 0 or i >= int(c.frontier_count[parity]):
+            raise RuntimeError("frontier index out of range")
+        return bytes(self._frontier_tensor(parity)[i, : int(self.cfg["state_len"])].cpu().numpy())
+
+    def history_entry(self, depth: int, local_index: int) -> Dict[str, int]:
+        """Back-pointer of row ``local_index`` of the depth ``depth``+1 frontier (beam_engine.cpp:1200-1219)."""
+        from .records import unpack_payload
+        h = self.buffers["history_payload"]
+        if depth < 0 or depth >= h.shape[0] or local_index < 0 or local_index >= h.shape[1]:
+            return {"valid": 0, "parent_idx": -1, "parent_rank": -1, "action": -1}
+        payload = int(h[depth, local_index].item()) & 0xFFFFFFFF
+        p, r, m = unpack_payload(payload)
+        return {"valid": 1, "parent_idx": int(p), "parent_rank": int(r), "action": int(m)}
+
+    def reconstruct_path(self) -> Optional[List[int]]:
+        """Moves from the start state to the solved state after a successful single-GPU search."""
+        from .records import unpack_payload
+        c = self._read_ctrl()
+        if not c.found:
+            return None
+        if c.found_depth == 0:
+            return []
+        if c.found_payload == 0xFFFFFFFF or int(self.cfg["world_size"]) > 1:
+            return None
+        p, _, m = unpack_payload(c.found_payload)
+        moves = [int(m)]
+        idx = int(p)
+        hist = self.buffers["history_payload"]
+        for d in range(c.found_depth - 2, -1, -1):
+            pp, _, mm = unpack_payload(int(hist[d, idx].item()) & 0xFFFFFFFF)
+            moves.append(int(mm))
+            idx = int(pp)
+        return moves[::-1]
+
+
+def create_nccl_id(ext: _Ext, cfg: Dict[str, Any]) -> bytes:
+    """Rank 0 creates the id, every rank receives it over torch.distributed (beam_engine.py:512-519)."""
+    if cfg["world_size"] <= 1:
+        return bytes(128)
+    obj = [ext.get_nccl_unique_id() if cfg["rank"] == 0 else None]
+    dist.broadcast_object_list(obj, src=0)
+    return obj[0]
+
+
+def configure_engine(puzzle: Puzzle, cfg: Optional[Dict[str, Any]] = None, scorer=None, **overrides: Any):
+    """Build, allocate, construct and wire one engine for a puzzle (configure_engine, beam_engine.py:2553-2603)."""
+    cfg = dict(cfg) if cfg is not None else config_for_puzzle(puzzle, **overrides)
+    ext = build_extension(verbose=False)
+    init_distributed_if_needed(cfg)
+    if scorer is not None:
+        cfg["inference_backend"] = "mlp"
+    buffers = allocate_buffers(ext, cfg)
+    engine = ext.BeamEngine(cfg, buffers, cfg["inference_backend"])
+    engine.set_action_permutation_table(puzzle.action_table_bytes())
+    engine.set_central_state(bytes(puzzle.solved))
+    if scorer is not None:
+        engine.set_scorer(scorer)
+    if cfg["world_size"] > 1:
+        engine.init_nccl(create_nccl_id(ext, cfg))
+    engine.enable_cuda_graphs(bool(cfg.get("use_cuda_graphs", True)))
+    return ext, cfg, buffers, engine
+
+
+def run_one_search(engine: BeamEngine, state: np.ndarray, max_depth: int) -> Dict[str, Any]:
+    """Reset on the owner rank and search (run_one_search, beam_engine.py)."""
+    state = np.ascontiguousarray(state, dtype=np.uint8)
+    world, rank = int(engine.cfg["world_size"]), int(engine.cfg["rank"])
+    n = int(engine.cfg["state_len"])
+    owner = int(engine.lib.mgbs_hash64_host(state.ctypes.data_as(C.c_void_p), n) % world)
+    engine.reset_search(bytes(state), active_on_this_rank=(owner == rank))
+    return engine.search(max_depth)

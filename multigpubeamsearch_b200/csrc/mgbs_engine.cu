@@ -1,0 +1,471 @@
+// Host side of the step library: the engine object, the per-depth enqueue order, CUDA-graph capture, and the
+// NCCL exchange for world > 1.  Takes the place of BeamEngine::enqueue_one_depth / capture_cuda_graph / search
+// (beam_engine.cpp:1465-1672, 1147-1171).  No device memory is allocated here: every buffer comes in through
+// MgbsConfig, as the reference's engine takes torch tensors from allocate_buffers.
+
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <new>
+
+#include "mgbs.h"
+#include "mgbs_device.cuh"
+#include "mgbs_internal.cuh"
+
+namespace {
+
+// NCCL is resolved at run time so that the library loads on a host without it (and without a link-time dependency
+// on a particular libnccl build).
+struct NcclApi {
+  void* handle = nullptr;
+  ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+  ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+  ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
+  bool ok = false;
+};
+
+NcclApi g_nccl;
+
+int load_nccl(const char* path) {
+  if (g_nccl.ok) return 0;
+  void* h = nullptr;
+  if (path && path[0]) h = dlopen(path, RTLD_NOW | RTLD_GLOBAL);
+  if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) return MGBS_ERR_NCCL;
+  g_nccl.handle = h;
+#define MGBS_SYM(field, name)                                          \
+  *reinterpret_cast<void**>(&g_nccl.field) = dlsym(h, name);           \
+  if (!g_nccl.field) return MGBS_ERR_NCCL;
+  MGBS_SYM(GetUniqueId, "ncclGetUniqueId")
+  MGBS_SYM(CommInitRank, "ncclCommInitRank")
+  MGBS_SYM(CommDestroy, "ncclCommDestroy")
+  MGBS_SYM(AllReduce, "ncclAllReduce")
+  MGBS_SYM(AllGather, "ncclAllGather")
+  MGBS_SYM(Send, "ncclSend")
+  MGBS_SYM(Recv, "ncclRecv")
+  MGBS_SYM(GroupStart, "ncclGroupStart")
+  MGBS_SYM(GroupEnd, "ncclGroupEnd")
+#undef MGBS_SYM
+  g_nccl.ok = true;
+  return 0;
+}
+
+}  // namespace
+
+struct MgbsEngine {
+  MgbsConfig cfg;
+  int sms = 148;
+  int key_bits = 64;
+  int final_levels = 6;
+  ncclComm_t comm = nullptr;
+  mgbs_scorer_fn scorer = nullptr;
+  void* scorer_user = nullptr;
+  cudaGraphExec_t graph[2] = {nullptr, nullptr};
+  MgbsCtrl host_ctrl;
+};
+
+#define MGBS_TRY(expr)            \
+  do {                            \
+    int _e = (int)(expr);         \
+    if (_e != 0) return _e;       \
+  } while (0)
+
+#define MGBS_NCCL(expr)                              \
+  do {                                               \
+    if ((expr) != ncclSuccess) return MGBS_ERR_NCCL; \
+  } while (0)
+
+extern "C" {
+
+int mgbs_version(void) { return 100; }
+int mgbs_sizeof_ctrl(void) { return (int)sizeof(MgbsCtrl); }
+int mgbs_sizeof_config(void) { return (int)sizeof(MgbsConfig); }
+
+static int64_t round_half_up(double x) { return (int64_t)(x + 0.5); }
+
+int mgbs_derive_sizes(int64_t global_beam_width, int32_t world_size, double gamma, double beta, double hash_load_factor,
+                      int32_t band_rounds, int32_t band_levels, int64_t* out6) {
+  if (global_beam_width <= 0 || world_size <= 0 || world_size > MGBS_MAX_WORLD || !out6) return MGBS_ERR_ARG;
+  if (gamma < 1.0 || beta < 1.0 || hash_load_factor <= 0.0 || hash_load_factor >= 1.0) return MGBS_ERR_ARG;
+  if (band_rounds < 1 || band_rounds > MGBS_MAX_ROUNDS || band_levels < 1 || band_levels > MGBS_MAX_LEVELS) return MGBS_ERR_ARG;
+  const int64_t n_local = (global_beam_width + world_size - 1) / world_size;  // beam_engine.cpp:245
+  const int64_t k_keep = round_half_up(gamma * (double)n_local);              // :247
+  const int64_t k_work = round_half_up(beta * (double)k_keep);                // :249
+  int64_t hash_capacity = round_half_up((double)k_work / hash_load_factor);   // :251-252
+  if (hash_capacity < 1024) hash_capacity = 1024;
+  out6[0] = n_local;
+  out6[1] = k_keep;
+  out6[2] = k_work;
+  out6[3] = hash_capacity;
+  out6[4] = round_half_up(beta * (double)n_local);
+  out6[5] = (int64_t)(band_rounds * band_levels + MGBS_MAX_LEVELS) * MGBS_HIST_STRIDE;
+  return 0;
+}
+
+uint64_t mgbs_hash64_host(const uint8_t* state, int32_t n) {
+  uint64_t h = mgbs::kFnvOffset;
+  for (int i = 0; i < n; ++i) h = (h ^ (uint64_t)state[i]) * mgbs::kFnvPrime;
+  return mgbs::finish_hash(h);
+}
+
+uint64_t mgbs_fingerprint64_host(const uint8_t* state, int32_t n) {
+  uint64_t f = mgbs::kGolden;
+  for (int i = 0; i < n; ++i) f ^= (uint64_t)state[i] + mgbs::kGolden + (f << 6) + (f >> 2);
+  return mgbs::finish_fingerprint(f);
+}
+
+int mgbs_engine_create(const MgbsConfig* cfg, MgbsEngine** out) {
+  if (!cfg || !out) return MGBS_ERR_ARG;
+  const MgbsConfig& c = *cfg;
+  if (c.state_len < 1 || c.state_len > MGBS_MAX_STATE_LEN) return MGBS_ERR_ARG;
+  if (c.state_stride < c.state_len || (c.state_stride % 16) != 0 || c.state_stride > MGBS_MAX_STATE_LEN) return MGBS_ERR_ARG;
+  const int words = c.state_stride / 4;
+  if (words != 4 && words != 8 && words != 16 && words != 24 && words != 32) return MGBS_ERR_UNSUPPORTED;
+  if (c.fanout < 1 || c.fanout > MGBS_MAX_FANOUT) return MGBS_ERR_ARG;
+  if (c.world_size < 1 || c.world_size > MGBS_MAX_WORLD || c.rank < 0 || c.rank >= c.world_size) return MGBS_ERR_ARG;
+  if (c.hash_bits < 0 || c.hash_bits > 44) return MGBS_ERR_ARG;
+  if (c.band_levels < 1 || c.band_levels > MGBS_MAX_LEVELS || c.band_rounds < 1 || c.band_rounds > MGBS_MAX_ROUNDS) return MGBS_ERR_ARG;
+  if (c.probe_limit < 1 || c.global_beam_width < 1) return MGBS_ERR_ARG;
+  if (c.frontier_cap < 1 || c.frontier_cap > (1 << 23) || c.hash_capacity < c.frontier_cap) return MGBS_ERR_ARG;
+  if (c.cand_cap < c.frontier_cap * c.fanout || c.cand_cap > 0xffffffffll) return MGBS_ERR_ARG;
+  if (!c.frontier[0] || !c.frontier[1] || !c.gens || !c.solved || !c.cand_hash || !c.cand_fp || !c.cand_score ||
+      !c.cand_payload || !c.table || !c.hist || !c.tie_buf || !c.ctrl)
+    return MGBS_ERR_ARG;
+  if (c.world_size > 1) {
+    if (!c.children || c.bucket_cap < 1 || !c.send_hash || !c.send_fp || !c.send_score || !c.send_payload ||
+        !c.send_states || !c.recv_hash || !c.recv_fp || !c.recv_score || !c.recv_payload || !c.recv_states ||
+        !c.send_counts || !c.recv_counts)
+      return MGBS_ERR_ARG;
+  }
+  if (c.select_mode != MGBS_SELECT_EXACT_K && c.hash_bits != 0) return MGBS_ERR_ARG;  // score-only order for the other modes
+  MgbsEngine* e = new (std::nothrow) MgbsEngine();
+  if (!e) return MGBS_ERR_STATE;
+  e->cfg = c;
+  e->key_bits = 20 + c.hash_bits;
+  e->final_levels = (e->key_bits + MGBS_RADIX_BITS - 1) / MGBS_RADIX_BITS;
+  if (e->cfg.band_levels > e->final_levels) e->cfg.band_levels = e->final_levels;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) e->sms = sms;
+  }
+  memset(&e->host_ctrl, 0, sizeof(MgbsCtrl));
+  *out = e;
+  return 0;
+}
+
+int mgbs_engine_destroy(MgbsEngine* e) {
+  if (!e) return 0;
+  for (int p = 0; p < 2; ++p)
+    if (e->graph[p]) cudaGraphExecDestroy(e->graph[p]);
+  if (e->comm && g_nccl.ok) g_nccl.CommDestroy(e->comm);
+  delete e;
+  return 0;
+}
+
+int mgbs_nccl_unique_id(const char* libnccl_path, uint8_t* out128) {
+  if (!out128) return MGBS_ERR_ARG;
+  MGBS_TRY(load_nccl(libnccl_path));
+  ncclUniqueId id;
+  MGBS_NCCL(g_nccl.GetUniqueId(&id));
+  static_assert(sizeof(ncclUniqueId) == 128, "unique id is 128 bytes");
+  memcpy(out128, &id, 128);
+  return 0;
+}
+
+int mgbs_engine_init_nccl(MgbsEngine* e, const char* libnccl_path, const uint8_t* unique_id128) {
+  if (!e || !unique_id128) return MGBS_ERR_ARG;
+  if (e->cfg.world_size == 1) return 0;
+  MGBS_TRY(load_nccl(libnccl_path));
+  ncclUniqueId id;
+  memcpy(&id, unique_id128, 128);
+  MGBS_NCCL(g_nccl.CommInitRank(&e->comm, e->cfg.world_size, id, e->cfg.rank));
+  return 0;
+}
+
+int mgbs_engine_set_scorer(MgbsEngine* e, mgbs_scorer_fn fn, void* user) {
+  if (!e) return MGBS_ERR_ARG;
+  e->scorer = fn;
+  e->scorer_user = user;
+  for (int p = 0; p < 2; ++p)
+    if (e->graph[p]) { cudaGraphExecDestroy(e->graph[p]); e->graph[p] = nullptr; }
+  return 0;
+}
+
+int mgbs_engine_set_score_mode(MgbsEngine* e, int32_t score_mode, int32_t uniform_score) {
+  if (!e || score_mode < MGBS_SCORE_EXTERNAL || score_mode > MGBS_SCORE_UNIFORM) return MGBS_ERR_ARG;
+  e->cfg.score_mode = score_mode;
+  e->cfg.uniform_score = uniform_score;
+  for (int p = 0; p < 2; ++p)
+    if (e->graph[p]) { cudaGraphExecDestroy(e->graph[p]); e->graph[p] = nullptr; }
+  return 0;
+}
+
+int mgbs_engine_reset(MgbsEngine* e, const uint8_t* start_state_host, int32_t active_on_this_rank,
+                      int32_t start_is_solved, void* stream) {
+  if (!e || !start_state_host) return MGBS_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  const MgbsConfig& c = e->cfg;
+  MgbsCtrl& h = e->host_ctrl;
+  memset(&h, 0, sizeof(MgbsCtrl));
+  h.frontier_count[0] = active_on_this_rank ? 1 : 0;
+  h.found_payload = 0xffffffffu;
+  h.rho_num = 1;
+  h.rho_den = 1;
+  if (start_is_solved) { h.found = 1; h.found_depth = 0; }
+  MGBS_TRY(cudaMemcpyAsync(c.ctrl, &h, sizeof(MgbsCtrl), cudaMemcpyHostToDevice, st));
+  if (active_on_this_rank) {
+    uint8_t row[MGBS_MAX_STATE_LEN];
+    memset(row, 0, sizeof(row));
+    memcpy(row, start_state_host, (size_t)c.state_len);
+    MGBS_TRY(cudaMemcpyAsync(c.frontier[0], row, (size_t)c.state_stride, cudaMemcpyHostToDevice, st));
+  }
+  MGBS_TRY(cudaStreamSynchronize(st));
+  return 0;
+}
+
+// Load a whole frontier (rows of state_len bytes, host memory) as the current frontier of buffer `parity`.
+int mgbs_engine_load_frontier(MgbsEngine* e, const uint8_t* rows_host, int64_t count, int32_t parity, int32_t depth,
+                              void* stream) {
+  if (!e || count < 0 || count > e->cfg.frontier_cap || (count > 0 && !rows_host)) return MGBS_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  const MgbsConfig& c = e->cfg;
+  MgbsCtrl& h = e->host_ctrl;
+  memset(&h, 0, sizeof(MgbsCtrl));
+  h.frontier_count[parity & 1] = (int32_t)count;
+  h.depth = depth;
+  h.found_payload = 0xffffffffu;
+  h.rho_num = 1;
+  h.rho_den = 1;
+  MGBS_TRY(cudaMemcpyAsync(c.ctrl, &h, sizeof(MgbsCtrl), cudaMemcpyHostToDevice, st));
+  if (count > 0) {
+    MGBS_TRY(cudaMemsetAsync(c.frontier[parity & 1], 0, (size_t)count * c.state_stride, st));
+    MGBS_TRY(cudaMemcpy2DAsync(c.frontier[parity & 1], (size_t)c.state_stride, rows_host, (size_t)c.state_len,
+                               (size_t)c.state_len, (size_t)count, cudaMemcpyHostToDevice, st));
+  }
+  MGBS_TRY(cudaStreamSynchronize(st));
+  return 0;
+}
+
+static int allreduce_hist(MgbsEngine* e, uint32_t* hist, cudaStream_t st) {
+  if (e->cfg.world_size == 1) return 0;
+  if (!e->comm) return MGBS_ERR_STATE;
+  MGBS_NCCL(g_nccl.AllReduce(hist, hist, MGBS_HIST_STRIDE, ncclUint32, ncclSum, e->comm, st));
+  return 0;
+}
+
+static int exchange(MgbsEngine* e, cudaStream_t st) {
+  const MgbsConfig& c = e->cfg;
+  if (!e->comm) return MGBS_ERR_STATE;
+  const size_t cap = (size_t)c.bucket_cap;
+  MGBS_NCCL(g_nccl.GroupStart());
+  for (int r = 0; r < c.world_size; ++r) {
+    MGBS_NCCL(g_nccl.Send(c.send_counts + r, 1, ncclUint32, r, e->comm, st));
+    MGBS_NCCL(g_nccl.Recv(c.recv_counts + r, 1, ncclUint32, r, e->comm, st));
+    MGBS_NCCL(g_nccl.Send(c.send_hash + r * cap, cap, ncclUint64, r, e->comm, st));
+    MGBS_NCCL(g_nccl.Recv(c.recv_hash + r * cap, cap, ncclUint64, r, e->comm, st));
+    MGBS_NCCL(g_nccl.Send(c.send_fp + r * cap, cap, ncclUint64, r, e->comm, st));
+    MGBS_NCCL(g_nccl.Recv(c.recv_fp + r * cap, cap, ncclUint64, r, e->comm, st));
+    MGBS_NCCL(g_nccl.Send(c.send_score + r * cap, cap, ncclUint32, r, e->comm, st));
+    MGBS_NCCL(g_nccl.Recv(c.recv_score + r * cap, cap, ncclUint32, r, e->comm, st));
+    MGBS_NCCL(g_nccl.Send(c.send_payload + r * cap, cap, ncclUint32, r, e->comm, st));
+    MGBS_NCCL(g_nccl.Recv(c.recv_payload + r * cap, cap, ncclUint32, r, e->comm, st));
+    MGBS_NCCL(g_nccl.Send(c.send_states + r * cap * c.state_stride, cap * c.state_stride, ncclUint8, r, e->comm, st));
+    MGBS_NCCL(g_nccl.Recv(c.recv_states + r * cap * c.state_stride, cap * c.state_stride, ncclUint8, r, e->comm, st));
+  }
+  MGBS_NCCL(g_nccl.GroupEnd());
+  return 0;
+}
+
+int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void* stream) {
+  if (!e || phase < 0 || phase > 2) return MGBS_ERR_ARG;
+  using namespace mgbs;
+  cudaStream_t st = (cudaStream_t)stream;
+  const MgbsConfig& c = e->cfg;
+  parity &= 1;
+  const int W = c.world_size;
+  const int Lb = c.band_levels, R = c.band_rounds, Lf = e->final_levels;
+  unsigned long long* tie_buf = reinterpret_cast<unsigned long long*>(c.tie_buf);
+
+  if (phase == 0 || phase == 1) {
+    MGBS_TRY(launch_depth_begin(c.ctrl, parity, c.fanout, c.cand_cap, tie_buf + (int64_t)c.rank * kTieSegWords,
+                                W > 1 ? c.send_counts : nullptr, W, st));
+    MGBS_TRY(cudaMemsetAsync(c.table, 0, (size_t)c.hash_capacity * 32, st));
+    MGBS_TRY(cudaMemsetAsync(c.hist, 0, (size_t)(R * Lb + MGBS_MAX_LEVELS) * MGBS_HIST_STRIDE * sizeof(uint32_t), st));
+    ExpandArgs x;
+    x.frontier = c.frontier[parity];
+    x.count_dev = &c.ctrl->frontier_count[parity];
+    x.count = 0;
+    x.gens = c.gens;
+    x.solved = c.solved;
+    x.n = c.state_len; x.stride = c.state_stride; x.fanout = c.fanout; x.rank = c.rank;
+    x.score_mode = c.score_mode; x.uniform_score = c.uniform_score;
+    x.children = c.children;
+    x.cand_hash = c.cand_hash; x.cand_fp = c.cand_fp; x.cand_score = c.cand_score; x.cand_payload = c.cand_payload;
+    x.ctrl = c.ctrl;
+    MGBS_TRY(launch_expand(x, c.frontier_cap, e->sms, st));
+    if (phase == 0 && c.score_mode == MGBS_SCORE_EXTERNAL) {
+      if (!e->scorer) return MGBS_ERR_STATE;
+      MGBS_TRY(e->scorer(e->scorer_user, c.children, &c.ctrl->cand_count, c.cand_score, stream));
+    }
+    if (phase == 1) return 0;
+  }
+
+  StepArgs a;
+  memset(&a, 0, sizeof(a));
+  int64_t items;
+  if (W == 1) {
+    a.cv.hash = c.cand_hash; a.cv.fp = c.cand_fp; a.cv.score = c.cand_score; a.cv.payload = c.cand_payload;
+    a.cv.states = c.children;
+    a.cv.counts = &c.ctrl->cand_count;
+    a.cv.nbuckets = 1;
+    a.cv.cap = (uint32_t)c.cand_cap;
+    items = c.cand_cap;
+  } else {
+    RouteArgs r;
+    r.hash = c.cand_hash; r.fp = c.cand_fp; r.score = c.cand_score; r.payload = c.cand_payload; r.states = c.children;
+    r.s_hash = c.send_hash; r.s_fp = c.send_fp; r.s_score = c.send_score; r.s_payload = c.send_payload;
+    r.s_states = c.send_states;
+    r.send_counts = c.send_counts;
+    r.ctrl = c.ctrl;
+    r.world = W; r.stride = c.state_stride; r.bucket_cap = (uint32_t)c.bucket_cap;
+    MGBS_TRY(launch_route(r, c.cand_cap, e->sms, st));
+    MGBS_TRY(exchange(e, st));
+    MGBS_TRY(launch_clamp_counts(c.recv_counts, W, (uint32_t)c.bucket_cap, st));
+    a.cv.hash = c.recv_hash; a.cv.fp = c.recv_fp; a.cv.score = c.recv_score; a.cv.payload = c.recv_payload;
+    a.cv.states = c.recv_states;
+    a.cv.counts = c.recv_counts;
+    a.cv.nbuckets = W;
+    a.cv.cap = (uint32_t)c.bucket_cap;
+    items = c.bucket_cap;  // per bucket; kernels loop over buckets
+  }
+  a.ctrl = c.ctrl;
+  a.table = c.table;
+  a.tie_buf = tie_buf;
+  a.hash_capacity = c.hash_capacity;
+  a.beam = c.global_beam_width;
+  a.pool_target = c.pool_target;
+  a.frontier_cap = c.frontier_cap;
+  a.world = W; a.rank = c.rank;
+  a.key_bits = e->key_bits; a.hash_bits = c.hash_bits;
+  a.rounds = R;
+  a.select_mode = c.select_mode; a.probe_limit = c.probe_limit;
+  a.frontier_cur = c.frontier[parity];
+  a.frontier_next = c.frontier[parity ^ 1];
+  a.gens = c.gens;
+  a.history = c.history;
+  a.history_depths = c.history_depths;
+  a.next_score = c.frontier_score[parity ^ 1];
+  a.next_hash = c.frontier_hash[parity ^ 1];
+  a.n = c.state_len; a.stride = c.state_stride; a.fanout = c.fanout; a.parity = parity;
+
+  // band rounds: place a threshold by histogram levels, then insert that band into the table
+  for (int r = 0; r < R; ++r) {
+    a.round = r;
+    a.levels = Lb;
+    for (int l = 0; l < Lb; ++l) {
+      a.level = l;
+      a.hist = c.hist + (int64_t)(r * Lb + l) * MGBS_HIST_STRIDE;
+      a.hist_prev = l > 0 ? c.hist + (int64_t)(r * Lb + l - 1) * MGBS_HIST_STRIDE : nullptr;
+      MGBS_TRY(launch_band_hist(a, items, e->sms, st));
+      MGBS_TRY(allreduce_hist(e, a.hist, st));
+    }
+    a.hist = nullptr;
+    a.hist_prev = c.hist + (int64_t)(r * Lb + Lb - 1) * MGBS_HIST_STRIDE;
+    MGBS_TRY(launch_band_insert(a, items, e->sms, st));
+  }
+  // final cut over the table
+  uint32_t* fin = c.hist + (int64_t)(R * Lb) * MGBS_HIST_STRIDE;
+  a.levels = Lf;
+  a.hist_stats = fin;
+  for (int l = 0; l < Lf; ++l) {
+    a.level = l;
+    a.hist = fin + (int64_t)l * MGBS_HIST_STRIDE;
+    a.hist_prev = l > 0 ? fin + (int64_t)(l - 1) * MGBS_HIST_STRIDE : nullptr;
+    MGBS_TRY(launch_final_hist(a, c.hash_capacity, e->sms, st));
+    MGBS_TRY(allreduce_hist(e, a.hist, st));
+  }
+  a.hist = nullptr;
+  a.hist_prev = fin + (int64_t)(Lf - 1) * MGBS_HIST_STRIDE;
+  MGBS_TRY(launch_emit(a, items, e->sms, st));
+  if (W > 1) {
+    MGBS_NCCL(g_nccl.AllGather(tie_buf + (int64_t)c.rank * kTieSegWords, tie_buf, kTieSegWords, ncclUint64, e->comm, st));
+  }
+  MGBS_TRY(launch_finish(a, st));
+  return 0;
+}
+
+// One depth step through a captured CUDA graph (one graph per frontier parity; captured on first use).
+// Replaces BeamEngine::step with capture_cuda_graph (beam_engine.cpp:1104-1116, 1658-1672).
+int mgbs_engine_step_graph(MgbsEngine* e, int32_t parity, void* stream) {
+  if (!e) return MGBS_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  parity &= 1;
+  if (!e->graph[parity]) {
+    cudaGraph_t g = nullptr;
+    MGBS_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    int rc = mgbs_engine_enqueue_depth(e, parity, 0, stream);
+    cudaError_t ce = cudaStreamEndCapture(st, &g);
+    if (rc != 0) { if (g) cudaGraphDestroy(g); return rc; }
+    if (ce != cudaSuccess) return (int)ce;
+    ce = cudaGraphInstantiate(&e->graph[parity], g, 0);
+    cudaGraphDestroy(g);
+    if (ce != cudaSuccess) return (int)ce;
+  }
+  return (int)cudaGraphLaunch(e->graph[parity], st);
+}
+
+int mgbs_engine_read_ctrl(MgbsEngine* e, MgbsCtrl* out_host, void* stream) {
+  if (!e || !out_host) return MGBS_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  MGBS_TRY(cudaMemcpyAsync(out_host, e->cfg.ctrl, sizeof(MgbsCtrl), cudaMemcpyDeviceToHost, st));
+  MGBS_TRY(cudaStreamSynchronize(st));
+  return 0;
+}
+
+// Depth loop on the host: step until found, max_depth or an empty frontier (BeamEngine::search,
+// beam_engine.cpp:1147-1171).  The control block is read once per depth (one small copy, one stream sync);
+// world > 1 ranks see the same found flag and global frontier size because both ride in all-reduced statistics.
+int mgbs_engine_search(MgbsEngine* e, int32_t max_depth, int32_t use_graph, MgbsCtrl* out_host, void* stream) {
+  if (!e || !out_host) return MGBS_ERR_ARG;
+  MGBS_TRY(mgbs_engine_read_ctrl(e, out_host, stream));
+  while (!out_host->found && out_host->depth < max_depth) {
+    const int parity = out_host->depth & 1;
+    if (e->cfg.world_size == 1 && out_host->frontier_count[parity] == 0) break;
+    if (use_graph) MGBS_TRY(mgbs_engine_step_graph(e, parity, stream));
+    else MGBS_TRY(mgbs_engine_enqueue_depth(e, parity, 0, stream));
+    MGBS_TRY(mgbs_engine_read_ctrl(e, out_host, stream));
+    if (e->cfg.world_size > 1 && out_host->unique_total == 0) break;
+  }
+  return 0;
+}
+
+int mgbs_launch_expand(const uint8_t* frontier, const int32_t* count_dev, int64_t count, const uint8_t* gens,
+                       const uint8_t* solved, int32_t state_len, int32_t state_stride, int32_t fanout, int32_t rank,
+                       int32_t score_mode, int32_t uniform_score, uint8_t* children, uint64_t* cand_hash,
+                       uint64_t* cand_fp, uint32_t* cand_score, uint32_t* cand_payload, MgbsCtrl* ctrl, void* stream) {
+  if (!frontier || !gens || !solved || !cand_hash || !cand_fp || !cand_payload) return MGBS_ERR_ARG;
+  if (score_mode != MGBS_SCORE_EXTERNAL && !cand_score) return MGBS_ERR_ARG;
+  if (state_len < 1 || state_stride < state_len || (state_stride % 16) != 0 || state_stride > MGBS_MAX_STATE_LEN) return MGBS_ERR_ARG;
+  if (fanout < 1 || fanout > MGBS_MAX_FANOUT || count < 0) return MGBS_ERR_ARG;
+  mgbs::ExpandArgs x;
+  x.frontier = frontier; x.count_dev = count_dev; x.count = count; x.gens = gens; x.solved = solved;
+  x.n = state_len; x.stride = state_stride; x.fanout = fanout; x.rank = rank;
+  x.score_mode = score_mode; x.uniform_score = uniform_score;
+  x.children = children; x.cand_hash = cand_hash; x.cand_fp = cand_fp; x.cand_score = cand_score;
+  x.cand_payload = cand_payload; x.ctrl = ctrl;
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  return mgbs::launch_expand(x, count_dev ? (int64_t)1 << 22 : count, sms, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,91 @@
+// Argument blocks and launcher prototypes shared by the step kernels and the engine.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "mgbs.h"
+
+namespace mgbs {
+
+constexpr int kExpandThreads = 256;
+constexpr int kExpandTile = 64;  // parents per block iteration
+constexpr int kStreamThreads = 256;
+
+// Tie records of all ranks: world segments of {count, then MGBS_TIE_CAP x (hash, fingerprint, candidate index)}.
+constexpr int kTieSegWords = 1 + 3 * MGBS_TIE_CAP;
+
+struct ExpandArgs {
+  const uint8_t* frontier;
+  const int32_t* count_dev;
+  int64_t count;
+  const uint8_t* gens;
+  const uint8_t* solved;
+  int32_t n, stride, fanout, rank, score_mode, uniform_score;
+  uint8_t* children;
+  uint64_t* cand_hash;
+  uint64_t* cand_fp;
+  uint32_t* cand_score;
+  uint32_t* cand_payload;
+  MgbsCtrl* ctrl;
+};
+
+// Candidate view: one or more buckets of `cap` entries with device-side fill counts.
+// world = 1: a single bucket (the arrays the expansion wrote).  world > 1: one receive bucket per peer.
+struct CandView {
+  const uint64_t* hash;
+  const uint64_t* fp;
+  const uint32_t* score;
+  const uint32_t* payload;
+  const uint8_t* states;  // rows of `stride` bytes; may be null (world = 1 without materialised children)
+  const uint32_t* counts;
+  int32_t nbuckets;
+  uint32_t cap;
+};
+
+struct StepArgs {
+  CandView cv;
+  MgbsCtrl* ctrl;
+  uint32_t* hist;             // histogram this kernel fills
+  const uint32_t* hist_prev;  // histogram of the previous level, consumed in the prologue
+  const uint32_t* hist_stats; // level-0 histogram of the final cut (carries the all-reduced statistics)
+  uint8_t* table;
+  unsigned long long* tie_buf;
+  int64_t hash_capacity;
+  int64_t beam;
+  int64_t pool_target;
+  int64_t frontier_cap;
+  int32_t world, rank;
+  int32_t key_bits, hash_bits;
+  int32_t level, levels, round, rounds;
+  int32_t select_mode, probe_limit;
+  const uint8_t* frontier_cur;
+  uint8_t* frontier_next;
+  const uint8_t* gens;
+  uint32_t* history;
+  int64_t history_depths;
+  uint32_t* next_score;
+  uint64_t* next_hash;
+  int32_t n, stride, fanout, parity;
+};
+
+struct RouteArgs {
+  const uint64_t* hash; const uint64_t* fp; const uint32_t* score; const uint32_t* payload; const uint8_t* states;
+  uint64_t* s_hash; uint64_t* s_fp; uint32_t* s_score; uint32_t* s_payload; uint8_t* s_states;
+  uint32_t* send_counts;
+  MgbsCtrl* ctrl;
+  int32_t world, stride;
+  uint32_t bucket_cap;
+};
+
+int launch_expand(const ExpandArgs& a, int64_t max_parents, int sms, cudaStream_t st);
+int launch_depth_begin(MgbsCtrl* c, int parity, int fanout, int64_t cand_cap, unsigned long long* tie_seg,
+                       uint32_t* send_counts, int world, cudaStream_t st);
+int launch_band_hist(const StepArgs& a, int64_t items, int sms, cudaStream_t st);
+int launch_band_insert(const StepArgs& a, int64_t items, int sms, cudaStream_t st);
+int launch_final_hist(const StepArgs& a, int64_t slots, int sms, cudaStream_t st);
+int launch_emit(const StepArgs& a, int64_t items, int sms, cudaStream_t st);
+int launch_finish(const StepArgs& a, cudaStream_t st);
+int launch_route(const RouteArgs& a, int64_t items, int sms, cudaStream_t st);
+int launch_clamp_counts(uint32_t* counts, int world, uint32_t cap, cudaStream_t st);
+
+}  // namespace mgbs

@@ -1,0 +1,25 @@
+"""Host-side views of the engine's packed records."""
+
+from __future__ import annotations
+
+MOVE_BITS = 5
+RANK_BITS = 4
+
+
+def pack_payload(parent: int, rank: int, move: int) -> int:
+    """Back-pointer word: parent row (23 bits) | source rank (4 bits) | move (5 bits)."""
+    return ((int(parent) << (RANK_BITS + MOVE_BITS)) | (int(rank) << MOVE_BITS) | int(move)) & 0xFFFFFFFF
+
+
+def unpack_payload(payload):
+    """(parent, rank, move) of a back-pointer word; works on ints and numpy arrays."""
+    move = payload & ((1 << MOVE_BITS) - 1)
+    rank = (payload >> MOVE_BITS) & ((1 << RANK_BITS) - 1)
+    parent = payload >> (RANK_BITS + MOVE_BITS)
+    return parent, rank, move
+
+
+def order_key(score: int, h: int, hash_bits: int = 44) -> int:
+    """The 64-bit selection key of the engine: score above the top ``hash_bits`` bits of the 64-bit hash."""
+    k = min(int(score), 0xFFFFF)
+    return ((k << hash_bits) | (int(h) >> (64 - hash_bits))) if hash_bits else k

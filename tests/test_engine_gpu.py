@@ -1,0 +1,239 @@
+"""GPU parity tests: the CUDA step, called through the C ABI, against the numpy oracle (bit-exact)."""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import beam_oracle as bo
+from multigpubeamsearch_b200 import beam_engine as be
+from multigpubeamsearch_b200 import puzzles, _lib
+
+pytestmark = pytest.mark.gpu
+
+
+def make_engine(pz, **kw):
+    kw.setdefault("global_beam_width", 1024)
+    kw.setdefault("max_depth", 64)
+    kw.setdefault("beta", 1.2)
+    kw.setdefault("hash_load_factor", 0.45)
+    kw.setdefault("probe_limit", 256)
+    kw.setdefault("band_rounds", 8)
+    ext, cfg, buffers, engine = be.configure_engine(pz, **kw)
+    return engine
+
+
+def random_frontier(pz, count, seed, walk=25):
+    rng = np.random.default_rng(seed)
+    g = pz.generators.astype(np.int64)
+    rows = np.tile(pz.solved, (count, 1))
+    for _ in range(walk):
+        mv = rng.integers(0, pz.fanout, size=count)
+        rows = np.take_along_axis(rows, g[mv], axis=1)
+    return np.unique(rows, axis=0)
+
+
+@pytest.mark.parametrize("n,fanout", [(16, 3), (54, 12), (96, 18), (120, 24), (33, 7)])
+def test_expand_kernel_bit_exact(n, fanout):
+    lib = _lib.load()
+    rng = np.random.default_rng(n * 100 + fanout)
+    stride = (n + 15) // 16 * 16
+    if stride // 4 not in (4, 8, 16, 24, 32):
+        stride = 64
+    P = 777
+    frontier = rng.integers(0, 8, size=(P, n), dtype=np.uint8)
+    gens = np.stack([rng.permutation(n) for _ in range(fanout)]).astype(np.uint8)
+    solved = frontier[5][gens[2].astype(np.int64)].copy()  # make one child equal to "solved"
+    dev = torch.device("cuda", 0)
+    f_pad = np.zeros((P, stride), np.uint8)
+    f_pad[:, :n] = frontier
+    t_f = torch.from_numpy(f_pad).to(dev)
+    t_g = torch.from_numpy(gens).to(dev)
+    t_s = torch.from_numpy(solved).to(dev)
+    Cn = P * fanout
+    t_children = torch.zeros((Cn, stride), dtype=torch.uint8, device=dev)
+    t_h = torch.zeros(Cn, dtype=torch.int64, device=dev)
+    t_fp = torch.zeros(Cn, dtype=torch.int64, device=dev)
+    t_k = torch.zeros(Cn, dtype=torch.int32, device=dev)
+    t_p = torch.zeros(Cn, dtype=torch.int32, device=dev)
+    ctrl = torch.zeros(C.sizeof(_lib.MgbsCtrl), dtype=torch.uint8, device=dev)
+    host = _lib.MgbsCtrl()
+    host.found_payload = 0xFFFFFFFF
+    ctrl.copy_(torch.frombuffer(bytearray(bytes(host)), dtype=torch.uint8))
+    rc = lib.mgbs_launch_expand(t_f.data_ptr(), None, P, t_g.data_ptr(), t_s.data_ptr(), n, stride, fanout, 3,
+                                _lib.SCORE_HAMMING, 0, t_children.data_ptr(), t_h.data_ptr(), t_fp.data_ptr(),
+                                t_k.data_ptr(), t_p.data_ptr(), ctrl.data_ptr(),
+                                C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    want_c = bo.expand(frontier, gens)
+    assert np.array_equal(t_children.cpu().numpy()[:, :n], want_c)
+    assert not t_children.cpu().numpy()[:, n:].any()
+    assert np.array_equal(t_h.cpu().numpy().view(np.uint64), bo.hash64(want_c))
+    assert np.array_equal(t_fp.cpu().numpy().view(np.uint64), bo.fingerprint64(want_c))
+    assert np.array_equal(t_k.cpu().numpy().view(np.uint32), bo.hamming(want_c, solved))
+    pidx = np.repeat(np.arange(P, dtype=np.uint32), fanout)
+    mv = np.tile(np.arange(fanout, dtype=np.uint32), P)
+    assert np.array_equal(t_p.cpu().numpy().view(np.uint32), bo.pack_payload(pidx, np.full_like(pidx, 3), mv))
+    got = _lib.MgbsCtrl.from_buffer_copy(bytes(ctrl.cpu().numpy()))
+    goal = (want_c == solved[None, :]).all(axis=1)
+    assert got.found_payload == int(bo.pack_payload(pidx, np.full_like(pidx, 3), mv)[goal].min())
+    # host helpers use the same arithmetic
+    row = np.ascontiguousarray(want_c[17])
+    assert lib.mgbs_hash64_host(row.ctypes.data_as(C.c_void_p), n) == int(bo.hash64(row)[0])
+    assert lib.mgbs_fingerprint64_host(row.ctypes.data_as(C.c_void_p), n) == int(bo.fingerprint64(row)[0])
+
+
+def check_step(engine, pz, frontier, beam, mode="exact_k", graph=False):
+    engine.load_frontier(frontier, depth=0)
+    engine.enable_cuda_graphs(graph)
+    engine.step()
+    st = engine.status()
+    want = bo.depth_step([frontier], pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam, mode)
+    assert st["status_bits"] == 0, st["status_names"]
+    got_rows = engine.frontier()
+    assert got_rows.shape[0] == want.states.shape[0]
+    assert np.array_equal(bo.sorted_rows(got_rows), bo.sorted_rows(want.states))
+    # back-pointers: same winner (parent, rank, move) for every surviving state
+    got_pay = engine.frontier_payloads()
+    got_map = {bytes(r): int(p) for r, p in zip(got_rows, got_pay)}
+    want_map = {bytes(r): int(p) for r, p in zip(want.states, want.payload)}
+    assert got_map == want_map
+    got_scores = engine.frontier_scores()
+    assert {bytes(r): int(k) for r, k in zip(got_rows, got_scores)} == \
+        {bytes(r): int(k) for r, k in zip(want.states, want.score)}
+    assert st["counters"][2] == want.candidates
+    assert bool(st["found"]) == want.found_child
+    return st, want
+
+
+@pytest.mark.parametrize("name,count,beam", [("lrx16", 300, 256), ("rand54", 500, 1024), ("rand96", 400, 2048),
+                                             ("rand54", 40, 100000), ("rand54", 1, 16)])
+def test_single_step_matches_oracle(name, count, beam):
+    pz = puzzles.by_name(name)
+    engine = make_engine(pz, global_beam_width=beam)
+    frontier = random_frontier(pz, count, seed=count + beam)[: engine.sizes()["k_work"]]
+    for graph in (False, True):
+        st, want = check_step(engine, pz, frontier, beam, graph=graph)
+    assert st["counters"][3] >= min(beam, want.unique) or st["counters"][3] == want.unique
+
+
+@pytest.mark.parametrize("mode", ["v6_inclusive", "legacy_strict"])
+def test_threshold_modes_match_oracle(mode):
+    pz = puzzles.puzzle54()
+    # score-only order: a whole score level must fit the pool, so give the pool room (beta) and keep beams small
+    engine = make_engine(pz, global_beam_width=300, select_mode=mode, beta=8.0)
+    frontier = random_frontier(pz, 120, seed=9)
+    check_step(engine, pz, frontier, 300, mode=mode)
+
+
+def test_tie_resolution_path():
+    # few hash bits in the order key -> many candidates share the cut key; the result must still be exact
+    pz = puzzles.puzzle54()
+    for hb in (1, 3, 6):
+        engine = make_engine(pz, global_beam_width=64, hash_bits=hb, beta=4.0)
+        frontier = random_frontier(pz, 30, seed=hb)
+        check_step(engine, pz, frontier, 64)
+
+
+def test_empty_frontier_and_status_reset():
+    pz = puzzles.puzzle54()
+    engine = make_engine(pz, global_beam_width=64)
+    engine.load_frontier(np.zeros((0, pz.state_len), np.uint8))
+    engine.step()
+    st = engine.status()
+    assert st["current_size"] == 0 and st["status_bits"] == 0 and not st["found"]
+
+
+def test_probe_limit_overflow_is_reported_not_trapped():
+    pz = puzzles.puzzle54()
+    engine = make_engine(pz, global_beam_width=4096, probe_limit=1, hash_load_factor=0.9, beta=1.0, gamma=1.0)
+    frontier = random_frontier(pz, 2000, seed=4)
+    engine.load_frontier(frontier)
+    engine.step()
+    st = engine.status()
+    assert st["status_bits"] & _lib.ST_HASH_OVERFLOW
+    assert st["counters"][4] > 0
+    # the engine is still usable
+    engine2 = make_engine(pz, global_beam_width=512)
+    check_step(engine2, pz, frontier[:200], 512)
+
+
+@pytest.mark.parametrize("scramble", [0, 1, 2, 3])
+def test_full_search_lrx16_matches_oracle(scramble):
+    # the reference's CPU-runnable case: S_16 under L, R, X; beam 1024; depth 40; Hamming scorer
+    pz = puzzles.lrx(16)
+    start = pz.scramble(scramble, 30)
+    want = bo.search(start, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam=1024, max_depth=40,
+                     keep_frontiers=True)
+    engine = make_engine(pz, global_beam_width=1024, max_depth=40)
+    engine.reset_search(bytes(start))
+    depth = 0
+    while True:
+        rows = engine.frontier()
+        assert np.array_equal(bo.sorted_rows(rows), want.frontiers[depth]), f"depth {depth}"
+        st = engine.status()
+        if st["found"] or depth == 40 or rows.shape[0] == 0:
+            break
+        engine.step()
+        depth += 1
+        st = engine.status()
+        assert st["status_bits"] == 0, st["status_names"]
+        if st["found"]:
+            break
+    st = engine.status()
+    assert bool(st["found"]) == want.found
+    if want.found:
+        assert st["found_depth"] == want.depth
+        path = engine.reconstruct_path()
+        assert len(path) == want.depth
+        assert np.array_equal(bo.replay(start, pz.generators, path), pz.solved)
+    # the same search through the engine's own depth loop (graph replay)
+    engine.enable_cuda_graphs(True)
+    res = be.run_one_search(engine, start, 40)
+    assert res["found"] == want.found and res["depth"] == want.depth
+    assert engine.cuda_graph_captured()
+
+
+def test_known_shallow_scrambles_rand54():
+    # scrambles of length 0, 1, 2 are found at depth 0, 1, 2 (scripts/kaggle_correctness_check.py:154-179)
+    pz = puzzles.puzzle54()
+    g = pz.generators.astype(np.int64)
+    engine = make_engine(pz, global_beam_width=4096, max_depth=8)
+    s = pz.solved.copy()
+    for depth, mv in enumerate([None, 0, 1]):
+        if mv is not None:
+            s = s[g[mv]]
+        res = be.run_one_search(engine, s, 6)
+        assert res["found"] and res["depth"] == depth
+        path = engine.reconstruct_path()
+        assert np.array_equal(bo.replay(s, pz.generators, path), pz.solved)
+
+
+def test_uniform_prepass_fill():
+    # uniform score: every child ties, the cut is by hash alone; still exact and deterministic
+    pz = puzzles.puzzle54()
+    engine = make_engine(pz, global_beam_width=500)
+    frontier = random_frontier(pz, 100, seed=77)
+    engine.begin_uniform_score(7)
+    engine.load_frontier(frontier)
+    engine.step()
+    rows = engine.frontier()
+    want = bo.depth_step([frontier], pz.generators, pz.solved, lambda c: np.full(c.shape[0], 7, np.uint32), 500)
+    assert np.array_equal(bo.sorted_rows(rows), bo.sorted_rows(want.states))
+    engine.end_uniform_score()
+    check_step(engine, pz, frontier, 500)
+
+
+def test_rejects_bad_arguments():
+    pz = puzzles.puzzle54()
+    engine = make_engine(pz, global_beam_width=64)
+    with pytest.raises(RuntimeError):
+        engine.set_action_permutation_table(b"\x00" * 5)
+    with pytest.raises(RuntimeError):
+        engine.set_central_state(b"\x00" * 5)
+    with pytest.raises(RuntimeError):
+        engine.reset_search(b"\x00" * 3)
+    with pytest.raises(RuntimeError):
+        be.BeamEngine(engine.cfg, engine.buffers, "no_such_backend")
