@@ -196,7 +196,9 @@ class BeamEngine:
             raise RuntimeError(f"unknown inference backend: {backend}")
         self.backend = backend
         self._sizes = _Ext(self.lib).derive_sizes(cfg)
-        self._stream = torch.cuda.current_stream()
+        # the engine owns its stream (the reference owns stream_infer_/ingest_/net_, beam_engine.cpp:705-709); stream
+        # capture is not allowed on the legacy default stream
+        self._stream = torch.cuda.Stream()
         self._use_graph = bool(cfg.get("use_cuda_graphs", True))
         self._graph_used = False
         self._scorer = None
@@ -270,6 +272,8 @@ class BeamEngine:
 
     # -- set-up ---------------------------------------------------------------------------------
     def _sp(self):
+        # work queued by torch on the caller's stream (table uploads, scorer weights) happens-before engine work
+        self._stream.wait_stream(torch.cuda.current_stream())
         return C.c_void_p(self._stream.cuda_stream)
 
     def init_nccl(self, unique_id: bytes) -> None:
