@@ -1,0 +1,470 @@
+// Value-network scorer for sm_100a: a 3-layer MLP  one-hot(n*V) -> H -> H -> 1  evaluated on every child state.
+// The two H-wide layers are GEMMs on the 5th-generation tensor cores: tcgen05.mma issued by one thread, operands
+// staged in shared memory by TMA (128-byte swizzle, K-major), accumulators in tensor memory, epilogues read with
+// tcgen05.ld.  The last layer (H -> 1) and the score-key quantisation are fused into the second GEMM's epilogue.
+//
+// Takes the place of FullBeamNiceStaticBackend::forward and its Turing-era CUTLASS HMMA GEMMs
+// (beam_engine.cpp:621-667, beam_kernels.cu:208-344, 970-1038).  Unlike the reference's action-value network on
+// parents, this is the value network on children that the benchmark configurations name.
+//
+// Warp roles of the GEMM kernel (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
+// warps 2..5 = epilogue (one TMEM lane quadrant each).  Every mbarrier wait is bounded: after the limit the
+// waiter records an error code in global memory and the CTA drains and exits; nothing spins forever.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <new>
+
+#include "mgbs.h"
+
+namespace mgbs {
+
+constexpr int BM = 128;       // rows per tile (TMEM lanes)
+constexpr int BN = 256;       // accumulator columns per tile
+constexpr int BK = 64;        // bf16 elements per 128-byte swizzle row
+constexpr int UMMA_K = 16;    // K of one tcgen05.mma for 16-bit operands
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;  // 16 KB
+constexpr int B_BYTES = BN * BK * 2;  // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr uint32_t TMEM_COLS = 512;
+
+constexpr int ERR_WAIT_EMPTY = 1, ERR_WAIT_FULL = 2, ERR_WAIT_TMEM_EMPTY = 3, ERR_WAIT_TMEM_FULL = 4, ERR_WAIT_DRAIN = 5;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: about 1-2 s of polling at most, then report and give up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
+  for (uint32_t it = 0; it < (1u << 24); ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (it > 1024) __nanosleep(64);
+  }
+  if (err) atomicCAS(err, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem]; both operands K-major, described by shared-memory matrix descriptors
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+        "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+// Fields: start address >> 4 (bits 0-13), leading byte offset >> 4 (16-29, unused for swizzled K-major: 1),
+// stride byte offset >> 4 (32-45: 1024 >> 4), descriptor version 1 (46-47), layout type SWIZZLE_128B = 2 (61-63).
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor for kind::f16: D = f32 (bits 4-5 = 1), A = B = bf16 (bits 7-9 / 10-12 = 1), both K-major
+// (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+constexpr uint32_t kIdescBf16 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+struct GemmArgs {
+  const uint32_t* count_dev;  // rows to process (device value)
+  int64_t row_offset;         // first row of this launch (micro-batching)
+  int64_t row_limit;          // rows of this launch at most
+  int32_t n_total;            // output features (multiple of BN)
+  int32_t k_total;            // reduction length (multiple of BK)
+  const float* bias;          // [n_total]
+  const float* w_out;         // EPI 1: [n_total] weights of the scalar head
+  __nv_bfloat16* out_bf16;    // EPI 0: [rows, n_total]
+  float* out_q;               // EPI 1: [rows]
+  int32_t accumulate_q;       // EPI 1: add to out_q instead of overwriting (ensemble members after the first)
+  int* err;
+};
+
+// EPI 0: out = bf16(relu(acc + bias)).  EPI 1: q[row] (+)= sum_n relu(acc + bias[n]) * w_out[n].
+template <int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty, [2S+4] drain, then tmem base
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  int64_t rows = (int64_t)(*g.count_dev) - g.row_offset;
+  if (rows > g.row_limit) rows = g.row_limit;
+  if (rows < 0) rows = 0;
+  const int num_mtiles = (int)((rows + BM - 1) / BM);
+  const int n_chunks = g.n_total / BN;
+  const int k_blocks = g.k_total / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    mbar_init(drain_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_base_slot);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+        const int row0 = (int)(g.row_offset + (int64_t)mt * BM);
+        for (int nc = 0; nc < n_chunks && ok; ++nc) {
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+            mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+            tma_load_2d(sa, &tmA, kb * BK, row0, full_bar(stage));
+            tma_load_2d(sa + A_BYTES, &tmB, kb * BK, nc * BN, full_bar(stage));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_it = 0;
+      bool ok = true;
+      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+        for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
+          const uint32_t b = acc_it & 1u;
+          if (!mbar_wait(tempty_bar(b), ((acc_it >> 1) & 1u) ^ 1u, g.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + b * BN;
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+            const uint64_t adesc = make_desc_sw128(sa);
+            const uint64_t bdesc = make_desc_sw128(sa + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
+              tc_mma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, kIdescBf16, (kb | k) != 0 ? 1u : 0u);
+            }
+            tc_commit(empty_bar(stage));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+          if (ok) tc_commit(tfull_bar(b));
+        }
+      }
+      // drain: every MMA issued by this thread has retired before TMEM is released
+      tc_commit(drain_bar);
+      mbar_wait(drain_bar, 0, g.err, ERR_WAIT_DRAIN);
+    }
+  } else {
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+      const int64_t row_local = (int64_t)mt * BM + quad * 32 + lane;
+      const int64_t row = g.row_offset + row_local;
+      const bool row_ok = row_local < rows;
+      float rowsum = 0.f;
+      for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
+        const uint32_t b = acc_it & 1u;
+        if (!mbar_wait(tfull_bar(b), (acc_it >> 1) & 1u, g.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tc_ld32(taddr + c0, v);
+          tc_wait_ld();
+          const int n0 = nc * BN + c0;
+          if (EPI == 0) {
+            uint32_t packed[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float x0 = fmaxf(__uint_as_float(v[2 * j]) + __ldg(g.bias + n0 + 2 * j), 0.f);
+              const float x1 = fmaxf(__uint_as_float(v[2 * j + 1]) + __ldg(g.bias + n0 + 2 * j + 1), 0.f);
+              __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+              packed[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            if (row_ok) {
+              uint4* dst = reinterpret_cast<uint4*>(g.out_bf16 + row * g.n_total + n0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float x = fmaxf(__uint_as_float(v[j]) + __ldg(g.bias + n0 + j), 0.f);
+              rowsum = fmaf(x, __ldg(g.w_out + n0 + j), rowsum);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(b));
+      }
+      if (EPI == 1 && row_ok && ok) {
+        if (g.accumulate_q) g.out_q[row] += rowsum;
+        else g.out_q[row] = rowsum;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// children [rows, stride] u8 -> one-hot [rows, k_pad] bf16, column = pos * V + value; 8 columns (16 bytes) per thread
+__global__ void __launch_bounds__(256) k_onehot(const uint8_t* __restrict__ children, const uint32_t* count_dev,
+                                                int64_t row_offset, int64_t row_limit, int n, int stride, int V,
+                                                int k_pad, __nv_bfloat16* __restrict__ x) {
+  int64_t rows = (int64_t)(*count_dev) - row_offset;
+  if (rows > row_limit) rows = row_limit;
+  const int chunks = k_pad / 8;
+  const int64_t total = rows * chunks;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / chunks;
+    const int c0 = (int)(i - r * chunks) * 8;
+    const uint8_t* row = children + (row_offset + r) * stride;
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t acc = 0;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int col = c0 + 2 * j + h;
+        const int pos = col / V;
+        const int val = col - pos * V;
+        const bool on = pos < n && __ldg(row + pos) == val;
+        acc |= (on ? 0x3f80u : 0u) << (16 * h);  // bf16 1.0
+      }
+      w[j] = acc;
+    }
+    *reinterpret_cast<uint4*>(x + (row_offset + r) * k_pad + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// q (mean over ensemble members) -> u32 key = uint32(clamp(q - offset, 0, 300) * 256 + 0.5)
+// (kernel_fullbeamnice_q_to_score_key_ring, beam_kernels.cu:341-344)
+__global__ void __launch_bounds__(256) k_q_to_key(const float* __restrict__ q, const uint32_t* count_dev, float inv_models,
+                                                  float offset, uint32_t* __restrict__ keys) {
+  const int64_t rows = *count_dev;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < rows; i += (int64_t)gridDim.x * blockDim.x) {
+    float x = q[i] * inv_models - offset;
+    x = fminf(fmaxf(x, 0.f), 300.f);
+    keys[i] = (uint32_t)(x * 256.f + 0.5f);
+  }
+}
+
+}  // namespace mgbs
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+
+struct MgbsMlp {
+  MgbsMlpConfig cfg;
+  int sms = 148;
+  int k1_pad = 0;
+  CUtensorMap tm_x, tm_h1;
+  CUtensorMap tm_w1[MGBS_MAX_MODELS], tm_w2[MGBS_MAX_MODELS];
+};
+
+namespace {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess) return nullptr;
+  if (qres != cudaDriverEntryPointSuccess) return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] tensor, box = {64 columns (128 bytes), box_rows}, 128-byte swizzle
+int make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return MGBS_ERR_STATE;
+  if (((uintptr_t)base & 15u) != 0 || (cols * 2) % 16 != 0) return MGBS_ERR_ARG;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : MGBS_ERR_STATE;
+}
+
+}  // namespace
+
+extern "C" {
+
+int mgbs_sizeof_mlp_config(void) { return (int)sizeof(MgbsMlpConfig); }
+
+int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
+  if (!cfg || !out) return MGBS_ERR_ARG;
+  const MgbsMlpConfig& c = *cfg;
+  if (c.state_len < 1 || c.state_len > MGBS_MAX_STATE_LEN || c.num_values < 1 || c.num_values > 256) return MGBS_ERR_ARG;
+  if (c.hidden < mgbs::BN || c.hidden % mgbs::BN != 0) return MGBS_ERR_UNSUPPORTED;
+  if (c.num_models < 1 || c.num_models > MGBS_MAX_MODELS || c.max_rows < 1) return MGBS_ERR_ARG;
+  const int k1 = c.state_len * c.num_values;
+  const int k1_pad = (k1 + mgbs::BK - 1) / mgbs::BK * mgbs::BK;
+  if (c.k1_pad != k1_pad) return MGBS_ERR_ARG;
+  if (!c.x || !c.h1 || !c.q || !c.err) return MGBS_ERR_ARG;
+  MgbsMlp* m = new (std::nothrow) MgbsMlp();
+  if (!m) return MGBS_ERR_STATE;
+  m->cfg = c;
+  m->k1_pad = k1_pad;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) m->sms = sms;
+  }
+  const uint64_t rows_pad = ((uint64_t)c.max_rows + mgbs::BM - 1) / mgbs::BM * mgbs::BM;
+  int rc = make_map_bf16(&m->tm_x, c.x, rows_pad, (uint64_t)k1_pad, mgbs::BM);
+  if (!rc) rc = make_map_bf16(&m->tm_h1, c.h1, rows_pad, (uint64_t)c.hidden, mgbs::BM);
+  for (int i = 0; i < c.num_models && !rc; ++i) {
+    if (!c.w1[i] || !c.b1[i] || !c.w2[i] || !c.b2[i] || !c.w3[i]) rc = MGBS_ERR_ARG;
+    if (!rc) rc = make_map_bf16(&m->tm_w1[i], c.w1[i], (uint64_t)c.hidden, (uint64_t)k1_pad, mgbs::BN);
+    if (!rc) rc = make_map_bf16(&m->tm_w2[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden, mgbs::BN);
+  }
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
+  if (rc) { delete m; return rc; }
+  *out = m;
+  return 0;
+}
+
+int mgbs_mlp_destroy(MgbsMlp* m) {
+  delete m;
+  return 0;
+}
+
+int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_dev, uint32_t* scores, void* stream) {
+  MgbsMlp* m = static_cast<MgbsMlp*>(user);
+  if (!m || !children || !count_dev || !scores) return MGBS_ERR_ARG;
+  using namespace mgbs;
+  const MgbsMlpConfig& c = m->cfg;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t rows_cap = c.max_rows;
+  const int grid_gemm = m->sms;
+  {
+    const int64_t chunks = rows_cap * (m->k1_pad / 8);
+    int64_t g = (chunks + 255) / 256;
+    if (g > (int64_t)m->sms * 16) g = (int64_t)m->sms * 16;
+    k_onehot<<<(int)g, 256, 0, st>>>(children, count_dev, 0, rows_cap, c.state_len, c.state_stride, c.num_values,
+                                     m->k1_pad, reinterpret_cast<__nv_bfloat16*>(c.x));
+  }
+  for (int i = 0; i < c.num_models; ++i) {
+    GemmArgs g;
+    g.count_dev = count_dev;
+    g.row_offset = 0;
+    g.row_limit = rows_cap;
+    g.n_total = c.hidden;
+    g.k_total = m->k1_pad;
+    g.bias = c.b1[i];
+    g.w_out = nullptr;
+    g.out_bf16 = reinterpret_cast<__nv_bfloat16*>(c.h1);
+    g.out_q = nullptr;
+    g.accumulate_q = 0;
+    g.err = c.err;
+    k_mlp_gemm<0><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_x, m->tm_w1[i], g);
+    g.k_total = c.hidden;
+    g.bias = c.b2[i];
+    g.w_out = c.w3[i];
+    g.out_bf16 = nullptr;
+    g.out_q = c.q;
+    g.accumulate_q = i > 0 ? 1 : 0;
+    k_mlp_gemm<1><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h1, m->tm_w2[i], g);
+  }
+  {
+    int64_t g = (rows_cap + 255) / 256;
+    if (g > (int64_t)m->sms * 8) g = (int64_t)m->sms * 8;
+    float b3 = 0.f;
+    for (int i = 0; i < c.num_models; ++i) b3 += c.b3[i];
+    // mean over members of (q_i + b3_i) - offset
+    k_q_to_key<<<(int)g, 256, 0, st>>>(c.q, count_dev, 1.f / (float)c.num_models, c.score_offset - b3 / (float)c.num_models, scores);
+  }
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -1,0 +1,137 @@
+"""Device scorers that plug into BeamEngine.set_scorer.
+
+The reference's scorers.py wraps torch modules (MLPActionScorer 120->1024->256->24, scorers.py:21-53) and its C++
+engine runs them through InferenceBackend::forward.  Here the scorer is a value network on child states, evaluated
+by hand-written tcgen05 GEMM kernels inside libmgbs_b200.so; this module only prepares weights and work buffers
+(torch tensors) and hands the native object to the engine.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, List, Sequence, Union
+
+import numpy as np
+import torch
+
+from . import _lib
+from .records import unpack_payload  # noqa: F401  (re-exported for callers of the engine)
+
+MAX_MODELS = 4
+
+
+class MgbsMlpConfig(C.Structure):
+    _fields_ = [
+        ("state_len", C.c_int32), ("state_stride", C.c_int32), ("num_values", C.c_int32), ("hidden", C.c_int32),
+        ("num_models", C.c_int32), ("k1_pad", C.c_int32), ("max_rows", C.c_int64), ("score_offset", C.c_float),
+        ("b3", C.c_float * MAX_MODELS),
+        ("x", C.c_void_p), ("h1", C.c_void_p), ("q", C.c_void_p), ("err", C.c_void_p),
+        ("w1", C.c_void_p * MAX_MODELS), ("b1", C.c_void_p * MAX_MODELS), ("w2", C.c_void_p * MAX_MODELS),
+        ("b2", C.c_void_p * MAX_MODELS), ("w3", C.c_void_p * MAX_MODELS),
+    ]
+
+
+_SIGS = {
+    "mgbs_sizeof_mlp_config": (C.c_int, []),
+    "mgbs_mlp_create": (C.c_int, [C.POINTER(MgbsMlpConfig), C.POINTER(C.c_void_p)]),
+    "mgbs_mlp_destroy": (C.c_int, [C.c_void_p]),
+    "mgbs_mlp_enqueue": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+}
+_lib.SIGNATURES.update(_SIGS)
+
+
+class MLPValueScorer:
+    """Ensemble of value MLPs one-hot(n*V) -> hidden -> hidden -> 1 (ReLU), bf16 operands, fp32 accumulation.
+
+    ``weights``: one dict or a list of dicts with float32 arrays w1 [H, n*V], b1 [H], w2 [H, H], b2 [H], w3 [H], b3.
+    ``score_offset``: subtracted from the network output before it becomes the integer key
+    ``uint32(clamp(q - offset, 0, 300) * 256 + 0.5)``; choose it so that outputs land inside [0, 300].
+    """
+
+    def __init__(self, weights: Union[Dict[str, np.ndarray], Sequence[Dict[str, np.ndarray]]], state_len: int,
+                 state_stride: int, num_values: int, max_rows: int, score_offset: float = -150.0,
+                 device: Union[str, torch.device, None] = None):
+        self.lib = _lib.load()
+        for name, (res, args) in _SIGS.items():
+            fn = getattr(self.lib, name)
+            fn.restype, fn.argtypes = res, args
+        if self.lib.mgbs_sizeof_mlp_config() != C.sizeof(MgbsMlpConfig):
+            raise RuntimeError("structure layout mismatch between scorers.py and libmgbs_b200.so")
+        if isinstance(weights, dict):
+            weights = [weights]
+        if not 1 <= len(weights) <= MAX_MODELS:
+            raise RuntimeError(f"1..{MAX_MODELS} ensemble members supported")
+        dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        hidden = int(weights[0]["w1"].shape[0])
+        k1 = state_len * num_values
+        k1_pad = (k1 + 63) // 64 * 64
+        rows_pad = (int(max_rows) + 127) // 128 * 128
+        self.state_len, self.state_stride, self.num_values = state_len, state_stride, num_values
+        self.hidden, self.k1_pad, self.max_rows = hidden, k1_pad, int(max_rows)
+        self.score_offset = float(score_offset)
+        self.t: Dict[str, List[torch.Tensor]] = {k: [] for k in ("w1", "b1", "w2", "b2", "w3")}
+        cfg = MgbsMlpConfig()
+        for i, w in enumerate(weights):
+            if w["w1"].shape != (hidden, k1) or w["w2"].shape != (hidden, hidden) or w["w3"].shape != (hidden,):
+                raise RuntimeError("weight shapes must be w1 [H, n*V], w2 [H, H], w3 [H]")
+            w1 = torch.zeros((hidden, k1_pad), dtype=torch.bfloat16, device=dev)
+            w1[:, :k1] = torch.from_numpy(np.ascontiguousarray(w["w1"], dtype=np.float32)).to(dev).to(torch.bfloat16)
+            self.t["w1"].append(w1)
+            self.t["w2"].append(torch.from_numpy(np.ascontiguousarray(w["w2"], dtype=np.float32)).to(dev).to(torch.bfloat16).contiguous())
+            for k in ("b1", "b2", "w3"):
+                self.t[k].append(torch.from_numpy(np.ascontiguousarray(w[k], dtype=np.float32)).to(dev))
+            cfg.b3[i] = float(w["b3"])
+            for k in ("w1", "b1", "w2", "b2", "w3"):
+                getattr(cfg, k)[i] = self.t[k][i].data_ptr()
+        self.x = torch.zeros((rows_pad, k1_pad), dtype=torch.bfloat16, device=dev)
+        self.h1 = torch.zeros((rows_pad, hidden), dtype=torch.bfloat16, device=dev)
+        self.q = torch.zeros((rows_pad,), dtype=torch.float32, device=dev)
+        self.err = torch.zeros((1,), dtype=torch.int32, device=dev)
+        self._count = torch.zeros((1,), dtype=torch.int32, device=dev)
+        cfg.state_len, cfg.state_stride, cfg.num_values = state_len, state_stride, num_values
+        cfg.hidden, cfg.num_models, cfg.k1_pad = hidden, len(weights), k1_pad
+        cfg.max_rows = int(max_rows)
+        cfg.score_offset = float(score_offset)
+        cfg.x, cfg.h1, cfg.q, cfg.err = self.x.data_ptr(), self.h1.data_ptr(), self.q.data_ptr(), self.err.data_ptr()
+        self._cfg = cfg
+        h = C.c_void_p()
+        _lib.check(self.lib.mgbs_mlp_create(C.byref(cfg), C.byref(h)), "MLPValueScorer")
+        self._h = h
+        self.num_models = len(weights)
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            self.lib.mgbs_mlp_destroy(h)
+            self._h = None
+
+    def c_callback(self):
+        """(function pointer, user pointer) for mgbs_engine_set_scorer."""
+        return C.cast(self.lib.mgbs_mlp_enqueue, C.c_void_p), self._h
+
+    def flops_per_state(self) -> int:
+        """Dense multiply-add count x2 of one state through all ensemble members."""
+        k1 = self.state_len * self.num_values
+        return self.num_models * 2 * (k1 * self.hidden + self.hidden * self.hidden + self.hidden)
+
+    def score(self, children: torch.Tensor) -> torch.Tensor:
+        """Score rows of a [C, state_stride] uint8 CUDA tensor on the current stream; returns int32 keys [C]."""
+        if children.dtype != torch.uint8 or children.dim() != 2 or children.shape[1] != self.state_stride:
+            raise RuntimeError("children must be [C, state_stride] uint8")
+        if children.shape[0] > self.max_rows:
+            raise RuntimeError("more rows than the scorer was sized for")
+        children = children.contiguous()
+        self._count.fill_(children.shape[0])
+        keys = torch.zeros((children.shape[0],), dtype=torch.int32, device=children.device)
+        st = torch.cuda.current_stream().cuda_stream
+        _lib.check(self.lib.mgbs_mlp_enqueue(self._h, children.data_ptr(), self._count.data_ptr(), keys.data_ptr(),
+                                             C.c_void_p(st)), "MLPValueScorer.score")
+        return keys
+
+    def last_q(self, count: int) -> torch.Tensor:
+        """Sum over ensemble members of the raw head outputs of the last call (before bias, mean and offset)."""
+        return self.q[:count]
+
+    def error_code(self) -> int:
+        """0, or the code of the first bounded wait that gave up inside a GEMM kernel."""
+        return int(self.err.item())
