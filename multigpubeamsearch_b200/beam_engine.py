@@ -325,10 +325,21 @@ class BeamEngine:
         return self._graph_used
 
     def enable_step_timers(self, on: bool) -> None:
+        """Per-stage CUDA-event timers; enabling them drops the captured graphs and steps run eagerly
+        (beam_engine.cpp:1035-1038)."""
         self._events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) if on else None
+        _lib.check(self.lib.mgbs_engine_profile(self._h, int(bool(on))), "enable_step_timers")
+        self._profile = bool(on)
 
     def step_timing(self) -> Dict[str, float]:
-        return dict(self._timing)
+        """Milliseconds of the last step: total and per stage (step_timing, beam_engine.cpp:1040-1062)."""
+        out = dict(self._timing)
+        if getattr(self, "_profile", False):
+            ms = (C.c_float * 5)()
+            _lib.check(self.lib.mgbs_engine_profile_read(self._h, ms), "step_timing")
+            out.update({"expand_ms": ms[0], "scorer_ms": ms[1], "exchange_ms": ms[2], "bands_ms": ms[3],
+                        "final_ms": ms[4]})
+        return out
 
     # -- search ---------------------------------------------------------------------------------
     def reset_search(self, state: bytes, active_on_this_rank: bool = True) -> None:
@@ -365,7 +376,7 @@ class BeamEngine:
         parity = self._ctrl.depth & 1
         if self._events:
             self._events[0].record(self._stream)
-        if self._use_graph:
+        if self._use_graph and not getattr(self, "_profile", False):
             _lib.check(self.lib.mgbs_engine_step_graph(self._h, parity, self._sp()), "step")
             self._graph_used = True
         else:

@@ -71,6 +71,8 @@ struct MgbsEngine {
   void* scorer_user = nullptr;
   cudaGraphExec_t graph[2] = {nullptr, nullptr};
   MgbsCtrl host_ctrl;
+  bool profile = false;
+  cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 #define MGBS_TRY(expr)            \
@@ -168,6 +170,8 @@ int mgbs_engine_destroy(MgbsEngine* e) {
   for (int p = 0; p < 2; ++p)
     if (e->graph[p]) cudaGraphExecDestroy(e->graph[p]);
   if (e->comm && g_nccl.ok) g_nccl.CommDestroy(e->comm);
+  for (int i = 0; i < 6; ++i)
+    if (e->ev[i]) cudaEventDestroy(e->ev[i]);
   delete e;
   return 0;
 }
@@ -198,6 +202,24 @@ int mgbs_engine_set_scorer(MgbsEngine* e, mgbs_scorer_fn fn, void* user) {
   e->scorer_user = user;
   for (int p = 0; p < 2; ++p)
     if (e->graph[p]) { cudaGraphExecDestroy(e->graph[p]); e->graph[p] = nullptr; }
+  return 0;
+}
+
+int mgbs_engine_profile(MgbsEngine* e, int32_t on) {
+  if (!e) return MGBS_ERR_ARG;
+  if (on)
+    for (int i = 0; i < 6; ++i)
+      if (!e->ev[i]) MGBS_TRY(cudaEventCreate(&e->ev[i]));
+  e->profile = on != 0;
+  for (int p = 0; p < 2; ++p)
+    if (e->graph[p]) { cudaGraphExecDestroy(e->graph[p]); e->graph[p] = nullptr; }
+  return 0;
+}
+
+int mgbs_engine_profile_read(MgbsEngine* e, float* ms5) {
+  if (!e || !ms5 || !e->ev[0]) return MGBS_ERR_ARG;
+  MGBS_TRY(cudaEventSynchronize(e->ev[5]));
+  for (int i = 0; i < 5; ++i) MGBS_TRY(cudaEventElapsedTime(&ms5[i], e->ev[i], e->ev[i + 1]));
   return 0;
 }
 
@@ -296,6 +318,8 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
   const int Lb = c.band_levels, R = c.band_rounds, Lf = e->final_levels;
   unsigned long long* tie_buf = reinterpret_cast<unsigned long long*>(c.tie_buf);
 
+  const bool prof = e->profile && phase == 0;
+  if (prof) cudaEventRecord(e->ev[0], st);
   if (phase == 0 || phase == 1) {
     MGBS_TRY(launch_depth_begin(c.ctrl, parity, c.fanout, c.cand_cap, tie_buf + (int64_t)c.rank * kTieSegWords,
                                 W > 1 ? c.send_counts : nullptr, W, st));
@@ -313,12 +337,14 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     x.cand_hash = c.cand_hash; x.cand_fp = c.cand_fp; x.cand_score = c.cand_score; x.cand_payload = c.cand_payload;
     x.ctrl = c.ctrl;
     MGBS_TRY(launch_expand(x, c.frontier_cap, e->sms, st));
+    if (prof) cudaEventRecord(e->ev[1], st);
     if (phase == 0 && c.score_mode == MGBS_SCORE_EXTERNAL) {
       if (!e->scorer) return MGBS_ERR_STATE;
       MGBS_TRY(e->scorer(e->scorer_user, c.children, &c.ctrl->cand_count, c.cand_score, stream));
     }
     if (phase == 1) return 0;
   }
+  if (prof) cudaEventRecord(e->ev[2], st);
 
   StepArgs a;
   memset(&a, 0, sizeof(a));
@@ -348,6 +374,7 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     a.cv.cap = (uint32_t)c.bucket_cap;
     items = c.bucket_cap;  // per bucket; kernels loop over buckets
   }
+  if (prof) cudaEventRecord(e->ev[3], st);
   a.ctrl = c.ctrl;
   a.table = c.table;
   a.tie_buf = tie_buf;
@@ -383,6 +410,7 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     a.hist_prev = c.hist + (int64_t)(r * Lb + Lb - 1) * MGBS_HIST_STRIDE;
     MGBS_TRY(launch_band_insert(a, items, e->sms, st));
   }
+  if (prof) cudaEventRecord(e->ev[4], st);
   // final cut over the table
   uint32_t* fin = c.hist + (int64_t)(R * Lb) * MGBS_HIST_STRIDE;
   a.levels = Lf;
@@ -401,6 +429,7 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     MGBS_NCCL(g_nccl.AllGather(tie_buf + (int64_t)c.rank * kTieSegWords, tie_buf, kTieSegWords, ncclUint64, e->comm, st));
   }
   MGBS_TRY(launch_finish(a, st));
+  if (prof) cudaEventRecord(e->ev[5], st);
   return 0;
 }
 
@@ -410,6 +439,7 @@ int mgbs_engine_step_graph(MgbsEngine* e, int32_t parity, void* stream) {
   if (!e) return MGBS_ERR_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   parity &= 1;
+  if (e->profile) return MGBS_ERR_STATE;  // stage events cannot be timed from inside a graph
   if (!e->graph[parity]) {
     cudaGraph_t g = nullptr;
     MGBS_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));

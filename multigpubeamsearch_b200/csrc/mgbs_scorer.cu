@@ -340,6 +340,8 @@ struct MgbsMlp {
   int k1_pad = 0;
   CUtensorMap tm_x, tm_h1;
   CUtensorMap tm_w1[MGBS_MAX_MODELS], tm_w2[MGBS_MAX_MODELS];
+  bool profile = false;
+  cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 namespace {
@@ -415,7 +417,33 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
 }
 
 int mgbs_mlp_destroy(MgbsMlp* m) {
+  if (m)
+    for (int i = 0; i < 5; ++i)
+      if (m->ev[i]) cudaEventDestroy(m->ev[i]);
   delete m;
+  return 0;
+}
+
+int mgbs_mlp_profile(MgbsMlp* m, int32_t on) {
+  if (!m) return MGBS_ERR_ARG;
+  if (on)
+    for (int i = 0; i < 5; ++i)
+      if (!m->ev[i]) {
+        cudaError_t e = cudaEventCreate(&m->ev[i]);
+        if (e != cudaSuccess) return (int)e;
+      }
+  m->profile = on != 0;
+  return 0;
+}
+
+int mgbs_mlp_profile_read(MgbsMlp* m, float* ms4) {
+  if (!m || !ms4 || !m->ev[0]) return MGBS_ERR_ARG;
+  cudaError_t e = cudaEventSynchronize(m->ev[4]);
+  if (e != cudaSuccess) return (int)e;
+  for (int i = 0; i < 4; ++i) {
+    e = cudaEventElapsedTime(&ms4[i], m->ev[i], m->ev[i + 1]);
+    if (e != cudaSuccess) return (int)e;
+  }
   return 0;
 }
 
@@ -427,6 +455,8 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
   cudaStream_t st = (cudaStream_t)stream;
   const int64_t rows_cap = c.max_rows;
   const int grid_gemm = m->sms;
+  const bool prof = m->profile && c.num_models == 1;
+  if (prof) cudaEventRecord(m->ev[0], st);
   {
     const int64_t chunks = rows_cap * (m->k1_pad / 8);
     int64_t g = (chunks + 255) / 256;
@@ -447,7 +477,9 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
     g.out_q = nullptr;
     g.accumulate_q = 0;
     g.err = c.err;
+    if (prof) cudaEventRecord(m->ev[1], st);
     k_mlp_gemm<0><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_x, m->tm_w1[i], g);
+    if (prof) cudaEventRecord(m->ev[2], st);
     g.k_total = c.hidden;
     g.bias = c.b2[i];
     g.w_out = c.w3[i];
@@ -455,6 +487,7 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
     g.out_q = c.q;
     g.accumulate_q = i > 0 ? 1 : 0;
     k_mlp_gemm<1><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h1, m->tm_w2[i], g);
+    if (prof) cudaEventRecord(m->ev[3], st);
   }
   {
     int64_t g = (rows_cap + 255) / 256;
@@ -464,6 +497,7 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
     // mean over members of (q_i + b3_i) - offset
     k_q_to_key<<<(int)g, 256, 0, st>>>(c.q, count_dev, 1.f / (float)c.num_models, c.score_offset - b3 / (float)c.num_models, scores);
   }
+  if (prof) cudaEventRecord(m->ev[4], st);
   return (int)cudaGetLastError();
 }
 

@@ -35,6 +35,8 @@ _SIGS = {
     "mgbs_sizeof_mlp_config": (C.c_int, []),
     "mgbs_mlp_create": (C.c_int, [C.POINTER(MgbsMlpConfig), C.POINTER(C.c_void_p)]),
     "mgbs_mlp_destroy": (C.c_int, [C.c_void_p]),
+    "mgbs_mlp_profile": (C.c_int, [C.c_void_p, C.c_int32]),
+    "mgbs_mlp_profile_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
     "mgbs_mlp_enqueue": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
 _lib.SIGNATURES.update(_SIGS)
@@ -131,6 +133,15 @@ class MLPValueScorer:
     def last_q(self, count: int) -> torch.Tensor:
         """Sum over ensemble members of the raw head outputs of the last call (before bias, mean and offset)."""
         return self.q[:count]
+
+    def profile(self, on: bool) -> None:
+        """Record CUDA events between the scorer's kernels (eager launches only)."""
+        _lib.check(self.lib.mgbs_mlp_profile(self._h, int(on)), "MLPValueScorer.profile")
+
+    def profile_read(self) -> Dict[str, float]:
+        ms = (C.c_float * 4)()
+        _lib.check(self.lib.mgbs_mlp_profile_read(self._h, ms), "MLPValueScorer.profile_read")
+        return {"onehot_ms": ms[0], "gemm1_ms": ms[1], "gemm2_ms": ms[2], "key_ms": ms[3]}
 
     def error_code(self) -> int:
         """0, or the code of the first bounded wait that gave up inside a GEMM kernel."""
