@@ -1,0 +1,41 @@
+"""Small, self-ending workload for profiler captures of the scorer kernels.
+
+    python -m multigpubeamsearch_b200.profile_case [--rows R] [--repeat N]
+
+Scores R random child states (default 151 552 = 8 tiles per SM on 148 SMs; first-layer activations 310 MB, larger than
+L2) N times with the MLP 324 -> 1024 -> 1024 -> 1.  A dozen launches in total, a few hundred MB on the device.
+"""
+
+from __future__ import annotations
+
+import argparse
+
+import numpy as np
+import torch
+
+from . import puzzles, scorers
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows", type=int, default=151552)
+    ap.add_argument("--repeat", type=int, default=3)
+    args = ap.parse_args()
+    pz = puzzles.puzzle54()
+    rng = np.random.default_rng(0)
+    g = pz.generators.astype(np.int64)
+    rows = np.tile(pz.solved, (args.rows, 1))
+    for _ in range(20):
+        rows = np.take_along_axis(rows, g[rng.integers(0, pz.fanout, size=args.rows)], axis=1)
+    padded = np.zeros((args.rows, 64), np.uint8)
+    padded[:, :54] = rows
+    children = torch.from_numpy(padded).cuda()
+    sc = scorers.MLPValueScorer(puzzles.mlp_weights(324, 1024), 54, 64, 6, max_rows=args.rows)
+    for _ in range(args.repeat):
+        keys = sc.score(children)
+    torch.cuda.synchronize()
+    print("keys", int(keys.min()), int(keys.max()), "err", sc.error_code())
+
+
+if __name__ == "__main__":
+    main()
