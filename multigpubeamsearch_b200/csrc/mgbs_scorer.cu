@@ -502,3 +502,128 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free scoring for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc at the moment they need scores: code running inside a
+// stream-ordered region that forbids allocation, plugins whose memory budget is fixed at load time, or callers
+// holding locks that an allocating runtime call could take.  For them the scratch that mgbs_mlp_enqueue takes from
+// caller-allocated buffers (one-hot activations, first-layer activations, head outputs, the error word and the row
+// count) lives in one file-scope device array.  Every device that loads the library holds these bytes until the
+// process exits.
+// ------------------------------------------------------------------------------------------------
+
+constexpr int kNoAllocMaxRows = MGBS_NOALLOC_MAX_ROWS;
+constexpr int kNoAllocMaxK1 = MGBS_NOALLOC_MAX_K1;
+constexpr int kNoAllocMaxHidden = MGBS_NOALLOC_MAX_HIDDEN;
+constexpr size_t kNaX = (size_t)kNoAllocMaxRows * kNoAllocMaxK1 * 2;          // bf16 one-hot rows
+constexpr size_t kNaH1 = (size_t)kNoAllocMaxRows * kNoAllocMaxHidden * 2;     // bf16 first-layer activations
+constexpr size_t kNaQ = (size_t)kNoAllocMaxRows * 4;                           // f32 head outputs
+constexpr size_t kNaOffX = 0, kNaOffH1 = kNaOffX + kNaX, kNaOffQ = kNaOffH1 + kNaH1, kNaOffWords = kNaOffQ + kNaQ;
+constexpr size_t kNaTotal = kNaOffWords + 256;                                 // [0] row count, [1] error word
+
+static __device__ __align__(256) uint8_t g_noalloc_scratch[kNaTotal];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+// Device address of g_noalloc_scratch per device ordinal.  In host code the array's name is only a stand-in for
+// the symbol; the address a kernel may use comes from cudaGetSymbolAddress, asked once per device with that
+// device current.
+uint8_t* g_noalloc_base[kMaxDevices] = {nullptr};
+
+__global__ void k_noalloc_begin(uint32_t* words, uint32_t rows) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    words[0] = rows;  // the row count the kernels read
+    words[1] = 0;     // error word starts clean: the array keeps whatever the previous call left
+  }
+}
+
+}  // namespace
+
+extern "C" int mgbs_mlp_score_noalloc(const MgbsMlpNoAllocArgs* a, const uint8_t* children, int32_t rows,
+                                      uint32_t* scores, int32_t* err_out_host, void* stream) {
+  using namespace mgbs;
+  if (!a || !children || !scores || rows < 0) return MGBS_ERR_ARG;
+  if (!a->w1 || !a->b1 || !a->w2 || !a->b2 || !a->w3) return MGBS_ERR_ARG;
+  if (a->state_len < 1 || a->state_len > MGBS_MAX_STATE_LEN || a->num_values < 1 || a->num_values > 256) return MGBS_ERR_ARG;
+  if (a->state_stride < a->state_len || a->state_stride % 16 != 0) return MGBS_ERR_ARG;
+  const int k1_pad = (a->state_len * a->num_values + BK - 1) / BK * BK;
+  if (a->hidden < BN || a->hidden % BN != 0) return MGBS_ERR_UNSUPPORTED;
+  // sizes beyond the static scratch are refused, never truncated
+  if (rows > kNoAllocMaxRows || k1_pad > kNoAllocMaxK1 || a->hidden > kNoAllocMaxHidden) return MGBS_ERR_TOO_LARGE;
+  if (rows == 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  int dev = -1;
+  cudaError_t ce = cudaGetDevice(&dev);
+  if (ce != cudaSuccess) return (int)ce;
+  if (dev < 0 || dev >= kMaxDevices) return MGBS_ERR_UNSUPPORTED;
+  if (!g_noalloc_base[dev]) {
+    // first call on this device: resolve the symbol's device address and raise the kernels' shared-memory limit
+    void* p = nullptr;
+    ce = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (ce != cudaSuccess) return (int)ce;
+    ce = cudaFuncSetAttribute(k_mlp_gemm<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (ce != cudaSuccess) return (int)ce;
+    ce = cudaFuncSetAttribute(k_mlp_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (ce != cudaSuccess) return (int)ce;
+    g_noalloc_base[dev] = static_cast<uint8_t*>(p);
+  }
+  uint8_t* base = g_noalloc_base[dev];
+  __nv_bfloat16* x = reinterpret_cast<__nv_bfloat16*>(base + kNaOffX);
+  __nv_bfloat16* h1 = reinterpret_cast<__nv_bfloat16*>(base + kNaOffH1);
+  float* q = reinterpret_cast<float*>(base + kNaOffQ);
+  uint32_t* words = reinterpret_cast<uint32_t*>(base + kNaOffWords);
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+
+  // TMA descriptors are host-side objects; encoding them allocates nothing
+  CUtensorMap tm_x, tm_h1, tm_w1, tm_w2;
+  const uint64_t rows_pad = (uint64_t)kNoAllocMaxRows;  // multiple of 128
+  int rc = make_map_bf16(&tm_x, x, rows_pad, (uint64_t)k1_pad, BM);
+  if (!rc) rc = make_map_bf16(&tm_h1, h1, rows_pad, (uint64_t)a->hidden, BM);
+  if (!rc) rc = make_map_bf16(&tm_w1, a->w1, (uint64_t)a->hidden, (uint64_t)k1_pad, BN);
+  if (!rc) rc = make_map_bf16(&tm_w2, a->w2, (uint64_t)a->hidden, (uint64_t)a->hidden, BN);
+  if (rc) return rc;
+
+  k_noalloc_begin<<<1, 32, 0, st>>>(words, (uint32_t)rows);
+  {
+    const int64_t chunks = (int64_t)rows * (k1_pad / 8);
+    int64_t g = (chunks + 255) / 256;
+    if (g > (int64_t)sms * 16) g = (int64_t)sms * 16;
+    k_onehot<<<(int)g, 256, 0, st>>>(children, words, 0, rows, a->state_len, a->state_stride, a->num_values, k1_pad, x);
+  }
+  GemmArgs g;
+  g.count_dev = words;
+  g.row_offset = 0;
+  g.row_limit = rows;
+  g.n_total = a->hidden;
+  g.k_total = k1_pad;
+  g.bias = a->b1;
+  g.w_out = nullptr;
+  g.out_bf16 = h1;
+  g.out_q = nullptr;
+  g.accumulate_q = 0;
+  g.err = reinterpret_cast<int*>(words + 1);
+  k_mlp_gemm<0><<<sms, GEMM_THREADS, GEMM_SMEM, st>>>(tm_x, tm_w1, g);
+  g.k_total = a->hidden;
+  g.bias = a->b2;
+  g.w_out = a->w3;
+  g.out_bf16 = nullptr;
+  g.out_q = q;
+  k_mlp_gemm<1><<<sms, GEMM_THREADS, GEMM_SMEM, st>>>(tm_h1, tm_w2, g);
+  {
+    int64_t gq = ((int64_t)rows + 255) / 256;
+    k_q_to_key<<<(int)gq, 256, 0, st>>>(q, words, 1.f, a->score_offset - a->b3, scores);
+  }
+  ce = cudaGetLastError();
+  if (ce != cudaSuccess) return (int)ce;
+  if (err_out_host) {
+    // optional: wait for the call and hand back the error word (0 = every bounded wait completed)
+    ce = cudaMemcpyAsync(err_out_host, words + 1, sizeof(int32_t), cudaMemcpyDeviceToHost, st);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(st);
+    if (ce != cudaSuccess) return (int)ce;
+  }
+  return 0;
+}

@@ -31,7 +31,19 @@ class MgbsMlpConfig(C.Structure):
     ]
 
 
+class MgbsMlpNoAllocArgs(C.Structure):
+    _fields_ = [
+        ("state_len", C.c_int32), ("state_stride", C.c_int32), ("num_values", C.c_int32), ("hidden", C.c_int32),
+        ("score_offset", C.c_float), ("b3", C.c_float),
+        ("w1", C.c_void_p), ("b1", C.c_void_p), ("w2", C.c_void_p), ("b2", C.c_void_p), ("w3", C.c_void_p),
+    ]
+
+
+NOALLOC_MAX_ROWS = 4096
+
 _SIGS = {
+    "mgbs_mlp_score_noalloc": (C.c_int, [C.POINTER(MgbsMlpNoAllocArgs), C.c_void_p, C.c_int32, C.c_void_p,
+                                         C.POINTER(C.c_int32), C.c_void_p]),
     "mgbs_sizeof_mlp_config": (C.c_int, []),
     "mgbs_mlp_create": (C.c_int, [C.POINTER(MgbsMlpConfig), C.POINTER(C.c_void_p)]),
     "mgbs_mlp_destroy": (C.c_int, [C.c_void_p]),
@@ -142,6 +154,36 @@ class MLPValueScorer:
         ms = (C.c_float * 4)()
         _lib.check(self.lib.mgbs_mlp_profile_read(self._h, ms), "MLPValueScorer.profile_read")
         return {"onehot_ms": ms[0], "gemm1_ms": ms[1], "gemm2_ms": ms[2], "key_ms": ms[3]}
+
+    def score_no_alloc(self, children: torch.Tensor, out: torch.Tensor, member: int = 0) -> int:
+        """Score through the allocation-free entry point, for callers that may not allocate device memory.
+
+        Uses ensemble member ``member`` only.  ``children`` ([C, state_stride] uint8) and ``out`` ([C] int32) are the
+        caller's tensors; the library's own static device array is the only scratch.  At most NOALLOC_MAX_ROWS rows;
+        larger calls raise.  Do not overlap two such calls on the GPU: they share the scratch.  Returns the GEMM
+        error word (0 = clean) after waiting for the call.
+        """
+        if children.dtype != torch.uint8 or children.dim() != 2 or children.shape[1] != self.state_stride:
+            raise RuntimeError("children must be [C, state_stride] uint8")
+        if out.dtype != torch.int32 or out.numel() < children.shape[0] or not out.is_contiguous():
+            raise RuntimeError("out must be a contiguous int32 tensor with one element per row")
+        if not children.is_contiguous():
+            raise RuntimeError("children must be contiguous")
+        a = MgbsMlpNoAllocArgs()
+        a.state_len, a.state_stride, a.num_values, a.hidden = self.state_len, self.state_stride, self.num_values, self.hidden
+        a.score_offset = self.score_offset
+        a.b3 = float(self._cfg.b3[member])
+        a.w1, a.b1 = self.t["w1"][member].data_ptr(), self.t["b1"][member].data_ptr()
+        a.w2, a.b2 = self.t["w2"][member].data_ptr(), self.t["b2"][member].data_ptr()
+        a.w3 = self.t["w3"][member].data_ptr()
+        err = C.c_int32(0)
+        rc = self.lib.mgbs_mlp_score_noalloc(C.byref(a), children.data_ptr(), int(children.shape[0]), out.data_ptr(),
+                                             C.byref(err), C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        if rc == -5:
+            raise RuntimeError("score_no_alloc: request exceeds the library's static scratch "
+                               f"(at most {NOALLOC_MAX_ROWS} rows, one-hot width 768, hidden 1024)")
+        _lib.check(rc, "score_no_alloc")
+        return int(err.value)
 
     def error_code(self) -> int:
         """0, or the code of the first bounded wait that gave up inside a GEMM kernel."""
