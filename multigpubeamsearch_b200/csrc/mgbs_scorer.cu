@@ -286,6 +286,238 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Layer 1 with the one-hot operand built in shared memory.
+//
+// out[row, :] = bf16(relu(onehot(child[row]) * W1^T + b1)).  The A operand is never materialised in global
+// memory: four producer warps (one thread per tile row) write each 128 x 64 bf16 K-block of the one-hot matrix
+// straight into the 128-byte-swizzled stage the tensor core reads (zero the row, then set the ~11 ones that fall
+// into this K-block), while one thread streams the W1 K-block by TMA into the same stage.  The epilogue packs the
+// activated tile to bf16 in a swizzled staging buffer and writes it with TMA stores, so global writes are full
+// 128-byte rows instead of per-thread row segments.
+//
+// Warps: 0 = TMA (W1), 1 = MMA + TMEM owner, 2..5 = epilogue, 6..9 = one-hot producers.
+// ------------------------------------------------------------------------------------------------
+
+constexpr int L1_THREADS = 320;
+constexpr int L1_STAGES = 3;
+constexpr int L1_STAGING = 2 * A_BYTES;                  // two 128 x 64 bf16 output boxes
+constexpr int L1_CHILD_PITCH = MGBS_MAX_STATE_LEN + 4;   // bytes; odd word pitch -> conflict-free row reads
+constexpr int L1_SMEM = L1_STAGES * STAGE_BYTES + L1_STAGING + BM * L1_CHILD_PITCH + 1024 + 256;
+
+struct L1Args {
+  const uint8_t* children;   // [rows, stride]
+  const uint32_t* count_dev;
+  int64_t row_limit;
+  int32_t n, stride, V;
+  int32_t n_total;           // hidden (multiple of BN)
+  int32_t k_total;           // n*V rounded up to BK
+  const float* bias;
+  int* err;
+};
+
+__device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t byte_in_row) {
+  // 128-byte swizzle inside 1024-byte (8-row) atoms: 16-byte chunk index ^= row mod 8
+  return row * 128u + (byte_in_row ^ ((row & 7u) << 4));
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
+}
+
+__global__ void __launch_bounds__(L1_THREADS, 1)
+k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmOut, L1Args g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* staging = smem + L1_STAGES * STAGE_BYTES;              // 1024-aligned (STAGE_BYTES is a multiple of 1024)
+  uint8_t* child_s = staging + L1_STAGING;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(((uintptr_t)(child_s + BM * L1_CHILD_PITCH) + 7) & ~(uintptr_t)7);
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * L1_STAGES + 5);
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (L1_STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * L1_STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * L1_STAGES + 2 + b); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * L1_STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  int64_t rows = (int64_t)(*g.count_dev);
+  if (rows > g.row_limit) rows = g.row_limit;
+  const int num_mtiles = (int)((rows + BM - 1) / BM);
+  const int n_chunks = g.n_total / BN;
+  const int k_blocks = g.k_total / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L1_STAGES; ++s) { mbar_init(full_bar(s), 1 + 128); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    mbar_init(drain_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_base_slot);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+        for (int nc = 0; nc < n_chunks && ok; ++nc) {
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+            const uint32_t sb = smem_u32(smem + stage * STAGE_BYTES) + A_BYTES;
+            mbar_expect_tx(full_bar(stage), B_BYTES);
+            tma_load_2d(sb, &tmB, kb * BK, nc * BN, full_bar(stage));
+            if (++stage == L1_STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, acc_it = 0;
+      bool ok = true;
+      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+        for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
+          const uint32_t b = acc_it & 1u;
+          if (!mbar_wait(tempty_bar(b), ((acc_it >> 1) & 1u) ^ 1u, g.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + b * BN;
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+            const uint64_t adesc = make_desc_sw128(sa);
+            const uint64_t bdesc = make_desc_sw128(sa + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              tc_mma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, kIdescBf16, (kb | k) != 0 ? 1u : 0u);
+            tc_commit(empty_bar(stage));
+            if (++stage == L1_STAGES) { stage = 0; phase ^= 1u; }
+          }
+          if (ok) tc_commit(tfull_bar(b));
+        }
+      }
+      tc_commit(drain_bar);
+      mbar_wait(drain_bar, 0, g.err, ERR_WAIT_DRAIN);
+    }
+  } else if (warp < 6) {
+    // ---- epilogue: TMEM -> bias, ReLU, bf16 -> swizzled staging box -> TMA store ----
+    const int quad = warp & 3;
+    const int et = (warp - 2) * 32 + lane;       // 0..127 among epilogue threads
+    const uint32_t r = (uint32_t)(quad * 32 + lane);  // tile row owned by this thread
+    uint32_t acc_it = 0, box_it = 0;
+    bool ok = true;
+    for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+      const int row0 = mt * BM;
+      for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
+        const uint32_t b = acc_it & 1u;
+        if (!mbar_wait(tfull_bar(b), (acc_it >> 1) & 1u, g.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * BN;
+#pragma unroll 1
+        for (int gcol = 0; gcol < BN; gcol += 64, ++box_it) {
+          uint8_t* box = staging + (box_it & 1u) * A_BYTES;
+          // the TMA store that last read this box must be done before it is overwritten
+          if (et == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t v[32];
+            tc_ld32(taddr + gcol + half * 32, v);
+            tc_wait_ld();
+            const int n0 = nc * BN + gcol + half * 32;
+            uint32_t packed[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float x0 = fmaxf(__uint_as_float(v[2 * j]) + __ldg(g.bias + n0 + 2 * j), 0.f);
+              const float x1 = fmaxf(__uint_as_float(v[2 * j + 1]) + __ldg(g.bias + n0 + 2 * j + 1), 0.f);
+              __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+              packed[j] = *reinterpret_cast<uint32_t*>(&h);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t off = swz128(r, (uint32_t)(half * 64 + q * 16));
+              *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (et == 0) {
+            tma_store_2d(&tmOut, smem_u32(box), nc * BN + gcol, row0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(b));
+      }
+    }
+    if (et == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  } else {
+    // ---- one-hot producers: thread pt owns tile row pt ----
+    const int pt = (warp - 6) * 32 + lane;
+    uint8_t* my_child = child_s + pt * L1_CHILD_PITCH;
+    const int V = g.V, n = g.n;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+      const int64_t row = (int64_t)mt * BM + pt;
+      // own row of child bytes -> shared (only this thread reads it back)
+      if (row < rows) {
+        const uint4* src = reinterpret_cast<const uint4*>(g.children + row * g.stride);
+        for (int q = 0; q < (g.stride >> 4); ++q) {
+          const uint4 w = __ldg(src + q);
+          uint32_t* dst = reinterpret_cast<uint32_t*>(my_child + q * 16);
+          dst[0] = w.x; dst[1] = w.y; dst[2] = w.z; dst[3] = w.w;
+        }
+      } else {
+        for (int q = 0; q < (g.stride >> 2); ++q) reinterpret_cast<uint32_t*>(my_child)[q] = 0u;
+      }
+      for (int nc = 0; nc < n_chunks && ok; ++nc) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          uint8_t* a_stage = smem + stage * STAGE_BYTES;
+          // zero the 16 KB block cooperatively: consecutive lanes write consecutive 16-byte chunks (no bank
+          // conflicts; a thread zeroing its own 128-byte row would serialise 32 lanes on one bank group)
+          uint4* a4 = reinterpret_cast<uint4*>(a_stage);
+#pragma unroll
+          for (int q = 0; q < A_BYTES / 16 / 128; ++q) a4[q * 128 + pt] = make_uint4(0u, 0u, 0u, 0u);
+          asm volatile("bar.sync 2, 128;" ::: "memory");
+          // ones of this K-block: columns pos*V + value in [kb*64, kb*64 + 64)
+          const int c_lo = kb * BK;
+          int pos = c_lo / V;
+          for (; pos < n; ++pos) {
+            const int col = pos * V + (int)my_child[pos] - c_lo;
+            if (col >= BK) { if (pos * V - c_lo >= BK) break; else continue; }
+            if (col >= 0) *reinterpret_cast<uint16_t*>(a_stage + swz128((uint32_t)pt, (uint32_t)col * 2u)) = 0x3f80;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          mbar_arrive(full_bar(stage));
+          if (++stage == L1_STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // children [rows, stride] u8 -> one-hot [rows, k_pad] bf16, column = pos * V + value; 8 columns (16 bytes) per thread
 __global__ void __launch_bounds__(256) k_onehot(const uint8_t* __restrict__ children, const uint32_t* count_dev,
                                                 int64_t row_offset, int64_t row_limit, int n, int stride, int V,
@@ -340,6 +572,7 @@ struct MgbsMlp {
   int k1_pad = 0;
   CUtensorMap tm_x, tm_h1;
   CUtensorMap tm_w1[MGBS_MAX_MODELS], tm_w2[MGBS_MAX_MODELS];
+  bool fused_l1 = true;
   bool profile = false;
   cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
 };
@@ -411,6 +644,7 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
   }
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
   if (rc) { delete m; return rc; }
   *out = m;
   return 0;
@@ -421,6 +655,12 @@ int mgbs_mlp_destroy(MgbsMlp* m) {
     for (int i = 0; i < 5; ++i)
       if (m->ev[i]) cudaEventDestroy(m->ev[i]);
   delete m;
+  return 0;
+}
+
+int mgbs_mlp_set_l1_mode(MgbsMlp* m, int32_t fused) {
+  if (!m) return MGBS_ERR_ARG;
+  m->fused_l1 = fused != 0;
   return 0;
 }
 
@@ -457,7 +697,7 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
   const int grid_gemm = m->sms;
   const bool prof = m->profile && c.num_models == 1;
   if (prof) cudaEventRecord(m->ev[0], st);
-  {
+  if (!m->fused_l1) {
     const int64_t chunks = rows_cap * (m->k1_pad / 8);
     int64_t g = (chunks + 255) / 256;
     if (g > (int64_t)m->sms * 16) g = (int64_t)m->sms * 16;
@@ -478,7 +718,20 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
     g.accumulate_q = 0;
     g.err = c.err;
     if (prof) cudaEventRecord(m->ev[1], st);
-    k_mlp_gemm<0><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_x, m->tm_w1[i], g);
+    if (m->fused_l1) {
+      L1Args l;
+      l.children = children;
+      l.count_dev = count_dev;
+      l.row_limit = rows_cap;
+      l.n = c.state_len; l.stride = c.state_stride; l.V = c.num_values;
+      l.n_total = c.hidden;
+      l.k_total = m->k1_pad;
+      l.bias = c.b1[i];
+      l.err = c.err;
+      k_mlp_l1<<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
+    } else {
+      k_mlp_gemm<0><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_x, m->tm_w1[i], g);
+    }
     if (prof) cudaEventRecord(m->ev[2], st);
     g.k_total = c.hidden;
     g.bias = c.b2[i];

@@ -48,6 +48,7 @@ _SIGS = {
     "mgbs_mlp_create": (C.c_int, [C.POINTER(MgbsMlpConfig), C.POINTER(C.c_void_p)]),
     "mgbs_mlp_destroy": (C.c_int, [C.c_void_p]),
     "mgbs_mlp_profile": (C.c_int, [C.c_void_p, C.c_int32]),
+    "mgbs_mlp_set_l1_mode": (C.c_int, [C.c_void_p, C.c_int32]),
     "mgbs_mlp_profile_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
     "mgbs_mlp_enqueue": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
@@ -145,6 +146,10 @@ class MLPValueScorer:
     def last_q(self, count: int) -> torch.Tensor:
         """Sum over ensemble members of the raw head outputs of the last call (before bias, mean and offset)."""
         return self.q[:count]
+
+    def set_l1_mode(self, fused: bool) -> None:
+        """Layer 1 with the one-hot operand built in shared memory (default) or as one-hot kernel + plain GEMM."""
+        _lib.check(self.lib.mgbs_mlp_set_l1_mode(self._h, int(bool(fused))), "set_l1_mode")
 
     def profile(self, on: bool) -> None:
         """Record CUDA events between the scorer's kernels (eager launches only)."""

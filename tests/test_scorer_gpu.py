@@ -97,3 +97,22 @@ def test_engine_with_mlp_scorer_matches_oracle_on_device_scores():
     engine.enable_cuda_graphs(True)
     engine.step()
     assert np.array_equal(bo.sorted_rows(engine.frontier()), bo.sorted_rows(want.states))
+
+
+def test_fused_layer1_equals_unfused_path():
+    # the in-shared-memory one-hot operand and the TMA-store epilogue change no bit of the result
+    pz = puzzles.puzzle96()
+    ws = [puzzles.mlp_weights(96 * 8, 1024, model_idx=i) for i in range(2)]
+    ws[0]["b1"] = (np.random.default_rng(8).standard_normal(1024) * 0.05).astype(np.float32)
+    sc = scorers.MLPValueScorer(ws, 96, 96, 8, max_rows=20000)
+    rows = children_of(pz, 20000 - 37, seed=2)
+    dev = torch.from_numpy(padded(rows, 96)).cuda()
+    sc.set_l1_mode(True)
+    a = sc.score(dev).clone()
+    h1_a = sc.h1[: rows.shape[0]].clone()
+    sc.set_l1_mode(False)
+    b = sc.score(dev).clone()
+    torch.cuda.synchronize()
+    assert sc.error_code() == 0
+    assert torch.equal(h1_a, sc.h1[: rows.shape[0]])
+    assert torch.equal(a, b)
