@@ -307,7 +307,9 @@ def run_ours(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": workload_name(world), "global_beam": beam, "beam_per_gpu": BEAM_PER_GPU,
                        "candidates_per_step": total_cands / K, "l2": "256 MB buffer written between timed steps",
-                       "parallelism": f"hash-owner dp{world}", "cuda_graph": True},
+                       "parallelism": f"hash-owner dp{world}", "cuda_graph": True,
+                       "unique_per_step": st["counters"][3], "band_rounds_used": st["counters"][5],
+                       "table_inserts_per_step_rank0": st["counters"][1]},
             "roofline": roofline,
             "cpu_baseline": cpu_obj,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(pinned_in.numel()),

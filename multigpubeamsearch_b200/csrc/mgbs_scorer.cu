@@ -290,20 +290,24 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
 // Layer 1 with the one-hot operand built in shared memory.
 //
 // out[row, :] = bf16(relu(onehot(child[row]) * W1^T + b1)).  The A operand is never materialised in global
-// memory: four producer warps (one thread per tile row) write each 128 x 64 bf16 K-block of the one-hot matrix
-// straight into the 128-byte-swizzled stage the tensor core reads (zero the row, then set the ~11 ones that fall
-// into this K-block), while one thread streams the W1 K-block by TMA into the same stage.  The epilogue packs the
-// activated tile to bf16 in a swizzled staging buffer and writes it with TMA stores, so global writes are full
-// 128-byte rows instead of per-thread row segments.
+// memory.  Eight producer warps build the 128 x 64 bf16 K-blocks of the one-hot matrix straight into the
+// 128-byte-swizzled A stages the tensor core reads.  Each pair of producer warps owns one of four A stages and
+// works on every fourth K-block by itself (each warp zeroes its 64 rows = 8 KB with conflict-free 16-byte stores,
+// then sets the ones of two rows per lane with independent predicated stores), so four K-blocks are in production at any time and
+// the latency of one block is hidden behind the others.  W1 K-blocks stream by TMA through a separate 3-stage
+// ring.  The epilogue packs the activated tile to bf16 in a swizzled staging box and writes it with TMA stores
+// (full 128-byte rows instead of per-thread row segments).
 //
-// Warps: 0 = TMA (W1), 1 = MMA + TMEM owner, 2..5 = epilogue, 6..9 = one-hot producers.
+// Warps: 0 = TMA (W1), 1 = MMA + TMEM owner, 2..5 = epilogue, 6..13 = one-hot producers (two per A stage).
 // ------------------------------------------------------------------------------------------------
 
-constexpr int L1_THREADS = 320;
-constexpr int L1_STAGES = 3;
+constexpr int L1_THREADS = 448;
+constexpr int L1_A_STAGES = 4;                           // one per producer warp
+constexpr int L1_B_STAGES = 3;
 constexpr int L1_STAGING = 2 * A_BYTES;                  // two 128 x 64 bf16 output boxes
 constexpr int L1_CHILD_PITCH = MGBS_MAX_STATE_LEN + 4;   // bytes; odd word pitch -> conflict-free row reads
-constexpr int L1_SMEM = L1_STAGES * STAGE_BYTES + L1_STAGING + BM * L1_CHILD_PITCH + 1024 + 256;
+constexpr int L1_MAX_KBLOCKS = 16;
+constexpr int L1_SMEM = L1_A_STAGES * A_BYTES + L1_B_STAGES * B_BYTES + L1_STAGING + BM * L1_CHILD_PITCH + 1024 + 512;
 
 struct L1Args {
   const uint8_t* children;   // [rows, stride]
@@ -330,16 +334,23 @@ __global__ void __launch_bounds__(L1_THREADS, 1)
 k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmOut, L1Args g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* staging = smem + L1_STAGES * STAGE_BYTES;              // 1024-aligned (STAGE_BYTES is a multiple of 1024)
+  uint8_t* a_ring = smem;                                   // 4 x 16 KB, 1024-aligned
+  uint8_t* b_ring = a_ring + L1_A_STAGES * A_BYTES;         // 3 x 32 KB
+  uint8_t* staging = b_ring + L1_B_STAGES * B_BYTES;        // 2 x 16 KB
   uint8_t* child_s = staging + L1_STAGING;
   uint64_t* bars = reinterpret_cast<uint64_t*>(((uintptr_t)(child_s + BM * L1_CHILD_PITCH) + 7) & ~(uintptr_t)7);
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * L1_STAGES + 5);
+  // barriers: a_full[4], a_empty[4], b_full[3], b_empty[3], tmem_full[2], tmem_empty[2], drain
+  constexpr int NB = 2 * L1_A_STAGES + 2 * L1_B_STAGES + 5;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + NB);
+  int32_t* p_lo_tab = reinterpret_cast<int32_t*>(bars + NB + 1);  // first position of each K-block
   const uint32_t bar0 = smem_u32(bars);
-  auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (L1_STAGES + s); };
-  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * L1_STAGES + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * L1_STAGES + 2 + b); };
-  const uint32_t drain_bar = bar0 + 8u * (2 * L1_STAGES + 4);
+  auto a_full = [&](int s) { return bar0 + 8u * s; };
+  auto a_empty = [&](int s) { return bar0 + 8u * (L1_A_STAGES + s); };
+  auto b_full = [&](int s) { return bar0 + 8u * (2 * L1_A_STAGES + s); };
+  auto b_empty = [&](int s) { return bar0 + 8u * (2 * L1_A_STAGES + L1_B_STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * L1_A_STAGES + 2 * L1_B_STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * L1_A_STAGES + 2 * L1_B_STAGES + 2 + b); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * L1_A_STAGES + 2 * L1_B_STAGES + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -348,11 +359,14 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
   const int num_mtiles = (int)((rows + BM - 1) / BM);
   const int n_chunks = g.n_total / BN;
   const int k_blocks = g.k_total / BK;
+  const int blocks_per_tile = n_chunks * k_blocks;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < L1_STAGES; ++s) { mbar_init(full_bar(s), 1 + 128); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < L1_A_STAGES; ++s) { mbar_init(a_full(s), 2); mbar_init(a_empty(s), 1); }
+    for (int s = 0; s < L1_B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
     mbar_init(drain_bar, 1);
+    for (int kb = 0; kb < k_blocks && kb < L1_MAX_KBLOCKS; ++kb) p_lo_tab[kb] = (kb * BK) / g.V;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -366,6 +380,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_base_slot);
 
   if (warp == 0) {
+    // ---- W1 K-blocks by TMA ----
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
@@ -373,19 +388,19 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
       for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
         for (int nc = 0; nc < n_chunks && ok; ++nc) {
           for (int kb = 0; kb < k_blocks; ++kb) {
-            if (!mbar_wait(empty_bar(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-            const uint32_t sb = smem_u32(smem + stage * STAGE_BYTES) + A_BYTES;
-            mbar_expect_tx(full_bar(stage), B_BYTES);
-            tma_load_2d(sb, &tmB, kb * BK, nc * BN, full_bar(stage));
-            if (++stage == L1_STAGES) { stage = 0; phase ^= 1u; }
+            if (!mbar_wait(b_empty(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+            mbar_expect_tx(b_full(stage), B_BYTES);
+            tma_load_2d(smem_u32(b_ring + stage * B_BYTES), &tmB, kb * BK, nc * BN, b_full(stage));
+            if (++stage == L1_B_STAGES) { stage = 0; phase ^= 1u; }
           }
         }
       }
     }
   } else if (warp == 1) {
+    // ---- MMA issue ----
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0, acc_it = 0;
+      int sb = 0;
+      uint32_t pb = 0, acc_it = 0, it = 0;
       bool ok = true;
       for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
         for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
@@ -393,17 +408,19 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
           if (!mbar_wait(tempty_bar(b), ((acc_it >> 1) & 1u) ^ 1u, g.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + b * BN;
-          for (int kb = 0; kb < k_blocks; ++kb) {
-            if (!mbar_wait(full_bar(stage), phase, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+          for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            const int sa = (int)(it & (L1_A_STAGES - 1));
+            if (!mbar_wait(a_full(sa), (it / L1_A_STAGES) & 1u, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+            if (!mbar_wait(b_full(sb), pb, g.err, ERR_WAIT_FULL)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-            const uint64_t adesc = make_desc_sw128(sa);
-            const uint64_t bdesc = make_desc_sw128(sa + A_BYTES);
+            const uint64_t adesc = make_desc_sw128(smem_u32(a_ring + sa * A_BYTES));
+            const uint64_t bdesc = make_desc_sw128(smem_u32(b_ring + sb * B_BYTES));
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k)
               tc_mma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, kIdescBf16, (kb | k) != 0 ? 1u : 0u);
-            tc_commit(empty_bar(stage));
-            if (++stage == L1_STAGES) { stage = 0; phase ^= 1u; }
+            tc_commit(a_empty(sa));
+            tc_commit(b_empty(sb));
+            if (++sb == L1_B_STAGES) { sb = 0; pb ^= 1u; }
           }
           if (ok) tc_commit(tfull_bar(b));
         }
@@ -414,7 +431,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
   } else if (warp < 6) {
     // ---- epilogue: TMEM -> bias, ReLU, bf16 -> swizzled staging box -> TMA store ----
     const int quad = warp & 3;
-    const int et = (warp - 2) * 32 + lane;       // 0..127 among epilogue threads
+    const int et = (warp - 2) * 32 + lane;            // 0..127 among epilogue threads
     const uint32_t r = (uint32_t)(quad * 32 + lane);  // tile row owned by this thread
     uint32_t acc_it = 0, box_it = 0;
     bool ok = true;
@@ -465,48 +482,62 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
     }
     if (et == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else {
-    // ---- one-hot producers: thread pt owns tile row pt ----
-    const int pt = (warp - 6) * 32 + lane;
-    uint8_t* my_child = child_s + pt * L1_CHILD_PITCH;
+    // ---- one-hot producers: warp pw owns A stage pw and builds K-blocks pw, pw+4, pw+8, ... of the sequence ----
+    const int pw = (warp - 6) >> 1;        // A stage of this warp
+    const int half = (warp - 6) & 1;       // rows half*64 .. half*64+63 of the block
+    const int pt = (warp - 6) * 32 + lane;  // 0..255; threads 0..127 load the child tile
     const int V = g.V, n = g.n;
-    int stage = 0;
-    uint32_t phase = 0;
+    uint8_t* a_stage = a_ring + pw * A_BYTES;
+    uint32_t it_base = 0;           // index of this tile's first K-block in the CTA's K-block sequence
     bool ok = true;
-    for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
-      const int64_t row = (int64_t)mt * BM + pt;
-      // own row of child bytes -> shared (only this thread reads it back)
-      if (row < rows) {
-        const uint4* src = reinterpret_cast<const uint4*>(g.children + row * g.stride);
-        for (int q = 0; q < (g.stride >> 4); ++q) {
-          const uint4 w = __ldg(src + q);
-          uint32_t* dst = reinterpret_cast<uint32_t*>(my_child + q * 16);
-          dst[0] = w.x; dst[1] = w.y; dst[2] = w.z; dst[3] = w.w;
-        }
-      } else {
-        for (int q = 0; q < (g.stride >> 2); ++q) reinterpret_cast<uint32_t*>(my_child)[q] = 0u;
-      }
-      for (int nc = 0; nc < n_chunks && ok; ++nc) {
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-          uint8_t* a_stage = smem + stage * STAGE_BYTES;
-          // zero the 16 KB block cooperatively: consecutive lanes write consecutive 16-byte chunks (no bank
-          // conflicts; a thread zeroing its own 128-byte row would serialise 32 lanes on one bank group)
-          uint4* a4 = reinterpret_cast<uint4*>(a_stage);
-#pragma unroll
-          for (int q = 0; q < A_BYTES / 16 / 128; ++q) a4[q * 128 + pt] = make_uint4(0u, 0u, 0u, 0u);
-          asm volatile("bar.sync 2, 128;" ::: "memory");
-          // ones of this K-block: columns pos*V + value in [kb*64, kb*64 + 64)
-          const int c_lo = kb * BK;
-          int pos = c_lo / V;
-          for (; pos < n; ++pos) {
-            const int col = pos * V + (int)my_child[pos] - c_lo;
-            if (col >= BK) { if (pos * V - c_lo >= BK) break; else continue; }
-            if (col >= 0) *reinterpret_cast<uint16_t*>(a_stage + swz128((uint32_t)pt, (uint32_t)col * 2u)) = 0x3f80;
+    for (int mt = blockIdx.x; mt < num_mtiles; mt += gridDim.x, it_base += (uint32_t)blocks_per_tile) {
+      // all producer warps have finished reading the previous tile's child rows
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (pt < BM) {
+        const int64_t row = (int64_t)mt * BM + pt;
+        uint32_t* dst = reinterpret_cast<uint32_t*>(child_s + pt * L1_CHILD_PITCH);
+        if (row < rows) {
+          const uint4* src = reinterpret_cast<const uint4*>(g.children + row * g.stride);
+          for (int q = 0; q < (g.stride >> 4); ++q) {
+            const uint4 w = __ldg(src + q);
+            dst[4 * q] = w.x; dst[4 * q + 1] = w.y; dst[4 * q + 2] = w.z; dst[4 * q + 3] = w.w;
           }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          mbar_arrive(full_bar(stage));
-          if (++stage == L1_STAGES) { stage = 0; phase ^= 1u; }
+        } else {
+          for (int q = 0; q < (g.stride >> 2); ++q) dst[q] = 0u;
         }
+      }
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (!ok) continue;
+      // first K-block of this tile that belongs to this warp
+      const uint32_t first = (uint32_t)((pw - (int)(it_base & 3u)) & 3);
+      for (uint32_t j = first; j < (uint32_t)blocks_per_tile; j += L1_A_STAGES) {
+        const uint32_t it = it_base + j;
+        const int kb = (int)(j % (uint32_t)k_blocks);
+        if (!mbar_wait(a_empty(pw), ((it / L1_A_STAGES) & 1u) ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+        // zero this warp's 64 rows (8 KB, contiguous): consecutive lanes write consecutive 16-byte chunks
+        uint4* a4 = reinterpret_cast<uint4*>(a_stage + half * (A_BYTES / 2));
+#pragma unroll 8
+        for (int q = 0; q < A_BYTES / 2 / 16 / 32; ++q) a4[q * 32 + lane] = make_uint4(0u, 0u, 0u, 0u);
+        __syncwarp();
+        // ones: column pos*V + value inside [kb*64, kb*64+64); rows half*64 + lane and + 32
+        const int c_lo = kb * BK;
+        const int p_lo = p_lo_tab[kb];
+        int p_hi = p_lo + (BK + V - 1) / V;  // inclusive upper bound on positions that can reach this block
+        if (p_hi > n - 1) p_hi = n - 1;
+#pragma unroll 4
+        for (int pos = p_lo; pos <= p_hi; ++pos) {
+          const int cbase = pos * V - c_lo;
+#pragma unroll
+          for (int rr = 0; rr < 2; ++rr) {
+            const uint32_t row = (uint32_t)(half * 64 + lane + 32 * rr);
+            const int col = cbase + (int)child_s[row * L1_CHILD_PITCH + pos];
+            if (col >= 0 && col < BK)
+              *reinterpret_cast<uint16_t*>(a_stage + swz128(row, (uint32_t)col * 2u)) = 0x3f80;
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_full(pw));
       }
     }
   }
