@@ -174,7 +174,7 @@ def run_ours(args):
     sizes = ext.derive_sizes(cfg)
     sc = scorers.MLPValueScorer(puzzles.mlp_weights(pz.state_len * pz.num_values, 1024), pz.state_len,
                                 cfg["state_size_bytes"], pz.num_values, max_rows=sizes["cand_cap"],
-                                score_offset=SCORE_OFFSET)
+                                score_offset=SCORE_OFFSET, dtype=args.dtype)
     _, cfg, buffers, engine = be.configure_engine(pz, cfg=cfg, scorer=sc)
     dev = torch.device("cuda", local_rank)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # > 126 MB L2
@@ -290,6 +290,35 @@ def run_ours(args):
     e2e_value = float(e2e_c.item()) / float(e2e_t.item())
     clocks = sampler.stop()
 
+    # ---- the same steps with the scorer in FP8 (E4M3 operands, per-channel scales): short extra pass ----
+    fp8 = None
+    if args.dtype == "bf16" and not args.no_fp8:
+        del engine, buffers, sc
+        torch.cuda.empty_cache()
+        sc8 = scorers.MLPValueScorer(puzzles.mlp_weights(pz.state_len * pz.num_values, 1024), pz.state_len,
+                                     cfg["state_size_bytes"], pz.num_values, max_rows=sizes["cand_cap"],
+                                     score_offset=SCORE_OFFSET, dtype="fp8")
+        cfg8 = dict(cfg)
+        _, cfg8, buffers, engine = be.configure_engine(pz, cfg=cfg8, scorer=sc8)
+        stream = engine._stream
+        be.run_one_search(engine, start, PREP_DEPTHS)
+        timed_steps(W)
+        c0 = engine.status()["total_candidates"]
+        barrier()
+        k8 = max(3, min(K, 20))
+        ms8 = timed_steps(k8)
+        barrier()
+        st8 = engine.status()
+        t8 = torch.tensor([sum(ms8), float(st8["total_candidates"] - c0), float(st8["status_bits"]),
+                           float(sc8.error_code())], device=dev, dtype=torch.float64)
+        t8max = t8.clone()
+        if world > 1:
+            dist.all_reduce(t8max, op=dist.ReduceOp.MAX)
+            dist.all_reduce(t8, op=dist.ReduceOp.SUM)
+        fp8 = {"value": float(t8[1].item()) / (float(t8max[0].item()) * 1e-3), "unit": UNIT,
+               "ms_per_step": float(t8max[0].item()) / k8, "steps": k8, "status_bits": int(t8[2].item()),
+               "scorer_err": int(t8[3].item()), "dtype": "fp8 e4m3 operands, fp32 accumulation"}
+
     if rank == 0:
         cpu_val, _, cpu_sample = (None, None, None)
         cpu_obj = None
@@ -304,7 +333,7 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": total_ms / K, "p50_ms_per_step": statistics.median(ms), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
             "config": {"workload": workload_name(world), "global_beam": beam, "beam_per_gpu": BEAM_PER_GPU,
                        "candidates_per_step": total_cands / K, "l2": "256 MB buffer written between timed steps",
                        "parallelism": f"hash-owner dp{world}", "cuda_graph": True,
@@ -314,6 +343,7 @@ def run_ours(args):
             "cpu_baseline": cpu_obj,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(pinned_in.numel()),
                     "d2h_bytes_per_step": int(d2h), "steps": e2e_steps},
+            "fp8": fp8,
             "gpu_launches": launches_per_step * K,
             "clocks": clocks,
             "status_bits": int(t[2].item()), "scorer_err": int(t[3].item()),
@@ -331,6 +361,8 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"], help="scorer operand type of the headline run")
+    ap.add_argument("--no-fp8", action="store_true", help="skip the short extra FP8 pass")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -13,6 +13,7 @@
 
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <string.h>
@@ -26,6 +27,7 @@ namespace mgbs {
 constexpr int BM = 128;       // rows per tile (TMEM lanes)
 constexpr int BN = 256;       // accumulator columns per tile
 constexpr int BK = 64;        // bf16 elements per 128-byte swizzle row
+constexpr int BK8 = 128;      // e4m3 elements per 128-byte swizzle row
 constexpr int UMMA_K = 16;    // K of one tcgen05.mma for 16-bit operands
 constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;  // 16 KB
@@ -93,6 +95,19 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint
       : "memory");
 }
 
+// same for e4m3 operands (kind::f8f6f4, K = 32 elements per instruction)
+__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
+template <int F8>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate);
+
 __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -117,6 +132,13 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
 // Instruction descriptor for kind::f16: D = f32 (bits 4-5 = 1), A = B = bf16 (bits 7-9 / 10-12 = 1), both K-major
 // (bits 15, 16 = 0), N >> 3 in bits 17-22, M >> 4 in bits 24-28.
 constexpr uint32_t kIdescBf16 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// kind::f8f6f4 with A = B = E4M3 (format code 0), D = f32
+constexpr uint32_t kIdescE4m3 = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+template <>
+__device__ __forceinline__ void tc_mma<0>(uint32_t d, uint64_t a, uint64_t b, uint32_t acc) { tc_mma_f16(d, a, b, kIdescBf16, acc); }
+template <>
+__device__ __forceinline__ void tc_mma<1>(uint32_t d, uint64_t a, uint64_t b, uint32_t acc) { tc_mma_f8(d, a, b, kIdescE4m3, acc); }
 
 struct GemmArgs {
   const uint32_t* count_dev;  // rows to process (device value)
@@ -125,6 +147,7 @@ struct GemmArgs {
   int32_t n_total;            // output features (multiple of BN)
   int32_t k_total;            // reduction length (multiple of BK)
   const float* bias;          // [n_total]
+  const float* col_scale;     // fp8 only: [n_total] dequantisation factor of each output column
   const float* w_out;         // EPI 1: [n_total] weights of the scalar head
   __nv_bfloat16* out_bf16;    // EPI 0: [rows, n_total]
   float* out_q;               // EPI 1: [rows]
@@ -133,7 +156,7 @@ struct GemmArgs {
 };
 
 // EPI 0: out = bf16(relu(acc + bias)).  EPI 1: q[row] (+)= sum_n relu(acc + bias[n]) * w_out[n].
-template <int EPI>
+template <int EPI, int F8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
@@ -156,7 +179,8 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
   if (rows < 0) rows = 0;
   const int num_mtiles = (int)((rows + BM - 1) / BM);
   const int n_chunks = g.n_total / BN;
-  const int k_blocks = g.k_total / BK;
+  constexpr int BKE = F8 ? BK8 : BK;  // elements per 128-byte K-block
+  const int k_blocks = g.k_total / BKE;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -186,8 +210,8 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             if (!mbar_wait(empty_bar(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
             const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
             mbar_expect_tx(full_bar(stage), STAGE_BYTES);
-            tma_load_2d(sa, &tmA, kb * BK, row0, full_bar(stage));
-            tma_load_2d(sa + A_BYTES, &tmB, kb * BK, nc * BN, full_bar(stage));
+            tma_load_2d(sa, &tmA, kb * BKE, row0, full_bar(stage));
+            tma_load_2d(sa + A_BYTES, &tmB, kb * BKE, nc * BN, full_bar(stage));
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
           }
         }
@@ -213,8 +237,8 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             const uint64_t bdesc = make_desc_sw128(sa + A_BYTES);
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
-              // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the (address >> 4) field
-              tc_mma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, kIdescBf16, (kb | k) != 0 ? 1u : 0u);
+              // advancing K by one instruction (16 bf16 or 32 e4m3 = 32 bytes) inside the swizzle row: +2 in (address >> 4)
+              tc_mma<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
             }
             tc_commit(empty_bar(stage));
             if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -263,7 +287,9 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
           } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const float x = fmaxf(__uint_as_float(v[j]) + __ldg(g.bias + n0 + j), 0.f);
+              float acc = __uint_as_float(v[j]);
+              if (F8) acc *= __ldg(g.col_scale + n0 + j);
+              const float x = fmaxf(acc + __ldg(g.bias + n0 + j), 0.f);
               rowsum = fmaf(x, __ldg(g.w_out + n0 + j), rowsum);
             }
           }
@@ -315,8 +341,10 @@ struct L1Args {
   int64_t row_limit;
   int32_t n, stride, V;
   int32_t n_total;           // hidden (multiple of BN)
-  int32_t k_total;           // n*V rounded up to BK
+  int32_t k_total;           // n*V rounded up to the K-block width (64 bf16 / 128 e4m3)
   const float* bias;
+  const float* col_scale;    // fp8 only: [n_total] dequantisation factor of each W1 output channel
+  float out_inv_scale;       // fp8 only: activations are stored as e4m3(value * out_inv_scale)
   int* err;
 };
 
@@ -330,6 +358,7 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
                ::"l"(map), "r"(src), "r"(x), "r"(y) : "memory");
 }
 
+template <int F8>
 __global__ void __launch_bounds__(L1_THREADS, 1)
 k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmOut, L1Args g) {
   extern __shared__ uint8_t smem_raw[];
@@ -358,7 +387,8 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
   if (rows > g.row_limit) rows = g.row_limit;
   const int num_mtiles = (int)((rows + BM - 1) / BM);
   const int n_chunks = g.n_total / BN;
-  const int k_blocks = g.k_total / BK;
+  constexpr int BKE = F8 ? BK8 : BK;  // one-hot columns per 128-byte K-block
+  const int k_blocks = g.k_total / BKE;
   const int blocks_per_tile = n_chunks * k_blocks;
 
   if (threadIdx.x == 0) {
@@ -366,7 +396,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
     for (int s = 0; s < L1_B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
     mbar_init(drain_bar, 1);
-    for (int kb = 0; kb < k_blocks && kb < L1_MAX_KBLOCKS; ++kb) p_lo_tab[kb] = (kb * BK) / g.V;
+    for (int kb = 0; kb < k_blocks && kb < L1_MAX_KBLOCKS; ++kb) p_lo_tab[kb] = (kb * BKE) / g.V;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -390,7 +420,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
           for (int kb = 0; kb < k_blocks; ++kb) {
             if (!mbar_wait(b_empty(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
             mbar_expect_tx(b_full(stage), B_BYTES);
-            tma_load_2d(smem_u32(b_ring + stage * B_BYTES), &tmB, kb * BK, nc * BN, b_full(stage));
+            tma_load_2d(smem_u32(b_ring + stage * B_BYTES), &tmB, kb * BKE, nc * BN, b_full(stage));
             if (++stage == L1_B_STAGES) { stage = 0; phase ^= 1u; }
           }
         }
@@ -417,7 +447,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
             const uint64_t bdesc = make_desc_sw128(smem_u32(b_ring + sb * B_BYTES));
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k)
-              tc_mma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, kIdescBf16, (kb | k) != 0 ? 1u : 0u);
+              tc_mma<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
             tc_commit(a_empty(sa));
             tc_commit(b_empty(sb));
             if (++sb == L1_B_STAGES) { sb = 0; pb ^= 1u; }
@@ -443,29 +473,50 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * BN;
 #pragma unroll 1
-        for (int gcol = 0; gcol < BN; gcol += 64, ++box_it) {
+        for (int gcol = 0; gcol < BN; gcol += BKE, ++box_it) {  // one box = 128 bytes per row
           uint8_t* box = staging + (box_it & 1u) * A_BYTES;
           // the TMA store that last read this box must be done before it is overwritten
           if (et == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
           asm volatile("bar.sync 1, 128;" ::: "memory");
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
+          for (int sub = 0; sub < BKE / 32; ++sub) {
             uint32_t v[32];
-            tc_ld32(taddr + gcol + half * 32, v);
+            tc_ld32(taddr + gcol + sub * 32, v);
             tc_wait_ld();
-            const int n0 = nc * BN + gcol + half * 32;
-            uint32_t packed[16];
+            const int n0 = nc * BN + gcol + sub * 32;
+            if (F8) {
+              uint32_t packed[8];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float x0 = fmaxf(__uint_as_float(v[2 * j]) + __ldg(g.bias + n0 + 2 * j), 0.f);
-              const float x1 = fmaxf(__uint_as_float(v[2 * j + 1]) + __ldg(g.bias + n0 + 2 * j + 1), 0.f);
-              __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-              packed[j] = *reinterpret_cast<uint32_t*>(&h);
-            }
+              for (int j = 0; j < 8; ++j) {
+                float x[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint32_t off = swz128(r, (uint32_t)(half * 64 + q * 16));
-              *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                for (int e = 0; e < 4; ++e) {
+                  const int c = 4 * j + e;
+                  x[e] = fmaxf(__uint_as_float(v[c]) * __ldg(g.col_scale + n0 + c) + __ldg(g.bias + n0 + c), 0.f) * g.out_inv_scale;
+                }
+                const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(x[0], x[1]), __NV_SATFINITE, __NV_E4M3);
+                const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(x[2], x[3]), __NV_SATFINITE, __NV_E4M3);
+                packed[j] = lo | (hi << 16);
+              }
+#pragma unroll
+              for (int q = 0; q < 2; ++q) {
+                const uint32_t off = swz128(r, (uint32_t)(sub * 32 + q * 16));
+                *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+              }
+            } else {
+              uint32_t packed[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const float x0 = fmaxf(__uint_as_float(v[2 * j]) + __ldg(g.bias + n0 + 2 * j), 0.f);
+                const float x1 = fmaxf(__uint_as_float(v[2 * j + 1]) + __ldg(g.bias + n0 + 2 * j + 1), 0.f);
+                __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+                packed[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint32_t off = swz128(r, (uint32_t)(sub * 64 + q * 16));
+                *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+              }
             }
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -520,9 +571,9 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         for (int q = 0; q < A_BYTES / 2 / 16 / 32; ++q) a4[q * 32 + lane] = make_uint4(0u, 0u, 0u, 0u);
         __syncwarp();
         // ones: column pos*V + value inside [kb*64, kb*64+64); rows half*64 + lane and + 32
-        const int c_lo = kb * BK;
+        const int c_lo = kb * BKE;
         const int p_lo = p_lo_tab[kb];
-        int p_hi = p_lo + (BK + V - 1) / V;  // inclusive upper bound on positions that can reach this block
+        int p_hi = p_lo + (BKE + V - 1) / V;  // inclusive upper bound on positions that can reach this block
         if (p_hi > n - 1) p_hi = n - 1;
 #pragma unroll 4
         for (int pos = p_lo; pos <= p_hi; ++pos) {
@@ -531,8 +582,10 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
           for (int rr = 0; rr < 2; ++rr) {
             const uint32_t row = (uint32_t)(half * 64 + lane + 32 * rr);
             const int col = cbase + (int)child_s[row * L1_CHILD_PITCH + pos];
-            if (col >= 0 && col < BK)
-              *reinterpret_cast<uint16_t*>(a_stage + swz128(row, (uint32_t)col * 2u)) = 0x3f80;
+            if (col >= 0 && col < BKE) {
+              if (F8) a_stage[swz128(row, (uint32_t)col)] = 0x38;  // e4m3 1.0
+              else *reinterpret_cast<uint16_t*>(a_stage + swz128(row, (uint32_t)col * 2u)) = 0x3f80;  // bf16 1.0
+            }
           }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -625,19 +678,25 @@ EncodeTiledFn get_encode() {
   return fn;
 }
 
-// 2-D bf16 row-major [rows, cols] tensor, box = {64 columns (128 bytes), box_rows}, 128-byte swizzle
-int make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+// 2-D row-major [rows, cols] tensor of 2-byte (bf16) or 1-byte (e4m3) elements, box = {128 bytes of columns,
+// box_rows}, 128-byte swizzle
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, int elem_bytes) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return MGBS_ERR_STATE;
-  if (((uintptr_t)base & 15u) != 0 || (cols * 2) % 16 != 0) return MGBS_ERR_ARG;
+  if (((uintptr_t)base & 15u) != 0 || (cols * elem_bytes) % 16 != 0) return MGBS_ERR_ARG;
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
-  cuuint32_t box[2] = {64, box_rows};
+  cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                   const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : MGBS_ERR_STATE;
+}
+
+int make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  return make_map(map, base, rows, cols, box_rows, 2);
 }
 
 }  // namespace
@@ -653,9 +712,14 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
   if (c.hidden < mgbs::BN || c.hidden % mgbs::BN != 0) return MGBS_ERR_UNSUPPORTED;
   if (c.num_models < 1 || c.num_models > MGBS_MAX_MODELS || c.max_rows < 1) return MGBS_ERR_ARG;
   const int k1 = c.state_len * c.num_values;
-  const int k1_pad = (k1 + mgbs::BK - 1) / mgbs::BK * mgbs::BK;
-  if (c.k1_pad != k1_pad) return MGBS_ERR_ARG;
-  if (!c.x || !c.h1 || !c.q || !c.err) return MGBS_ERR_ARG;
+  if (c.dtype != 0 && c.dtype != 1) return MGBS_ERR_ARG;
+  const int f8 = c.dtype == 1;
+  const int kblk = f8 ? mgbs::BK8 : mgbs::BK;
+  const int eb = f8 ? 1 : 2;
+  const int k1_pad = (k1 + kblk - 1) / kblk * kblk;
+  if (c.k1_pad != k1_pad || k1_pad / kblk > mgbs::L1_MAX_KBLOCKS) return MGBS_ERR_ARG;
+  if ((!f8 && !c.x) || !c.h1 || !c.q || !c.err) return MGBS_ERR_ARG;
+  if (f8 && !(c.act_inv_scale > 0.f)) return MGBS_ERR_ARG;
   MgbsMlp* m = new (std::nothrow) MgbsMlp();
   if (!m) return MGBS_ERR_STATE;
   m->cfg = c;
@@ -666,16 +730,21 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) m->sms = sms;
   }
   const uint64_t rows_pad = ((uint64_t)c.max_rows + mgbs::BM - 1) / mgbs::BM * mgbs::BM;
-  int rc = make_map_bf16(&m->tm_x, c.x, rows_pad, (uint64_t)k1_pad, mgbs::BM);
-  if (!rc) rc = make_map_bf16(&m->tm_h1, c.h1, rows_pad, (uint64_t)c.hidden, mgbs::BM);
+  int rc = 0;
+  if (!f8) rc = make_map(&m->tm_x, c.x, rows_pad, (uint64_t)k1_pad, mgbs::BM, eb);
+  if (!rc) rc = make_map(&m->tm_h1, c.h1, rows_pad, (uint64_t)c.hidden, mgbs::BM, eb);
   for (int i = 0; i < c.num_models && !rc; ++i) {
     if (!c.w1[i] || !c.b1[i] || !c.w2[i] || !c.b2[i] || !c.w3[i]) rc = MGBS_ERR_ARG;
-    if (!rc) rc = make_map_bf16(&m->tm_w1[i], c.w1[i], (uint64_t)c.hidden, (uint64_t)k1_pad, mgbs::BN);
-    if (!rc) rc = make_map_bf16(&m->tm_w2[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden, mgbs::BN);
+    if (!rc && f8 && (!c.s1[i] || !c.s2[i])) rc = MGBS_ERR_ARG;
+    if (!rc) rc = make_map(&m->tm_w1[i], c.w1[i], (uint64_t)c.hidden, (uint64_t)k1_pad, mgbs::BN, eb);
+    if (!rc) rc = make_map(&m->tm_w2[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden, mgbs::BN, eb);
   }
-  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
-  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
-  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
+  if (f8) m->fused_l1 = true;
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
   if (rc) { delete m; return rc; }
   *out = m;
   return 0;
@@ -691,6 +760,7 @@ int mgbs_mlp_destroy(MgbsMlp* m) {
 
 int mgbs_mlp_set_l1_mode(MgbsMlp* m, int32_t fused) {
   if (!m) return MGBS_ERR_ARG;
+  if (m->cfg.dtype == 1 && !fused) return MGBS_ERR_UNSUPPORTED;  // the e4m3 path has no separate one-hot matrix
   m->fused_l1 = fused != 0;
   return 0;
 }
@@ -743,6 +813,7 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
     g.n_total = c.hidden;
     g.k_total = m->k1_pad;
     g.bias = c.b1[i];
+    g.col_scale = nullptr;
     g.w_out = nullptr;
     g.out_bf16 = reinterpret_cast<__nv_bfloat16*>(c.h1);
     g.out_q = nullptr;
@@ -758,10 +829,13 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
       l.n_total = c.hidden;
       l.k_total = m->k1_pad;
       l.bias = c.b1[i];
+      l.col_scale = c.s1[i];
+      l.out_inv_scale = c.act_inv_scale;
       l.err = c.err;
-      k_mlp_l1<<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
+      if (c.dtype == 1) k_mlp_l1<1><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
+      else k_mlp_l1<0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
     } else {
-      k_mlp_gemm<0><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_x, m->tm_w1[i], g);
+      k_mlp_gemm<0, 0><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_x, m->tm_w1[i], g);
     }
     if (prof) cudaEventRecord(m->ev[2], st);
     g.k_total = c.hidden;
@@ -770,7 +844,9 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
     g.out_bf16 = nullptr;
     g.out_q = c.q;
     g.accumulate_q = i > 0 ? 1 : 0;
-    k_mlp_gemm<1><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h1, m->tm_w2[i], g);
+    g.col_scale = c.s2[i];
+    if (c.dtype == 1) k_mlp_gemm<1, 1><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h1, m->tm_w2[i], g);
+    else k_mlp_gemm<1, 0><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h1, m->tm_w2[i], g);
     if (prof) cudaEventRecord(m->ev[3], st);
   }
   {
@@ -848,9 +924,9 @@ extern "C" int mgbs_mlp_score_noalloc(const MgbsMlpNoAllocArgs* a, const uint8_t
     void* p = nullptr;
     ce = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (ce != cudaSuccess) return (int)ce;
-    ce = cudaFuncSetAttribute(k_mlp_gemm<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    ce = cudaFuncSetAttribute(k_mlp_gemm<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     if (ce != cudaSuccess) return (int)ce;
-    ce = cudaFuncSetAttribute(k_mlp_gemm<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    ce = cudaFuncSetAttribute(k_mlp_gemm<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     if (ce != cudaSuccess) return (int)ce;
     g_noalloc_base[dev] = static_cast<uint8_t*>(p);
   }
@@ -885,18 +961,19 @@ extern "C" int mgbs_mlp_score_noalloc(const MgbsMlpNoAllocArgs* a, const uint8_t
   g.n_total = a->hidden;
   g.k_total = k1_pad;
   g.bias = a->b1;
+  g.col_scale = nullptr;
   g.w_out = nullptr;
   g.out_bf16 = h1;
   g.out_q = nullptr;
   g.accumulate_q = 0;
   g.err = reinterpret_cast<int*>(words + 1);
-  k_mlp_gemm<0><<<sms, GEMM_THREADS, GEMM_SMEM, st>>>(tm_x, tm_w1, g);
+  k_mlp_gemm<0, 0><<<sms, GEMM_THREADS, GEMM_SMEM, st>>>(tm_x, tm_w1, g);
   g.k_total = a->hidden;
   g.bias = a->b2;
   g.w_out = a->w3;
   g.out_bf16 = nullptr;
   g.out_q = q;
-  k_mlp_gemm<1><<<sms, GEMM_THREADS, GEMM_SMEM, st>>>(tm_h1, tm_w2, g);
+  k_mlp_gemm<1, 0><<<sms, GEMM_THREADS, GEMM_SMEM, st>>>(tm_h1, tm_w2, g);
   {
     int64_t gq = ((int64_t)rows + 255) / 256;
     k_q_to_key<<<(int)gq, 256, 0, st>>>(q, words, 1.f, a->score_offset - a->b3, scores);

@@ -28,6 +28,8 @@ class MgbsMlpConfig(C.Structure):
         ("x", C.c_void_p), ("h1", C.c_void_p), ("q", C.c_void_p), ("err", C.c_void_p),
         ("w1", C.c_void_p * MAX_MODELS), ("b1", C.c_void_p * MAX_MODELS), ("w2", C.c_void_p * MAX_MODELS),
         ("b2", C.c_void_p * MAX_MODELS), ("w3", C.c_void_p * MAX_MODELS),
+        ("s1", C.c_void_p * MAX_MODELS), ("s2", C.c_void_p * MAX_MODELS),
+        ("dtype", C.c_int32), ("act_inv_scale", C.c_float),
     ]
 
 
@@ -56,7 +58,12 @@ _lib.SIGNATURES.update(_SIGS)
 
 
 class MLPValueScorer:
-    """Ensemble of value MLPs one-hot(n*V) -> hidden -> hidden -> 1 (ReLU), bf16 operands, fp32 accumulation.
+    """Ensemble of value MLPs one-hot(n*V) -> hidden -> hidden -> 1 (ReLU); bf16 or FP8 (E4M3) operands, fp32
+    accumulation.
+
+    ``dtype="fp8"``: weights are quantised to E4M3 with one scale per output channel (max-abs / 448); first-layer
+    activations are stored as E4M3 with one per-tensor scale taken from a safe bound on their maximum
+    (sum over positions of the largest first-layer weight of that position, plus bias).
 
     ``weights``: one dict or a list of dicts with float32 arrays w1 [H, n*V], b1 [H], w2 [H, H], b2 [H], w3 [H], b3.
     ``score_offset``: subtracted from the network output before it becomes the integer key
@@ -65,7 +72,7 @@ class MLPValueScorer:
 
     def __init__(self, weights: Union[Dict[str, np.ndarray], Sequence[Dict[str, np.ndarray]]], state_len: int,
                  state_stride: int, num_values: int, max_rows: int, score_offset: float = -150.0,
-                 device: Union[str, torch.device, None] = None):
+                 device: Union[str, torch.device, None] = None, dtype: str = "bf16"):
         self.lib = _lib.load()
         for name, (res, args) in _SIGS.items():
             fn = getattr(self.lib, name)
@@ -79,27 +86,54 @@ class MLPValueScorer:
         dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         hidden = int(weights[0]["w1"].shape[0])
         k1 = state_len * num_values
-        k1_pad = (k1 + 63) // 64 * 64
+        if dtype not in ("bf16", "fp8"):
+            raise RuntimeError("dtype must be 'bf16' or 'fp8'")
+        f8 = dtype == "fp8"
+        self.dtype = dtype
+        kblk = 128 if f8 else 64
+        k1_pad = (k1 + kblk - 1) // kblk * kblk
         rows_pad = (int(max_rows) + 127) // 128 * 128
         self.state_len, self.state_stride, self.num_values = state_len, state_stride, num_values
         self.hidden, self.k1_pad, self.max_rows = hidden, k1_pad, int(max_rows)
         self.score_offset = float(score_offset)
-        self.t: Dict[str, List[torch.Tensor]] = {k: [] for k in ("w1", "b1", "w2", "b2", "w3")}
+        self.t: Dict[str, List[torch.Tensor]] = {k: [] for k in ("w1", "b1", "w2", "b2", "w3", "s1", "s2")}
         cfg = MgbsMlpConfig()
+        act_bound = 0.0
+        if f8:
+            for w in weights:
+                w1f = np.asarray(w["w1"], dtype=np.float32).reshape(hidden, state_len, num_values)
+                act_bound = max(act_bound, float((w1f.max(axis=2).sum(axis=1) + np.asarray(w["b1"], np.float32)).max()))
+            act_bound = max(act_bound, 1e-6)
+        act_scale = act_bound / 448.0 if f8 else 1.0
         for i, w in enumerate(weights):
             if w["w1"].shape != (hidden, k1) or w["w2"].shape != (hidden, hidden) or w["w3"].shape != (hidden,):
                 raise RuntimeError("weight shapes must be w1 [H, n*V], w2 [H, H], w3 [H]")
-            w1 = torch.zeros((hidden, k1_pad), dtype=torch.bfloat16, device=dev)
-            w1[:, :k1] = torch.from_numpy(np.ascontiguousarray(w["w1"], dtype=np.float32)).to(dev).to(torch.bfloat16)
-            self.t["w1"].append(w1)
-            self.t["w2"].append(torch.from_numpy(np.ascontiguousarray(w["w2"], dtype=np.float32)).to(dev).to(torch.bfloat16).contiguous())
+            w1_f = torch.from_numpy(np.ascontiguousarray(w["w1"], dtype=np.float32)).to(dev)
+            w2_f = torch.from_numpy(np.ascontiguousarray(w["w2"], dtype=np.float32)).to(dev)
+            if f8:
+                s1 = (w1_f.abs().amax(dim=1) / 448.0).clamp_min(1e-12)
+                s2w = (w2_f.abs().amax(dim=1) / 448.0).clamp_min(1e-12)
+                w1 = torch.zeros((hidden, k1_pad), dtype=torch.uint8, device=dev)
+                w1[:, :k1] = (w1_f / s1[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
+                self.t["w1"].append(w1)
+                self.t["w2"].append((w2_f / s2w[:, None]).to(torch.float8_e4m3fn).view(torch.uint8).contiguous())
+                self.t["s1"].append(s1.contiguous())
+                self.t["s2"].append((s2w * act_scale).contiguous())
+                cfg.s1[i] = self.t["s1"][i].data_ptr()
+                cfg.s2[i] = self.t["s2"][i].data_ptr()
+            else:
+                w1 = torch.zeros((hidden, k1_pad), dtype=torch.bfloat16, device=dev)
+                w1[:, :k1] = w1_f.to(torch.bfloat16)
+                self.t["w1"].append(w1)
+                self.t["w2"].append(w2_f.to(torch.bfloat16).contiguous())
             for k in ("b1", "b2", "w3"):
                 self.t[k].append(torch.from_numpy(np.ascontiguousarray(w[k], dtype=np.float32)).to(dev))
             cfg.b3[i] = float(w["b3"])
             for k in ("w1", "b1", "w2", "b2", "w3"):
                 getattr(cfg, k)[i] = self.t[k][i].data_ptr()
-        self.x = torch.zeros((rows_pad, k1_pad), dtype=torch.bfloat16, device=dev)
-        self.h1 = torch.zeros((rows_pad, hidden), dtype=torch.bfloat16, device=dev)
+        # bf16: the one-hot matrix is only used by the unfused layer-1 path; fp8 has no such path
+        self.x = None if f8 else torch.zeros((rows_pad, k1_pad), dtype=torch.bfloat16, device=dev)
+        self.h1 = torch.zeros((rows_pad, hidden), dtype=torch.uint8 if f8 else torch.bfloat16, device=dev)
         self.q = torch.zeros((rows_pad,), dtype=torch.float32, device=dev)
         self.err = torch.zeros((1,), dtype=torch.int32, device=dev)
         self._count = torch.zeros((1,), dtype=torch.int32, device=dev)
@@ -107,7 +141,11 @@ class MLPValueScorer:
         cfg.hidden, cfg.num_models, cfg.k1_pad = hidden, len(weights), k1_pad
         cfg.max_rows = int(max_rows)
         cfg.score_offset = float(score_offset)
-        cfg.x, cfg.h1, cfg.q, cfg.err = self.x.data_ptr(), self.h1.data_ptr(), self.q.data_ptr(), self.err.data_ptr()
+        cfg.x = None if f8 else self.x.data_ptr()
+        cfg.h1, cfg.q, cfg.err = self.h1.data_ptr(), self.q.data_ptr(), self.err.data_ptr()
+        cfg.dtype = 1 if f8 else 0
+        cfg.act_inv_scale = 1.0 / act_scale
+        self.act_scale = act_scale
         self._cfg = cfg
         h = C.c_void_p()
         _lib.check(self.lib.mgbs_mlp_create(C.byref(cfg), C.byref(h)), "MLPValueScorer")
@@ -168,6 +206,8 @@ class MLPValueScorer:
         larger calls raise.  Do not overlap two such calls on the GPU: they share the scratch.  Returns the GEMM
         error word (0 = clean) after waiting for the call.
         """
+        if self.dtype != "bf16":
+            raise RuntimeError("score_no_alloc is available for bf16 scorers only")
         if children.dtype != torch.uint8 or children.dim() != 2 or children.shape[1] != self.state_stride:
             raise RuntimeError("children must be [C, state_stride] uint8")
         if out.dtype != torch.int32 or out.numel() < children.shape[0] or not out.is_contiguous():

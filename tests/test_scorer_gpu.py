@@ -116,3 +116,34 @@ def test_fused_layer1_equals_unfused_path():
     assert sc.error_code() == 0
     assert torch.equal(h1_a, sc.h1[: rows.shape[0]])
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("name,count,models", [("rand54", 20000, 1), ("rand96", 5000, 2), ("rand54", 77, 1)])
+def test_fp8_scorer_within_tolerance(name, count, models):
+    # FP8 E4M3 operands with per-channel weight scales: max-abs error of the network output <= 2e-2 (stated bound)
+    pz = puzzles.by_name(name)
+    stride = (pz.state_len + 15) // 16 * 16
+    ws = [puzzles.mlp_weights(pz.state_len * pz.num_values, 1024, model_idx=10 + i) for i in range(models)]
+    rng = np.random.default_rng(4)
+    for w in ws:
+        w["b1"] = (rng.standard_normal(1024) * 0.05).astype(np.float32)
+        w["b2"] = (rng.standard_normal(1024) * 0.05).astype(np.float32)
+        w["b3"] = np.float32(0.1)
+    sc = scorers.MLPValueScorer(ws, pz.state_len, stride, pz.num_values, max_rows=count, dtype="fp8")
+    rows = children_of(pz, count, seed=count + 1)
+    dev = torch.from_numpy(padded(rows, stride)).cuda()
+    keys = sc.score(dev)
+    torch.cuda.synchronize()
+    assert sc.error_code() == 0
+    q_ref = bo.mlp_forward(rows, ws, pz.num_values)
+    q_dev = (sc.last_q(count).cpu().numpy() + sum(float(w["b3"]) for w in ws)) / models
+    err = np.abs(q_dev - q_ref).max()
+    assert err <= 2e-2, err
+    assert np.abs(q_dev - q_ref).mean() <= 5e-3
+    # keys are the quantisation of the device's own q (the host recomputation may round a .5 boundary differently)
+    rekey = bo.q_to_score_key(q_dev.astype(np.float32), -150.0).astype(np.int64)
+    assert np.abs(keys.cpu().numpy().astype(np.int64) - rekey).max() <= 1
+    # same rows in another order give the same keys
+    perm = np.random.default_rng(1).permutation(count)
+    keys2 = sc.score(dev[torch.from_numpy(perm).cuda()].contiguous())
+    assert np.array_equal(keys.cpu().numpy()[perm], keys2.cpu().numpy())
