@@ -293,6 +293,8 @@ def run_ours(args):
     # ---- the same steps with the scorer in FP8 (E4M3 operands, per-channel scales): short extra pass ----
     fp8 = None
     if args.dtype == "bf16" and not args.no_fp8:
+        engine.close()
+        barrier()
         del engine, buffers, sc
         torch.cuda.empty_cache()
         sc8 = scorers.MLPValueScorer(puzzles.mlp_weights(pz.state_len * pz.num_values, 1024), pz.state_len,
@@ -350,6 +352,7 @@ def run_ours(args):
             "wall_s_timed_region": wall,
         }
         print(json.dumps(line))
+    engine.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -30,10 +30,11 @@ ST_TIE_OVERFLOW = 4
 ST_FRONTIER_OVERFLOW = 8
 ST_BUCKET_OVERFLOW = 16
 ST_ROUNDS_EXHAUSTED = 32
+ST_PEER_TIMEOUT = 64
 STATUS_NAMES = {
     ST_HASH_OVERFLOW: "hash_overflow", ST_BAND_STALL: "band_stall", ST_TIE_OVERFLOW: "tie_overflow",
     ST_FRONTIER_OVERFLOW: "frontier_overflow", ST_BUCKET_OVERFLOW: "bucket_overflow",
-    ST_ROUNDS_EXHAUSTED: "rounds_exhausted",
+    ST_ROUNDS_EXHAUSTED: "rounds_exhausted", ST_PEER_TIMEOUT: "peer_timeout",
 }
 
 
@@ -52,6 +53,7 @@ class MgbsCtrl(C.Structure):
         ("table_count", C.c_uint32), ("next_count", C.c_uint32), ("tie_count", C.c_uint32),
         ("cand_count", C.c_uint32), ("unique_total", C.c_uint32), ("inserted_total", C.c_uint32),
         ("hash_overflow", C.c_uint32), ("rounds_used", C.c_uint32), ("bands_done", C.c_uint32),
+        ("epoch", C.c_uint32), ("pad0", C.c_uint32),
         ("band_lo", C.c_uint64 * (MAX_ROUNDS + 1)), ("threshold_key", C.c_uint64),
         ("rho_num", C.c_uint64), ("rho_den", C.c_uint64), ("total_candidates", C.c_uint64),
         ("band", (MgbsRadix * (MAX_LEVELS + 1)) * MAX_ROUNDS), ("fin", MgbsRadix * (MAX_LEVELS + 1)),
@@ -77,6 +79,7 @@ class MgbsConfig(C.Structure):
         ("send_hash", _P), ("send_fp", _P), ("send_score", _P), ("send_payload", _P), ("send_states", _P),
         ("recv_hash", _P), ("recv_fp", _P), ("recv_score", _P), ("recv_payload", _P), ("recv_states", _P),
         ("send_counts", _P), ("recv_counts", _P),
+        ("exchange_mode", C.c_int32), ("pad1", C.c_int32), ("sym", _P), ("sym_bytes", C.c_int64), ("tickets", _P),
     ]
 
 
@@ -91,6 +94,9 @@ SIGNATURES = {
     "mgbs_engine_destroy": (C.c_int, [_P]),
     "mgbs_nccl_unique_id": (C.c_int, [C.c_char_p, _P]),
     "mgbs_engine_init_nccl": (C.c_int, [_P, C.c_char_p, _P]),
+    "mgbs_sym_bytes": (C.c_int, [C.POINTER(MgbsConfig), C.POINTER(_I64), C.POINTER(_I64)]),
+    "mgbs_engine_set_peers": (C.c_int, [_P, _P, C.POINTER(_I64)]),
+    "mgbs_ipc_export": (C.c_int, [_P, _P, C.POINTER(_I64)]),
     "mgbs_engine_set_scorer": (C.c_int, [_P, _P, _P]),
     "mgbs_engine_set_score_mode": (C.c_int, [_P, _I32, _I32]),
     "mgbs_engine_reset": (C.c_int, [_P, _P, _I32, _I32, _P]),

@@ -67,6 +67,9 @@ def make_default_config() -> Dict[str, Any]:
         "materialize_children": _flag_enabled("MATERIALIZE_CHILDREN"),
         "use_cuda_graphs": _flag_enabled("USE_CUDA_GRAPHS", "1"),
         "score_offset": float(os.environ.get("NN_SCORE_BIAS", "0.0")),
+        # world > 1: "peer" = candidates stored straight into the owner's buckets over NVLink peer mappings and
+        # histograms reduced in-kernel; "nccl" = grouped send/recv + all-reduce (the reference's scheme)
+        "exchange": os.environ.get("MGBS_EXCHANGE", "peer"),
     }
 
 
@@ -171,7 +174,18 @@ def allocate_buffers(ext: _Ext, cfg: Dict[str, Any]) -> Dict[str, torch.Tensor]:
     }
     if need_children:
         buffers["next_state_pool"] = z((cand_cap, stride), torch.uint8)
-    if world > 1:
+    if world > 1 and str(cfg.get("exchange", "peer")) == "peer":
+        tmp = _lib.MgbsConfig()
+        tmp.world_size, tmp.state_stride, tmp.bucket_cap = world, stride, sizes["bucket_cap_per_peer"]
+        tmp.band_rounds, tmp.band_levels = int(cfg["band_rounds"]), int(cfg["band_levels"])
+        tmp.hash_bits = int(cfg.get("hash_bits", 44)) if str(cfg.get("select_mode", "exact_k")) == "exact_k" else 0
+        nbytes, ntick = C.c_int64(0), C.c_int64(0)
+        _lib.check(ext.lib.mgbs_sym_bytes(C.byref(tmp), C.byref(nbytes), C.byref(ntick)), "mgbs_sym_bytes")
+        # its own allocation (not a slice of a bigger one): the whole storage is what gets mapped into the peers
+        buffers["sym"] = z((int(nbytes.value),), torch.uint8)
+        buffers["tickets"] = z((int(ntick.value),), torch.int32)
+        buffers["send_counts"] = z((world,), torch.int32)
+    elif world > 1:
         cap = sizes["bucket_cap_per_peer"]
         for side in ("send", "recv"):
             buffers[f"{side}_hash"] = z((world * cap,), torch.int64)
@@ -255,6 +269,14 @@ class BeamEngine:
             setattr(c, f"{side}_payload", p(f"{side}_payload"))
             setattr(c, f"{side}_states", p(f"{side}_states"))
             setattr(c, f"{side}_counts", p(f"{side}_counts"))
+        self._peer = int(cfg["world_size"]) > 1 and str(cfg.get("exchange", "peer")) == "peer"
+        if str(cfg.get("exchange", "peer")) not in ("peer", "nccl"):
+            raise RuntimeError("exchange must be 'peer' or 'nccl'")
+        c.exchange_mode = 1 if self._peer else 0
+        if self._peer:
+            c.sym = p("sym")
+            c.sym_bytes = int(b["sym"].numel())
+            c.tickets = p("tickets")
         if c.score_mode == _lib.SCORE_EXTERNAL and not c.children:
             raise RuntimeError("a neural backend needs the next_state_pool buffer (materialised children)")
         self._c = c
@@ -264,11 +286,18 @@ class BeamEngine:
         self._ctrl = _lib.MgbsCtrl()
         self._central: Optional[np.ndarray] = None
 
-    def __del__(self):
+    def close(self) -> None:
+        """Destroy the native engine (unmaps the peers' regions).  With exchange mode "peer" every rank should call
+        this, then synchronise with the other ranks, before the buffers are freed: a region must not be released
+        while another rank still has it mapped."""
         h = getattr(self, "_h", None)
         if h:
+            torch.cuda.synchronize()
             self.lib.mgbs_engine_destroy(h)
             self._h = None
+
+    def __del__(self):
+        self.close()
 
     # -- set-up ---------------------------------------------------------------------------------
     def _sp(self):
@@ -282,6 +311,28 @@ class BeamEngine:
         buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
         _lib.check(self.lib.mgbs_engine_init_nccl(self._h, _build.nccl_library_path().encode(), C.addressof(buf)),
                    "init_nccl")
+
+    def map_peers(self) -> None:
+        """Exchange IPC handles of the symmetric regions over torch.distributed and map every peer's region.
+
+        Collective: every rank of the world calls it once, after construction (exchange mode "peer" only)."""
+        if not self._peer:
+            return
+        sym = self.buffers["sym"]
+        hbuf = (C.c_uint8 * 64)()
+        off = C.c_int64(0)
+        _lib.check(self.lib.mgbs_ipc_export(C.c_void_p(sym.data_ptr()), C.addressof(hbuf), C.byref(off)), "mgbs_ipc_export")
+        handle, offset = bytes(hbuf), int(off.value)
+        world = int(self.cfg["world_size"])
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (handle, offset))
+        handles = b"".join(h for h, _ in gathered)
+        if any(len(h) != 64 for h, _ in gathered):
+            raise RuntimeError("unexpected CUDA IPC handle size")
+        offs = (C.c_int64 * world)(*[o for _, o in gathered])
+        buf = (C.c_uint8 * (64 * world)).from_buffer_copy(handles)
+        _lib.check(self.lib.mgbs_engine_set_peers(self._h, C.addressof(buf), offs), "map_peers")
+        dist.barrier()
 
     def set_action_permutation_table(self, table: bytes) -> None:
         """fanout x state_len bytes, row-major gather tables (beam_engine.cpp:979-985)."""
@@ -519,6 +570,7 @@ def configure_engine(puzzle: Puzzle, cfg: Optional[Dict[str, Any]] = None, score
         engine.set_scorer(scorer)
     if cfg["world_size"] > 1:
         engine.init_nccl(create_nccl_id(ext, cfg))
+        engine.map_peers()
     engine.enable_cuda_graphs(bool(cfg.get("use_cuda_graphs", True)))
     return ext, cfg, buffers, engine
 

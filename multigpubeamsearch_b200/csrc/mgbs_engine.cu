@@ -3,6 +3,7 @@
 // (beam_engine.cpp:1465-1672, 1147-1171).  No device memory is allocated here: every buffer comes in through
 // MgbsConfig, as the reference's engine takes torch tensors from allocate_buffers.
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 #include <nccl.h>
@@ -71,6 +72,10 @@ struct MgbsEngine {
   void* scorer_user = nullptr;
   cudaGraphExec_t graph[2] = {nullptr, nullptr};
   MgbsCtrl host_ctrl;
+  mgbs::SymLayout sym{};
+  uint8_t* peer_base[MGBS_MAX_WORLD] = {nullptr};
+  void* peer_opened[MGBS_MAX_WORLD] = {nullptr};
+  bool peers_ready = false;
   bool profile = false;
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
@@ -142,7 +147,10 @@ int mgbs_engine_create(const MgbsConfig* cfg, MgbsEngine** out) {
   if (!c.frontier[0] || !c.frontier[1] || !c.gens || !c.solved || !c.cand_hash || !c.cand_fp || !c.cand_score ||
       !c.cand_payload || !c.table || !c.hist || !c.tie_buf || !c.ctrl)
     return MGBS_ERR_ARG;
-  if (c.world_size > 1) {
+  if (c.exchange_mode != MGBS_EXCHANGE_NCCL && c.exchange_mode != MGBS_EXCHANGE_PEER) return MGBS_ERR_ARG;
+  if (c.world_size > 1 && c.exchange_mode == MGBS_EXCHANGE_PEER) {
+    if (!c.children || c.bucket_cap < 1 || !c.send_counts || !c.sym || !c.tickets) return MGBS_ERR_ARG;
+  } else if (c.world_size > 1) {
     if (!c.children || c.bucket_cap < 1 || !c.send_hash || !c.send_fp || !c.send_score || !c.send_payload ||
         !c.send_states || !c.recv_hash || !c.recv_fp || !c.recv_score || !c.recv_payload || !c.recv_states ||
         !c.send_counts || !c.recv_counts)
@@ -155,6 +163,11 @@ int mgbs_engine_create(const MgbsConfig* cfg, MgbsEngine** out) {
   e->key_bits = 20 + c.hash_bits;
   e->final_levels = (e->key_bits + MGBS_RADIX_BITS - 1) / MGBS_RADIX_BITS;
   if (e->cfg.band_levels > e->final_levels) e->cfg.band_levels = e->final_levels;
+  if (c.world_size > 1 && c.exchange_mode == MGBS_EXCHANGE_PEER) {
+    e->sym = mgbs::sym_layout(e->cfg, e->cfg.band_levels);
+    if (c.sym_bytes < e->sym.total) { delete e; return MGBS_ERR_ARG; }
+    e->peer_base[c.rank] = c.sym;
+  }
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) {
     int sms = 0;
@@ -172,6 +185,8 @@ int mgbs_engine_destroy(MgbsEngine* e) {
   if (e->comm && g_nccl.ok) g_nccl.CommDestroy(e->comm);
   for (int i = 0; i < 6; ++i)
     if (e->ev[i]) cudaEventDestroy(e->ev[i]);
+  for (int r = 0; r < MGBS_MAX_WORLD; ++r)
+    if (e->peer_opened[r]) cudaIpcCloseMemHandle(e->peer_opened[r]);
   delete e;
   return 0;
 }
@@ -193,6 +208,55 @@ int mgbs_engine_init_nccl(MgbsEngine* e, const char* libnccl_path, const uint8_t
   ncclUniqueId id;
   memcpy(&id, unique_id128, 128);
   MGBS_NCCL(g_nccl.CommInitRank(&e->comm, e->cfg.world_size, id, e->cfg.rank));
+  return 0;
+}
+
+int mgbs_sym_bytes(const MgbsConfig* cfg, int64_t* out_bytes, int64_t* out_tickets) {
+  if (!cfg || !out_bytes || !out_tickets) return MGBS_ERR_ARG;
+  if (cfg->world_size < 1 || cfg->world_size > MGBS_MAX_WORLD || cfg->bucket_cap < 0 || cfg->state_stride < 16) return MGBS_ERR_ARG;
+  int key_bits = 20 + cfg->hash_bits;
+  int final_levels = (key_bits + MGBS_RADIX_BITS - 1) / MGBS_RADIX_BITS;
+  int bl = cfg->band_levels > final_levels ? final_levels : cfg->band_levels;
+  mgbs::SymLayout L = mgbs::sym_layout(*cfg, bl);
+  *out_bytes = L.total;
+  *out_tickets = L.slots + 1;
+  return 0;
+}
+
+// IPC handle of the allocation that contains ptr, and ptr's byte offset inside it (the region may be a
+// sub-allocation of a caching allocator's block).
+int mgbs_ipc_export(const void* ptr, uint8_t* handle64, int64_t* offset) {
+  if (!ptr || !handle64 || !offset) return MGBS_ERR_ARG;
+  typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  MGBS_TRY(cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qres));
+  if (qres != cudaDriverEntryPointSuccess || !fn) return MGBS_ERR_STATE;
+  CUdeviceptr base = 0;
+  size_t size = 0;
+  if (reinterpret_cast<RangeFn>(fn)(&base, &size, (CUdeviceptr)ptr) != CUDA_SUCCESS) return MGBS_ERR_STATE;
+  cudaIpcMemHandle_t h;
+  MGBS_TRY(cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)));
+  memcpy(handle64, &h, 64);
+  *offset = (int64_t)((CUdeviceptr)ptr - base);
+  return 0;
+}
+
+int mgbs_engine_set_peers(MgbsEngine* e, const uint8_t* handles, const int64_t* offsets) {
+  if (!e || !handles || !offsets) return MGBS_ERR_ARG;
+  const MgbsConfig& c = e->cfg;
+  if (c.world_size == 1 || c.exchange_mode != MGBS_EXCHANGE_PEER) return 0;
+  for (int r = 0; r < c.world_size; ++r) {
+    if (r == c.rank) { e->peer_base[r] = c.sym; continue; }
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+    memcpy(&h, handles + 64 * r, 64);
+    void* base = nullptr;
+    MGBS_TRY(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+    e->peer_opened[r] = base;
+    e->peer_base[r] = static_cast<uint8_t*>(base) + offsets[r];
+  }
+  e->peers_ready = true;
   return 0;
 }
 
@@ -238,7 +302,11 @@ int mgbs_engine_reset(MgbsEngine* e, const uint8_t* start_state_host, int32_t ac
   cudaStream_t st = (cudaStream_t)stream;
   const MgbsConfig& c = e->cfg;
   MgbsCtrl& h = e->host_ctrl;
+  uint32_t epoch = 0;  // cross-rank flags are tagged with it: it must never go back
+  MGBS_TRY(cudaMemcpyAsync(&epoch, &c.ctrl->epoch, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+  MGBS_TRY(cudaStreamSynchronize(st));
   memset(&h, 0, sizeof(MgbsCtrl));
+  h.epoch = epoch;
   h.frontier_count[0] = active_on_this_rank ? 1 : 0;
   h.found_payload = 0xffffffffu;
   h.rho_num = 1;
@@ -262,7 +330,11 @@ int mgbs_engine_load_frontier(MgbsEngine* e, const uint8_t* rows_host, int64_t c
   cudaStream_t st = (cudaStream_t)stream;
   const MgbsConfig& c = e->cfg;
   MgbsCtrl& h = e->host_ctrl;
+  uint32_t epoch = 0;
+  MGBS_TRY(cudaMemcpyAsync(&epoch, &c.ctrl->epoch, sizeof(uint32_t), cudaMemcpyDeviceToHost, st));
+  MGBS_TRY(cudaStreamSynchronize(st));
   memset(&h, 0, sizeof(MgbsCtrl));
+  h.epoch = epoch;
   h.frontier_count[parity & 1] = (int32_t)count;
   h.depth = depth;
   h.found_payload = 0xffffffffu;
@@ -279,7 +351,7 @@ int mgbs_engine_load_frontier(MgbsEngine* e, const uint8_t* rows_host, int64_t c
 }
 
 static int allreduce_hist(MgbsEngine* e, uint32_t* hist, cudaStream_t st) {
-  if (e->cfg.world_size == 1) return 0;
+  if (e->cfg.world_size == 1 || e->cfg.exchange_mode == MGBS_EXCHANGE_PEER) return 0;  // peer mode reduces in-kernel
   if (!e->comm) return MGBS_ERR_STATE;
   MGBS_NCCL(g_nccl.AllReduce(hist, hist, MGBS_HIST_STRIDE, ncclUint32, ncclSum, e->comm, st));
   return 0;
@@ -356,8 +428,41 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     a.cv.nbuckets = 1;
     a.cv.cap = (uint32_t)c.cand_cap;
     items = c.cand_cap;
+  } else if (c.exchange_mode == MGBS_EXCHANGE_PEER) {
+    if (!e->peers_ready) return MGBS_ERR_STATE;
+    const SymLayout& L = e->sym;
+    RouteArgs r;
+    memset(&r, 0, sizeof(r));
+    r.hash = c.cand_hash; r.fp = c.cand_fp; r.score = c.cand_score; r.payload = c.cand_payload; r.states = c.children;
+    r.send_counts = c.send_counts;
+    r.ctrl = c.ctrl;
+    r.world = W; r.stride = c.state_stride; r.bucket_cap = (uint32_t)c.bucket_cap;
+    r.rank = c.rank;
+    for (int q = 0; q < W; ++q) r.peer.base[q] = e->peer_base[q];
+    r.peer.enabled = 1;
+    r.peer.tickets = c.tickets;
+    r.peer.slot = L.slots;  // the ticket word after the histogram slots
+    r.off_hash = L.hash[parity]; r.off_fp = L.fp[parity]; r.off_score = L.score[parity];
+    r.off_payload = L.payload[parity]; r.off_states = L.states[parity]; r.off_counts = L.counts[parity];
+    r.off_route_flag = L.route_flag;
+    MGBS_TRY(launch_route(r, c.cand_cap, e->sms, st));
+    a.cv.hash = reinterpret_cast<const uint64_t*>(c.sym + L.hash[parity]);
+    a.cv.fp = reinterpret_cast<const uint64_t*>(c.sym + L.fp[parity]);
+    a.cv.score = reinterpret_cast<const uint32_t*>(c.sym + L.score[parity]);
+    a.cv.payload = reinterpret_cast<const uint32_t*>(c.sym + L.payload[parity]);
+    a.cv.states = c.sym + L.states[parity];
+    a.cv.counts = reinterpret_cast<const uint32_t*>(c.sym + L.counts[parity]);
+    a.cv.nbuckets = W;
+    a.cv.cap = (uint32_t)c.bucket_cap;
+    items = c.bucket_cap;
+    for (int q = 0; q < W; ++q) a.peer.base[q] = e->peer_base[q];
+    a.peer.enabled = 1;
+    a.peer.tickets = c.tickets;
+    a.peer.off_hx = L.hx;
+    a.peer.off_hflag = L.hflag;
   } else {
     RouteArgs r;
+    memset(&r, 0, sizeof(r));
     r.hash = c.cand_hash; r.fp = c.cand_fp; r.score = c.cand_score; r.payload = c.cand_payload; r.states = c.children;
     r.s_hash = c.send_hash; r.s_fp = c.send_fp; r.s_score = c.send_score; r.s_payload = c.send_payload;
     r.s_states = c.send_states;
@@ -402,6 +507,7 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     for (int l = 0; l < Lb; ++l) {
       a.level = l;
       a.hist = c.hist + (int64_t)(r * Lb + l) * MGBS_HIST_STRIDE;
+      a.peer.slot = r * Lb + l;
       a.hist_prev = l > 0 ? c.hist + (int64_t)(r * Lb + l - 1) * MGBS_HIST_STRIDE : nullptr;
       MGBS_TRY(launch_band_hist(a, items, e->sms, st));
       MGBS_TRY(allreduce_hist(e, a.hist, st));
@@ -418,6 +524,7 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
   for (int l = 0; l < Lf; ++l) {
     a.level = l;
     a.hist = fin + (int64_t)l * MGBS_HIST_STRIDE;
+    a.peer.slot = R * Lb + l;
     a.hist_prev = l > 0 ? fin + (int64_t)(l - 1) * MGBS_HIST_STRIDE : nullptr;
     MGBS_TRY(launch_final_hist(a, c.hash_capacity, e->sms, st));
     MGBS_TRY(allreduce_hist(e, a.hist, st));

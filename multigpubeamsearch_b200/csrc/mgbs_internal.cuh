@@ -14,6 +14,25 @@ constexpr int kStreamThreads = 256;
 // Tie records of all ranks: world segments of {count, then MGBS_TIE_CAP x (hash, fingerprint, candidate index)}.
 constexpr int kTieSegWords = 1 + 3 * MGBS_TIE_CAP;
 
+// Peer-mapped symmetric regions (MGBS_EXCHANGE_PEER).  base[r] is rank r's region as seen from this GPU
+// (base[rank] is the local one).  Offsets are the same on every rank.
+struct SymLayout {
+  int64_t hash[2], fp[2], score[2], payload[2], states[2], counts[2];  // receive buckets per frontier parity
+  int64_t route_flag;  // [world] u32: sender r finished routing (value = epoch)
+  int64_t hx;          // [slots][world][MGBS_HIST_STRIDE] u32 histogram exchange
+  int64_t hflag;       // [slots][world] u32
+  int64_t total;
+  int32_t slots;
+};
+
+struct PeerCtx {
+  uint8_t* base[MGBS_MAX_WORLD];
+  int64_t off_hx, off_hflag;
+  uint32_t* tickets;
+  int32_t enabled;
+  int32_t slot;  // histogram slot of this launch
+};
+
 struct ExpandArgs {
   const uint8_t* frontier;
   const int32_t* count_dev;
@@ -66,6 +85,7 @@ struct StepArgs {
   uint32_t* next_score;
   uint64_t* next_hash;
   int32_t n, stride, fanout, parity;
+  PeerCtx peer;
 };
 
 struct RouteArgs {
@@ -75,6 +95,10 @@ struct RouteArgs {
   MgbsCtrl* ctrl;
   int32_t world, stride;
   uint32_t bucket_cap;
+  // peer mode: records go straight into the owner's receive buckets; offsets of the bucket arrays of this parity
+  PeerCtx peer;
+  int64_t off_hash, off_fp, off_score, off_payload, off_states, off_counts, off_route_flag;
+  int32_t rank;
 };
 
 int launch_expand(const ExpandArgs& a, int64_t max_parents, int sms, cudaStream_t st);
@@ -86,6 +110,7 @@ int launch_final_hist(const StepArgs& a, int64_t slots, int sms, cudaStream_t st
 int launch_emit(const StepArgs& a, int64_t items, int sms, cudaStream_t st);
 int launch_finish(const StepArgs& a, cudaStream_t st);
 int launch_route(const RouteArgs& a, int64_t items, int sms, cudaStream_t st);
+SymLayout sym_layout(const MgbsConfig& c, int band_levels_effective);
 int launch_clamp_counts(uint32_t* counts, int world, uint32_t cap, cudaStream_t st);
 
 }  // namespace mgbs

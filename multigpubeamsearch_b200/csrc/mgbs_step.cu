@@ -361,6 +361,54 @@ __device__ __forceinline__ void publish_stats(const StepArgs& a) {
   }
 }
 
+// One-shot all-reduce of a finished histogram over peer-mapped memory.  Called by every thread of every block
+// after its contribution was added to the local histogram; the block that arrives last pushes the local
+// histogram into slot [rank] of every rank's exchange area, raises its flag there (value = epoch), waits - with a
+// limit - for the flags of all ranks in its own area, and replaces the local histogram by the sum.  Consumers then
+// read the local histogram exactly as in the NCCL mode.
+__device__ void peer_allreduce_hist(const StepArgs& a) {
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned t = atomicAdd(&a.peer.tickets[a.peer.slot], 1u);
+    s_last = ((t + 1u) % gridDim.x) == 0u;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const uint32_t epoch = a.ctrl->epoch;
+  const int W = a.world;
+  const int64_t slot_words = (int64_t)a.peer.slot * W * MGBS_HIST_STRIDE;
+  for (int r = 0; r < W; ++r) {
+    uint32_t* dst = reinterpret_cast<uint32_t*>(a.peer.base[r] + a.peer.off_hx) + slot_words + (int64_t)a.rank * MGBS_HIST_STRIDE;
+    for (int i = threadIdx.x; i < MGBS_HIST_STRIDE; i += blockDim.x) dst[i] = __ldcg(a.hist + i);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < W) {
+    volatile uint32_t* f = reinterpret_cast<volatile uint32_t*>(a.peer.base[threadIdx.x] + a.peer.off_hflag) +
+                           (int64_t)a.peer.slot * W + a.rank;
+    *f = epoch;
+    volatile uint32_t* mine = reinterpret_cast<volatile uint32_t*>(a.peer.base[a.rank] + a.peer.off_hflag) +
+                              (int64_t)a.peer.slot * W + threadIdx.x;
+    bool ok = false;
+    for (uint32_t it = 0; it < (1u << 22); ++it) {
+      if ((int32_t)(*mine - epoch) >= 0) { ok = true; break; }
+      if (it > 256) __nanosleep(200);
+    }
+    if (!ok) atomicOr(&a.ctrl->status, MGBS_ST_PEER_TIMEOUT);
+  }
+  __threadfence_system();
+  __syncthreads();
+  const volatile uint32_t* src = reinterpret_cast<const volatile uint32_t*>(a.peer.base[a.rank] + a.peer.off_hx) + slot_words;
+  for (int i = threadIdx.x; i < MGBS_HIST_STRIDE; i += blockDim.x) {
+    uint32_t sum = 0;
+    for (int r = 0; r < W; ++r) sum += src[(int64_t)r * MGBS_HIST_STRIDE + i];
+    a.hist[i] = sum;
+  }
+}
+
 // Band histogram of one level.  Level 0 needs only the lower bound D; deeper levels first consume the previous
 // level's (all-reduced) histogram to learn which prefix to refine.
 __global__ void __launch_bounds__(kStreamThreads) k_band_hist(StepArgs a) {
@@ -378,7 +426,11 @@ __global__ void __launch_bounds__(kStreamThreads) k_band_hist(StepArgs a) {
     if (blockIdx.x == 0 && threadIdx.x == 0) a.ctrl->band[a.round][a.level] = st;
   }
   __syncthreads();
-  if (st.done) return;
+  if (st.done) {
+    // nothing to count; level-0 histograms still carry the per-rank statistics to every rank
+    if (a.peer.enabled && a.level == 0) peer_allreduce_hist(a);
+    return;
+  }
   const int db = digit_bits_at(a.key_bits, (int)st.bits_done);
   const int shift = a.key_bits - (int)st.bits_done - db;
   const uint32_t mask = (1u << db) - 1u;
@@ -397,6 +449,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_band_hist(StepArgs a) {
     hist_add(sh, in, digit);
   });
   hist_flush(sh, a.hist);
+  if (a.peer.enabled) peer_allreduce_hist(a);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -522,7 +575,11 @@ __global__ void __launch_bounds__(kStreamThreads) k_final_hist(StepArgs a) {
     if (blockIdx.x == 0 && threadIdx.x == 0) a.ctrl->fin[a.level] = st;
   }
   __syncthreads();
-  if (st.done) return;
+  if (st.done) {
+    // nothing to count; level-0 histograms still carry the per-rank statistics to every rank
+    if (a.peer.enabled && a.level == 0) peer_allreduce_hist(a);
+    return;
+  }
   const int db = digit_bits_at(a.key_bits, (int)st.bits_done);
   const int shift = a.key_bits - (int)st.bits_done - db;
   const uint32_t mask = (1u << db) - 1u;
@@ -548,6 +605,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_final_hist(StepArgs a) {
     hist_add(sh, in, digit);
   }
   hist_flush(sh, a.hist);
+  if (a.peer.enabled) peer_allreduce_hist(a);
 }
 
 // Write one survivor into the next frontier.
@@ -709,6 +767,7 @@ __global__ void k_depth_begin(MgbsCtrl* c, int parity, int fanout, int64_t cand_
   c->rounds_used = 0;
   c->bands_done = 0;
   c->found_payload = 0xffffffffu;
+  c->epoch += 1;
   c->band_lo[0] = 0;
   tie_seg[0] = 0;
   if (send_counts)
@@ -754,6 +813,76 @@ __global__ void __launch_bounds__(kStreamThreads) k_route(RouteArgs a) {
   }
 }
 
+// MGBS_EXCHANGE_PEER: the same bucketing, fused with the exchange.  Every record is stored straight into bucket
+// [this rank] of its owner's receive arrays through the peer mapping (plain stores over NVLink; the position comes
+// from this rank's own per-destination cursor, so no remote atomics).  The block that finishes last publishes the
+// bucket fills and this rank's flag to every owner, then waits - with a limit - until every sender has flagged this
+// rank, so that when the kernel ends the receive buckets of this depth are complete.
+__global__ void __launch_bounds__(kStreamThreads) k_route_peer(RouteArgs a) {
+  __shared__ int s_last;
+  const uint32_t cnt = a.ctrl->cand_count;
+  const uint32_t rounded = (cnt + 31u) & ~31u;
+  const int lane = threadIdx.x & 31;
+  const int vecs = a.stride >> 4;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < rounded; i += gridDim.x * blockDim.x) {
+    const bool valid = i < cnt;
+    uint64_t h = 0;
+    uint32_t owner = 0;
+    if (valid) {
+      h = __ldg(a.hash + i);
+      owner = (uint32_t)(h % (uint64_t)a.world);
+    }
+    const unsigned vm = __ballot_sync(0xffffffffu, valid);
+    if (!valid) continue;
+    const unsigned peers = __match_any_sync(vm, owner);
+    const int leader = __ffs(peers) - 1;
+    uint32_t base = 0;
+    if (lane == leader) base = atomicAdd(&a.send_counts[owner], (uint32_t)__popc(peers));
+    base = __shfl_sync(peers, base, leader);
+    const uint32_t pos = base + __popc(peers & ((1u << lane) - 1u));
+    if (pos >= a.bucket_cap) {
+      atomicOr(&a.ctrl->status, MGBS_ST_BUCKET_OVERFLOW);
+      continue;
+    }
+    uint8_t* ob = a.peer.base[owner];
+    const uint64_t d = (uint64_t)a.rank * a.bucket_cap + pos;
+    reinterpret_cast<uint64_t*>(ob + a.off_hash)[d] = h;
+    reinterpret_cast<uint64_t*>(ob + a.off_fp)[d] = __ldg(a.fp + i);
+    reinterpret_cast<uint32_t*>(ob + a.off_score)[d] = __ldg(a.score + i);
+    reinterpret_cast<uint32_t*>(ob + a.off_payload)[d] = __ldg(a.payload + i);
+    const uint4* src = reinterpret_cast<const uint4*>(a.states + (uint64_t)i * a.stride);
+    uint4* dst = reinterpret_cast<uint4*>(ob + a.off_states + d * a.stride);
+    for (int q = 0; q < vecs; ++q) dst[q] = __ldg(src + q);
+  }
+  // completion: all of this rank's stores are ordered before its flag
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned t = atomicAdd(&a.peer.tickets[a.peer.slot], 1u);
+    s_last = ((t + 1u) % gridDim.x) == 0u;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const uint32_t epoch = a.ctrl->epoch;
+  if ((int)threadIdx.x < a.world) {
+    const int r = threadIdx.x;
+    uint32_t fill = *reinterpret_cast<volatile uint32_t*>(&a.send_counts[r]);
+    if (fill > a.bucket_cap) fill = a.bucket_cap;
+    *reinterpret_cast<volatile uint32_t*>(a.peer.base[r] + a.off_counts + 4 * a.rank) = fill;
+    __threadfence_system();
+    *reinterpret_cast<volatile uint32_t*>(a.peer.base[r] + a.off_route_flag + 4 * a.rank) = epoch;
+    volatile uint32_t* mine = reinterpret_cast<volatile uint32_t*>(a.peer.base[a.rank] + a.off_route_flag + 4 * r);
+    bool ok = false;
+    for (uint32_t it = 0; it < (1u << 22); ++it) {
+      if ((int32_t)(*mine - epoch) >= 0) { ok = true; break; }
+      if (it > 256) __nanosleep(200);
+    }
+    if (!ok) atomicOr(&a.ctrl->status, MGBS_ST_PEER_TIMEOUT);
+  }
+  __threadfence_system();
+}
+
 // After the exchange a bucket may claim more than it holds when the sender overflowed: clamp.
 __global__ void k_clamp_counts(uint32_t* counts, int world, uint32_t cap) {
   const int r = threadIdx.x;
@@ -767,6 +896,28 @@ __global__ void k_clamp_counts(uint32_t* counts, int world, uint32_t cap) {
 // ------------------------------------------------------------------------------------------------
 
 namespace mgbs {
+
+static inline int64_t align256(int64_t x) { return (x + 255) / 256 * 256; }
+
+SymLayout sym_layout(const MgbsConfig& c, int band_levels_effective) {
+  SymLayout L;
+  const int64_t W = c.world_size, cap = c.bucket_cap;
+  int64_t off = 0;
+  for (int p = 0; p < 2; ++p) {
+    L.hash[p] = off;    off += align256(W * cap * 8);
+    L.fp[p] = off;      off += align256(W * cap * 8);
+    L.score[p] = off;   off += align256(W * cap * 4);
+    L.payload[p] = off; off += align256(W * cap * 4);
+    L.states[p] = off;  off += align256(W * cap * c.state_stride);
+    L.counts[p] = off;  off += align256(W * 4);
+  }
+  L.route_flag = off; off += align256(W * 4);
+  L.slots = c.band_rounds * band_levels_effective + MGBS_MAX_LEVELS;
+  L.hx = off;         off += align256((int64_t)L.slots * W * MGBS_HIST_STRIDE * 4);
+  L.hflag = off;      off += align256((int64_t)L.slots * W * 4);
+  L.total = off;
+  return L;
+}
 
 static inline int grid_for(int64_t items, int sms) {
   int64_t g = (items + kStreamThreads * 4 - 1) / (kStreamThreads * 4);
@@ -823,7 +974,8 @@ int launch_finish(const StepArgs& a, cudaStream_t st) {
 }
 
 int launch_route(const RouteArgs& a, int64_t items, int sms, cudaStream_t st) {
-  k_route<<<grid_for(items, sms), kStreamThreads, 0, st>>>(a);
+  if (a.peer.enabled) k_route_peer<<<grid_for(items, sms), kStreamThreads, 0, st>>>(a);
+  else k_route<<<grid_for(items, sms), kStreamThreads, 0, st>>>(a);
   return (int)cudaGetLastError();
 }
 

@@ -22,12 +22,12 @@ def gather_rows(rows):
     return out
 
 
-def run_case(name, beam, scramble_len, depths, backend, graph):
+def run_case(name, beam, scramble_len, depths, backend, graph, exchange="peer"):
     world, rank = dist.get_world_size(), dist.get_rank()
     pz = puzzles.by_name(name)
     cfg = be.config_for_puzzle(pz, world_size=world, rank=rank, global_beam_width=beam, max_depth=depths + 2,
                                beta=1.2, gamma=1.25, hash_load_factor=0.45, probe_limit=256, band_rounds=8,
-                               inference_backend=backend, use_cuda_graphs=graph)
+                               inference_backend=backend, use_cuda_graphs=graph, exchange=exchange)
     sc = None
     weights = None
     if backend == "mlp":
@@ -79,18 +79,21 @@ def run_case(name, beam, scramble_len, depths, backend, graph):
         if st["found"]:
             break
     if rank == 0:
-        print(f"CASE_OK {name} beam={beam} backend={backend} graph={graph} depths={depth + 1} "
+        print(f"CASE_OK {name} beam={beam} backend={backend} graph={graph} exchange={exchange} depths={depth + 1} "
               f"frontier={sum(f.shape[0] for f in fronts)}", flush=True)
-    del engine
+    engine.close()
+    dist.barrier()
+    del engine, buffers
 
 
 def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    run_case("lrx16", 1024, 30, 12, "central_hamming", False)
-    run_case("rand54", 4096, 12, 6, "central_hamming", True)
-    run_case("rand54", 2048, 30, 5, "mlp", True)
+    for exchange in ("peer", "nccl"):
+        run_case("lrx16", 1024, 30, 12, "central_hamming", False, exchange)
+        run_case("rand54", 4096, 12, 6, "central_hamming", True, exchange)
+        run_case("rand54", 2048, 30, 5, "mlp", True, exchange)
     # the engine's own depth loop: all ranks stop at the same depth with the same answer
     pz = puzzles.puzzle54()
     world, rank = dist.get_world_size(), dist.get_rank()
@@ -102,6 +105,7 @@ def main():
     assert res["found"] == want.found and res["depth"] == want.depth, (res["found"], res["depth"], want.found, want.depth)
     if rank == 0:
         print(f"SEARCH_OK found={res['found']} depth={res['depth']}", flush=True)
+    engine.close()
     dist.barrier()
     dist.destroy_process_group()
 
