@@ -167,7 +167,7 @@ def run_ours(args):
     K, W = args.steps, max(args.warmup, 3)
     depths = PREP_DEPTHS + 2 * (W + K) + 8  # history rows: later depths than this are simply not recorded
     cfg = be.config_for_puzzle(pz, world_size=world, rank=rank, global_beam_width=beam, max_depth=depths, beta=1.2,
-                               gamma=1.05, hash_load_factor=0.45, probe_limit=256, band_rounds=6, band_levels=3,
+                               gamma=1.05, hash_load_factor=0.45, probe_limit=256, band_rounds=3, band_levels=3,
                                inference_backend="mlp", use_cuda_graphs=True)
     ext = be.build_extension()
     be.init_distributed_if_needed(cfg)
