@@ -1,0 +1,531 @@
+// Transformer value scorer for sm_100a: an ensemble of pre-LayerNorm encoders (token + position embedding,
+// L layers of multi-head self-attention and a GELU feed-forward block, final LayerNorm, mean pooling, scalar head)
+// evaluated on every child state.  All projections (QKV, attention output, both feed-forward matrices) run as
+// tcgen05 GEMMs fed by TMA with accumulators in tensor memory; LayerNorm, the 54-token attention core and the
+// pooling head are bandwidth/latency kernels on the CUDA cores.  States are processed in micro-batches so that the
+// activation buffers have a fixed, modest size.
+//
+// The reference has no transformer scorer; its InferenceBackend interface (beam_engine.cpp:423-668) is the slot
+// this fills, through the same mgbs_scorer_fn hook as the MLP.
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <string.h>
+
+#include <new>
+
+#include "mgbs.h"
+#include "mgbs_tc.cuh"
+
+namespace mgbs {
+
+constexpr int TF_THREADS = 192;
+constexpr int TF_STAGING = 2 * A_BYTES;
+constexpr int TF_SMEM = STAGES * STAGE_BYTES + TF_STAGING + 1024 + 256;
+
+enum { TF_EPI_STORE = 0, TF_EPI_STORE_GELU = 1, TF_EPI_RESID = 2 };
+
+struct TfGemmArgs {
+  const uint32_t* count_dev;  // states to score (device value)
+  int32_t tokens;             // rows per state
+  int64_t row_offset;         // first row (state * tokens) of this micro-batch
+  int64_t row_limit;          // rows of one micro-batch at most
+  int32_t n_total, k_total;   // multiples of BN / BK
+  const float* bias;          // [n_total]
+  float* resid;               // TF_EPI_RESID: [rows, n_total] f32, updated in place (micro-batch local rows)
+  int* err;
+};
+
+__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+
+// C = A * W^T (+ bias) with A [rows, K] and W [N, K] bf16, K-major, both by TMA.
+// TF_EPI_STORE / _GELU: bf16 output through a swizzled staging box and TMA stores (tmOut: [rows, N] bf16).
+// TF_EPI_RESID: resid[row, n] += acc + bias[n] in float32 (each thread owns one row; 128-byte runs per access).
+template <int EPI>
+__global__ void __launch_bounds__(TF_THREADS, 1)
+k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+          const __grid_constant__ CUtensorMap tmOut, TfGemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* staging = smem + STAGES * STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + TF_STAGING);
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  int64_t rows = (int64_t)(*g.count_dev) * g.tokens - g.row_offset;
+  if (rows > g.row_limit) rows = g.row_limit;
+  if (rows < 0) rows = 0;
+  const int num_mtiles = (int)((rows + BM - 1) / BM);
+  const int n_chunks = g.n_total / BN;
+  const int k_blocks = g.k_total / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    mbar_init(drain_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_base_slot);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+        for (int nc = 0; nc < n_chunks && ok; ++nc) {
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+            mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+            tma_load_2d(sa, &tmA, kb * BK, mt * BM, full_bar(stage));
+            tma_load_2d(sa + A_BYTES, &tmB, kb * BK, nc * BN, full_bar(stage));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, acc_it = 0;
+      bool ok = true;
+      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+        for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
+          const uint32_t b = acc_it & 1u;
+          if (!mbar_wait(tempty_bar(b), ((acc_it >> 1) & 1u) ^ 1u, g.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + b * BN;
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+            const uint64_t adesc = make_desc_sw128(sa);
+            const uint64_t bdesc = make_desc_sw128(sa + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              tc_mma<0>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
+            tc_commit(empty_bar(stage));
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+          if (ok) tc_commit(tfull_bar(b));
+        }
+      }
+      tc_commit(drain_bar);
+      mbar_wait(drain_bar, 0, g.err, ERR_WAIT_DRAIN);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int et = (warp - 2) * 32 + lane;
+    const uint32_t r = (uint32_t)(quad * 32 + lane);
+    uint32_t acc_it = 0, box_it = 0;
+    bool ok = true;
+    for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+      const int row0 = mt * BM;
+      const int64_t row = (int64_t)row0 + r;
+      const bool row_ok = row < rows;
+      for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
+        const uint32_t b = acc_it & 1u;
+        if (!mbar_wait(tfull_bar(b), (acc_it >> 1) & 1u, g.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * BN;
+        if (EPI == TF_EPI_RESID) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t v[32];
+            tc_ld32(taddr + c0, v);
+            tc_wait_ld();
+            if (row_ok) {
+              const int n0 = nc * BN + c0;
+              float4* p = reinterpret_cast<float4*>(g.resid + row * g.n_total + n0);
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                float4 x = p[q];
+                x.x += __uint_as_float(v[4 * q]) + __ldg(g.bias + n0 + 4 * q);
+                x.y += __uint_as_float(v[4 * q + 1]) + __ldg(g.bias + n0 + 4 * q + 1);
+                x.z += __uint_as_float(v[4 * q + 2]) + __ldg(g.bias + n0 + 4 * q + 2);
+                x.w += __uint_as_float(v[4 * q + 3]) + __ldg(g.bias + n0 + 4 * q + 3);
+                p[q] = x;
+              }
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int gcol = 0; gcol < BN; gcol += 64, ++box_it) {
+            uint8_t* box = staging + (box_it & 1u) * A_BYTES;
+            if (et == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t v[32];
+              tc_ld32(taddr + gcol + half * 32, v);
+              tc_wait_ld();
+              const int n0 = nc * BN + gcol + half * 32;
+              uint32_t packed[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                float x0 = __uint_as_float(v[2 * j]) + __ldg(g.bias + n0 + 2 * j);
+                float x1 = __uint_as_float(v[2 * j + 1]) + __ldg(g.bias + n0 + 2 * j + 1);
+                if (EPI == TF_EPI_STORE_GELU) { x0 = gelu_erf(x0); x1 = gelu_erf(x1); }
+                __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+                packed[j] = *reinterpret_cast<uint32_t*>(&h);
+              }
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint32_t off = swz128(r, (uint32_t)(half * 64 + q * 16));
+                *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+              }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (et == 0) {
+              tma_store_2d(&tmOut, smem_u32(box), nc * BN + gcol, row0);
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(b));
+      }
+    }
+    if (EPI != TF_EPI_RESID && et == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// rows of one micro-batch: min(max(count*tokens - row_offset, 0), row_limit)
+__device__ __forceinline__ int64_t tf_rows(const uint32_t* count_dev, int tokens, int64_t row_offset, int64_t row_limit) {
+  int64_t rows = (int64_t)(*count_dev) * tokens - row_offset;
+  if (rows > row_limit) rows = row_limit;
+  return rows < 0 ? 0 : rows;
+}
+
+// x[row, :] = tok_emb[value] + pos_emb[position]; row = state * tokens + position.  One warp per row.
+__global__ void __launch_bounds__(256) k_tf_embed(const uint8_t* __restrict__ children, const uint32_t* count_dev,
+                                                  int tokens, int stride, int d, int64_t row_offset, int64_t row_limit,
+                                                  const float* __restrict__ tok_emb, const float* __restrict__ pos_emb,
+                                                  float* __restrict__ x) {
+  const int64_t rows = tf_rows(count_dev, tokens, row_offset, row_limit);
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+    const int64_t grow = row_offset + r;
+    const int64_t state = grow / tokens;
+    const int pos = (int)(grow - state * tokens);
+    const int val = __ldg(children + state * stride + pos);
+    const float* te = tok_emb + (int64_t)val * d;
+    const float* pe = pos_emb + (int64_t)pos * d;
+    for (int c = lane * 4; c < d; c += 128) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(te + c));
+      const float4 b = __ldg(reinterpret_cast<const float4*>(pe + c));
+      *reinterpret_cast<float4*>(x + r * d + c) = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+    }
+  }
+}
+
+// y = bf16(LayerNorm(x) * gamma + beta), d = 256: one warp per row, 8 elements per lane.
+__global__ void __launch_bounds__(256) k_tf_layernorm(const float* __restrict__ x, const uint32_t* count_dev, int tokens,
+                                                      int64_t row_offset, int64_t row_limit,
+                                                      const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                      __nv_bfloat16* __restrict__ y) {
+  constexpr int D = 256;
+  const int64_t rows = tf_rows(count_dev, tokens, row_offset, row_limit);
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+    const float4 a = *reinterpret_cast<const float4*>(x + r * D + lane * 8);
+    const float4 b = *reinterpret_cast<const float4*>(x + r * D + lane * 8 + 4);
+    float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += v[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float mu = s * (1.f / D);
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { v[i] -= mu; q += v[i] * v[i]; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
+    const float rstd = rsqrtf(q * (1.f / D) + 1e-5f);
+    uint32_t packed[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = lane * 8 + 2 * i;
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i] * rstd * __ldg(gamma + c) + __ldg(beta + c),
+                                               v[2 * i + 1] * rstd * __ldg(gamma + c + 1) + __ldg(beta + c + 1));
+      packed[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(y + r * D + lane * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+}
+
+// Self-attention core of one layer: out[row, h*32:(h+1)*32] = softmax(q k^T / sqrt(32)) v per state and head.
+// One block of 4 warps per (state, group of 4 heads), one warp per head; K and V of the head live in shared memory
+// as float (row pitch 33: conflict-free), every lane owns the query rows lane and lane+32 and runs an online
+// softmax over the keys.
+constexpr int TF_MAX_T = 64;
+constexpr int TF_ATT_HEADS = 4;
+__global__ void __launch_bounds__(128) k_tf_attention(const __nv_bfloat16* __restrict__ qkv, const uint32_t* count_dev,
+                                                      int tokens, int64_t row_offset, int64_t row_limit,
+                                                      __nv_bfloat16* __restrict__ out) {
+  constexpr int D = 256, HD = 32, P = HD + 1;
+  extern __shared__ float att_smem[];
+  const int hw = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* ks = att_smem + (size_t)hw * 2 * tokens * P;
+  float* vs = ks + (size_t)tokens * P;
+  const int64_t rows = tf_rows(count_dev, tokens, row_offset, row_limit);
+  const int64_t units = (rows / tokens) * (D / HD / TF_ATT_HEADS);
+  const float scale = 0.17677669529663687f;  // 1/sqrt(32)
+  for (int64_t u = blockIdx.x; u < units; u += gridDim.x) {
+    const int64_t s = u / (D / HD / TF_ATT_HEADS);
+    const int h = (int)(u - s * (D / HD / TF_ATT_HEADS)) * TF_ATT_HEADS + hw;
+    const __nv_bfloat16* base = qkv + s * tokens * (3 * D);
+    __syncwarp();
+    for (int t = 0; t < tokens; ++t) {
+      ks[t * P + lane] = __bfloat162float(base[(int64_t)t * 3 * D + D + h * HD + lane]);
+      vs[t * P + lane] = __bfloat162float(base[(int64_t)t * 3 * D + 2 * D + h * HD + lane]);
+    }
+    __syncwarp();
+    for (int qr = lane; qr < tokens; qr += 32) {
+      float q[HD];
+      const __nv_bfloat162* qp = reinterpret_cast<const __nv_bfloat162*>(base + (int64_t)qr * 3 * D + h * HD);
+#pragma unroll
+      for (int i = 0; i < HD / 2; ++i) {
+        const float2 f = __bfloat1622float2(qp[i]);
+        q[2 * i] = f.x * scale;
+        q[2 * i + 1] = f.y * scale;
+      }
+      float m = -1e30f, l = 0.f, acc[HD];
+#pragma unroll
+      for (int i = 0; i < HD; ++i) acc[i] = 0.f;
+      for (int j = 0; j < tokens; ++j) {
+        float sc = 0.f;
+#pragma unroll
+        for (int i = 0; i < HD; ++i) sc = fmaf(q[i], ks[j * P + i], sc);
+        const float mn = fmaxf(m, sc);
+        const float corr = __expf(m - mn);
+        const float p = __expf(sc - mn);
+        l = l * corr + p;
+#pragma unroll
+        for (int i = 0; i < HD; ++i) acc[i] = fmaf(acc[i], corr, p * vs[j * P + i]);
+        m = mn;
+      }
+      const float inv = 1.f / l;
+      __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(out + (s * tokens + qr) * D + h * HD);
+#pragma unroll
+      for (int i = 0; i < HD / 2; ++i) op[i] = __floats2bfloat162_rn(acc[2 * i] * inv, acc[2 * i + 1] * inv);
+    }
+  }
+}
+
+// Final LayerNorm, mean over the tokens of a state, scalar head: q[state] (+)= mean_t(LN(x_t)) . w_head.
+// One warp per state.
+__global__ void __launch_bounds__(256) k_tf_pool_head(const float* __restrict__ x, const uint32_t* count_dev, int tokens,
+                                                      int64_t row_offset, int64_t row_limit,
+                                                      const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                      const float* __restrict__ w_head, int accumulate,
+                                                      float* __restrict__ q_out) {
+  constexpr int D = 256;
+  const int64_t rows = tf_rows(count_dev, tokens, row_offset, row_limit);
+  const int64_t states = rows / tokens;
+  const int64_t state0 = row_offset / tokens;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (int64_t s = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); s < states; s += warps) {
+    float pooled[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pooled[i] = 0.f;
+    for (int t = 0; t < tokens; ++t) {
+      const float* xr = x + (s * tokens + t) * D + lane * 8;
+      const float4 a = *reinterpret_cast<const float4*>(xr);
+      const float4 b = *reinterpret_cast<const float4*>(xr + 4);
+      float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sum += v[i];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      const float mu = sum * (1.f / D);
+      float var = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { v[i] -= mu; var += v[i] * v[i]; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) var += __shfl_xor_sync(0xffffffffu, var, o);
+      const float rstd = rsqrtf(var * (1.f / D) + 1e-5f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) pooled[i] += v[i] * rstd;
+    }
+    float dot = 0.f;
+    const float inv_t = 1.f / (float)tokens;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = lane * 8 + i;
+      dot += (pooled[i] * inv_t * __ldg(gamma + c) + __ldg(beta + c)) * __ldg(w_head + c);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (lane == 0) {
+      if (accumulate) q_out[state0 + s] += dot;
+      else q_out[state0 + s] = dot;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) k_tf_q_to_key(const float* __restrict__ q, const uint32_t* count_dev, float inv_models,
+                                                     float offset, uint32_t* __restrict__ keys) {
+  const int64_t rows = *count_dev;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < rows; i += (int64_t)gridDim.x * blockDim.x) {
+    float x = q[i] * inv_models - offset;
+    x = fminf(fmaxf(x, 0.f), 300.f);
+    keys[i] = (uint32_t)(x * 256.f + 0.5f);
+  }
+}
+
+}  // namespace mgbs
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+
+struct MgbsTf {
+  MgbsTfConfig cfg;
+  int sms = 148;
+  int64_t mb_rows = 0;      // rows of one micro-batch (micro_batch * tokens)
+  int64_t mb_rows_pad = 0;  // rounded up to 128
+  int n_micro = 0;
+  CUtensorMap tm_y, tm_qkv, tm_att, tm_hid;  // activations (load as A operand / store as output)
+  CUtensorMap tm_wqkv[MGBS_TF_MAX_ENCODERS][MGBS_TF_MAX_LAYERS], tm_wo[MGBS_TF_MAX_ENCODERS][MGBS_TF_MAX_LAYERS],
+      tm_w1[MGBS_TF_MAX_ENCODERS][MGBS_TF_MAX_LAYERS], tm_w2[MGBS_TF_MAX_ENCODERS][MGBS_TF_MAX_LAYERS];
+};
+
+extern "C" {
+
+int mgbs_sizeof_tf_config(void) { return (int)sizeof(MgbsTfConfig); }
+
+int mgbs_tf_create(const MgbsTfConfig* cfg, MgbsTf** out) {
+  if (!cfg || !out) return MGBS_ERR_ARG;
+  const MgbsTfConfig& c = *cfg;
+  if (c.d_model != 256 || c.heads != 8) return MGBS_ERR_UNSUPPORTED;
+  if (c.ffn < mgbs::BN || c.ffn % mgbs::BN != 0) return MGBS_ERR_UNSUPPORTED;
+  if (c.state_len < 1 || c.state_len > mgbs::TF_MAX_T || c.state_stride < c.state_len) return MGBS_ERR_ARG;
+  if (c.layers < 1 || c.layers > MGBS_TF_MAX_LAYERS || c.encoders < 1 || c.encoders > MGBS_TF_MAX_ENCODERS) return MGBS_ERR_ARG;
+  if (c.max_states < 1 || c.micro_batch < 1) return MGBS_ERR_ARG;
+  if (!c.x || !c.y || !c.qkv || !c.att || !c.hid || !c.q || !c.err) return MGBS_ERR_ARG;
+  MgbsTf* t = new (std::nothrow) MgbsTf();
+  if (!t) return MGBS_ERR_STATE;
+  t->cfg = c;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) t->sms = sms;
+  }
+  t->mb_rows = c.micro_batch * c.state_len;
+  t->mb_rows_pad = (t->mb_rows + mgbs::BM - 1) / mgbs::BM * mgbs::BM;
+  t->n_micro = (int)((c.max_states + c.micro_batch - 1) / c.micro_batch);
+  const uint64_t R = (uint64_t)t->mb_rows_pad;
+  int rc = mgbs::make_map_bf16(&t->tm_y, c.y, R, 256, mgbs::BM);
+  if (!rc) rc = mgbs::make_map_bf16(&t->tm_qkv, c.qkv, R, 768, mgbs::BM);
+  if (!rc) rc = mgbs::make_map_bf16(&t->tm_att, c.att, R, 256, mgbs::BM);
+  if (!rc) rc = mgbs::make_map_bf16(&t->tm_hid, c.hid, R, (uint64_t)c.ffn, mgbs::BM);
+  for (int e = 0; e < c.encoders && !rc; ++e) {
+    if (!c.tok_emb[e] || !c.pos_emb[e] || !c.lnf_g[e] || !c.lnf_b[e] || !c.w_head[e]) rc = MGBS_ERR_ARG;
+    for (int l = 0; l < c.layers && !rc; ++l) {
+      const MgbsTfLayer& L = c.layer[e][l];
+      if (!L.ln1_g || !L.ln1_b || !L.wqkv || !L.bqkv || !L.wo || !L.bo || !L.ln2_g || !L.ln2_b || !L.w1 || !L.b1 ||
+          !L.w2 || !L.b2)
+        rc = MGBS_ERR_ARG;
+      if (!rc) rc = mgbs::make_map_bf16(&t->tm_wqkv[e][l], L.wqkv, 768, 256, mgbs::BN);
+      if (!rc) rc = mgbs::make_map_bf16(&t->tm_wo[e][l], L.wo, 256, 256, mgbs::BN);
+      if (!rc) rc = mgbs::make_map_bf16(&t->tm_w1[e][l], L.w1, (uint64_t)c.ffn, 256, mgbs::BN);
+      if (!rc) rc = mgbs::make_map_bf16(&t->tm_w2[e][l], L.w2, 256, (uint64_t)c.ffn, mgbs::BN);
+    }
+  }
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_tf_gemm<mgbs::TF_EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::TF_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_tf_gemm<mgbs::TF_EPI_STORE_GELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::TF_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_tf_gemm<mgbs::TF_EPI_RESID>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::TF_SMEM);
+  const int att_smem = mgbs::TF_ATT_HEADS * 2 * c.state_len * 33 * (int)sizeof(float);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_tf_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, att_smem);
+  if (rc) { delete t; return rc; }
+  *out = t;
+  return 0;
+}
+
+int mgbs_tf_destroy(MgbsTf* t) {
+  delete t;
+  return 0;
+}
+
+int mgbs_tf_enqueue(void* user, const uint8_t* children, const uint32_t* count_dev, uint32_t* scores, void* stream) {
+  MgbsTf* t = static_cast<MgbsTf*>(user);
+  if (!t || !children || !count_dev || !scores) return MGBS_ERR_ARG;
+  using namespace mgbs;
+  const MgbsTfConfig& c = t->cfg;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int T = c.state_len;
+  const int ew_grid = t->sms * 8;
+  const int att_smem = TF_ATT_HEADS * 2 * T * 33 * (int)sizeof(float);
+  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(c.y);
+  __nv_bfloat16* qkv = reinterpret_cast<__nv_bfloat16*>(c.qkv);
+  __nv_bfloat16* att = reinterpret_cast<__nv_bfloat16*>(c.att);
+  for (int mb = 0; mb < t->n_micro; ++mb) {
+    const int64_t off = (int64_t)mb * t->mb_rows;
+    TfGemmArgs g;
+    g.count_dev = count_dev;
+    g.tokens = T;
+    g.row_offset = off;
+    g.row_limit = t->mb_rows;
+    g.err = c.err;
+    for (int e = 0; e < c.encoders; ++e) {
+      k_tf_embed<<<ew_grid, 256, 0, st>>>(children, count_dev, T, c.state_stride, 256, off, t->mb_rows, c.tok_emb[e],
+                                          c.pos_emb[e], c.x);
+      for (int l = 0; l < c.layers; ++l) {
+        const MgbsTfLayer& L = c.layer[e][l];
+        k_tf_layernorm<<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln1_g, L.ln1_b, y);
+        g.n_total = 768; g.k_total = 256; g.bias = L.bqkv; g.resid = nullptr;
+        k_tf_gemm<TF_EPI_STORE><<<t->sms, TF_THREADS, TF_SMEM, st>>>(t->tm_y, t->tm_wqkv[e][l], t->tm_qkv, g);
+        k_tf_attention<<<t->sms * 16, 128, att_smem, st>>>(qkv, count_dev, T, off, t->mb_rows, att);
+        g.n_total = 256; g.k_total = 256; g.bias = L.bo; g.resid = c.x;
+        k_tf_gemm<TF_EPI_RESID><<<t->sms, TF_THREADS, TF_SMEM, st>>>(t->tm_att, t->tm_wo[e][l], t->tm_att, g);
+        k_tf_layernorm<<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln2_g, L.ln2_b, y);
+        g.n_total = c.ffn; g.k_total = 256; g.bias = L.b1; g.resid = nullptr;
+        k_tf_gemm<TF_EPI_STORE_GELU><<<t->sms, TF_THREADS, TF_SMEM, st>>>(t->tm_y, t->tm_w1[e][l], t->tm_hid, g);
+        g.n_total = 256; g.k_total = c.ffn; g.bias = L.b2; g.resid = c.x;
+        k_tf_gemm<TF_EPI_RESID><<<t->sms, TF_THREADS, TF_SMEM, st>>>(t->tm_hid, t->tm_w2[e][l], t->tm_hid, g);
+      }
+      k_tf_pool_head<<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, c.lnf_g[e], c.lnf_b[e], c.w_head[e],
+                                              e > 0 ? 1 : 0, c.q);
+    }
+  }
+  float bh = 0.f;
+  for (int e = 0; e < c.encoders; ++e) bh += c.b_head[e];
+  k_tf_q_to_key<<<t->sms * 4, 256, 0, st>>>(c.q, count_dev, 1.f / (float)c.encoders,
+                                            c.score_offset - bh / (float)c.encoders, scores);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -118,3 +118,28 @@ def mlp_weights(in_features: int, hidden: int = 1024, seed: int = 7000, model_id
         "w3": (rng.standard_normal((hidden,)) * std).astype(np.float32),
         "b3": np.float32(0.0),
     }
+
+
+def transformer_weights(tokens: int, vocab: int, d_model: int = 256, layers: int = 4, ffn: int = 1024,
+                        seed: int = 8000, model_idx: int = 0, std: float = 0.02) -> Dict:
+    """Random-init pre-LayerNorm encoder: Gaussian std 0.02 matrices and embeddings, zero biases, LayerNorm 1/0."""
+    rng = np.random.default_rng(seed + model_idx)
+
+    def g(*shape):
+        return (rng.standard_normal(shape) * std).astype(np.float32)
+
+    def z(*shape):
+        return np.zeros(shape, dtype=np.float32)
+
+    def ones(*shape):
+        return np.ones(shape, dtype=np.float32)
+
+    return {
+        "tok_emb": g(vocab, d_model), "pos_emb": g(tokens, d_model),
+        "layers": [{
+            "ln1_g": ones(d_model), "ln1_b": z(d_model), "wqkv": g(3 * d_model, d_model), "bqkv": z(3 * d_model),
+            "wo": g(d_model, d_model), "bo": z(d_model), "ln2_g": ones(d_model), "ln2_b": z(d_model),
+            "w1": g(ffn, d_model), "b1": z(ffn), "w2": g(d_model, ffn), "b2": z(d_model),
+        } for _ in range(layers)],
+        "lnf_g": ones(d_model), "lnf_b": z(d_model), "w_head": g(d_model), "b_head": np.float32(0.0),
+    }

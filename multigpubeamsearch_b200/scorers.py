@@ -233,3 +233,142 @@ class MLPValueScorer:
     def error_code(self) -> int:
         """0, or the code of the first bounded wait that gave up inside a GEMM kernel."""
         return int(self.err.item())
+
+
+# ----------------------------------------------------------------------------------------------
+# Transformer value scorer
+# ----------------------------------------------------------------------------------------------
+
+TF_MAX_ENCODERS = 4
+TF_MAX_LAYERS = 8
+_LAYER_FIELDS = ("ln1_g", "ln1_b", "wqkv", "bqkv", "wo", "bo", "ln2_g", "ln2_b", "w1", "b1", "w2", "b2")
+_LAYER_BF16 = {"wqkv", "wo", "w1", "w2"}
+
+
+class MgbsTfLayer(C.Structure):
+    _fields_ = [(name, C.c_void_p) for name in _LAYER_FIELDS]
+
+
+class MgbsTfConfig(C.Structure):
+    _fields_ = [
+        ("state_len", C.c_int32), ("state_stride", C.c_int32), ("num_values", C.c_int32), ("d_model", C.c_int32),
+        ("heads", C.c_int32), ("ffn", C.c_int32), ("layers", C.c_int32), ("encoders", C.c_int32),
+        ("max_states", C.c_int64), ("micro_batch", C.c_int64), ("score_offset", C.c_float),
+        ("b_head", C.c_float * TF_MAX_ENCODERS),
+        ("tok_emb", C.c_void_p * TF_MAX_ENCODERS), ("pos_emb", C.c_void_p * TF_MAX_ENCODERS),
+        ("lnf_g", C.c_void_p * TF_MAX_ENCODERS), ("lnf_b", C.c_void_p * TF_MAX_ENCODERS),
+        ("w_head", C.c_void_p * TF_MAX_ENCODERS),
+        ("layer", (MgbsTfLayer * TF_MAX_LAYERS) * TF_MAX_ENCODERS),
+        ("x", C.c_void_p), ("y", C.c_void_p), ("qkv", C.c_void_p), ("att", C.c_void_p), ("hid", C.c_void_p),
+        ("q", C.c_void_p), ("err", C.c_void_p),
+    ]
+
+
+_TF_SIGS = {
+    "mgbs_sizeof_tf_config": (C.c_int, []),
+    "mgbs_tf_create": (C.c_int, [C.POINTER(MgbsTfConfig), C.POINTER(C.c_void_p)]),
+    "mgbs_tf_destroy": (C.c_int, [C.c_void_p]),
+    "mgbs_tf_enqueue": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+}
+_lib.SIGNATURES.update(_TF_SIGS)
+
+
+class TransformerValueScorer:
+    """Ensemble of pre-LayerNorm transformer encoders scoring child states (see puzzles.transformer_weights for the
+    weight layout): d_model 256, 8 heads, GELU feed-forward, mean pooling, scalar head.  bf16 GEMM operands with fp32
+    accumulation on the tcgen05 tensor cores, fp32 residual stream; states go through in micro-batches of
+    ``micro_batch`` (the reference's B_MICRO knob)."""
+
+    def __init__(self, encoders: Sequence[Dict], state_len: int, state_stride: int, num_values: int, max_rows: int,
+                 micro_batch: int = 32768, score_offset: float = -150.0, device=None):
+        self.lib = _lib.load()
+        for name, (res, args) in _TF_SIGS.items():
+            fn = getattr(self.lib, name)
+            fn.restype, fn.argtypes = res, args
+        if self.lib.mgbs_sizeof_tf_config() != C.sizeof(MgbsTfConfig):
+            raise RuntimeError("structure layout mismatch between scorers.py and libmgbs_b200.so")
+        if isinstance(encoders, dict):
+            encoders = [encoders]
+        if not 1 <= len(encoders) <= TF_MAX_ENCODERS:
+            raise RuntimeError(f"1..{TF_MAX_ENCODERS} encoders supported")
+        dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        d = int(encoders[0]["tok_emb"].shape[1])
+        layers = len(encoders[0]["layers"])
+        ffn = int(encoders[0]["layers"][0]["w1"].shape[0])
+        micro_batch = int(min(micro_batch, max_rows))
+        rows_pad = (micro_batch * state_len + 127) // 128 * 128
+        self.state_len, self.state_stride, self.num_values = state_len, state_stride, num_values
+        self.max_rows, self.micro_batch, self.score_offset = int(max_rows), micro_batch, float(score_offset)
+        self.d_model, self.layers, self.ffn, self.num_models = d, layers, ffn, len(encoders)
+        self._keep: List[torch.Tensor] = []
+
+        def f32(a):
+            t = torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dev)
+            self._keep.append(t)
+            return t.data_ptr()
+
+        def bf16(a):
+            t = torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dev).to(torch.bfloat16).contiguous()
+            self._keep.append(t)
+            return t.data_ptr()
+
+        cfg = MgbsTfConfig()
+        cfg.state_len, cfg.state_stride, cfg.num_values = state_len, state_stride, num_values
+        cfg.d_model, cfg.heads, cfg.ffn, cfg.layers, cfg.encoders = d, 8, ffn, layers, len(encoders)
+        cfg.max_states, cfg.micro_batch, cfg.score_offset = int(max_rows), micro_batch, float(score_offset)
+        for e, w in enumerate(encoders):
+            if w["tok_emb"].shape != (num_values, d) or w["pos_emb"].shape[0] < state_len or len(w["layers"]) != layers:
+                raise RuntimeError("encoder weight shapes do not match the puzzle")
+            cfg.b_head[e] = float(w["b_head"])
+            cfg.tok_emb[e], cfg.pos_emb[e] = f32(w["tok_emb"]), f32(w["pos_emb"][:state_len])
+            cfg.lnf_g[e], cfg.lnf_b[e], cfg.w_head[e] = f32(w["lnf_g"]), f32(w["lnf_b"]), f32(w["w_head"])
+            for li, L in enumerate(w["layers"]):
+                for name in _LAYER_FIELDS:
+                    setattr(cfg.layer[e][li], name, bf16(L[name]) if name in _LAYER_BF16 else f32(L[name]))
+        self.x = torch.zeros((rows_pad, d), dtype=torch.float32, device=dev)
+        self.y = torch.zeros((rows_pad, d), dtype=torch.bfloat16, device=dev)
+        self.qkv = torch.zeros((rows_pad, 3 * d), dtype=torch.bfloat16, device=dev)
+        self.att = torch.zeros((rows_pad, d), dtype=torch.bfloat16, device=dev)
+        self.hid = torch.zeros((rows_pad, ffn), dtype=torch.bfloat16, device=dev)
+        self.q = torch.zeros((int(max_rows),), dtype=torch.float32, device=dev)
+        self.err = torch.zeros((1,), dtype=torch.int32, device=dev)
+        self._count = torch.zeros((1,), dtype=torch.int32, device=dev)
+        cfg.x, cfg.y, cfg.qkv, cfg.att, cfg.hid = (t.data_ptr() for t in (self.x, self.y, self.qkv, self.att, self.hid))
+        cfg.q, cfg.err = self.q.data_ptr(), self.err.data_ptr()
+        self._cfg = cfg
+        h = C.c_void_p()
+        _lib.check(self.lib.mgbs_tf_create(C.byref(cfg), C.byref(h)), "TransformerValueScorer")
+        self._h = h
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            self.lib.mgbs_tf_destroy(h)
+            self._h = None
+
+    def c_callback(self):
+        return C.cast(self.lib.mgbs_tf_enqueue, C.c_void_p), self._h
+
+    def flops_per_state(self) -> int:
+        d, t, f = self.d_model, self.state_len, self.ffn
+        per_layer = 2 * t * (3 * d * d + d * d + 2 * d * f) + 2 * 2 * t * t * d
+        return self.num_models * self.layers * per_layer
+
+    def score(self, children: torch.Tensor) -> torch.Tensor:
+        if children.dtype != torch.uint8 or children.dim() != 2 or children.shape[1] != self.state_stride:
+            raise RuntimeError("children must be [C, state_stride] uint8")
+        if children.shape[0] > self.max_rows:
+            raise RuntimeError("more rows than the scorer was sized for")
+        children = children.contiguous()
+        self._count.fill_(children.shape[0])
+        keys = torch.zeros((children.shape[0],), dtype=torch.int32, device=children.device)
+        _lib.check(self.lib.mgbs_tf_enqueue(self._h, children.data_ptr(), self._count.data_ptr(), keys.data_ptr(),
+                                            C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                   "TransformerValueScorer.score")
+        return keys
+
+    def last_q(self, count: int) -> torch.Tensor:
+        return self.q[:count]
+
+    def error_code(self) -> int:
+        return int(self.err.item())

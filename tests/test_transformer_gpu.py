@@ -1,0 +1,77 @@
+"""GPU tests of the transformer value scorer against the float32 evaluation."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import beam_oracle as bo
+from multigpubeamsearch_b200 import beam_engine as be
+from multigpubeamsearch_b200 import puzzles, scorers
+
+pytestmark = pytest.mark.gpu
+
+
+def _states(pz, count, seed):
+    rng = np.random.default_rng(seed)
+    g = pz.generators.astype(np.int64)
+    rows = np.tile(pz.solved, (count, 1))
+    for _ in range(30):
+        rows = np.take_along_axis(rows, g[rng.integers(0, pz.fanout, size=count)], axis=1)
+    return rows
+
+
+def _pad(rows, stride):
+    out = np.zeros((rows.shape[0], stride), np.uint8)
+    out[:, : rows.shape[1]] = rows
+    return out
+
+
+@pytest.mark.parametrize("count,encoders,micro", [(300, 1, 32768), (700, 2, 256), (1, 1, 64)])
+def test_transformer_scorer_matches_fp32(count, encoders, micro):
+    pz = puzzles.puzzle54()
+    ws = [puzzles.transformer_weights(54, 6, model_idx=i) for i in range(encoders)]
+    rng = np.random.default_rng(11)
+    for w in ws:  # non-trivial biases / LayerNorm parameters so that every term is exercised
+        w["b_head"] = np.float32(0.05)
+        w["lnf_g"] = (1.0 + 0.1 * rng.standard_normal(256)).astype(np.float32)
+        w["lnf_b"] = (0.1 * rng.standard_normal(256)).astype(np.float32)
+        for L in w["layers"]:
+            for k in ("bqkv", "bo", "b1", "b2", "ln1_b", "ln2_b"):
+                L[k] = (0.05 * rng.standard_normal(L[k].shape)).astype(np.float32)
+            for k in ("ln1_g", "ln2_g"):
+                L[k] = (1.0 + 0.1 * rng.standard_normal(256)).astype(np.float32)
+    sc = scorers.TransformerValueScorer(ws, 54, 64, 6, max_rows=count, micro_batch=micro)
+    rows = _states(pz, count, seed=count)
+    keys = sc.score(torch.from_numpy(_pad(rows, 64)).cuda())
+    torch.cuda.synchronize()
+    assert sc.error_code() == 0
+    q_ref = bo.transformer_forward(rows, ws)
+    q_dev = (sc.last_q(count).cpu().numpy() + sum(float(w["b_head"]) for w in ws)) / encoders
+    # bf16 GEMM operands and bf16 activations between GEMMs, fp32 residual stream: observed error ~1e-3
+    assert np.abs(q_dev - q_ref).max() <= 1e-2, np.abs(q_dev - q_ref).max()
+    rekey = bo.q_to_score_key(q_dev.astype(np.float32), -150.0).astype(np.int64)
+    assert np.abs(keys.cpu().numpy().astype(np.int64) - rekey).max() <= 1
+
+
+def test_engine_with_transformer_scorer():
+    pz = puzzles.puzzle54()
+    beam = 512
+    ws = [puzzles.transformer_weights(54, 6, model_idx=i) for i in range(2)]
+    cfg = be.config_for_puzzle(pz, global_beam_width=beam, max_depth=6, beta=1.2, hash_load_factor=0.45,
+                               probe_limit=256, band_rounds=8, inference_backend="mlp")
+    ext = be.build_extension()
+    be.init_distributed_if_needed(cfg)
+    sizes = ext.derive_sizes(cfg)
+    sc = scorers.TransformerValueScorer(ws, 54, 64, 6, max_rows=sizes["cand_cap"], micro_batch=2048)
+    _, cfg, buffers, engine = be.configure_engine(pz, cfg=cfg, scorer=sc)
+    frontier = np.unique(_states(pz, 300, seed=2), axis=0)
+    for graph in (False, True):
+        engine.load_frontier(frontier)
+        engine.enable_cuda_graphs(graph)
+        engine.step()
+        st = engine.status()
+        assert st["status_bits"] == 0 and sc.error_code() == 0
+        ncand = frontier.shape[0] * pz.fanout
+        dev_scores = buffers["cand_score"][:ncand].cpu().numpy().astype(np.uint32)
+        want = bo.depth_step([frontier], pz.generators, pz.solved, None, beam, score_override=[dev_scores])
+        assert np.array_equal(bo.sorted_rows(engine.frontier()), bo.sorted_rows(want.states))
