@@ -22,9 +22,13 @@
 
 namespace mgbs {
 
-constexpr int TF_THREADS = 192;
-constexpr int TF_STAGING = 2 * A_BYTES;
-constexpr int TF_SMEM = STAGES * STAGE_BYTES + TF_STAGING + 1024 + 256;
+// Warps: 0 = TMA, 1 = MMA + TMEM owner, 2..9 = epilogue.  Eight epilogue warps (two per TMEM lane quadrant, each
+// taking one 128-column half of the 256-column accumulator) because the GEMMs here have short reductions (K = 256):
+// per output tile the epilogue (bias, GELU, bf16 packing) costs more instructions than the tensor core needs cycles.
+constexpr int TF_THREADS = 320;
+constexpr int TF_STAGES = 3;
+constexpr int TF_STAGING = 4 * A_BYTES;  // two 128 x 64 bf16 boxes per column half
+constexpr int TF_SMEM = TF_STAGES * STAGE_BYTES + TF_STAGING + 1024 + 256;
 
 enum { TF_EPI_STORE = 0, TF_EPI_STORE_GELU = 1, TF_EPI_RESID = 2 };
 
@@ -50,15 +54,15 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           const __grid_constant__ CUtensorMap tmOut, TfGemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* staging = smem + STAGES * STAGE_BYTES;
+  uint8_t* staging = smem + TF_STAGES * STAGE_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(staging + TF_STAGING);
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 5);
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * TF_STAGES + 5);
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
-  const uint32_t drain_bar = bar0 + 8u * (2 * STAGES + 4);
+  auto empty_bar = [&](int s) { return bar0 + 8u * (TF_STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * TF_STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * TF_STAGES + 2 + b); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * TF_STAGES + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -70,8 +74,8 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   const int k_blocks = g.k_total / BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    for (int s = 0; s < TF_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 8); }
     mbar_init(drain_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -98,7 +102,7 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             mbar_expect_tx(full_bar(stage), STAGE_BYTES);
             tma_load_2d(sa, &tmA, kb * BK, mt * BM, full_bar(stage));
             tma_load_2d(sa + A_BYTES, &tmB, kb * BK, nc * BN, full_bar(stage));
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            if (++stage == TF_STAGES) { stage = 0; phase ^= 1u; }
           }
         }
       }
@@ -124,7 +128,7 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             for (int k = 0; k < BK / UMMA_K; ++k)
               tc_mma<0>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
             tc_commit(empty_bar(stage));
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            if (++stage == TF_STAGES) { stage = 0; phase ^= 1u; }
           }
           if (ok) tc_commit(tfull_bar(b));
         }
@@ -134,7 +138,8 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
     }
   } else {
     const int quad = warp & 3;
-    const int et = (warp - 2) * 32 + lane;
+    const int half = (warp - 2) >> 2;              // which 128 columns of the accumulator
+    const int et = ((warp - 2) & 3) * 32 + lane;   // 0..127 inside this half's group
     const uint32_t r = (uint32_t)(quad * 32 + lane);
     uint32_t acc_it = 0, box_it = 0;
     bool ok = true;
@@ -149,7 +154,7 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * BN;
         if (EPI == TF_EPI_RESID) {
 #pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += 32) {
+          for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
             uint32_t v[32];
             tc_ld32(taddr + c0, v);
             tc_wait_ld();
@@ -169,10 +174,10 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           }
         } else {
 #pragma unroll 1
-          for (int gcol = 0; gcol < BN; gcol += 64, ++box_it) {
-            uint8_t* box = staging + (box_it & 1u) * A_BYTES;
+          for (int gcol = half * (BN / 2); gcol < (half + 1) * (BN / 2); gcol += 64, ++box_it) {
+            uint8_t* box = staging + (half * 2 + (box_it & 1u)) * A_BYTES;
             if (et == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               uint32_t v[32];
@@ -195,7 +200,7 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
               }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
             if (et == 0) {
               tma_store_2d(&tmOut, smem_u32(box), nc * BN + gcol, row0);
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -284,61 +289,139 @@ __global__ void __launch_bounds__(256) k_tf_layernorm(const float* __restrict__ 
   }
 }
 
-// Self-attention core of one layer: out[row, h*32:(h+1)*32] = softmax(q k^T / sqrt(32)) v per state and head.
-// One block of 4 warps per (state, group of 4 heads), one warp per head; K and V of the head live in shared memory
-// as float (row pitch 33: conflict-free), every lane owns the query rows lane and lane+32 and runs an online
-// softmax over the keys.
+// Self-attention core of one layer: out[row, h*32:(h+1)*32] = softmax(q k^T / sqrt(32)) v per state and head,
+// on the tensor cores with warp-level mma (m16n8k16, bf16 in, fp32 accumulate).  A warp owns one (state, head):
+// it stages Q and K ([token][32], row pitch 40 bf16) and V transposed ([32][token], row pitch 72 bf16) in shared
+// memory (pitches chosen so that fragment loads are bank-conflict free), then for each block of 16 query rows
+// computes S = Q K^T (8 key blocks), a masked softmax in registers, and O = P V with the probabilities re-packed
+// from accumulator layout into A fragments.  Tokens are padded to 64; padded keys are masked out.
 constexpr int TF_MAX_T = 64;
-constexpr int TF_ATT_HEADS = 4;
-__global__ void __launch_bounds__(128) k_tf_attention(const __nv_bfloat16* __restrict__ qkv, const uint32_t* count_dev,
-                                                      int tokens, int64_t row_offset, int64_t row_limit,
-                                                      __nv_bfloat16* __restrict__ out) {
-  constexpr int D = 256, HD = 32, P = HD + 1;
-  extern __shared__ float att_smem[];
-  const int hw = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* ks = att_smem + (size_t)hw * 2 * tokens * P;
-  float* vs = ks + (size_t)tokens * P;
+constexpr int TF_ATT_WARPS = 4;
+constexpr int TF_QK_PITCH = 40;   // bf16 per row of Q / K
+constexpr int TF_VT_PITCH = 72;   // bf16 per row of V^T
+constexpr int TF_ATT_WARP_ELEMS = 2 * TF_MAX_T * TF_QK_PITCH + 32 * TF_VT_PITCH;
+constexpr int TF_ATT_SMEM = TF_ATT_WARPS * TF_ATT_WARP_ELEMS * 2;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(TF_ATT_WARPS * 32) k_tf_attention(const __nv_bfloat16* __restrict__ qkv,
+                                                                    const uint32_t* count_dev, int tokens,
+                                                                    int64_t row_offset, int64_t row_limit,
+                                                                    __nv_bfloat16* __restrict__ out) {
+  constexpr int D = 256, HD = 32, NH = D / HD;
+  extern __shared__ __align__(16) uint8_t att_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(att_raw) + (size_t)warp * TF_ATT_WARP_ELEMS;
+  __nv_bfloat16* ks = qs + TF_MAX_T * TF_QK_PITCH;
+  __nv_bfloat16* vt = ks + TF_MAX_T * TF_QK_PITCH;
   const int64_t rows = tf_rows(count_dev, tokens, row_offset, row_limit);
-  const int64_t units = (rows / tokens) * (D / HD / TF_ATT_HEADS);
-  const float scale = 0.17677669529663687f;  // 1/sqrt(32)
-  for (int64_t u = blockIdx.x; u < units; u += gridDim.x) {
-    const int64_t s = u / (D / HD / TF_ATT_HEADS);
-    const int h = (int)(u - s * (D / HD / TF_ATT_HEADS)) * TF_ATT_HEADS + hw;
-    const __nv_bfloat16* base = qkv + s * tokens * (3 * D);
+  const int64_t units = (rows / tokens) * NH;
+  const float scale_log2 = 0.17677669529663687f * 1.4426950408889634f;  // 1/sqrt(32) * log2(e)
+  for (int64_t u = (int64_t)blockIdx.x * TF_ATT_WARPS + warp; u < units; u += (int64_t)gridDim.x * TF_ATT_WARPS) {
+    const int64_t s = u / NH;
+    const int h = (int)(u - s * NH);
+    const __nv_bfloat16* base = qkv + s * tokens * (3 * D) + h * HD;
     __syncwarp();
-    for (int t = 0; t < tokens; ++t) {
-      ks[t * P + lane] = __bfloat162float(base[(int64_t)t * 3 * D + D + h * HD + lane]);
-      vs[t * P + lane] = __bfloat162float(base[(int64_t)t * 3 * D + 2 * D + h * HD + lane]);
+    // stage: 64 tokens x {q, k, v} x 4 chunks of 8 bf16; padded tokens are zero
+    for (int c = lane; c < TF_MAX_T * 12; c += 32) {
+      const int t = c / 12, rem = c - t * 12, m = rem >> 2, part = rem & 3;
+      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      if (t < tokens) val = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)t * 3 * D + m * D + part * 8));
+      if (m == 0) *reinterpret_cast<uint4*>(qs + t * TF_QK_PITCH + part * 8) = val;
+      else if (m == 1) *reinterpret_cast<uint4*>(ks + t * TF_QK_PITCH + part * 8) = val;
+      else {
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&val);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vt[(part * 8 + i) * TF_VT_PITCH + t] = e[i];
+      }
     }
     __syncwarp();
-    for (int qr = lane; qr < tokens; qr += 32) {
-      float q[HD];
-      const __nv_bfloat162* qp = reinterpret_cast<const __nv_bfloat162*>(base + (int64_t)qr * 3 * D + h * HD);
+    const int mblocks = (tokens + 15) >> 4;
+    for (int mb = 0; mb < mblocks; ++mb) {
+      // Q fragments of this 16-row block: two k-steps of 16
+      uint32_t qa[2][4];
 #pragma unroll
-      for (int i = 0; i < HD / 2; ++i) {
-        const float2 f = __bfloat1622float2(qp[i]);
-        q[2 * i] = f.x * scale;
-        q[2 * i + 1] = f.y * scale;
+      for (int kk = 0; kk < 2; ++kk) {
+        const __nv_bfloat16* q0 = qs + (mb * 16 + gid) * TF_QK_PITCH + kk * 16 + 2 * tig;
+        qa[kk][0] = *reinterpret_cast<const uint32_t*>(q0);
+        qa[kk][1] = *reinterpret_cast<const uint32_t*>(q0 + 8 * TF_QK_PITCH);
+        qa[kk][2] = *reinterpret_cast<const uint32_t*>(q0 + 8);
+        qa[kk][3] = *reinterpret_cast<const uint32_t*>(q0 + 8 * TF_QK_PITCH + 8);
       }
-      float m = -1e30f, l = 0.f, acc[HD];
+      float sc[8][4];
 #pragma unroll
-      for (int i = 0; i < HD; ++i) acc[i] = 0.f;
-      for (int j = 0; j < tokens; ++j) {
-        float sc = 0.f;
+      for (int nb = 0; nb < 8; ++nb) {
+        sc[nb][0] = sc[nb][1] = sc[nb][2] = sc[nb][3] = 0.f;
 #pragma unroll
-        for (int i = 0; i < HD; ++i) sc = fmaf(q[i], ks[j * P + i], sc);
-        const float mn = fmaxf(m, sc);
-        const float corr = __expf(m - mn);
-        const float p = __expf(sc - mn);
-        l = l * corr + p;
-#pragma unroll
-        for (int i = 0; i < HD; ++i) acc[i] = fmaf(acc[i], corr, p * vs[j * P + i]);
-        m = mn;
+        for (int kk = 0; kk < 2; ++kk) {
+          const __nv_bfloat16* k0 = ks + (nb * 8 + gid) * TF_QK_PITCH + kk * 16 + 2 * tig;
+          mma_bf16_16816(sc[nb], qa[kk], *reinterpret_cast<const uint32_t*>(k0), *reinterpret_cast<const uint32_t*>(k0 + 8));
+        }
       }
-      const float inv = 1.f / l;
-      __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(out + (s * tokens + qr) * D + h * HD);
+      // masked softmax over keys for rows gid (c0, c1) and gid + 8 (c2, c3); a row is spread over the 4 lanes of a group
+      float mx0 = -1e30f, mx1 = -1e30f;
 #pragma unroll
-      for (int i = 0; i < HD / 2; ++i) op[i] = __floats2bfloat162_rn(acc[2 * i] * inv, acc[2 * i + 1] * inv);
+      for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const bool valid = nb * 8 + 2 * tig + e < tokens;
+          sc[nb][e] = valid ? sc[nb][e] * scale_log2 : -1e30f;
+          sc[nb][2 + e] = valid ? sc[nb][2 + e] * scale_log2 : -1e30f;
+          mx0 = fmaxf(mx0, sc[nb][e]);
+          mx1 = fmaxf(mx1, sc[nb][2 + e]);
+        }
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+      for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          sc[nb][e] = exp2f(sc[nb][e] - mx0);
+          sc[nb][2 + e] = exp2f(sc[nb][2 + e] - mx1);
+          sum0 += sc[nb][e];
+          sum1 += sc[nb][2 + e];
+        }
+      }
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1); sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1); sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+      // O = P V: probabilities of key blocks (2j, 2j+1) form the A fragment of k-step j
+      float o[4][4];
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t pa[4];
+        pa[0] = pack_bf16(sc[2 * j][0], sc[2 * j][1]);
+        pa[1] = pack_bf16(sc[2 * j][2], sc[2 * j][3]);
+        pa[2] = pack_bf16(sc[2 * j + 1][0], sc[2 * j + 1][1]);
+        pa[3] = pack_bf16(sc[2 * j + 1][2], sc[2 * j + 1][3]);
+#pragma unroll
+        for (int nb = 0; nb < 4; ++nb) {
+          const __nv_bfloat16* v0 = vt + (nb * 8 + gid) * TF_VT_PITCH + j * 16 + 2 * tig;
+          mma_bf16_16816(o[nb], pa, *reinterpret_cast<const uint32_t*>(v0), *reinterpret_cast<const uint32_t*>(v0 + 8));
+        }
+      }
+      const float inv0 = 1.f / sum0, inv1 = 1.f / sum1;
+      const int r0 = mb * 16 + gid, r1 = r0 + 8;
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+        const int col = h * HD + nb * 8 + 2 * tig;
+        if (r0 < tokens) *reinterpret_cast<uint32_t*>(out + (s * tokens + r0) * D + col) = pack_bf16(o[nb][0] * inv0, o[nb][1] * inv0);
+        if (r1 < tokens) *reinterpret_cast<uint32_t*>(out + (s * tokens + r1) * D + col) = pack_bf16(o[nb][2] * inv1, o[nb][3] * inv1);
+      }
     }
   }
 }
@@ -468,8 +551,7 @@ int mgbs_tf_create(const MgbsTfConfig* cfg, MgbsTf** out) {
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_tf_gemm<mgbs::TF_EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::TF_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_tf_gemm<mgbs::TF_EPI_STORE_GELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::TF_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_tf_gemm<mgbs::TF_EPI_RESID>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::TF_SMEM);
-  const int att_smem = mgbs::TF_ATT_HEADS * 2 * c.state_len * 33 * (int)sizeof(float);
-  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_tf_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, att_smem);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_tf_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::TF_ATT_SMEM);
   if (rc) { delete t; return rc; }
   *out = t;
   return 0;
@@ -488,7 +570,6 @@ int mgbs_tf_enqueue(void* user, const uint8_t* children, const uint32_t* count_d
   cudaStream_t st = (cudaStream_t)stream;
   const int T = c.state_len;
   const int ew_grid = t->sms * 8;
-  const int att_smem = TF_ATT_HEADS * 2 * T * 33 * (int)sizeof(float);
   __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(c.y);
   __nv_bfloat16* qkv = reinterpret_cast<__nv_bfloat16*>(c.qkv);
   __nv_bfloat16* att = reinterpret_cast<__nv_bfloat16*>(c.att);
@@ -508,7 +589,7 @@ int mgbs_tf_enqueue(void* user, const uint8_t* children, const uint32_t* count_d
         k_tf_layernorm<<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln1_g, L.ln1_b, y);
         g.n_total = 768; g.k_total = 256; g.bias = L.bqkv; g.resid = nullptr;
         k_tf_gemm<TF_EPI_STORE><<<t->sms, TF_THREADS, TF_SMEM, st>>>(t->tm_y, t->tm_wqkv[e][l], t->tm_qkv, g);
-        k_tf_attention<<<t->sms * 16, 128, att_smem, st>>>(qkv, count_dev, T, off, t->mb_rows, att);
+        k_tf_attention<<<t->sms * 12, TF_ATT_WARPS * 32, TF_ATT_SMEM, st>>>(qkv, count_dev, T, off, t->mb_rows, att);
         g.n_total = 256; g.k_total = 256; g.bias = L.bo; g.resid = c.x;
         k_tf_gemm<TF_EPI_RESID><<<t->sms, TF_THREADS, TF_SMEM, st>>>(t->tm_att, t->tm_wo[e][l], t->tm_att, g);
         k_tf_layernorm<<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln2_g, L.ln2_b, y);

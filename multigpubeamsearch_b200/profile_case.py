@@ -2,7 +2,7 @@
 
     python -m multigpubeamsearch_b200.profile_case [--rows R] [--repeat N]
 
-Scores R random child states (default 151 552 = 8 tiles per SM on 148 SMs; first-layer activations 310 MB, larger than
+Scores R random child states with the MLP (default), its FP8 variant or the transformer ensemble (default 151 552 = 8 tiles per SM on 148 SMs; first-layer activations 310 MB, larger than
 L2) N times with the MLP 324 -> 1024 -> 1024 -> 1.  A dozen launches in total, a few hundred MB on the device.
 """
 
@@ -20,6 +20,8 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--rows", type=int, default=151552)
     ap.add_argument("--repeat", type=int, default=3)
+    ap.add_argument("--scorer", default="mlp", choices=["mlp", "mlp_fp8", "transformer"])
+    ap.add_argument("--micro-batch", type=int, default=32768)
     args = ap.parse_args()
     pz = puzzles.puzzle54()
     rng = np.random.default_rng(0)
@@ -30,11 +32,23 @@ def main() -> None:
     padded = np.zeros((args.rows, 64), np.uint8)
     padded[:, :54] = rows
     children = torch.from_numpy(padded).cuda()
-    sc = scorers.MLPValueScorer(puzzles.mlp_weights(324, 1024), 54, 64, 6, max_rows=args.rows)
+    if args.scorer == "transformer":
+        sc = scorers.TransformerValueScorer([puzzles.transformer_weights(54, 6, model_idx=i) for i in range(2)], 54, 64, 6,
+                                            max_rows=args.rows, micro_batch=args.micro_batch)
+    else:
+        sc = scorers.MLPValueScorer(puzzles.mlp_weights(324, 1024), 54, 64, 6, max_rows=args.rows,
+                                    dtype="fp8" if args.scorer == "mlp_fp8" else "bf16")
+    times = []
     for _ in range(args.repeat):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
         keys = sc.score(children)
-    torch.cuda.synchronize()
-    print("keys", int(keys.min()), int(keys.max()), "err", sc.error_code())
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    ms = min(times)
+    print("keys", int(keys.min()), int(keys.max()), "err", sc.error_code(), "ms", [round(t, 3) for t in times],
+          "TFLOP/s", round(sc.flops_per_state() * args.rows / (ms * 1e-3) / 1e12, 1))
 
 
 if __name__ == "__main__":
