@@ -80,6 +80,7 @@ class MgbsConfig(C.Structure):
         ("recv_hash", _P), ("recv_fp", _P), ("recv_score", _P), ("recv_payload", _P), ("recv_states", _P),
         ("send_counts", _P), ("recv_counts", _P),
         ("exchange_mode", C.c_int32), ("pad1", C.c_int32), ("sym", _P), ("sym_bytes", C.c_int64), ("tickets", _P),
+        ("io_stage", _P),
     ]
 
 
@@ -101,6 +102,7 @@ SIGNATURES = {
     "mgbs_engine_set_score_mode": (C.c_int, [_P, _I32, _I32]),
     "mgbs_engine_reset": (C.c_int, [_P, _P, _I32, _I32, _P]),
     "mgbs_engine_load_frontier": (C.c_int, [_P, _P, _I64, _I32, _I32, _P]),
+    "mgbs_engine_read_frontier": (C.c_int, [_P, _I32, _P, _I64, C.POINTER(_I64), _P]),
     "mgbs_engine_enqueue_depth": (C.c_int, [_P, _I32, _I32, _P]),
     "mgbs_engine_step_graph": (C.c_int, [_P, _I32, _P]),
     "mgbs_engine_profile": (C.c_int, [_P, _I32]),

@@ -171,6 +171,7 @@ def allocate_buffers(ext: _Ext, cfg: Dict[str, Any]) -> Dict[str, torch.Tensor]:
         "score_current": z((k_work,), torch.int32),
         "score_next": z((k_work,), torch.int32),
         "ctrl": z((C.sizeof(_lib.MgbsCtrl),), torch.uint8),
+        "io_stage": z((k_work * int(cfg["state_len"]),), torch.uint8),
     }
     if need_children:
         buffers["next_state_pool"] = z((cand_cap, stride), torch.uint8)
@@ -262,6 +263,7 @@ class BeamEngine:
         c.history = p("history_payload")
         c.frontier_score[0], c.frontier_score[1] = p("score_current"), p("score_next")
         c.ctrl = p("ctrl")
+        c.io_stage = p("io_stage")
         for side in ("send", "recv"):
             setattr(c, f"{side}_hash", p(f"{side}_hash"))
             setattr(c, f"{side}_fp", p(f"{side}_fingerprint"))
@@ -494,6 +496,16 @@ class BeamEngine:
         k = int(c.frontier_count[parity])
         n = int(self.cfg["state_len"])
         return self._frontier_tensor(parity)[:k, :n].cpu().numpy()
+
+    def frontier_into(self, out: np.ndarray) -> int:
+        """Copy the current frontier into ``out`` ([capacity, state_len] uint8, C-contiguous; pinned memory is
+        fastest) and return the number of rows written."""
+        if out.dtype != np.uint8 or out.ndim != 2 or out.shape[1] != int(self.cfg["state_len"]) or not out.flags["C_CONTIGUOUS"]:
+            raise RuntimeError("out must be a C-contiguous [capacity, state_len] uint8 array")
+        n = C.c_int64(0)
+        _lib.check(self.lib.mgbs_engine_read_frontier(self._h, self._ctrl.depth & 1, out.ctypes.data_as(C.c_void_p),
+                                                      out.shape[0], C.byref(n), self._sp()), "frontier_into")
+        return int(n.value)
 
     def frontier_scores(self) -> np.ndarray:
         c = self._read_ctrl()

@@ -341,12 +341,43 @@ int mgbs_engine_load_frontier(MgbsEngine* e, const uint8_t* rows_host, int64_t c
   h.rho_num = 1;
   h.rho_den = 1;
   MGBS_TRY(cudaMemcpyAsync(c.ctrl, &h, sizeof(MgbsCtrl), cudaMemcpyHostToDevice, st));
-  if (count > 0) {
+  if (count > 0 && c.io_stage) {
+    MGBS_TRY(cudaMemcpyAsync(c.io_stage, rows_host, (size_t)count * c.state_len, cudaMemcpyHostToDevice, st));
+    MGBS_TRY(mgbs::launch_repack_rows(c.io_stage, c.frontier[parity & 1], count, c.state_len, c.state_stride,
+                                      c.state_len, e->sms, st));
+  } else if (count > 0) {
     MGBS_TRY(cudaMemsetAsync(c.frontier[parity & 1], 0, (size_t)count * c.state_stride, st));
     MGBS_TRY(cudaMemcpy2DAsync(c.frontier[parity & 1], (size_t)c.state_stride, rows_host, (size_t)c.state_len,
                                (size_t)c.state_len, (size_t)count, cudaMemcpyHostToDevice, st));
   }
   MGBS_TRY(cudaStreamSynchronize(st));
+  return 0;
+}
+
+// Copy the current frontier (buffer `parity`) to host memory as packed rows of state_len bytes; returns the row
+// count through *count_out.  dst_host must hold capacity_rows rows; pinned memory makes the copy asynchronous up to
+// the final synchronisation.
+int mgbs_engine_read_frontier(MgbsEngine* e, int32_t parity, uint8_t* dst_host, int64_t capacity_rows,
+                              int64_t* count_out, void* stream) {
+  if (!e || !dst_host || !count_out || capacity_rows < 0) return MGBS_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  const MgbsConfig& c = e->cfg;
+  int32_t cnt = 0;
+  MGBS_TRY(cudaMemcpyAsync(&cnt, &c.ctrl->frontier_count[parity & 1], sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  MGBS_TRY(cudaStreamSynchronize(st));
+  int64_t n = cnt < 0 ? 0 : cnt;
+  if (n > capacity_rows) n = capacity_rows;
+  if (n > 0 && c.io_stage) {
+    MGBS_TRY(mgbs::launch_repack_rows(c.frontier[parity & 1], c.io_stage, n, c.state_stride, c.state_len, c.state_len,
+                                      e->sms, st));
+    MGBS_TRY(cudaMemcpyAsync(dst_host, c.io_stage, (size_t)n * c.state_len, cudaMemcpyDeviceToHost, st));
+    MGBS_TRY(cudaStreamSynchronize(st));
+  } else if (n > 0) {
+    MGBS_TRY(cudaMemcpy2DAsync(dst_host, (size_t)c.state_len, c.frontier[parity & 1], (size_t)c.state_stride,
+                               (size_t)c.state_len, (size_t)n, cudaMemcpyDeviceToHost, st));
+    MGBS_TRY(cudaStreamSynchronize(st));
+  }
+  *count_out = n;
   return 0;
 }
 

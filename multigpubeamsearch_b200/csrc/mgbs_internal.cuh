@@ -111,6 +111,8 @@ int launch_emit(const StepArgs& a, int64_t items, int sms, cudaStream_t st);
 int launch_finish(const StepArgs& a, cudaStream_t st);
 int launch_route(const RouteArgs& a, int64_t items, int sms, cudaStream_t st);
 SymLayout sym_layout(const MgbsConfig& c, int band_levels_effective);
+int launch_repack_rows(const uint8_t* src, uint8_t* dst, int64_t rows, int src_pitch, int dst_pitch, int n, int sms,
+                       cudaStream_t st);
 int launch_clamp_counts(uint32_t* counts, int world, uint32_t cap, cudaStream_t st);
 
 }  // namespace mgbs

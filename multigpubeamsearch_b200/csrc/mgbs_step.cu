@@ -883,6 +883,17 @@ __global__ void __launch_bounds__(kStreamThreads) k_route_peer(RouteArgs a) {
   __threadfence_system();
 }
 
+// Copy rows of n bytes between a packed and a padded layout (bytes n..pitch of a padded destination row are zeroed).
+__global__ void __launch_bounds__(256) k_repack_rows(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                     int64_t rows, int src_pitch, int dst_pitch, int n) {
+  const int64_t total = rows * dst_pitch;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / dst_pitch;
+    const int c = (int)(i - r * dst_pitch);
+    dst[i] = c < n ? src[r * src_pitch + c] : (uint8_t)0;
+  }
+}
+
 // After the exchange a bucket may claim more than it holds when the sender overflowed: clamp.
 __global__ void k_clamp_counts(uint32_t* counts, int world, uint32_t cap) {
   const int r = threadIdx.x;
@@ -976,6 +987,13 @@ int launch_finish(const StepArgs& a, cudaStream_t st) {
 int launch_route(const RouteArgs& a, int64_t items, int sms, cudaStream_t st) {
   if (a.peer.enabled) k_route_peer<<<grid_for(items, sms), kStreamThreads, 0, st>>>(a);
   else k_route<<<grid_for(items, sms), kStreamThreads, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
+int launch_repack_rows(const uint8_t* src, uint8_t* dst, int64_t rows, int src_pitch, int dst_pitch, int n, int sms,
+                       cudaStream_t st) {
+  if (rows <= 0) return 0;
+  k_repack_rows<<<grid_for(rows * dst_pitch, sms), 256, 0, st>>>(src, dst, rows, src_pitch, dst_pitch, n);
   return (int)cudaGetLastError();
 }
 

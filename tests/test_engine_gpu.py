@@ -237,3 +237,17 @@ def test_rejects_bad_arguments():
         engine.reset_search(b"\x00" * 3)
     with pytest.raises(RuntimeError):
         be.BeamEngine(engine.cfg, engine.buffers, "no_such_backend")
+
+
+def test_frontier_into_pinned_buffer():
+    pz = puzzles.puzzle54()
+    engine = make_engine(pz, global_beam_width=300)
+    frontier = random_frontier(pz, 80, seed=12)
+    engine.load_frontier(frontier)
+    engine.step()
+    want = engine.frontier()
+    out = torch.empty((engine.sizes()["k_work"], pz.state_len), dtype=torch.uint8).pin_memory()
+    n = engine.frontier_into(out.numpy())
+    assert n == want.shape[0] and np.array_equal(out.numpy()[:n], want)
+    small = np.zeros((10, pz.state_len), np.uint8)
+    assert engine.frontier_into(small) == 10 and np.array_equal(small, want[:10])
