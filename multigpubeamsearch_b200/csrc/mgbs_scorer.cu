@@ -202,8 +202,9 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
 //
 // out[row, :] = bf16(relu(onehot(child[row]) * W1^T + b1)).  The A operand is never materialised in global
 // memory.  Eight producer warps build the 128 x 64 bf16 K-blocks of the one-hot matrix straight into the
-// 128-byte-swizzled A stages the tensor core reads.  Each pair of producer warps owns one of four A stages and
-// works on every fourth K-block by itself (each warp zeroes its 64 rows = 8 KB with conflict-free 16-byte stores,
+// 128-byte-swizzled A slots the tensor core reads.  When the whole one-hot tile fits the six A slots (K <= 384) each
+// K-block is built once per M-tile and reused by the four N-chunks; otherwise the slots form a ring and blocks are
+// rebuilt per N-chunk.  Each of four producer warp pairs works on every fourth block by itself (each warp zeroes its 64 rows = 8 KB with conflict-free 16-byte stores,
 // then sets the ones of two rows per lane with independent predicated stores), so four K-blocks are in production at any time and
 // the latency of one block is hidden behind the others.  W1 K-blocks stream by TMA through a separate 3-stage
 // ring.  The epilogue packs the activated tile to bf16 in a swizzled staging box and writes it with TMA stores
@@ -213,9 +214,10 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
 // ------------------------------------------------------------------------------------------------
 
 constexpr int L1_THREADS = 448;
-constexpr int L1_A_STAGES = 4;                           // one per producer warp
+constexpr int L1_A_STAGES = 6;                           // 6 x 16 KB: a whole 128 x 384 one-hot tile when K <= 384
 constexpr int L1_B_STAGES = 3;
-constexpr int L1_STAGING = 2 * A_BYTES;                  // two 128 x 64 bf16 output boxes
+constexpr int L1_PAIRS = 4;                              // producer warp pairs
+constexpr int L1_STAGING = A_BYTES;                      // one 128-row x 128-byte output box
 constexpr int L1_CHILD_PITCH = MGBS_MAX_STATE_LEN + 4;   // bytes; odd word pitch -> conflict-free row reads
 constexpr int L1_MAX_KBLOCKS = 16;
 constexpr int L1_SMEM = L1_A_STAGES * A_BYTES + L1_B_STAGES * B_BYTES + L1_STAGING + BM * L1_CHILD_PITCH + 1024 + 512;
@@ -264,7 +266,8 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
   const int n_chunks = g.n_total / BN;
   constexpr int BKE = F8 ? BK8 : BK;  // one-hot columns per 128-byte K-block
   const int k_blocks = g.k_total / BKE;
-  const int blocks_per_tile = n_chunks * k_blocks;
+  const bool resident = k_blocks <= L1_A_STAGES;  // one-hot tile stays in shared memory for all N-chunks
+  const int blocks_per_tile = resident ? k_blocks : n_chunks * k_blocks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L1_A_STAGES; ++s) { mbar_init(a_full(s), 2); mbar_init(a_empty(s), 1); }
@@ -305,16 +308,18 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
     // ---- MMA issue ----
     if (lane == 0) {
       int sb = 0;
-      uint32_t pb = 0, acc_it = 0, it = 0;
+      uint32_t pb = 0, acc_it = 0, it_base = 0;
       bool ok = true;
-      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x, it_base += (uint32_t)blocks_per_tile) {
         for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
           const uint32_t b = acc_it & 1u;
           if (!mbar_wait(tempty_bar(b), ((acc_it >> 1) & 1u) ^ 1u, g.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + b * BN;
-          for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-            const int sa = (int)(it & (L1_A_STAGES - 1));
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            const uint32_t it = it_base + (uint32_t)(resident ? kb : nc * k_blocks + kb);
+            const int sa = (int)(it % L1_A_STAGES);
+            // resident tile: N-chunks after the first find the phase already complete
             if (!mbar_wait(a_full(sa), (it / L1_A_STAGES) & 1u, g.err, ERR_WAIT_FULL)) { ok = false; break; }
             if (!mbar_wait(b_full(sb), pb, g.err, ERR_WAIT_FULL)) { ok = false; break; }
             tc_fence_after();
@@ -323,7 +328,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k)
               tc_mma<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
-            tc_commit(a_empty(sa));
+            if (!resident || nc == n_chunks - 1) tc_commit(a_empty(sa));
             tc_commit(b_empty(sb));
             if (++sb == L1_B_STAGES) { sb = 0; pb ^= 1u; }
           }
@@ -349,9 +354,9 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * BN;
 #pragma unroll 1
         for (int gcol = 0; gcol < BN; gcol += BKE, ++box_it) {  // one box = 128 bytes per row
-          uint8_t* box = staging + (box_it & 1u) * A_BYTES;
-          // the TMA store that last read this box must be done before it is overwritten
-          if (et == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          uint8_t* box = staging;
+          // the TMA store that last read the box must be done before it is overwritten
+          if (et == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           asm volatile("bar.sync 1, 128;" ::: "memory");
 #pragma unroll
           for (int sub = 0; sub < BKE / 32; ++sub) {
@@ -409,11 +414,10 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
     if (et == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else {
     // ---- one-hot producers: warp pw owns A stage pw and builds K-blocks pw, pw+4, pw+8, ... of the sequence ----
-    const int pw = (warp - 6) >> 1;        // A stage of this warp
+    const int pw = (warp - 6) >> 1;        // producer pair of this warp
     const int half = (warp - 6) & 1;       // rows half*64 .. half*64+63 of the block
     const int pt = (warp - 6) * 32 + lane;  // 0..255; threads 0..127 load the child tile
     const int V = g.V, n = g.n;
-    uint8_t* a_stage = a_ring + pw * A_BYTES;
     uint32_t it_base = 0;           // index of this tile's first K-block in the CTA's K-block sequence
     bool ok = true;
     for (int mt = blockIdx.x; mt < num_mtiles; mt += gridDim.x, it_base += (uint32_t)blocks_per_tile) {
@@ -436,10 +440,12 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
       if (!ok) continue;
       // first K-block of this tile that belongs to this warp
       const uint32_t first = (uint32_t)((pw - (int)(it_base & 3u)) & 3);
-      for (uint32_t j = first; j < (uint32_t)blocks_per_tile; j += L1_A_STAGES) {
+      for (uint32_t j = first; j < (uint32_t)blocks_per_tile; j += L1_PAIRS) {
         const uint32_t it = it_base + j;
         const int kb = (int)(j % (uint32_t)k_blocks);
-        if (!mbar_wait(a_empty(pw), ((it / L1_A_STAGES) & 1u) ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+        const int slot = (int)(it % L1_A_STAGES);
+        uint8_t* a_stage = a_ring + slot * A_BYTES;
+        if (!mbar_wait(a_empty(slot), ((it / L1_A_STAGES) & 1u) ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
         // zero this warp's 64 rows (8 KB, contiguous): consecutive lanes write consecutive 16-byte chunks
         uint4* a4 = reinterpret_cast<uint4*>(a_stage + half * (A_BYTES / 2));
 #pragma unroll 8
@@ -465,7 +471,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(a_full(pw));
+        if (lane == 0) mbar_arrive(a_full(slot));
       }
     }
   }
