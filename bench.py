@@ -246,6 +246,7 @@ def run_ours(args):
         tm.update(sc.profile_read())
         for k in prof:
             prof[k].append(tm[k])
+        last_trace = tm.get("trace_ms")
         prof_rows.append(rows_before * pz.fanout)
     sc.profile(False)
     engine.enable_step_timers(False)
@@ -261,7 +262,8 @@ def run_ours(args):
                 "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                 "frac": achieved_tflops / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"] + " (sustained bf16)",
                 "traffic": traffic,
-                "stage_ms": {k: statistics.mean(v) for k, v in prof.items()}}
+                "stage_ms": {k: statistics.mean(v) for k, v in prof.items()},
+                "last_step_trace_ms": last_trace}
 
     # ---- end to end: host frontier in pinned memory -> device -> one step -> host frontier ----
     n = pz.state_len

@@ -107,6 +107,7 @@ SIGNATURES = {
     "mgbs_engine_step_graph": (C.c_int, [_P, _I32, _P]),
     "mgbs_engine_profile": (C.c_int, [_P, _I32]),
     "mgbs_engine_profile_read": (C.c_int, [_P, C.POINTER(C.c_float)]),
+    "mgbs_engine_trace_read": (C.c_int, [_P, C.POINTER(C.c_float), _I32]),
     "mgbs_engine_read_ctrl": (C.c_int, [_P, C.POINTER(MgbsCtrl), _P]),
     "mgbs_engine_search": (C.c_int, [_P, _I32, _I32, C.POINTER(MgbsCtrl), _P]),
     "mgbs_launch_expand": (C.c_int, [_P, _P, _I64, _P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P]),

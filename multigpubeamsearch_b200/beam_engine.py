@@ -392,6 +392,9 @@ class BeamEngine:
             _lib.check(self.lib.mgbs_engine_profile_read(self._h, ms), "step_timing")
             out.update({"expand_ms": ms[0], "scorer_ms": ms[1], "exchange_ms": ms[2], "bands_ms": ms[3],
                         "final_ms": ms[4]})
+            tr = (C.c_float * 96)()
+            n = self.lib.mgbs_engine_trace_read(self._h, tr, 96)
+            out["trace_ms"] = [round(float(tr[i]), 4) for i in range(n)]
         return out
 
     # -- search ---------------------------------------------------------------------------------

@@ -78,6 +78,8 @@ struct MgbsEngine {
   bool peers_ready = false;
   bool profile = false;
   cudaEvent_t ev[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t tev[96] = {nullptr};  // per-launch trace (profile mode)
+  int trace_n = 0;
 };
 
 #define MGBS_TRY(expr)            \
@@ -185,6 +187,8 @@ int mgbs_engine_destroy(MgbsEngine* e) {
   if (e->comm && g_nccl.ok) g_nccl.CommDestroy(e->comm);
   for (int i = 0; i < 6; ++i)
     if (e->ev[i]) cudaEventDestroy(e->ev[i]);
+  for (int i = 0; i < 96; ++i)
+    if (e->tev[i]) cudaEventDestroy(e->tev[i]);
   for (int r = 0; r < MGBS_MAX_WORLD; ++r)
     if (e->peer_opened[r]) cudaIpcCloseMemHandle(e->peer_opened[r]);
   delete e;
@@ -274,6 +278,9 @@ int mgbs_engine_profile(MgbsEngine* e, int32_t on) {
   if (on)
     for (int i = 0; i < 6; ++i)
       if (!e->ev[i]) MGBS_TRY(cudaEventCreate(&e->ev[i]));
+  if (on)
+    for (int i = 0; i < 96; ++i)
+      if (!e->tev[i]) MGBS_TRY(cudaEventCreate(&e->tev[i]));
   e->profile = on != 0;
   for (int p = 0; p < 2; ++p)
     if (e->graph[p]) { cudaGraphExecDestroy(e->graph[p]); e->graph[p] = nullptr; }
@@ -285,6 +292,17 @@ int mgbs_engine_profile_read(MgbsEngine* e, float* ms5) {
   MGBS_TRY(cudaEventSynchronize(e->ev[5]));
   for (int i = 0; i < 5; ++i) MGBS_TRY(cudaEventElapsedTime(&ms5[i], e->ev[i], e->ev[i + 1]));
   return 0;
+}
+
+// Per-launch trace of the last profiled step: ms[i] = time between consecutive trace points (one after every kernel,
+// memset or collective enqueued by mgbs_engine_enqueue_depth, in enqueue order); returns the number of intervals.
+int mgbs_engine_trace_read(MgbsEngine* e, float* ms, int32_t capacity) {
+  if (!e || !ms || e->trace_n < 2) return 0;
+  if (cudaEventSynchronize(e->tev[e->trace_n - 1]) != cudaSuccess) return 0;
+  int n = 0;
+  for (int i = 0; i + 1 < e->trace_n && n < capacity; ++i, ++n)
+    if (cudaEventElapsedTime(&ms[n], e->tev[i], e->tev[i + 1]) != cudaSuccess) return n;
+  return n;
 }
 
 int mgbs_engine_set_score_mode(MgbsEngine* e, int32_t score_mode, int32_t uniform_score) {
@@ -422,7 +440,9 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
   unsigned long long* tie_buf = reinterpret_cast<unsigned long long*>(c.tie_buf);
 
   const bool prof = e->profile && phase == 0;
-  if (prof) cudaEventRecord(e->ev[0], st);
+  if (prof) { cudaEventRecord(e->ev[0], st); e->trace_n = 0; }
+#define MGBS_TRACE() do { if (prof && e->trace_n < 96) cudaEventRecord(e->tev[e->trace_n++], st); } while (0)
+  MGBS_TRACE();
   if (phase == 0 || phase == 1) {
     MGBS_TRY(launch_depth_begin(c.ctrl, parity, c.fanout, c.cand_cap, tie_buf + (int64_t)c.rank * kTieSegWords,
                                 W > 1 ? c.send_counts : nullptr, W, st));
@@ -439,7 +459,9 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     x.children = c.children;
     x.cand_hash = c.cand_hash; x.cand_fp = c.cand_fp; x.cand_score = c.cand_score; x.cand_payload = c.cand_payload;
     x.ctrl = c.ctrl;
+    MGBS_TRACE();  // depth_begin + clears
     MGBS_TRY(launch_expand(x, c.frontier_cap, e->sms, st));
+    MGBS_TRACE();  // expand
     if (prof) cudaEventRecord(e->ev[1], st);
     if (phase == 0 && c.score_mode == MGBS_SCORE_EXTERNAL) {
       if (!e->scorer) return MGBS_ERR_STATE;
@@ -448,6 +470,7 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     if (phase == 1) return 0;
   }
   if (prof) cudaEventRecord(e->ev[2], st);
+  MGBS_TRACE();  // scorer
 
   StepArgs a;
   memset(&a, 0, sizeof(a));
@@ -511,6 +534,7 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     items = c.bucket_cap;  // per bucket; kernels loop over buckets
   }
   if (prof) cudaEventRecord(e->ev[3], st);
+  MGBS_TRACE();  // route + exchange
   a.ctrl = c.ctrl;
   a.table = c.table;
   a.tie_buf = tie_buf;
@@ -542,10 +566,12 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
       a.hist_prev = l > 0 ? c.hist + (int64_t)(r * Lb + l - 1) * MGBS_HIST_STRIDE : nullptr;
       MGBS_TRY(launch_band_hist(a, items, e->sms, st));
       MGBS_TRY(allreduce_hist(e, a.hist, st));
+      MGBS_TRACE();  // band histogram (+ reduction)
     }
     a.hist = nullptr;
     a.hist_prev = c.hist + (int64_t)(r * Lb + Lb - 1) * MGBS_HIST_STRIDE;
     MGBS_TRY(launch_band_insert(a, items, e->sms, st));
+    MGBS_TRACE();  // band insert
   }
   if (prof) cudaEventRecord(e->ev[4], st);
   // final cut over the table
@@ -559,14 +585,18 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     a.hist_prev = l > 0 ? fin + (int64_t)(l - 1) * MGBS_HIST_STRIDE : nullptr;
     MGBS_TRY(launch_final_hist(a, c.hash_capacity, e->sms, st));
     MGBS_TRY(allreduce_hist(e, a.hist, st));
+    MGBS_TRACE();  // final histogram (+ reduction)
   }
   a.hist = nullptr;
   a.hist_prev = fin + (int64_t)(Lf - 1) * MGBS_HIST_STRIDE;
   MGBS_TRY(launch_emit(a, items, e->sms, st));
+  MGBS_TRACE();  // emit
   if (W > 1) {
     MGBS_NCCL(g_nccl.AllGather(tie_buf + (int64_t)c.rank * kTieSegWords, tie_buf, kTieSegWords, ncclUint64, e->comm, st));
   }
   MGBS_TRY(launch_finish(a, st));
+  MGBS_TRACE();  // tie all-gather + finish
+#undef MGBS_TRACE
   if (prof) cudaEventRecord(e->ev[5], st);
   return 0;
 }

@@ -380,32 +380,57 @@ __device__ void peer_allreduce_hist(const StepArgs& a) {
   const uint32_t epoch = a.ctrl->epoch;
   const int W = a.world;
   const int64_t slot_words = (int64_t)a.peer.slot * W * MGBS_HIST_STRIDE;
+  // every thread keeps its words of the local histogram in registers (independent loads, issued together) and
+  // stores them to all peers: stores do not stall, so the push costs one load latency instead of one per word
+  constexpr int PER = (MGBS_HIST_STRIDE + kStreamThreads - 1) / kStreamThreads;
+  uint32_t mine_v[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = threadIdx.x + j * kStreamThreads;
+    mine_v[j] = i < MGBS_HIST_STRIDE ? __ldcg(a.hist + i) : 0u;
+  }
   for (int r = 0; r < W; ++r) {
     uint32_t* dst = reinterpret_cast<uint32_t*>(a.peer.base[r] + a.peer.off_hx) + slot_words + (int64_t)a.rank * MGBS_HIST_STRIDE;
-    for (int i = threadIdx.x; i < MGBS_HIST_STRIDE; i += blockDim.x) dst[i] = __ldcg(a.hist + i);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = threadIdx.x + j * kStreamThreads;
+      if (i < MGBS_HIST_STRIDE) dst[i] = mine_v[j];
+    }
   }
   __threadfence_system();
   __syncthreads();
   if ((int)threadIdx.x < W) {
-    volatile uint32_t* f = reinterpret_cast<volatile uint32_t*>(a.peer.base[threadIdx.x] + a.peer.off_hflag) +
+    const int r = threadIdx.x;
+    volatile uint32_t* f = reinterpret_cast<volatile uint32_t*>(a.peer.base[r] + a.peer.off_hflag) +
                            (int64_t)a.peer.slot * W + a.rank;
     *f = epoch;
     volatile uint32_t* mine = reinterpret_cast<volatile uint32_t*>(a.peer.base[a.rank] + a.peer.off_hflag) +
-                              (int64_t)a.peer.slot * W + threadIdx.x;
+                              (int64_t)a.peer.slot * W + r;
     bool ok = false;
     for (uint32_t it = 0; it < (1u << 22); ++it) {
       if ((int32_t)(*mine - epoch) >= 0) { ok = true; break; }
-      if (it > 256) __nanosleep(200);
+      if (it > 1024) __nanosleep(100);
     }
     if (!ok) atomicOr(&a.ctrl->status, MGBS_ST_PEER_TIMEOUT);
   }
   __threadfence_system();
   __syncthreads();
-  const volatile uint32_t* src = reinterpret_cast<const volatile uint32_t*>(a.peer.base[a.rank] + a.peer.off_hx) + slot_words;
-  for (int i = threadIdx.x; i < MGBS_HIST_STRIDE; i += blockDim.x) {
-    uint32_t sum = 0;
-    for (int r = 0; r < W; ++r) sum += src[(int64_t)r * MGBS_HIST_STRIDE + i];
-    a.hist[i] = sum;
+  // sum the W contributions that peers stored into this rank's slots (L2 is the point of coherence for them)
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(a.peer.base[a.rank] + a.peer.off_hx) + slot_words;
+  uint32_t sum[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) sum[j] = 0u;
+  for (int r = 0; r < W; ++r) {
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = threadIdx.x + j * kStreamThreads;
+      if (i < MGBS_HIST_STRIDE) sum[j] += __ldcg(src + (int64_t)r * MGBS_HIST_STRIDE + i);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = threadIdx.x + j * kStreamThreads;
+    if (i < MGBS_HIST_STRIDE) a.hist[i] = sum[j];
   }
 }
 
