@@ -294,7 +294,10 @@ class BeamEngine:
         while another rank still has it mapped."""
         h = getattr(self, "_h", None)
         if h:
-            torch.cuda.synchronize()
+            try:
+                torch.cuda.synchronize()
+            except Exception:  # interpreter shutdown: torch may already be torn down
+                pass
             self.lib.mgbs_engine_destroy(h)
             self._h = None
 
