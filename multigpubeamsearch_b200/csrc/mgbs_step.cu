@@ -32,7 +32,7 @@ namespace mgbs {
 
 
 template <int WORDS>
-__global__ void __launch_bounds__(kExpandThreads) k_expand(ExpandArgs a) {
+__global__ void __launch_bounds__(kExpandThreads, 3) k_expand(ExpandArgs a) {
   constexpr int PITCH_W = WORDS + 1;
   __shared__ uint32_t par_s[kExpandTile * PITCH_W];
   __shared__ uint32_t gen_s[MGBS_MAX_FANOUT * WORDS];
@@ -71,38 +71,41 @@ __global__ void __launch_bounds__(kExpandThreads) k_expand(ExpandArgs a) {
       const uint8_t* row = reinterpret_cast<const uint8_t*>(par_s + pl * PITCH_W);
       uint64_t h = kFnvOffset, f = kGolden;
       int ham = 0;
-      uint32_t cw[WORDS];
+      const int64_t c = p * G + g;
+      uint4* child_dst = a.children ? reinterpret_cast<uint4*>(a.children + c * (int64_t)a.stride) : nullptr;
+      // 16 bytes of the child at a time: the four words are stored as soon as they are complete, so that only
+      // four of them are live (the register count decides how many warps hide the shared-memory latency)
 #pragma unroll
-      for (int wi = 0; wi < WORDS; ++wi) {
-        const uint32_t gi = gen_s[g * WORDS + wi];
-        const uint32_t sv = sol_s[wi];
-        uint32_t acc = 0;
+      for (int q = 0; q < WORDS / 4; ++q) {
+        uint32_t cw[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (wi * 4 + j < n) {
-            const uint32_t v = row[(gi >> (8 * j)) & 0xffu];
-            h = (h ^ (uint64_t)v) * kFnvPrime;
-            f ^= (uint64_t)v + kGolden + (f << 6) + (f >> 2);
-            ham += (v != ((sv >> (8 * j)) & 0xffu));
-            acc |= v << (8 * j);
+        for (int w4 = 0; w4 < 4; ++w4) {
+          const int wi = q * 4 + w4;
+          const uint32_t gi = gen_s[g * WORDS + wi];
+          const uint32_t sv = sol_s[wi];
+          uint32_t acc = 0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (wi * 4 + j < n) {
+              const uint32_t v = row[(gi >> (8 * j)) & 0xffu];
+              h = (h ^ (uint64_t)v) * kFnvPrime;
+              f ^= (uint64_t)v + kGolden + (f << 6) + (f >> 2);
+              ham += (v != ((sv >> (8 * j)) & 0xffu));
+              acc |= v << (8 * j);
+            }
           }
+          cw[w4] = acc;
         }
-        cw[wi] = acc;
+        if (child_dst) child_dst[q] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
       }
       h = finish_hash(h);
       f = finish_fingerprint(f);
-      const int64_t c = p * G + g;
       const uint32_t payload = pack_payload((uint32_t)p, (uint32_t)a.rank, (uint32_t)g);
       a.cand_hash[c] = h;
       a.cand_fp[c] = f;
       a.cand_payload[c] = payload;
       if (a.score_mode == MGBS_SCORE_HAMMING) a.cand_score[c] = (uint32_t)ham;
       else if (a.score_mode == MGBS_SCORE_UNIFORM) a.cand_score[c] = (uint32_t)a.uniform_score;
-      if (a.children) {
-        uint4* dst = reinterpret_cast<uint4*>(a.children + c * (int64_t)a.stride);
-#pragma unroll
-        for (int q = 0; q < WORDS / 4; ++q) dst[q] = make_uint4(cw[4 * q], cw[4 * q + 1], cw[4 * q + 2], cw[4 * q + 3]);
-      }
       if (ham == 0 && a.ctrl) atomicMin(&a.ctrl->found_payload, payload);
     }
   }

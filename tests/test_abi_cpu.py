@@ -1,0 +1,83 @@
+"""CPU checks of the C ABI: the library loads, exports every symbol the header declares, and its host-only helpers
+(size derivation, structure sizes, host hash) agree with the oracle and the reference's formulas.  No compute calls."""
+
+import ctypes as C
+import re
+from pathlib import Path
+
+import numpy as np
+
+from oracle import beam_oracle as bo
+from multigpubeamsearch_b200 import _lib, scorers, beam_engine as be
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def declared_functions():
+    text = (ROOT / "include" / "mgbs.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mgbs_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = declared_functions()
+    assert len(names) >= 30
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_structure_sizes_match_ctypes_mirrors():
+    lib = _lib.load()
+    assert lib.mgbs_sizeof_ctrl() == C.sizeof(_lib.MgbsCtrl)
+    assert lib.mgbs_sizeof_config() == C.sizeof(_lib.MgbsConfig)
+    lib.mgbs_sizeof_mlp_config.restype = C.c_int
+    lib.mgbs_sizeof_tf_config.restype = C.c_int
+    assert lib.mgbs_sizeof_mlp_config() == C.sizeof(scorers.MgbsMlpConfig)
+    assert lib.mgbs_sizeof_tf_config() == C.sizeof(scorers.MgbsTfConfig)
+
+
+def test_derive_sizes_follow_reference_formulas():
+    # EngineConfig::derive (beam_engine.cpp:244-252): n_local = ceil(B/W), k_keep = round(gamma n_local),
+    # k_work = round(beta k_keep), hash_capacity = max(1024, round(k_work / load))
+    ext = be._Ext(_lib.load())
+    cfg = be.make_default_config()
+    cfg.update(global_beam_width=65536, world_size=2, gamma=1.05, beta=1.2, hash_load_factor=0.45, fanout=12,
+               state_size_bytes=64, max_depth=10, band_rounds=3, band_levels=3)
+    s = ext.derive_sizes(cfg)
+    assert s["n_local"] == 32768 and s["k_keep"] == 34406 and s["k_work"] == 41287
+    assert s["hash_capacity"] == round(41287 / 0.45)
+    assert s["cand_cap"] == 41287 * 12 and s["bucket_cap_per_peer"] > s["cand_cap"] // 2
+    cfg.update(global_beam_width=100, world_size=1)
+    assert ext.derive_sizes(cfg)["hash_capacity"] == 1024
+    lib = _lib.load()
+    out = (C.c_int64 * 6)()
+    assert lib.mgbs_derive_sizes(0, 1, 1.05, 1.2, 0.45, 3, 3, out) == -1        # bad beam
+    assert lib.mgbs_derive_sizes(100, 1, 1.05, 1.2, 1.5, 3, 3, out) == -1      # bad load factor
+    assert lib.mgbs_derive_sizes(100, 99, 1.05, 1.2, 0.45, 3, 3, out) == -1    # too many ranks
+
+
+def test_host_hash_matches_oracle():
+    lib = _lib.load()
+    rng = np.random.default_rng(3)
+    for n in (16, 54, 96, 120):
+        s = np.ascontiguousarray(rng.integers(0, 8, size=(5, n), dtype=np.uint8))
+        want_h, want_f = bo.hash64(s), bo.fingerprint64(s)
+        for i in range(5):
+            row = np.ascontiguousarray(s[i])
+            assert lib.mgbs_hash64_host(row.ctypes.data_as(C.c_void_p), n) == int(want_h[i])
+            assert lib.mgbs_fingerprint64_host(row.ctypes.data_as(C.c_void_p), n) == int(want_f[i])
+
+
+def test_engine_create_rejects_bad_configs_without_a_gpu():
+    lib = _lib.load()
+    c = _lib.MgbsConfig()
+    h = C.c_void_p()
+    assert lib.mgbs_engine_create(C.byref(c), C.byref(h)) == -1  # empty config
+    c.state_len, c.state_stride, c.fanout, c.world_size = 54, 48, 12, 1
+    assert lib.mgbs_engine_create(C.byref(c), C.byref(h)) == -1  # stride smaller than the state
+    nb, nt = C.c_int64(0), C.c_int64(0)
+    c.state_stride, c.world_size, c.bucket_cap, c.band_rounds, c.band_levels, c.hash_bits = 64, 4, 1000, 3, 3, 44
+    assert lib.mgbs_sym_bytes(C.byref(c), C.byref(nb), C.byref(nt)) == 0
+    # two parities of (hash, fp, score, payload, rows) buckets + counts + flags + histogram slots
+    assert nb.value > 2 * 4 * 1000 * (8 + 8 + 4 + 4 + 64) and nt.value == 3 * 3 + 6 + 1

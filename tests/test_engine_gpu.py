@@ -251,3 +251,17 @@ def test_frontier_into_pinned_buffer():
     assert n == want.shape[0] and np.array_equal(out.numpy()[:n], want)
     small = np.zeros((10, pz.state_len), np.uint8)
     assert engine.frontier_into(small) == 10 and np.array_equal(small, want[:10])
+
+
+def test_maximum_shape_state128_fanout32():
+    # largest supported shape: 128-byte states, 32 generators
+    rng = np.random.default_rng(77)
+    n, g = 128, 32
+    base = [rng.permutation(n) for _ in range(g // 2)]
+    gens = np.stack(base + [np.argsort(b) for b in base]).astype(np.uint8)
+    solved = (np.arange(n) // 16).astype(np.uint8)
+    pz = puzzles.Puzzle("max128", n, 8, gens, solved, scramble_seed=9000)
+    engine = make_engine(pz, global_beam_width=3000)
+    frontier = np.unique(np.stack([pz.scramble(j, 9) for j in range(200)]), axis=0)
+    for graph in (False, True):
+        check_step(engine, pz, frontier, 3000, graph=graph)
