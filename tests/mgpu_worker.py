@@ -103,8 +103,17 @@ def main():
     res = be.run_one_search(engine, start, 12)
     want = bo.search(start, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam=4096, max_depth=12)
     assert res["found"] == want.found and res["depth"] == want.depth, (res["found"], res["depth"], want.found, want.depth)
+    # the solver loop (prepass + cross-rank path walk-back): every found path must replay to the solved state
+    from multigpubeamsearch_b200 import solver
+    starts = [pz.scramble(j, 6) for j in range(20, 24)]
+    summary = solver.solve_many(engine, pz, starts, 10)
+    for s, r in zip(starts, summary["results"]):
+        w = bo.search(s, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam=4096, max_depth=10)
+        assert (r["found"], r["depth"]) == (w.found, w.depth), (r, w.found, w.depth)
+        assert (not w.found) or (r["valid"] and len(r["path"]) == w.depth), r
+    assert summary["status_bits"] == 0
     if rank == 0:
-        print(f"SEARCH_OK found={res['found']} depth={res['depth']}", flush=True)
+        print(f"SEARCH_OK found={res['found']} depth={res['depth']} solved={summary['solved']}", flush=True)
     engine.close()
     dist.barrier()
     dist.destroy_process_group()

@@ -265,3 +265,26 @@ def test_maximum_shape_state128_fanout32():
     frontier = np.unique(np.stack([pz.scramble(j, 9) for j in range(200)]), axis=0)
     for graph in (False, True):
         check_step(engine, pz, frontier, 3000, graph=graph)
+
+
+def test_solver_loop_with_prepass_matches_oracle(tmp_path):
+    # the per-sample driver: uniform-fill prepass, scored steps, depth log, path validation
+    from multigpubeamsearch_b200 import solver
+    pz = puzzles.lrx(16)
+    engine = make_engine(pz, global_beam_width=1024, max_depth=40)
+    starts = [pz.scramble(j, 30) for j in range(8, 14)]
+    log = tmp_path / "run.jsonl"
+    summary = solver.solve_many(engine, pz, starts, 40, log_path=str(log))
+    assert summary["status_bits"] == 0 and summary["invalid_paths"] == 0
+    for s, r in zip(starts, summary["results"]):
+        want = bo.search(s, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam=1024, max_depth=40)
+        assert (r["found"], r["depth"]) == (want.found, want.depth)
+        assert r["depths_prepass"] >= 5  # 3^d * 3 <= 1024 for the first depths
+        if want.found:
+            assert r["valid"] and len(r["path"]) == want.depth
+    rows = [__import__("json").loads(x) for x in log.read_text().splitlines()]
+    assert sum(1 for x in rows if x["tag"] == "SAMPLE_RESULT") == len(starts)
+    assert any(x["tag"] == "DEPTH_TUNING" and x["prepass"] for x in rows)
+    # same answers without the prepass
+    r2 = solver.solve_one(engine, pz, starts[0], 40, prepass=False)
+    assert (r2["found"], r2["depth"]) == (summary["results"][0]["found"], summary["results"][0]["depth"])
