@@ -210,7 +210,7 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
 // ring.  The epilogue packs the activated tile to bf16 in a swizzled staging box and writes it with TMA stores
 // (full 128-byte rows instead of per-thread row segments).
 //
-// Warps: 0 = TMA (W1), 1 = MMA + TMEM owner, 2..5 = epilogue, 6..13 = one-hot producers (two per A stage).
+// Warps: 0 = TMA (W1), 1 = MMA + TMEM owner, then EW epilogue warps, then 12 - EW one-hot producer warps.
 // ------------------------------------------------------------------------------------------------
 
 constexpr int L1_THREADS = 448;
@@ -235,7 +235,10 @@ struct L1Args {
   int* err;
 };
 
-template <int F8>
+// EW = epilogue warps (4 or 8); the other 12 - EW warps of the 14 build the one-hot operand.  With the resident
+// tile (K <= 384) production is light and the epilogue is the bottleneck: EW = 8 (two warps per TMEM lane quadrant,
+// each taking every other 32-column group of a box).  With the ring (K > 384) production dominates: EW = 4.
+template <int F8, int EW>
 __global__ void __launch_bounds__(L1_THREADS, 1)
 k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmOut, L1Args g) {
   extern __shared__ uint8_t smem_raw[];
@@ -270,9 +273,9 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
   const int blocks_per_tile = resident ? k_blocks : n_chunks * k_blocks;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < L1_A_STAGES; ++s) { mbar_init(a_full(s), 2); mbar_init(a_empty(s), 1); }
+    for (int s = 0; s < L1_A_STAGES; ++s) { mbar_init(a_full(s), (12 - EW) / 4); mbar_init(a_empty(s), 1); }
     for (int s = 0; s < L1_B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), EW); }
     mbar_init(drain_bar, 1);
     for (int kb = 0; kb < k_blocks && kb < L1_MAX_KBLOCKS; ++kb) p_lo_tab[kb] = (kb * BKE) / g.V;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -338,10 +341,11 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
       tc_commit(drain_bar);
       mbar_wait(drain_bar, 0, g.err, ERR_WAIT_DRAIN);
     }
-  } else if (warp < 6) {
+  } else if (warp < 2 + EW) {
     // ---- epilogue: TMEM -> bias, ReLU, bf16 -> swizzled staging box -> TMA store ----
     const int quad = warp & 3;
-    const int et = (warp - 2) * 32 + lane;            // 0..127 among epilogue threads
+    const int sg = (warp - 2) >> 2;                   // sub-group: which 32-column groups of a box this warp takes
+    const int et = (warp - 2) * 32 + lane;            // index among the epilogue threads
     const uint32_t r = (uint32_t)(quad * 32 + lane);  // tile row owned by this thread
     uint32_t acc_it = 0, box_it = 0;
     bool ok = true;
@@ -357,9 +361,9 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
           uint8_t* box = staging;
           // the TMA store that last read the box must be done before it is overwritten
           if (et == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          asm volatile("bar.sync 1, 128;" ::: "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");
 #pragma unroll
-          for (int sub = 0; sub < BKE / 32; ++sub) {
+          for (int sub = sg; sub < BKE / 32; sub += EW / 4) {
             uint32_t v[32];
             tc_ld32(taddr + gcol + sub * 32, v);
             tc_wait_ld();
@@ -400,7 +404,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
             }
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          asm volatile("bar.sync 1, 128;" ::: "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");
           if (et == 0) {
             tma_store_2d(&tmOut, smem_u32(box), nc * BN + gcol, row0);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -414,15 +418,18 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
     if (et == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else {
     // ---- one-hot producers: warp pw owns A stage pw and builds K-blocks pw, pw+4, pw+8, ... of the sequence ----
-    const int pw = (warp - 6) >> 1;        // producer pair of this warp
-    const int half = (warp - 6) & 1;       // rows half*64 .. half*64+63 of the block
-    const int pt = (warp - 6) * 32 + lane;  // 0..255; threads 0..127 load the child tile
+    constexpr int PROD_W = 12 - EW;          // producer warps
+    constexpr int WPG = PROD_W / 4;          // warps per producer group (one group works on one K-block)
+    constexpr int ROWS_W = BM / WPG;         // tile rows per warp
+    const int pw = (warp - 2 - EW) / WPG;    // producer group of this warp
+    const int half = (warp - 2 - EW) % WPG;  // rows half*ROWS_W .. of the block
+    const int pt = (warp - 2 - EW) * 32 + lane;  // threads 0..127 load the child tile
     const int V = g.V, n = g.n;
     uint32_t it_base = 0;           // index of this tile's first K-block in the CTA's K-block sequence
     bool ok = true;
     for (int mt = blockIdx.x; mt < num_mtiles; mt += gridDim.x, it_base += (uint32_t)blocks_per_tile) {
       // all producer warps have finished reading the previous tile's child rows
-      asm volatile("bar.sync 2, 256;" ::: "memory");
+      asm volatile("bar.sync 2, %0;" ::"n"(PROD_W * 32) : "memory");
       if (pt < BM) {
         const int64_t row = (int64_t)mt * BM + pt;
         uint32_t* dst = reinterpret_cast<uint32_t*>(child_s + pt * L1_CHILD_PITCH);
@@ -436,7 +443,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
           for (int q = 0; q < (g.stride >> 2); ++q) dst[q] = 0u;
         }
       }
-      asm volatile("bar.sync 2, 256;" ::: "memory");
+      asm volatile("bar.sync 2, %0;" ::"n"(PROD_W * 32) : "memory");
       if (!ok) continue;
       // first K-block of this tile that belongs to this warp
       const uint32_t first = (uint32_t)((pw - (int)(it_base & 3u)) & 3);
@@ -447,9 +454,9 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         uint8_t* a_stage = a_ring + slot * A_BYTES;
         if (!mbar_wait(a_empty(slot), ((it / L1_A_STAGES) & 1u) ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
         // zero this warp's 64 rows (8 KB, contiguous): consecutive lanes write consecutive 16-byte chunks
-        uint4* a4 = reinterpret_cast<uint4*>(a_stage + half * (A_BYTES / 2));
+        uint4* a4 = reinterpret_cast<uint4*>(a_stage + half * (A_BYTES / WPG));
 #pragma unroll 8
-        for (int q = 0; q < A_BYTES / 2 / 16 / 32; ++q) a4[q * 32 + lane] = make_uint4(0u, 0u, 0u, 0u);
+        for (int q = 0; q < A_BYTES / WPG / 16 / 32; ++q) a4[q * 32 + lane] = make_uint4(0u, 0u, 0u, 0u);
         __syncwarp();
         // ones: column pos*V + value inside [kb*64, kb*64+64); rows half*64 + lane and + 32
         const int c_lo = kb * BKE;
@@ -460,8 +467,8 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         for (int pos = p_lo; pos <= p_hi; ++pos) {
           const int cbase = pos * V - c_lo;
 #pragma unroll
-          for (int rr = 0; rr < 2; ++rr) {
-            const uint32_t row = (uint32_t)(half * 64 + lane + 32 * rr);
+          for (int rr = 0; rr < ROWS_W / 32; ++rr) {
+            const uint32_t row = (uint32_t)(half * ROWS_W + lane + 32 * rr);
             const int col = cbase + (int)child_s[row * L1_CHILD_PITCH + pos];
             if (col >= 0 && col < BKE) {
               if (F8) a_stage[swz128(row, (uint32_t)col)] = 0x38;  // e4m3 1.0
@@ -586,9 +593,10 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
   if (f8) m->fused_l1 = true;
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
-  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1<0, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
-  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
   if (rc) { delete m; return rc; }
   *out = m;
   return 0;
@@ -676,8 +684,13 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
       l.col_scale = c.s1[i];
       l.out_inv_scale = c.act_inv_scale;
       l.err = c.err;
-      if (c.dtype == 1) k_mlp_l1<1><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
-      else k_mlp_l1<0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
+      const bool resident = m->k1_pad / (c.dtype == 1 ? BK8 : BK) <= L1_A_STAGES;
+      if (c.dtype == 1 && resident) k_mlp_l1<1, 8><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
+      else if (c.dtype == 1) k_mlp_l1<1, 4><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
+      // bf16 builds six K-blocks per tile: eight producer warps are needed even with the resident tile (measured:
+      // 0.69-0.76 ms with 4 epilogue + 8 producer warps against 0.82 ms with 8 + 4 on the 786 432-row case);
+      // e4m3 builds three and gains from the wider epilogue
+      else k_mlp_l1<0, 4><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
     } else {
       k_mlp_gemm<0, 0><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_x, m->tm_w1[i], g);
     }
