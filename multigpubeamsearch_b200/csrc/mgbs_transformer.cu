@@ -39,16 +39,39 @@ struct TfGemmArgs {
   int64_t row_limit;          // rows of one micro-batch at most
   int32_t n_total, k_total;   // multiples of BN / BK
   const float* bias;          // [n_total]
-  float* resid;               // TF_EPI_RESID: [rows, n_total] f32, updated in place (micro-batch local rows)
+  const float* col_scale;     // e4m3 operands: [n_total] = activation scale * weight-row scale
+  float out_inv_scale;        // e4m3 output (TF_EPI_STORE_GELU with e4m3 operands): stored value = x * out_inv_scale
   int* err;
 };
 
-__device__ __forceinline__ float gelu_erf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+// x * Phi(x) with erf from the rational-exponential approximation of Abramowitz & Stegun 7.1.26 (absolute error
+// below 1.5e-7 plus ~1e-6 from the approximate reciprocal and exponential: far under half a unit in the last
+// place of the bf16 and e4m3 values this feeds).  A dozen instructions, two of them on the special-function unit;
+// it matters because the feed-forward epilogue evaluates it once per output element.
+__device__ __forceinline__ float gelu_erf(float x) {
+  const float z = fabsf(x) * 0.70710678118654752f;
+  float t, e;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(fmaf(0.3275911f, z, 1.f)));
+  float p = fmaf(1.061405429f, t, -1.453152027f);
+  p = fmaf(p, t, 1.421413741f);
+  p = fmaf(p, t, -0.284496736f);
+  p = fmaf(p, t, 0.254829592f);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * z * z));
+  const float erf_abs = fmaf(-p * t, e, 1.f);          // erf(|x| / sqrt 2)
+  return 0.5f * x + 0.5f * fabsf(x) * erf_abs;         // x/2 (1 + sign(x) erf(|x|/sqrt 2))
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
 
 // C = A * W^T (+ bias) with A [rows, K] and W [N, K] bf16, K-major, both by TMA.
 // TF_EPI_STORE / _GELU: bf16 output through a swizzled staging box and TMA stores (tmOut: [rows, N] bf16).
-// TF_EPI_RESID: resid[row, n] += acc + bias[n] in float32 (each thread owns one row; 128-byte runs per access).
-template <int EPI>
+// TF_EPI_RESID: resid[row, n] += acc + bias[n] in float32 through TMA reduce-add (tmOut: [rows, N] float32).
+// F8 = 1: both operands e4m3 (kind::f8f6f4, 128-element K-blocks), accumulators multiplied by col_scale; the GELU
+// variant then also writes e4m3 (one 128-column box per epilogue half), the plain store variant still writes bf16.
+template <int EPI, int F8>
 __global__ void __launch_bounds__(TF_THREADS, 1)
 k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
           const __grid_constant__ CUtensorMap tmOut, TfGemmArgs g) {
@@ -71,7 +94,8 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   if (rows < 0) rows = 0;
   const int num_mtiles = (int)((rows + BM - 1) / BM);
   const int n_chunks = g.n_total / BN;
-  const int k_blocks = g.k_total / BK;
+  constexpr int BKE = F8 ? BK8 : BK;
+  const int k_blocks = g.k_total / BKE;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TF_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -100,8 +124,8 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             if (!mbar_wait(empty_bar(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
             const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
             mbar_expect_tx(full_bar(stage), STAGE_BYTES);
-            tma_load_2d(sa, &tmA, kb * BK, mt * BM, full_bar(stage));
-            tma_load_2d(sa + A_BYTES, &tmB, kb * BK, nc * BN, full_bar(stage));
+            tma_load_2d(sa, &tmA, kb * BKE, mt * BM, full_bar(stage));
+            tma_load_2d(sa + A_BYTES, &tmB, kb * BKE, nc * BN, full_bar(stage));
             if (++stage == TF_STAGES) { stage = 0; phase ^= 1u; }
           }
         }
@@ -126,7 +150,7 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
             const uint64_t bdesc = make_desc_sw128(sa + A_BYTES);
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k)
-              tc_mma<0>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
+              tc_mma<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
             tc_commit(empty_bar(stage));
             if (++stage == TF_STAGES) { stage = 0; phase ^= 1u; }
           }
@@ -153,50 +177,91 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * BN;
         if (EPI == TF_EPI_RESID) {
+          // acc * scale + bias goes to a swizzled float32 box (128 rows x 32 columns) and from there into the
+          // residual stream by a TMA reduce-add: the read-modify-write happens in the memory system, in whole
+          // 128-byte rows, instead of as 16-byte accesses to 32 different rows per warp instruction
 #pragma unroll 1
-          for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
+          for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32, ++box_it) {
+            uint8_t* box = staging + (half * 2 + (box_it & 1u)) * A_BYTES;
+            if (et == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
             uint32_t v[32];
             tc_ld32(taddr + c0, v);
             tc_wait_ld();
-            if (row_ok) {
-              const int n0 = nc * BN + c0;
-              float4* p = reinterpret_cast<float4*>(g.resid + row * g.n_total + n0);
+            const int n0 = nc * BN + c0;
 #pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                float4 x = p[q];
-                x.x += __uint_as_float(v[4 * q]) + __ldg(g.bias + n0 + 4 * q);
-                x.y += __uint_as_float(v[4 * q + 1]) + __ldg(g.bias + n0 + 4 * q + 1);
-                x.z += __uint_as_float(v[4 * q + 2]) + __ldg(g.bias + n0 + 4 * q + 2);
-                x.w += __uint_as_float(v[4 * q + 3]) + __ldg(g.bias + n0 + 4 * q + 3);
-                p[q] = x;
-              }
+            for (int q = 0; q < 8; ++q) {
+              const float4 bq = __ldg(reinterpret_cast<const float4*>(g.bias + n0) + q);
+              float4 cq = make_float4(1.f, 1.f, 1.f, 1.f);
+              if (F8) cq = __ldg(reinterpret_cast<const float4*>(g.col_scale + n0) + q);
+              float4 x;
+              x.x = row_ok ? fmaf(__uint_as_float(v[4 * q]), cq.x, bq.x) : 0.f;
+              x.y = row_ok ? fmaf(__uint_as_float(v[4 * q + 1]), cq.y, bq.y) : 0.f;
+              x.z = row_ok ? fmaf(__uint_as_float(v[4 * q + 2]), cq.z, bq.z) : 0.f;
+              x.w = row_ok ? fmaf(__uint_as_float(v[4 * q + 3]), cq.w, bq.w) : 0.f;
+              *reinterpret_cast<float4*>(box + swz128(r, (uint32_t)(q * 16))) = x;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+            if (et == 0) {
+              tma_reduce_add_2d(&tmOut, smem_u32(box), n0, row0);
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
           }
         } else {
+          constexpr bool OUT8 = F8 && EPI == TF_EPI_STORE_GELU;   // e4m3 output
+          constexpr int BOXC = OUT8 ? 128 : 64;                   // columns per 128-byte box row
 #pragma unroll 1
-          for (int gcol = half * (BN / 2); gcol < (half + 1) * (BN / 2); gcol += 64, ++box_it) {
+          for (int gcol = half * (BN / 2); gcol < (half + 1) * (BN / 2); gcol += BOXC, ++box_it) {
             uint8_t* box = staging + (half * 2 + (box_it & 1u)) * A_BYTES;
             if (et == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
+            for (int sub = 0; sub < BOXC / 32; ++sub) {
               uint32_t v[32];
-              tc_ld32(taddr + gcol + half * 32, v);
+              tc_ld32(taddr + gcol + sub * 32, v);
               tc_wait_ld();
-              const int n0 = nc * BN + gcol + half * 32;
-              uint32_t packed[16];
+              const int n0 = nc * BN + gcol + sub * 32;
+              float x[32];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                float x0 = __uint_as_float(v[2 * j]) + __ldg(g.bias + n0 + 2 * j);
-                float x1 = __uint_as_float(v[2 * j + 1]) + __ldg(g.bias + n0 + 2 * j + 1);
-                if (EPI == TF_EPI_STORE_GELU) { x0 = gelu_erf(x0); x1 = gelu_erf(x1); }
-                __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-                packed[j] = *reinterpret_cast<uint32_t*>(&h);
+              for (int j4 = 0; j4 < 8; ++j4) {
+                const float4 bq = __ldg(reinterpret_cast<const float4*>(g.bias + n0) + j4);
+                float4 cq = make_float4(1.f, 1.f, 1.f, 1.f);
+                if (F8) cq = __ldg(reinterpret_cast<const float4*>(g.col_scale + n0) + j4);
+                x[4 * j4] = fmaf(__uint_as_float(v[4 * j4]), cq.x, bq.x);
+                x[4 * j4 + 1] = fmaf(__uint_as_float(v[4 * j4 + 1]), cq.y, bq.y);
+                x[4 * j4 + 2] = fmaf(__uint_as_float(v[4 * j4 + 2]), cq.z, bq.z);
+                x[4 * j4 + 3] = fmaf(__uint_as_float(v[4 * j4 + 3]), cq.w, bq.w);
               }
+              if (EPI == TF_EPI_STORE_GELU) {
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint32_t off = swz128(r, (uint32_t)(half * 64 + q * 16));
-                *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                for (int j = 0; j < 32; ++j) x[j] = gelu_erf(x[j]);
+              }
+              if (OUT8) {
+                uint32_t packed[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(x[4 * j] * g.out_inv_scale, x[4 * j + 1] * g.out_inv_scale), __NV_SATFINITE, __NV_E4M3);
+                  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(x[4 * j + 2] * g.out_inv_scale, x[4 * j + 3] * g.out_inv_scale), __NV_SATFINITE, __NV_E4M3);
+                  packed[j] = lo | (hi << 16);
+                }
+#pragma unroll
+                for (int q = 0; q < 2; ++q) {
+                  const uint32_t off = swz128(r, (uint32_t)(sub * 32 + q * 16));
+                  *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+              } else {
+                uint32_t packed[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+                  packed[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const uint32_t off = swz128(r, (uint32_t)(sub * 64 + q * 16));
+                  *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
               }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -212,7 +277,7 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         if (lane == 0) mbar_arrive(tempty_bar(b));
       }
     }
-    if (EPI != TF_EPI_RESID && et == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (et == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
@@ -253,10 +318,11 @@ __global__ void __launch_bounds__(256) k_tf_embed(const uint8_t* __restrict__ ch
 }
 
 // y = bf16(LayerNorm(x) * gamma + beta), d = 256: one warp per row, 8 elements per lane.
+template <int OUT8>
 __global__ void __launch_bounds__(256) k_tf_layernorm(const float* __restrict__ x, const uint32_t* count_dev, int tokens,
                                                       int64_t row_offset, int64_t row_limit,
                                                       const float* __restrict__ gamma, const float* __restrict__ beta,
-                                                      __nv_bfloat16* __restrict__ y) {
+                                                      void* __restrict__ y_out, float out_inv_scale) {
   constexpr int D = 256;
   const int64_t rows = tf_rows(count_dev, tokens, row_offset, row_limit);
   const int lane = threadIdx.x & 31;
@@ -277,29 +343,39 @@ __global__ void __launch_bounds__(256) k_tf_layernorm(const float* __restrict__ 
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) q += __shfl_xor_sync(0xffffffffu, q, o);
     const float rstd = rsqrtf(q * (1.f / D) + 1e-5f);
-    uint32_t packed[4];
+    float o[8];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c = lane * 8 + 2 * i;
-      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i] * rstd * __ldg(gamma + c) + __ldg(beta + c),
-                                               v[2 * i + 1] * rstd * __ldg(gamma + c + 1) + __ldg(beta + c + 1));
-      packed[i] = *reinterpret_cast<uint32_t*>(&h);
+    for (int i = 0; i < 8; ++i) o[i] = v[i] * rstd * __ldg(gamma + lane * 8 + i) + __ldg(beta + lane * 8 + i);
+    if (OUT8) {
+      uint32_t w[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(o[4 * i] * out_inv_scale, o[4 * i + 1] * out_inv_scale), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(o[4 * i + 2] * out_inv_scale, o[4 * i + 3] * out_inv_scale), __NV_SATFINITE, __NV_E4M3);
+        w[i] = lo | (hi << 16);
+      }
+      *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(y_out) + r * D + lane * 8) = make_uint2(w[0], w[1]);
+    } else {
+      uint32_t packed[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) packed[i] = pack_bf16(o[2 * i], o[2 * i + 1]);
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(y_out) + r * D + lane * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
-    *reinterpret_cast<uint4*>(y + r * D + lane * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
   }
 }
 
 // Self-attention core of one layer: out[row, h*32:(h+1)*32] = softmax(q k^T / sqrt(32)) v per state and head,
 // on the tensor cores with warp-level mma (m16n8k16, bf16 in, fp32 accumulate).  A warp owns one (state, head):
-// it stages Q and K ([token][32], row pitch 40 bf16) and V transposed ([32][token], row pitch 72 bf16) in shared
-// memory (pitches chosen so that fragment loads are bank-conflict free), then for each block of 16 query rows
-// computes S = Q K^T (8 key blocks), a masked softmax in registers, and O = P V with the probabilities re-packed
-// from accumulator layout into A fragments.  Tokens are padded to 64; padded keys are masked out.
+// it stages Q, K and V ([token][32], row pitch 40 bf16, so that fragment loads and ldmatrix rows hit distinct
+// banks) in shared memory with one batch of 16-byte cp.async copies - every copy of a task is in flight at once,
+// the task pays one global-memory latency - then for each block of 16 query rows computes S = Q K^T (8 key
+// blocks), a masked softmax in registers, and O = P V with the probabilities re-packed from accumulator layout
+// into A fragments and V fragments read transposed by ldmatrix.  Tokens are padded to 64; padded rows are zeroed
+// once per warp and padded keys are masked out.
 constexpr int TF_MAX_T = 64;
-constexpr int TF_ATT_WARPS = 4;
-constexpr int TF_QK_PITCH = 40;   // bf16 per row of Q / K
-constexpr int TF_VT_PITCH = 72;   // bf16 per row of V^T
-constexpr int TF_ATT_WARP_ELEMS = 2 * TF_MAX_T * TF_QK_PITCH + 32 * TF_VT_PITCH;
+constexpr int TF_ATT_WARPS = 7;   // 15 KB of staging per warp: two CTAs of seven warps per SM
+constexpr int TF_QK_PITCH = 40;   // bf16 per row of Q / K / V
+constexpr int TF_ATT_WARP_ELEMS = 3 * TF_MAX_T * TF_QK_PITCH;
 constexpr int TF_ATT_SMEM = TF_ATT_WARPS * TF_ATT_WARP_ELEMS * 2;
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -309,43 +385,47 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-
+template <int OUT8>
 __global__ void __launch_bounds__(TF_ATT_WARPS * 32) k_tf_attention(const __nv_bfloat16* __restrict__ qkv,
                                                                     const uint32_t* count_dev, int tokens,
                                                                     int64_t row_offset, int64_t row_limit,
-                                                                    __nv_bfloat16* __restrict__ out) {
+                                                                    void* __restrict__ out_v, float out_inv_scale) {
   constexpr int D = 256, HD = 32, NH = D / HD;
   extern __shared__ __align__(16) uint8_t att_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tig = lane & 3;
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(att_raw) + (size_t)warp * TF_ATT_WARP_ELEMS;
   __nv_bfloat16* ks = qs + TF_MAX_T * TF_QK_PITCH;
-  __nv_bfloat16* vt = ks + TF_MAX_T * TF_QK_PITCH;
+  __nv_bfloat16* vs = ks + TF_MAX_T * TF_QK_PITCH;
   const int64_t rows = tf_rows(count_dev, tokens, row_offset, row_limit);
   const int64_t units = (rows / tokens) * NH;
   const float scale_log2 = 0.17677669529663687f * 1.4426950408889634f;  // 1/sqrt(32) * log2(e)
+  // rows tokens..63 of the three matrices stay zero for the whole kernel (the copies below never touch them)
+  for (int c = tokens * 4 + lane; c < TF_MAX_T * 4; c += 32) {
+    const int t = c >> 2, part = c & 3;
+#pragma unroll
+    for (int m = 0; m < 3; ++m)
+      *reinterpret_cast<uint4*>(qs + m * TF_MAX_T * TF_QK_PITCH + t * TF_QK_PITCH + part * 8) = make_uint4(0u, 0u, 0u, 0u);
+  }
+  const uint32_t qs_u32 = smem_u32(qs);
+  // ldmatrix row address of this lane inside a 16-token x 16-column block of V
+  const uint32_t v_lane = smem_u32(vs) + (uint32_t)((((lane & 7) + ((lane >> 3) & 1) * 8) * TF_QK_PITCH + (lane >> 4) * 8) * 2);
   for (int64_t u = (int64_t)blockIdx.x * TF_ATT_WARPS + warp; u < units; u += (int64_t)gridDim.x * TF_ATT_WARPS) {
     const int64_t s = u / NH;
     const int h = (int)(u - s * NH);
     const __nv_bfloat16* base = qkv + s * tokens * (3 * D) + h * HD;
     __syncwarp();
-    // stage: 64 tokens x {q, k, v} x 4 chunks of 8 bf16; padded tokens are zero
-    for (int c = lane; c < TF_MAX_T * 12; c += 32) {
-      const int t = c / 12, rem = c - t * 12, m = rem >> 2, part = rem & 3;
-      uint4 val = make_uint4(0u, 0u, 0u, 0u);
-      if (t < tokens) val = __ldg(reinterpret_cast<const uint4*>(base + (int64_t)t * 3 * D + m * D + part * 8));
-      if (m == 0) *reinterpret_cast<uint4*>(qs + t * TF_QK_PITCH + part * 8) = val;
-      else if (m == 1) *reinterpret_cast<uint4*>(ks + t * TF_QK_PITCH + part * 8) = val;
-      else {
-        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&val);
+    // stage: tokens x {q, k, v} x 4 chunks of 8 bf16
+    for (int c = lane; c < tokens * 4; c += 32) {
+      const int t = c >> 2, part = c & 3;
+      const __nv_bfloat16* src = base + (int64_t)t * 3 * D + part * 8;
+      const uint32_t dst = qs_u32 + (uint32_t)((t * TF_QK_PITCH + part * 8) * 2);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) vt[(part * 8 + i) * TF_VT_PITCH + t] = e[i];
-      }
+      for (int m = 0; m < 3; ++m)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)(m * TF_MAX_T * TF_QK_PITCH * 2)), "l"(__cvta_generic_to_global(src + m * D)) : "memory");
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncwarp();
     const int mblocks = (tokens + 15) >> 4;
     for (int mb = 0; mb < mblocks; ++mb) {
@@ -409,9 +489,13 @@ __global__ void __launch_bounds__(TF_ATT_WARPS * 32) k_tf_attention(const __nv_b
         pa[2] = pack_bf16(sc[2 * j + 1][0], sc[2 * j + 1][1]);
         pa[3] = pack_bf16(sc[2 * j + 1][2], sc[2 * j + 1][3]);
 #pragma unroll
-        for (int nb = 0; nb < 4; ++nb) {
-          const __nv_bfloat16* v0 = vt + (nb * 8 + gid) * TF_VT_PITCH + j * 16 + 2 * tig;
-          mma_bf16_16816(o[nb], pa, *reinterpret_cast<const uint32_t*>(v0), *reinterpret_cast<const uint32_t*>(v0 + 8));
+        for (int nb = 0; nb < 4; nb += 2) {
+          uint32_t b0, b1, b2, b3;   // V[j*16 .. +15][nb*8 .. +7] and [(nb+1)*8 .. +7], transposed into B fragments
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                       : "r"(v_lane + (uint32_t)((j * 16 * TF_QK_PITCH + nb * 8) * 2)));
+          mma_bf16_16816(o[nb], pa, b0, b1);
+          mma_bf16_16816(o[nb + 1], pa, b2, b3);
         }
       }
       const float inv0 = 1.f / sum0, inv1 = 1.f / sum1;
@@ -419,8 +503,19 @@ __global__ void __launch_bounds__(TF_ATT_WARPS * 32) k_tf_attention(const __nv_b
 #pragma unroll
       for (int nb = 0; nb < 4; ++nb) {
         const int col = h * HD + nb * 8 + 2 * tig;
-        if (r0 < tokens) *reinterpret_cast<uint32_t*>(out + (s * tokens + r0) * D + col) = pack_bf16(o[nb][0] * inv0, o[nb][1] * inv0);
-        if (r1 < tokens) *reinterpret_cast<uint32_t*>(out + (s * tokens + r1) * D + col) = pack_bf16(o[nb][2] * inv1, o[nb][3] * inv1);
+        if (OUT8) {
+          uint8_t* out8 = reinterpret_cast<uint8_t*>(out_v);
+          if (r0 < tokens)
+            *reinterpret_cast<uint16_t*>(out8 + (s * tokens + r0) * D + col) = (uint16_t)__nv_cvt_float2_to_fp8x2(
+                make_float2(o[nb][0] * inv0 * out_inv_scale, o[nb][1] * inv0 * out_inv_scale), __NV_SATFINITE, __NV_E4M3);
+          if (r1 < tokens)
+            *reinterpret_cast<uint16_t*>(out8 + (s * tokens + r1) * D + col) = (uint16_t)__nv_cvt_float2_to_fp8x2(
+                make_float2(o[nb][2] * inv1 * out_inv_scale, o[nb][3] * inv1 * out_inv_scale), __NV_SATFINITE, __NV_E4M3);
+        } else {
+          __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(out_v);
+          if (r0 < tokens) *reinterpret_cast<uint32_t*>(out + (s * tokens + r0) * D + col) = pack_bf16(o[nb][0] * inv0, o[nb][1] * inv0);
+          if (r1 < tokens) *reinterpret_cast<uint32_t*>(out + (s * tokens + r1) * D + col) = pack_bf16(o[nb][2] * inv1, o[nb][3] * inv1);
+        }
       }
     }
   }
@@ -502,6 +597,7 @@ struct MgbsTf {
   int64_t mb_rows_pad = 0;  // rounded up to 128
   int n_micro = 0;
   CUtensorMap tm_y, tm_qkv, tm_att, tm_hid;  // activations (load as A operand / store as output)
+  CUtensorMap tm_x;                          // float32 residual stream (reduce-add target)
   CUtensorMap tm_wqkv[MGBS_TF_MAX_ENCODERS][MGBS_TF_MAX_LAYERS], tm_wo[MGBS_TF_MAX_ENCODERS][MGBS_TF_MAX_LAYERS],
       tm_w1[MGBS_TF_MAX_ENCODERS][MGBS_TF_MAX_LAYERS], tm_w2[MGBS_TF_MAX_ENCODERS][MGBS_TF_MAX_LAYERS];
 };
@@ -531,10 +627,13 @@ int mgbs_tf_create(const MgbsTfConfig* cfg, MgbsTf** out) {
   t->mb_rows_pad = (t->mb_rows + mgbs::BM - 1) / mgbs::BM * mgbs::BM;
   t->n_micro = (int)((c.max_states + c.micro_batch - 1) / c.micro_batch);
   const uint64_t R = (uint64_t)t->mb_rows_pad;
-  int rc = mgbs::make_map_bf16(&t->tm_y, c.y, R, 256, mgbs::BM);
+  if (c.dtype != 0 && c.dtype != 1) { delete t; return MGBS_ERR_ARG; }
+  const int eb = c.dtype == 1 ? 1 : 2;  // bytes per GEMM operand element
+  int rc = mgbs::make_map(&t->tm_y, c.y, R, 256, mgbs::BM, eb);
   if (!rc) rc = mgbs::make_map_bf16(&t->tm_qkv, c.qkv, R, 768, mgbs::BM);
-  if (!rc) rc = mgbs::make_map_bf16(&t->tm_att, c.att, R, 256, mgbs::BM);
-  if (!rc) rc = mgbs::make_map_bf16(&t->tm_hid, c.hid, R, (uint64_t)c.ffn, mgbs::BM);
+  if (!rc) rc = mgbs::make_map(&t->tm_x, c.x, R, 256, mgbs::BM, 4);
+  if (!rc) rc = mgbs::make_map(&t->tm_att, c.att, R, 256, mgbs::BM, eb);
+  if (!rc) rc = mgbs::make_map(&t->tm_hid, c.hid, R, (uint64_t)c.ffn, mgbs::BM, eb);
   for (int e = 0; e < c.encoders && !rc; ++e) {
     if (!c.tok_emb[e] || !c.pos_emb[e] || !c.lnf_g[e] || !c.lnf_b[e] || !c.w_head[e]) rc = MGBS_ERR_ARG;
     for (int l = 0; l < c.layers && !rc; ++l) {
@@ -542,16 +641,24 @@ int mgbs_tf_create(const MgbsTfConfig* cfg, MgbsTf** out) {
       if (!L.ln1_g || !L.ln1_b || !L.wqkv || !L.bqkv || !L.wo || !L.bo || !L.ln2_g || !L.ln2_b || !L.w1 || !L.b1 ||
           !L.w2 || !L.b2)
         rc = MGBS_ERR_ARG;
-      if (!rc) rc = mgbs::make_map_bf16(&t->tm_wqkv[e][l], L.wqkv, 768, 256, mgbs::BN);
-      if (!rc) rc = mgbs::make_map_bf16(&t->tm_wo[e][l], L.wo, 256, 256, mgbs::BN);
-      if (!rc) rc = mgbs::make_map_bf16(&t->tm_w1[e][l], L.w1, (uint64_t)c.ffn, 256, mgbs::BN);
-      if (!rc) rc = mgbs::make_map_bf16(&t->tm_w2[e][l], L.w2, 256, (uint64_t)c.ffn, mgbs::BN);
+      if (!rc && c.dtype == 1 && (!L.cs_qkv || !L.cs_o || !L.cs_1 || !L.cs_2)) rc = MGBS_ERR_ARG;
+      if (!rc) rc = mgbs::make_map(&t->tm_wqkv[e][l], L.wqkv, 768, 256, mgbs::BN, eb);
+      if (!rc) rc = mgbs::make_map(&t->tm_wo[e][l], L.wo, 256, 256, mgbs::BN, eb);
+      if (!rc) rc = mgbs::make_map(&t->tm_w1[e][l], L.w1, (uint64_t)c.ffn, 256, mgbs::BN, eb);
+      if (!rc) rc = mgbs::make_map(&t->tm_w2[e][l], L.w2, 256, (uint64_t)c.ffn, mgbs::BN, eb);
     }
   }
-  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_tf_gemm<mgbs::TF_EPI_STORE>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::TF_SMEM);
-  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_tf_gemm<mgbs::TF_EPI_STORE_GELU>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::TF_SMEM);
-  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_tf_gemm<mgbs::TF_EPI_RESID>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::TF_SMEM);
-  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_tf_attention, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::TF_ATT_SMEM);
+  auto big_smem = [&](const void* fn, int bytes) {
+    if (!rc) rc = (int)cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  };
+  big_smem((const void*)mgbs::k_tf_gemm<mgbs::TF_EPI_STORE, 0>, mgbs::TF_SMEM);
+  big_smem((const void*)mgbs::k_tf_gemm<mgbs::TF_EPI_STORE_GELU, 0>, mgbs::TF_SMEM);
+  big_smem((const void*)mgbs::k_tf_gemm<mgbs::TF_EPI_RESID, 0>, mgbs::TF_SMEM);
+  big_smem((const void*)mgbs::k_tf_gemm<mgbs::TF_EPI_STORE, 1>, mgbs::TF_SMEM);
+  big_smem((const void*)mgbs::k_tf_gemm<mgbs::TF_EPI_STORE_GELU, 1>, mgbs::TF_SMEM);
+  big_smem((const void*)mgbs::k_tf_gemm<mgbs::TF_EPI_RESID, 1>, mgbs::TF_SMEM);
+  big_smem((const void*)mgbs::k_tf_attention<0>, mgbs::TF_ATT_SMEM);
+  big_smem((const void*)mgbs::k_tf_attention<1>, mgbs::TF_ATT_SMEM);
   if (rc) { delete t; return rc; }
   *out = t;
   return 0;
@@ -570,9 +677,9 @@ int mgbs_tf_enqueue(void* user, const uint8_t* children, const uint32_t* count_d
   cudaStream_t st = (cudaStream_t)stream;
   const int T = c.state_len;
   const int ew_grid = t->sms * 8;
-  __nv_bfloat16* y = reinterpret_cast<__nv_bfloat16*>(c.y);
-  __nv_bfloat16* qkv = reinterpret_cast<__nv_bfloat16*>(c.qkv);
-  __nv_bfloat16* att = reinterpret_cast<__nv_bfloat16*>(c.att);
+  const __nv_bfloat16* qkv = reinterpret_cast<const __nv_bfloat16*>(c.qkv);
+  const bool f8 = c.dtype == 1;
+  const dim3 gg(t->sms), gb(TF_THREADS);
   for (int mb = 0; mb < t->n_micro; ++mb) {
     const int64_t off = (int64_t)mb * t->mb_rows;
     TfGemmArgs g;
@@ -581,22 +688,47 @@ int mgbs_tf_enqueue(void* user, const uint8_t* children, const uint32_t* count_d
     g.row_offset = off;
     g.row_limit = t->mb_rows;
     g.err = c.err;
+    g.col_scale = nullptr;
+    g.out_inv_scale = 1.f;
     for (int e = 0; e < c.encoders; ++e) {
       k_tf_embed<<<ew_grid, 256, 0, st>>>(children, count_dev, T, c.state_stride, 256, off, t->mb_rows, c.tok_emb[e],
                                           c.pos_emb[e], c.x);
       for (int l = 0; l < c.layers; ++l) {
         const MgbsTfLayer& L = c.layer[e][l];
-        k_tf_layernorm<<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln1_g, L.ln1_b, y);
-        g.n_total = 768; g.k_total = 256; g.bias = L.bqkv; g.resid = nullptr;
-        k_tf_gemm<TF_EPI_STORE><<<t->sms, TF_THREADS, TF_SMEM, st>>>(t->tm_y, t->tm_wqkv[e][l], t->tm_qkv, g);
-        k_tf_attention<<<t->sms * 12, TF_ATT_WARPS * 32, TF_ATT_SMEM, st>>>(qkv, count_dev, T, off, t->mb_rows, att);
-        g.n_total = 256; g.k_total = 256; g.bias = L.bo; g.resid = c.x;
-        k_tf_gemm<TF_EPI_RESID><<<t->sms, TF_THREADS, TF_SMEM, st>>>(t->tm_att, t->tm_wo[e][l], t->tm_att, g);
-        k_tf_layernorm<<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln2_g, L.ln2_b, y);
-        g.n_total = c.ffn; g.k_total = 256; g.bias = L.b1; g.resid = nullptr;
-        k_tf_gemm<TF_EPI_STORE_GELU><<<t->sms, TF_THREADS, TF_SMEM, st>>>(t->tm_y, t->tm_w1[e][l], t->tm_hid, g);
-        g.n_total = 256; g.k_total = c.ffn; g.bias = L.b2; g.resid = c.x;
-        k_tf_gemm<TF_EPI_RESID><<<t->sms, TF_THREADS, TF_SMEM, st>>>(t->tm_hid, t->tm_w2[e][l], t->tm_hid, g);
+        g.n_total = 768; g.k_total = 256; g.bias = L.bqkv;
+        if (f8) {
+          k_tf_layernorm<1><<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln1_g, L.ln1_b, c.y, L.inv_y1);
+          g.col_scale = L.cs_qkv;
+          k_tf_gemm<TF_EPI_STORE, 1><<<gg, gb, TF_SMEM, st>>>(t->tm_y, t->tm_wqkv[e][l], t->tm_qkv, g);
+          k_tf_attention<1><<<t->sms * 2, TF_ATT_WARPS * 32, TF_ATT_SMEM, st>>>(qkv, count_dev, T, off, t->mb_rows, c.att, L.inv_att);
+        } else {
+          k_tf_layernorm<0><<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln1_g, L.ln1_b, c.y, 1.f);
+          k_tf_gemm<TF_EPI_STORE, 0><<<gg, gb, TF_SMEM, st>>>(t->tm_y, t->tm_wqkv[e][l], t->tm_qkv, g);
+          k_tf_attention<0><<<t->sms * 2, TF_ATT_WARPS * 32, TF_ATT_SMEM, st>>>(qkv, count_dev, T, off, t->mb_rows, c.att, 1.f);
+        }
+        g.n_total = 256; g.k_total = 256; g.bias = L.bo;
+        if (f8) {
+          g.col_scale = L.cs_o;
+          k_tf_gemm<TF_EPI_RESID, 1><<<gg, gb, TF_SMEM, st>>>(t->tm_att, t->tm_wo[e][l], t->tm_x, g);
+          k_tf_layernorm<1><<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln2_g, L.ln2_b, c.y, L.inv_y2);
+        } else {
+          k_tf_gemm<TF_EPI_RESID, 0><<<gg, gb, TF_SMEM, st>>>(t->tm_att, t->tm_wo[e][l], t->tm_x, g);
+          k_tf_layernorm<0><<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln2_g, L.ln2_b, c.y, 1.f);
+        }
+        g.n_total = c.ffn; g.k_total = 256; g.bias = L.b1;
+        if (f8) {
+          g.col_scale = L.cs_1; g.out_inv_scale = L.inv_hid;
+          k_tf_gemm<TF_EPI_STORE_GELU, 1><<<gg, gb, TF_SMEM, st>>>(t->tm_y, t->tm_w1[e][l], t->tm_hid, g);
+        } else {
+          k_tf_gemm<TF_EPI_STORE_GELU, 0><<<gg, gb, TF_SMEM, st>>>(t->tm_y, t->tm_w1[e][l], t->tm_hid, g);
+        }
+        g.n_total = 256; g.k_total = c.ffn; g.bias = L.b2;
+        if (f8) {
+          g.col_scale = L.cs_2;
+          k_tf_gemm<TF_EPI_RESID, 1><<<gg, gb, TF_SMEM, st>>>(t->tm_hid, t->tm_w2[e][l], t->tm_x, g);
+        } else {
+          k_tf_gemm<TF_EPI_RESID, 0><<<gg, gb, TF_SMEM, st>>>(t->tm_hid, t->tm_w2[e][l], t->tm_x, g);
+        }
       }
       k_tf_pool_head<<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, c.lnf_g[e], c.lnf_b[e], c.w_head[e],
                                               e > 0 ? 1 : 0, c.q);

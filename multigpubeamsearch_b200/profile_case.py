@@ -2,8 +2,9 @@
 
     python -m multigpubeamsearch_b200.profile_case [--rows R] [--repeat N]
 
-Scores R random child states with the MLP (default), its FP8 variant or the transformer ensemble (default 151 552 = 8 tiles per SM on 148 SMs; first-layer activations 310 MB, larger than
-L2) N times with the MLP 324 -> 1024 -> 1024 -> 1.  A dozen launches in total, a few hundred MB on the device.
+Scores R random child states N times with the MLP 324 -> 1024 -> 1024 -> 1 (default), its e4m3 variant, or the
+two-encoder transformer ensemble in bf16 or e4m3.  The default R = 151 552 is 8 row tiles per SM on 148 SMs; the
+MLP's first-layer activations are then 310 MB, larger than L2.  A few hundred MB on the device.
 """
 
 from __future__ import annotations
@@ -20,7 +21,7 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--rows", type=int, default=151552)
     ap.add_argument("--repeat", type=int, default=3)
-    ap.add_argument("--scorer", default="mlp", choices=["mlp", "mlp_fp8", "transformer"])
+    ap.add_argument("--scorer", default="mlp", choices=["mlp", "mlp_fp8", "transformer", "transformer_fp8"])
     ap.add_argument("--micro-batch", type=int, default=32768)
     args = ap.parse_args()
     pz = puzzles.puzzle54()
@@ -32,9 +33,10 @@ def main() -> None:
     padded = np.zeros((args.rows, 64), np.uint8)
     padded[:, :54] = rows
     children = torch.from_numpy(padded).cuda()
-    if args.scorer == "transformer":
+    if args.scorer.startswith("transformer"):
         sc = scorers.TransformerValueScorer([puzzles.transformer_weights(54, 6, model_idx=i) for i in range(2)], 54, 64, 6,
-                                            max_rows=args.rows, micro_batch=args.micro_batch)
+                                            max_rows=args.rows, micro_batch=args.micro_batch,
+                                            dtype="fp8" if args.scorer.endswith("fp8") else "bf16")
     else:
         sc = scorers.MLPValueScorer(puzzles.mlp_weights(324, 1024), 54, 64, 6, max_rows=args.rows,
                                     dtype="fp8" if args.scorer == "mlp_fp8" else "bf16")

@@ -243,10 +243,13 @@ TF_MAX_ENCODERS = 4
 TF_MAX_LAYERS = 8
 _LAYER_FIELDS = ("ln1_g", "ln1_b", "wqkv", "bqkv", "wo", "bo", "ln2_g", "ln2_b", "w1", "b1", "w2", "b2")
 _LAYER_BF16 = {"wqkv", "wo", "w1", "w2"}
+E4M3_MAX = 448.0
 
 
 class MgbsTfLayer(C.Structure):
-    _fields_ = [(name, C.c_void_p) for name in _LAYER_FIELDS]
+    _fields_ = ([(name, C.c_void_p) for name in _LAYER_FIELDS]
+                + [(name, C.c_void_p) for name in ("cs_qkv", "cs_o", "cs_1", "cs_2")]
+                + [(name, C.c_float) for name in ("inv_y1", "inv_att", "inv_y2", "inv_hid")])
 
 
 class MgbsTfConfig(C.Structure):
@@ -260,7 +263,7 @@ class MgbsTfConfig(C.Structure):
         ("w_head", C.c_void_p * TF_MAX_ENCODERS),
         ("layer", (MgbsTfLayer * TF_MAX_LAYERS) * TF_MAX_ENCODERS),
         ("x", C.c_void_p), ("y", C.c_void_p), ("qkv", C.c_void_p), ("att", C.c_void_p), ("hid", C.c_void_p),
-        ("q", C.c_void_p), ("err", C.c_void_p),
+        ("q", C.c_void_p), ("err", C.c_void_p), ("dtype", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -277,10 +280,16 @@ class TransformerValueScorer:
     """Ensemble of pre-LayerNorm transformer encoders scoring child states (see puzzles.transformer_weights for the
     weight layout): d_model 256, 8 heads, GELU feed-forward, mean pooling, scalar head.  bf16 GEMM operands with fp32
     accumulation on the tcgen05 tensor cores, fp32 residual stream; states go through in micro-batches of
-    ``micro_batch`` (the reference's B_MICRO knob)."""
+    ``micro_batch`` (the reference's B_MICRO knob).
+
+    ``dtype="fp8"`` stores the four matrices of every layer as e4m3 with one scale per output row and feeds the GEMMs
+    e4m3 activations (LayerNorm output, attention output, GELU output) with one scale per tensor.  The activation
+    scales come from bounds that hold for every input (a LayerNorm row has L2 norm 16 before its gain, so
+    |row . w| <= (16 max|gain| + |shift|) |w|), not from calibration data; q, k, v stay bf16 for the attention
+    kernel."""
 
     def __init__(self, encoders: Sequence[Dict], state_len: int, state_stride: int, num_values: int, max_rows: int,
-                 micro_batch: int = 32768, score_offset: float = -150.0, device=None):
+                 micro_batch: int = 32768, score_offset: float = -150.0, device=None, dtype: str = "bf16"):
         self.lib = _lib.load()
         for name, (res, args) in _TF_SIGS.items():
             fn = getattr(self.lib, name)
@@ -312,7 +321,30 @@ class TransformerValueScorer:
             self._keep.append(t)
             return t.data_ptr()
 
+        if dtype not in ("bf16", "fp8"):
+            raise RuntimeError("dtype must be 'bf16' or 'fp8'")
+        self.dtype = dtype
+        fp8 = dtype == "fp8"
+
+        def e4m3(w, act_scale):
+            """Rows of w as e4m3 with per-row scales; returns (weights ptr, column-scale ptr)."""
+            w = torch.from_numpy(np.ascontiguousarray(w, dtype=np.float32))
+            ws = (w.abs().amax(dim=1).clamp_min(1e-30) / E4M3_MAX).to(torch.float32)
+            q8 = (w / ws[:, None]).to(torch.float8_e4m3fn).contiguous().to(dev)
+            cs = (ws * float(act_scale)).to(dev)
+            self._keep += [q8, cs]
+            return q8.data_ptr(), cs.data_ptr()
+
+        def ln_bound(gain, shift):
+            """Upper bound of the L2 norm of a LayerNorm output row of width d."""
+            return float(np.sqrt(d) * np.abs(gain).max() + np.linalg.norm(shift))
+
+        def out_bound(w, b, in_norm):
+            """Upper bound of |x . w_row + b| over rows, for |x|_2 <= in_norm."""
+            return float((np.linalg.norm(np.asarray(w, dtype=np.float64), axis=1) * in_norm + np.abs(b)).max())
+
         cfg = MgbsTfConfig()
+        cfg.dtype = 1 if fp8 else 0
         cfg.state_len, cfg.state_stride, cfg.num_values = state_len, state_stride, num_values
         cfg.d_model, cfg.heads, cfg.ffn, cfg.layers, cfg.encoders = d, 8, ffn, layers, len(encoders)
         cfg.max_states, cfg.micro_batch, cfg.score_offset = int(max_rows), micro_batch, float(score_offset)
@@ -323,13 +355,27 @@ class TransformerValueScorer:
             cfg.tok_emb[e], cfg.pos_emb[e] = f32(w["tok_emb"]), f32(w["pos_emb"][:state_len])
             cfg.lnf_g[e], cfg.lnf_b[e], cfg.w_head[e] = f32(w["lnf_g"]), f32(w["lnf_b"]), f32(w["w_head"])
             for li, L in enumerate(w["layers"]):
+                dst = cfg.layer[e][li]
                 for name in _LAYER_FIELDS:
-                    setattr(cfg.layer[e][li], name, bf16(L[name]) if name in _LAYER_BF16 else f32(L[name]))
+                    if not (fp8 and name in _LAYER_BF16):
+                        setattr(dst, name, bf16(L[name]) if name in _LAYER_BF16 else f32(L[name]))
+                if fp8:
+                    n1, n2 = ln_bound(L["ln1_g"], L["ln1_b"]), ln_bound(L["ln2_g"], L["ln2_b"])
+                    # element bounds: LN rows by their norm, attention output by the largest |v|, GELU by |input|
+                    s_y1, s_y2 = n1 / E4M3_MAX, n2 / E4M3_MAX
+                    s_att = out_bound(L["wqkv"][2 * d:], L["bqkv"][2 * d:], n1) / E4M3_MAX
+                    s_hid = out_bound(L["w1"], L["b1"], n2) / E4M3_MAX
+                    dst.wqkv, dst.cs_qkv = e4m3(L["wqkv"], s_y1)
+                    dst.wo, dst.cs_o = e4m3(L["wo"], s_att)
+                    dst.w1, dst.cs_1 = e4m3(L["w1"], s_y2)
+                    dst.w2, dst.cs_2 = e4m3(L["w2"], s_hid)
+                    dst.inv_y1, dst.inv_att, dst.inv_y2, dst.inv_hid = 1 / s_y1, 1 / s_att, 1 / s_y2, 1 / s_hid
+        act = torch.uint8 if fp8 else torch.bfloat16
         self.x = torch.zeros((rows_pad, d), dtype=torch.float32, device=dev)
-        self.y = torch.zeros((rows_pad, d), dtype=torch.bfloat16, device=dev)
+        self.y = torch.zeros((rows_pad, d), dtype=act, device=dev)
         self.qkv = torch.zeros((rows_pad, 3 * d), dtype=torch.bfloat16, device=dev)
-        self.att = torch.zeros((rows_pad, d), dtype=torch.bfloat16, device=dev)
-        self.hid = torch.zeros((rows_pad, ffn), dtype=torch.bfloat16, device=dev)
+        self.att = torch.zeros((rows_pad, d), dtype=act, device=dev)
+        self.hid = torch.zeros((rows_pad, ffn), dtype=act, device=dev)
         self.q = torch.zeros((int(max_rows),), dtype=torch.float32, device=dev)
         self.err = torch.zeros((1,), dtype=torch.int32, device=dev)
         self._count = torch.zeros((1,), dtype=torch.int32, device=dev)

@@ -26,9 +26,7 @@ def _pad(rows, stride):
     return out
 
 
-@pytest.mark.parametrize("count,encoders,micro", [(300, 1, 32768), (700, 2, 256), (1, 1, 64)])
-def test_transformer_scorer_matches_fp32(count, encoders, micro):
-    pz = puzzles.puzzle54()
+def _perturbed_weights(encoders):
     ws = [puzzles.transformer_weights(54, 6, model_idx=i) for i in range(encoders)]
     rng = np.random.default_rng(11)
     for w in ws:  # non-trivial biases / LayerNorm parameters so that every term is exercised
@@ -40,6 +38,13 @@ def test_transformer_scorer_matches_fp32(count, encoders, micro):
                 L[k] = (0.05 * rng.standard_normal(L[k].shape)).astype(np.float32)
             for k in ("ln1_g", "ln2_g"):
                 L[k] = (1.0 + 0.1 * rng.standard_normal(256)).astype(np.float32)
+    return ws
+
+
+@pytest.mark.parametrize("count,encoders,micro", [(300, 1, 32768), (700, 2, 256), (1, 1, 64)])
+def test_transformer_scorer_matches_fp32(count, encoders, micro):
+    pz = puzzles.puzzle54()
+    ws = _perturbed_weights(encoders)
     sc = scorers.TransformerValueScorer(ws, 54, 64, 6, max_rows=count, micro_batch=micro)
     rows = _states(pz, count, seed=count)
     keys = sc.score(torch.from_numpy(_pad(rows, 64)).cuda())
@@ -49,6 +54,31 @@ def test_transformer_scorer_matches_fp32(count, encoders, micro):
     q_dev = (sc.last_q(count).cpu().numpy() + sum(float(w["b_head"]) for w in ws)) / encoders
     # bf16 GEMM operands and bf16 activations between GEMMs, fp32 residual stream: observed error ~1e-3
     assert np.abs(q_dev - q_ref).max() <= 1e-2, np.abs(q_dev - q_ref).max()
+    rekey = bo.q_to_score_key(q_dev.astype(np.float32), -150.0).astype(np.int64)
+    assert np.abs(keys.cpu().numpy().astype(np.int64) - rekey).max() <= 1
+
+
+@pytest.mark.parametrize("count,encoders,micro", [(700, 2, 256), (129, 1, 32768)])
+def test_transformer_scorer_fp8(count, encoders, micro):
+    """e4m3 GEMM operands.  Checked twice: tightly against the float32 evaluation of the SAME rounded operands
+    (weights per row, activations per tensor, scales from the same bounds) - this is the kernel check - and loosely
+    against the unrounded float32 model, where weight rounding of ~3 % per element, amplified by the final
+    LayerNorm of a small residual stream, shifts every output by about the same amount."""
+    pz = puzzles.puzzle54()
+    ws = _perturbed_weights(encoders)
+    sc = scorers.TransformerValueScorer(ws, 54, 64, 6, max_rows=count, micro_batch=micro, dtype="fp8")
+    rows = _states(pz, count, seed=count)
+    keys = sc.score(torch.from_numpy(_pad(rows, 64)).cuda())
+    torch.cuda.synchronize()
+    assert sc.error_code() == 0
+    q_dev = (sc.last_q(count).cpu().numpy() + sum(float(w["b_head"]) for w in ws)) / encoders
+    q_model = bo.transformer_forward(rows, ws, e4m3=True)
+    q_ref = bo.transformer_forward(rows, ws)
+    err_model, err_ref = np.abs(q_dev - q_model).max(), np.abs(q_dev - q_ref).max()
+    print("fp8 transformer: vs rounded-operand model", err_model, "vs float32", err_ref)
+    # bf16 q/k/v between the GEMMs and values that sit on an e4m3 rounding boundary leave ~1e-3
+    assert err_model <= 2e-2, err_model
+    assert err_ref <= 6e-2, err_ref
     rekey = bo.q_to_score_key(q_dev.astype(np.float32), -150.0).astype(np.int64)
     assert np.abs(keys.cpu().numpy().astype(np.int64) - rekey).max() <= 1
 
