@@ -344,7 +344,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
   } else if (warp < 2 + EW) {
     // ---- epilogue: TMEM -> bias, ReLU, bf16 -> swizzled staging box -> TMA store ----
     const int quad = warp & 3;
-    const int sg = (warp - 2) >> 2;                   // sub-group: which 32-column groups of a box this warp takes
+    const int sg = EW == 4 ? 0 : (warp - 2) >> 2;     // sub-group: which 32-column groups of a box this warp takes
     const int et = (warp - 2) * 32 + lane;            // index among the epilogue threads
     const uint32_t r = (uint32_t)(quad * 32 + lane);  // tile row owned by this thread
     uint32_t acc_it = 0, box_it = 0;
@@ -363,7 +363,8 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
           if (et == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");
 #pragma unroll
-          for (int sub = sg; sub < BKE / 32; sub += EW / 4) {
+          for (int sub0 = 0; sub0 < BKE / 32; sub0 += EW / 4) {   // constant trip count: unrolls completely
+            const int sub = sub0 + sg;
             uint32_t v[32];
             tc_ld32(taddr + gcol + sub * 32, v);
             tc_wait_ld();
