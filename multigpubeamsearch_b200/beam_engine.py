@@ -63,7 +63,7 @@ def make_default_config() -> Dict[str, Any]:
         "select_mode": os.environ.get("SELECT_MODE", "exact_k"),
         "band_rounds": int(os.environ.get("BAND_ROUNDS", "6")),
         "band_levels": int(os.environ.get("BAND_LEVELS", "3")),
-        "hash_bits": int(os.environ.get("ORDER_KEY_HASH_BITS", "44")),
+        "hash_bits": int(os.environ.get("ORDER_KEY_HASH_BITS", "24")),
         "materialize_children": _flag_enabled("MATERIALIZE_CHILDREN"),
         "use_cuda_graphs": _flag_enabled("USE_CUDA_GRAPHS", "1"),
         "score_offset": float(os.environ.get("NN_SCORE_BIAS", "0.0")),
@@ -179,11 +179,17 @@ def allocate_buffers(ext: _Ext, cfg: Dict[str, Any]) -> Dict[str, torch.Tensor]:
         tmp = _lib.MgbsConfig()
         tmp.world_size, tmp.state_stride, tmp.bucket_cap = world, stride, sizes["bucket_cap_per_peer"]
         tmp.band_rounds, tmp.band_levels = int(cfg["band_rounds"]), int(cfg["band_levels"])
-        tmp.hash_bits = int(cfg.get("hash_bits", 44)) if str(cfg.get("select_mode", "exact_k")) == "exact_k" else 0
+        tmp.hash_bits = int(cfg.get("hash_bits", 24)) if str(cfg.get("select_mode", "exact_k")) == "exact_k" else 0
+        tmp.frontier_cap = k_work
         nbytes, ntick = C.c_int64(0), C.c_int64(0)
         _lib.check(ext.lib.mgbs_sym_bytes(C.byref(tmp), C.byref(nbytes), C.byref(ntick)), "mgbs_sym_bytes")
+        offs = (C.c_int64 * 2)()
+        _lib.check(ext.lib.mgbs_sym_frontier_offsets(C.byref(tmp), offs), "mgbs_sym_frontier_offsets")
         # its own allocation (not a slice of a bigger one): the whole storage is what gets mapped into the peers
         buffers["sym"] = z((int(nbytes.value),), torch.uint8)
+        # the frontier buffers live inside the region: peers read parent rows from them
+        for name, off in (("beam_current", int(offs[0])), ("beam_next", int(offs[1]))):
+            buffers[name] = buffers["sym"][off:off + k_work * stride].view(k_work, stride)
         buffers["tickets"] = z((int(ntick.value),), torch.int32)
         buffers["send_counts"] = z((world,), torch.int32)
     elif world > 1:
@@ -230,7 +236,7 @@ class BeamEngine:
         if mode not in _lib.SELECT_MODES:
             raise RuntimeError(f"unknown select_mode {mode!r}")
         c.select_mode = _lib.SELECT_MODES[mode]
-        c.hash_bits = int(cfg.get("hash_bits", 44)) if mode == "exact_k" else 0
+        c.hash_bits = int(cfg.get("hash_bits", 24)) if mode == "exact_k" else 0
         c.score_mode = {"dummy": _lib.SCORE_HAMMING, "central_hamming": _lib.SCORE_HAMMING,
                         "uniform": _lib.SCORE_UNIFORM, "mlp": _lib.SCORE_EXTERNAL}[backend]
         c.band_levels = int(cfg["band_levels"])

@@ -168,6 +168,9 @@ int mgbs_engine_create(const MgbsConfig* cfg, MgbsEngine** out) {
   if (c.world_size > 1 && c.exchange_mode == MGBS_EXCHANGE_PEER) {
     e->sym = mgbs::sym_layout(e->cfg, e->cfg.band_levels);
     if (c.sym_bytes < e->sym.total) { delete e; return MGBS_ERR_ARG; }
+    // peers rebuild survivors from parent rows of this rank's frontiers: both buffers must sit inside the region
+    for (int p = 0; p < 2; ++p)
+      if (c.frontier[p] != c.sym + e->sym.frontier[p]) { delete e; return MGBS_ERR_ARG; }
     e->peer_base[c.rank] = c.sym;
   }
   int dev = 0;
@@ -217,13 +220,29 @@ int mgbs_engine_init_nccl(MgbsEngine* e, const char* libnccl_path, const uint8_t
 
 int mgbs_sym_bytes(const MgbsConfig* cfg, int64_t* out_bytes, int64_t* out_tickets) {
   if (!cfg || !out_bytes || !out_tickets) return MGBS_ERR_ARG;
-  if (cfg->world_size < 1 || cfg->world_size > MGBS_MAX_WORLD || cfg->bucket_cap < 0 || cfg->state_stride < 16) return MGBS_ERR_ARG;
+  if (cfg->world_size < 1 || cfg->world_size > MGBS_MAX_WORLD || cfg->bucket_cap < 0 || cfg->state_stride < 16 ||
+      cfg->frontier_cap < 0)
+    return MGBS_ERR_ARG;
   int key_bits = 20 + cfg->hash_bits;
   int final_levels = (key_bits + MGBS_RADIX_BITS - 1) / MGBS_RADIX_BITS;
   int bl = cfg->band_levels > final_levels ? final_levels : cfg->band_levels;
   mgbs::SymLayout L = mgbs::sym_layout(*cfg, bl);
   *out_bytes = L.total;
   *out_tickets = L.slots + 1;
+  return 0;
+}
+
+int mgbs_sym_frontier_offsets(const MgbsConfig* cfg, int64_t* out2) {
+  if (!cfg || !out2) return MGBS_ERR_ARG;
+  int64_t bytes = 0, tickets = 0;
+  int rc = mgbs_sym_bytes(cfg, &bytes, &tickets);
+  if (rc) return rc;
+  int key_bits = 20 + cfg->hash_bits;
+  int final_levels = (key_bits + MGBS_RADIX_BITS - 1) / MGBS_RADIX_BITS;
+  int bl = cfg->band_levels > final_levels ? final_levels : cfg->band_levels;
+  mgbs::SymLayout L = mgbs::sym_layout(*cfg, bl);
+  out2[0] = L.frontier[0];
+  out2[1] = L.frontier[1];
   return 0;
 }
 
@@ -444,8 +463,10 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
 #define MGBS_TRACE() do { if (prof && e->trace_n < 96) cudaEventRecord(e->tev[e->trace_n++], st); } while (0)
   MGBS_TRACE();
   if (phase == 0 || phase == 1) {
+    const bool peer_mode = W > 1 && c.exchange_mode == MGBS_EXCHANGE_PEER;
     MGBS_TRY(launch_depth_begin(c.ctrl, parity, c.fanout, c.cand_cap, tie_buf + (int64_t)c.rank * kTieSegWords,
-                                W > 1 ? c.send_counts : nullptr, W, st));
+                                W > 1 ? c.send_counts : nullptr,
+                                peer_mode ? reinterpret_cast<uint32_t*>(c.sym + e->sym.counts[parity]) : nullptr, W, st));
     MGBS_TRY(cudaMemsetAsync(c.table, 0, (size_t)c.hash_capacity * 32, st));
     MGBS_TRY(cudaMemsetAsync(c.hist, 0, (size_t)(R * Lb + MGBS_MAX_LEVELS) * MGBS_HIST_STRIDE * sizeof(uint32_t), st));
     ExpandArgs x;
@@ -474,6 +495,9 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
 
   StepArgs a;
   memset(&a, 0, sizeof(a));
+  RouteArgs pr;  // peer mode: routing of one band
+  memset(&pr, 0, sizeof(pr));
+  const bool peer = W > 1 && c.exchange_mode == MGBS_EXCHANGE_PEER;
   int64_t items;
   if (W == 1) {
     a.cv.hash = c.cand_hash; a.cv.fp = c.cand_fp; a.cv.score = c.cand_score; a.cv.payload = c.cand_payload;
@@ -482,32 +506,38 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     a.cv.nbuckets = 1;
     a.cv.cap = (uint32_t)c.cand_cap;
     items = c.cand_cap;
-  } else if (c.exchange_mode == MGBS_EXCHANGE_PEER) {
+    a.cvh = a.cv;
+  } else if (peer) {
+    // nothing moves yet: every band round counts its histograms over this rank's own candidates (the sums over
+    // ranks are what matters), then routes just that band to the owners, who insert it
     if (!e->peers_ready) return MGBS_ERR_STATE;
     const SymLayout& L = e->sym;
-    RouteArgs r;
-    memset(&r, 0, sizeof(r));
-    r.hash = c.cand_hash; r.fp = c.cand_fp; r.score = c.cand_score; r.payload = c.cand_payload; r.states = c.children;
-    r.send_counts = c.send_counts;
-    r.ctrl = c.ctrl;
-    r.world = W; r.stride = c.state_stride; r.bucket_cap = (uint32_t)c.bucket_cap;
-    r.rank = c.rank;
-    for (int q = 0; q < W; ++q) r.peer.base[q] = e->peer_base[q];
-    r.peer.enabled = 1;
-    r.peer.tickets = c.tickets;
-    r.peer.slot = L.slots;  // the ticket word after the histogram slots
-    r.off_hash = L.hash[parity]; r.off_fp = L.fp[parity]; r.off_score = L.score[parity];
-    r.off_payload = L.payload[parity]; r.off_states = L.states[parity]; r.off_counts = L.counts[parity];
-    r.off_route_flag = L.route_flag;
-    MGBS_TRY(launch_route(r, c.cand_cap, e->sms, st));
+    pr.hash = c.cand_hash; pr.fp = c.cand_fp; pr.score = c.cand_score; pr.payload = c.cand_payload;
+    pr.send_counts = c.send_counts;
+    pr.ctrl = c.ctrl;
+    pr.world = W; pr.stride = c.state_stride; pr.bucket_cap = (uint32_t)c.bucket_cap;
+    pr.rank = c.rank;
+    for (int q = 0; q < W; ++q) pr.peer.base[q] = e->peer_base[q];
+    pr.peer.enabled = 1;
+    pr.peer.tickets = c.tickets;
+    pr.peer.slot = L.slots;  // the ticket word after the histogram slots
+    pr.off_hash = L.hash[parity]; pr.off_fp = L.fp[parity]; pr.off_score = L.score[parity];
+    pr.off_payload = L.payload[parity]; pr.off_counts = L.counts[parity];
+    pr.off_route_flag = L.route_flag;
+    a.cvh.hash = c.cand_hash; a.cvh.fp = c.cand_fp; a.cvh.score = c.cand_score; a.cvh.payload = c.cand_payload;
+    a.cvh.states = nullptr;
+    a.cvh.counts = &c.ctrl->cand_count;
+    a.cvh.nbuckets = 1;
+    a.cvh.cap = (uint32_t)c.cand_cap;
     a.cv.hash = reinterpret_cast<const uint64_t*>(c.sym + L.hash[parity]);
     a.cv.fp = reinterpret_cast<const uint64_t*>(c.sym + L.fp[parity]);
     a.cv.score = reinterpret_cast<const uint32_t*>(c.sym + L.score[parity]);
     a.cv.payload = reinterpret_cast<const uint32_t*>(c.sym + L.payload[parity]);
-    a.cv.states = c.sym + L.states[parity];
+    a.cv.states = nullptr;  // survivors are rebuilt from their parents' rows in the senders' frontiers
     a.cv.counts = reinterpret_cast<const uint32_t*>(c.sym + L.counts[parity]);
     a.cv.nbuckets = W;
     a.cv.cap = (uint32_t)c.bucket_cap;
+    a.off_frontier_cur = L.frontier[parity];
     items = c.bucket_cap;
     for (int q = 0; q < W; ++q) a.peer.base[q] = e->peer_base[q];
     a.peer.enabled = 1;
@@ -532,6 +562,7 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     a.cv.nbuckets = W;
     a.cv.cap = (uint32_t)c.bucket_cap;
     items = c.bucket_cap;  // per bucket; kernels loop over buckets
+    a.cvh = a.cv;
   }
   if (prof) cudaEventRecord(e->ev[3], st);
   MGBS_TRACE();  // route + exchange
@@ -564,12 +595,16 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
       a.hist = c.hist + (int64_t)(r * Lb + l) * MGBS_HIST_STRIDE;
       a.peer.slot = r * Lb + l;
       a.hist_prev = l > 0 ? c.hist + (int64_t)(r * Lb + l - 1) * MGBS_HIST_STRIDE : nullptr;
-      MGBS_TRY(launch_band_hist(a, items, e->sms, st));
+      MGBS_TRY(launch_band_hist(a, peer ? c.cand_cap : items, e->sms, st));
       MGBS_TRY(allreduce_hist(e, a.hist, st));
       MGBS_TRACE();  // band histogram (+ reduction)
     }
     a.hist = nullptr;
     a.hist_prev = c.hist + (int64_t)(r * Lb + Lb - 1) * MGBS_HIST_STRIDE;
+    if (peer) {
+      MGBS_TRY(launch_route_band(a, pr, c.cand_cap, e->sms, st));
+      MGBS_TRACE();  // band route
+    }
     MGBS_TRY(launch_band_insert(a, items, e->sms, st));
     MGBS_TRACE();  // band insert
   }

@@ -17,8 +17,9 @@ constexpr int kTieSegWords = 1 + 3 * MGBS_TIE_CAP;
 // Peer-mapped symmetric regions (MGBS_EXCHANGE_PEER).  base[r] is rank r's region as seen from this GPU
 // (base[rank] is the local one).  Offsets are the same on every rank.
 struct SymLayout {
-  int64_t hash[2], fp[2], score[2], payload[2], states[2], counts[2];  // receive buckets per frontier parity
-  int64_t route_flag;  // [world] u32: sender r finished routing (value = epoch)
+  int64_t hash[2], fp[2], score[2], payload[2], counts[2];  // receive buckets per frontier parity (records only)
+  int64_t frontier[2];  // the two frontier buffers: peers read parent rows from them when they rebuild survivors
+  int64_t route_flag;   // [world] u32: sender r finished routing a band (value = epoch * 16 + round)
   int64_t hx;          // [slots][world][MGBS_HIST_STRIDE] u32 histogram exchange
   int64_t hflag;       // [slots][world] u32
   int64_t total;
@@ -62,7 +63,9 @@ struct CandView {
 };
 
 struct StepArgs {
-  CandView cv;
+  CandView cv;   // candidates this rank owns (world = 1: all of them; world > 1: the receive buckets)
+  CandView cvh;  // candidates the band histograms count: cv, or in peer mode the ones this rank generated
+                 // (the histograms are summed over ranks, so either partition gives the same sums)
   MgbsCtrl* ctrl;
   uint32_t* hist;             // histogram this kernel fills
   const uint32_t* hist_prev;  // histogram of the previous level, consumed in the prologue
@@ -86,6 +89,7 @@ struct StepArgs {
   uint64_t* next_hash;
   int32_t n, stride, fanout, parity;
   PeerCtx peer;
+  int64_t off_frontier_cur;  // peer mode: offset of the current frontier inside every rank's symmetric region
 };
 
 struct RouteArgs {
@@ -97,19 +101,20 @@ struct RouteArgs {
   uint32_t bucket_cap;
   // peer mode: records go straight into the owner's receive buckets; offsets of the bucket arrays of this parity
   PeerCtx peer;
-  int64_t off_hash, off_fp, off_score, off_payload, off_states, off_counts, off_route_flag;
+  int64_t off_hash, off_fp, off_score, off_payload, off_counts, off_route_flag;
   int32_t rank;
 };
 
 int launch_expand(const ExpandArgs& a, int64_t max_parents, int sms, cudaStream_t st);
 int launch_depth_begin(MgbsCtrl* c, int parity, int fanout, int64_t cand_cap, unsigned long long* tie_seg,
-                       uint32_t* send_counts, int world, cudaStream_t st);
+                       uint32_t* send_counts, uint32_t* recv_counts, int world, cudaStream_t st);
 int launch_band_hist(const StepArgs& a, int64_t items, int sms, cudaStream_t st);
 int launch_band_insert(const StepArgs& a, int64_t items, int sms, cudaStream_t st);
 int launch_final_hist(const StepArgs& a, int64_t slots, int sms, cudaStream_t st);
 int launch_emit(const StepArgs& a, int64_t items, int sms, cudaStream_t st);
 int launch_finish(const StepArgs& a, cudaStream_t st);
 int launch_route(const RouteArgs& a, int64_t items, int sms, cudaStream_t st);
+int launch_route_band(const StepArgs& a, const RouteArgs& r, int64_t items, int sms, cudaStream_t st);
 SymLayout sym_layout(const MgbsConfig& c, int band_levels_effective);
 int launch_repack_rows(const uint8_t* src, uint8_t* dst, int64_t rows, int src_pitch, int dst_pitch, int n, int sms,
                        cudaStream_t st);

@@ -442,6 +442,9 @@ __device__ void peer_allreduce_hist(const StepArgs& a) {
 __global__ void __launch_bounds__(kStreamThreads) k_band_hist(StepArgs a) {
   __shared__ uint32_t sh[MGBS_RADIX_BINS];
   for (int b = threadIdx.x; b < MGBS_RADIX_BINS; b += blockDim.x) sh[b] = 0;
+  // an earlier round found the pool complete (from summed statistics, so every rank agrees): nothing left to do,
+  // not even the reduction
+  if (a.ctrl->bands_done) return;
   const uint64_t D = a.ctrl->band_lo[a.round];
   MgbsRadix st = radix_zero();
   if (a.level == 0) {
@@ -466,11 +469,11 @@ __global__ void __launch_bounds__(kStreamThreads) k_band_hist(StepArgs a) {
   const bool any_prefix = st.bits_done != 0;
   const uint64_t pfx = any_prefix ? (st.prefix >> pshift) : 0;
   const int hb = a.hash_bits;
-  for_each_candidate(a.cv, [&](uint64_t i, bool valid) {
+  for_each_candidate(a.cvh, [&](uint64_t i, bool valid) {
     bool in = false;
     uint32_t digit = 0;
     if (valid) {
-      const uint64_t s = order_key(__ldg(a.cv.score + i), __ldg(a.cv.hash + i), hb);
+      const uint64_t s = order_key(__ldg(a.cvh.score + i), __ldg(a.cvh.hash + i), hb);
       in = s >= D && (!any_prefix || (s >> pshift) == pfx);
       digit = (uint32_t)(s >> shift) & mask;
     }
@@ -544,6 +547,10 @@ __device__ __forceinline__ const Slot* table_find(const Slot* table, uint64_t ca
 // Insert the band [D, E) of candidates.  The prologue consumes the last band-level histogram to get E.
 __global__ void __launch_bounds__(kStreamThreads) k_band_insert(StepArgs a) {
   const uint64_t D = a.ctrl->band_lo[a.round];
+  if (a.ctrl->bands_done) {  // set by an earlier round of this depth
+    if (blockIdx.x == 0 && threadIdx.x == 0) a.ctrl->band_lo[a.round + 1] = D;
+    return;
+  }
   MgbsRadix st;
   if (a.levels == 1) st = band_initial(a, a.hist_prev, D);
   else st = a.ctrl->band[a.round][a.levels - 1];
@@ -647,6 +654,36 @@ __device__ __forceinline__ void emit_row(const StepArgs& a, uint64_t i, uint32_t
   if (a.cv.states) {
     const uint4* src = reinterpret_cast<const uint4*>(a.cv.states + i * (uint64_t)a.stride);
     for (int q = 0; q < vecs; ++q) dst[q] = __ldg(src + q);
+  } else if (a.peer.enabled) {
+    // the record travelled without its state: fetch the parent row from the rank that expanded it (its current
+    // frontier is mapped here; nobody writes that buffer before the next depth's histograms have been summed over
+    // all ranks) with 16-byte loads, then apply the move
+    uint32_t parent, rank, move;
+    unpack_payload(payload, parent, rank, move);
+    const uint4* src = reinterpret_cast<const uint4*>(a.peer.base[rank] + a.off_frontier_cur + (int64_t)parent * a.stride);
+    uint32_t row[MGBS_MAX_STATE_LEN / 4];
+    for (int q = 0; q < vecs; ++q) {
+      const uint4 v = __ldcg(src + q);
+      row[4 * q] = v.x; row[4 * q + 1] = v.y; row[4 * q + 2] = v.z; row[4 * q + 3] = v.w;
+    }
+    const uint8_t* g = a.gens + (int64_t)move * a.n;
+    for (int q = 0; q < vecs; ++q) {
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t acc = 0;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int idx = q * 16 + j * 4 + b;
+          if (idx < a.n) {
+            const uint32_t sidx = __ldg(g + idx);
+            acc |= ((row[sidx >> 2] >> (8 * (sidx & 3u))) & 0xffu) << (8 * b);
+          }
+        }
+        w[j] = acc;
+      }
+      dst[q] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
   } else {
     // regenerate the child from its parent row (world = 1: the parent is local)
     uint32_t parent, rank, move;
@@ -782,7 +819,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_finish(StepArgs a) {
 
 // One thread: open the depth.
 __global__ void k_depth_begin(MgbsCtrl* c, int parity, int fanout, int64_t cand_cap, unsigned long long* tie_seg,
-                              uint32_t* send_counts, int world) {
+                              uint32_t* send_counts, uint32_t* recv_counts, int world) {
   if (blockIdx.x != 0 || threadIdx.x != 0) return;
   int64_t cand = (int64_t)c->frontier_count[parity] * fanout;
   if (cand > cand_cap) cand = cand_cap;
@@ -800,6 +837,11 @@ __global__ void k_depth_begin(MgbsCtrl* c, int parity, int fanout, int64_t cand_
   tie_seg[0] = 0;
   if (send_counts)
     for (int r = 0; r < world; ++r) send_counts[r] = 0;
+  // peer mode: this rank's receive fills of the depth (senders rewrite them after every band they route; no sender
+  // can be that far before this rank has contributed to the depth's first histogram sum, which comes later in
+  // this stream)
+  if (recv_counts)
+    for (int r = 0; r < world; ++r) recv_counts[r] = 0;
 }
 
 // world > 1: bucket this rank's candidates by owner = hash mod world (beam_kernels.cu:582) into the send arrays.
@@ -841,69 +883,81 @@ __global__ void __launch_bounds__(kStreamThreads) k_route(RouteArgs a) {
   }
 }
 
-// MGBS_EXCHANGE_PEER: the same bucketing, fused with the exchange.  Every record is stored straight into bucket
-// [this rank] of its owner's receive arrays through the peer mapping (plain stores over NVLink; the position comes
-// from this rank's own per-destination cursor, so no remote atomics).  The block that finishes last publishes the
-// bucket fills and this rank's flag to every owner, then waits - with a limit - until every sender has flagged this
-// rank, so that when the kernel ends the receive buckets of this depth are complete.
-__global__ void __launch_bounds__(kStreamThreads) k_route_peer(RouteArgs a) {
+// MGBS_EXCHANGE_PEER routing of one band.  The band histograms were counted where the candidates were generated
+// and summed over ranks, so every rank derives the same band [D, E) here.  Each candidate of this rank inside the
+// band goes to its owner as a 24-byte record (hash, fingerprint, score, back-pointer; the owner rebuilds the
+// survivors' states from the back-pointers afterwards), appended to bucket [this rank] in the owner's symmetric
+// region over NVLink; positions come from this rank's own per-destination cursor, which keeps growing over the
+// rounds of a depth, so no remote atomics.  Only ~pool_target * duplicate ratio records cross the links instead of
+// every candidate with its state.  The block that finishes last publishes the cursors and this rank's flag
+// (epoch * 16 + round) to every owner, then waits - with a limit - until every sender has flagged this rank, so
+// that when the kernel ends the receive buckets hold the whole band.
+__global__ void __launch_bounds__(kStreamThreads) k_route_band(StepArgs a, RouteArgs r) {
   __shared__ int s_last;
+  if (a.ctrl->bands_done) return;
+  const uint64_t D = a.ctrl->band_lo[a.round];
+  MgbsRadix st;
+  if (a.levels == 1) st = band_initial(a, a.hist_prev, D);
+  else st = a.ctrl->band[a.round][a.levels - 1];
+  st = band_advance(st, a.hist_prev, a.key_bits, true, D);
+  const uint64_t E = st.result;
+  if (E <= D) return;  // same decision on every rank: nobody sends, nobody waits
   const uint32_t cnt = a.ctrl->cand_count;
   const uint32_t rounded = (cnt + 31u) & ~31u;
   const int lane = threadIdx.x & 31;
-  const int vecs = a.stride >> 4;
+  const int hb = a.hash_bits;
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < rounded; i += gridDim.x * blockDim.x) {
-    const bool valid = i < cnt;
+    bool in = false;
     uint64_t h = 0;
-    uint32_t owner = 0;
-    if (valid) {
-      h = __ldg(a.hash + i);
-      owner = (uint32_t)(h % (uint64_t)a.world);
+    uint32_t k = 0, owner = 0;
+    if (i < cnt) {
+      h = __ldg(r.hash + i);
+      k = __ldg(r.score + i);
+      const uint64_t s = order_key(k, h, hb);
+      in = s >= D && s < E;
+      owner = (uint32_t)(h % (uint64_t)r.world);
     }
-    const unsigned vm = __ballot_sync(0xffffffffu, valid);
-    if (!valid) continue;
+    const unsigned vm = __ballot_sync(0xffffffffu, in);
+    if (!in) continue;
     const unsigned peers = __match_any_sync(vm, owner);
     const int leader = __ffs(peers) - 1;
     uint32_t base = 0;
-    if (lane == leader) base = atomicAdd(&a.send_counts[owner], (uint32_t)__popc(peers));
+    if (lane == leader) base = atomicAdd(&r.send_counts[owner], (uint32_t)__popc(peers));
     base = __shfl_sync(peers, base, leader);
     const uint32_t pos = base + __popc(peers & ((1u << lane) - 1u));
-    if (pos >= a.bucket_cap) {
+    if (pos >= r.bucket_cap) {
       atomicOr(&a.ctrl->status, MGBS_ST_BUCKET_OVERFLOW);
       continue;
     }
-    uint8_t* ob = a.peer.base[owner];
-    const uint64_t d = (uint64_t)a.rank * a.bucket_cap + pos;
-    reinterpret_cast<uint64_t*>(ob + a.off_hash)[d] = h;
-    reinterpret_cast<uint64_t*>(ob + a.off_fp)[d] = __ldg(a.fp + i);
-    reinterpret_cast<uint32_t*>(ob + a.off_score)[d] = __ldg(a.score + i);
-    reinterpret_cast<uint32_t*>(ob + a.off_payload)[d] = __ldg(a.payload + i);
-    const uint4* src = reinterpret_cast<const uint4*>(a.states + (uint64_t)i * a.stride);
-    uint4* dst = reinterpret_cast<uint4*>(ob + a.off_states + d * a.stride);
-    for (int q = 0; q < vecs; ++q) dst[q] = __ldg(src + q);
+    uint8_t* ob = r.peer.base[owner];
+    const uint64_t d = (uint64_t)r.rank * r.bucket_cap + pos;
+    reinterpret_cast<uint64_t*>(ob + r.off_hash)[d] = h;
+    reinterpret_cast<uint64_t*>(ob + r.off_fp)[d] = __ldg(r.fp + i);
+    reinterpret_cast<uint32_t*>(ob + r.off_score)[d] = k;
+    reinterpret_cast<uint32_t*>(ob + r.off_payload)[d] = __ldg(r.payload + i);
   }
   // completion: all of this rank's stores are ordered before its flag
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
-    const unsigned t = atomicAdd(&a.peer.tickets[a.peer.slot], 1u);
+    const unsigned t = atomicAdd(&r.peer.tickets[r.peer.slot], 1u);
     s_last = ((t + 1u) % gridDim.x) == 0u;
   }
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  const uint32_t epoch = a.ctrl->epoch;
-  if ((int)threadIdx.x < a.world) {
-    const int r = threadIdx.x;
-    uint32_t fill = *reinterpret_cast<volatile uint32_t*>(&a.send_counts[r]);
-    if (fill > a.bucket_cap) fill = a.bucket_cap;
-    *reinterpret_cast<volatile uint32_t*>(a.peer.base[r] + a.off_counts + 4 * a.rank) = fill;
+  const uint32_t want = a.ctrl->epoch * 16u + (uint32_t)a.round;
+  if ((int)threadIdx.x < r.world) {
+    const int q = threadIdx.x;
+    uint32_t fill = *reinterpret_cast<volatile uint32_t*>(&r.send_counts[q]);
+    if (fill > r.bucket_cap) fill = r.bucket_cap;
+    *reinterpret_cast<volatile uint32_t*>(r.peer.base[q] + r.off_counts + 4 * r.rank) = fill;
     __threadfence_system();
-    *reinterpret_cast<volatile uint32_t*>(a.peer.base[r] + a.off_route_flag + 4 * a.rank) = epoch;
-    volatile uint32_t* mine = reinterpret_cast<volatile uint32_t*>(a.peer.base[a.rank] + a.off_route_flag + 4 * r);
+    *reinterpret_cast<volatile uint32_t*>(r.peer.base[q] + r.off_route_flag + 4 * r.rank) = want;
+    volatile uint32_t* mine = reinterpret_cast<volatile uint32_t*>(r.peer.base[r.rank] + r.off_route_flag + 4 * q);
     bool ok = false;
     for (uint32_t it = 0; it < (1u << 22); ++it) {
-      if ((int32_t)(*mine - epoch) >= 0) { ok = true; break; }
+      if ((int32_t)(*mine - want) >= 0) { ok = true; break; }
       if (it > 256) __nanosleep(200);
     }
     if (!ok) atomicOr(&a.ctrl->status, MGBS_ST_PEER_TIMEOUT);
@@ -947,9 +1001,9 @@ SymLayout sym_layout(const MgbsConfig& c, int band_levels_effective) {
     L.fp[p] = off;      off += align256(W * cap * 8);
     L.score[p] = off;   off += align256(W * cap * 4);
     L.payload[p] = off; off += align256(W * cap * 4);
-    L.states[p] = off;  off += align256(W * cap * c.state_stride);
     L.counts[p] = off;  off += align256(W * 4);
   }
+  for (int p = 0; p < 2; ++p) { L.frontier[p] = off; off += align256(c.frontier_cap * (int64_t)c.state_stride); }
   L.route_flag = off; off += align256(W * 4);
   L.slots = c.band_rounds * band_levels_effective + MGBS_MAX_LEVELS;
   L.hx = off;         off += align256((int64_t)L.slots * W * MGBS_HIST_STRIDE * 4);
@@ -982,8 +1036,8 @@ int launch_expand(const ExpandArgs& a, int64_t max_parents, int sms, cudaStream_
 }
 
 int launch_depth_begin(MgbsCtrl* c, int parity, int fanout, int64_t cand_cap, unsigned long long* tie_seg,
-                       uint32_t* send_counts, int world, cudaStream_t st) {
-  k_depth_begin<<<1, 32, 0, st>>>(c, parity, fanout, cand_cap, tie_seg, send_counts, world);
+                       uint32_t* send_counts, uint32_t* recv_counts, int world, cudaStream_t st) {
+  k_depth_begin<<<1, 32, 0, st>>>(c, parity, fanout, cand_cap, tie_seg, send_counts, recv_counts, world);
   return (int)cudaGetLastError();
 }
 
@@ -1013,8 +1067,12 @@ int launch_finish(const StepArgs& a, cudaStream_t st) {
 }
 
 int launch_route(const RouteArgs& a, int64_t items, int sms, cudaStream_t st) {
-  if (a.peer.enabled) k_route_peer<<<grid_for(items, sms), kStreamThreads, 0, st>>>(a);
-  else k_route<<<grid_for(items, sms), kStreamThreads, 0, st>>>(a);
+  k_route<<<grid_for(items, sms), kStreamThreads, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
+int launch_route_band(const StepArgs& a, const RouteArgs& r, int64_t items, int sms, cudaStream_t st) {
+  k_route_band<<<grid_for(items, sms), kStreamThreads, 0, st>>>(a, r);
   return (int)cudaGetLastError();
 }
 

@@ -78,6 +78,10 @@ def test_engine_create_rejects_bad_configs_without_a_gpu():
     assert lib.mgbs_engine_create(C.byref(c), C.byref(h)) == -1  # stride smaller than the state
     nb, nt = C.c_int64(0), C.c_int64(0)
     c.state_stride, c.world_size, c.bucket_cap, c.band_rounds, c.band_levels, c.hash_bits = 64, 4, 1000, 3, 3, 44
+    c.frontier_cap = 500
     assert lib.mgbs_sym_bytes(C.byref(c), C.byref(nb), C.byref(nt)) == 0
-    # two parities of (hash, fp, score, payload, rows) buckets + counts + flags + histogram slots
-    assert nb.value > 2 * 4 * 1000 * (8 + 8 + 4 + 4 + 64) and nt.value == 3 * 3 + 6 + 1
+    # two parities of (hash, fp, score, payload) record buckets + two frontier buffers + counts, flags, histogram slots
+    assert nb.value > 2 * 4 * 1000 * (8 + 8 + 4 + 4) + 2 * 500 * 64 and nt.value == 3 * 3 + 6 + 1
+    offs = (C.c_int64 * 2)()
+    assert lib.mgbs_sym_frontier_offsets(C.byref(c), offs) == 0
+    assert offs[0] % 256 == 0 and offs[1] - offs[0] >= 500 * 64 and offs[1] + 500 * 64 <= nb.value
