@@ -26,7 +26,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, beam, hash_bits, out_q):
+def _worker(rank, world, port, beam, hash_bits, out_q, band_routed=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -41,17 +41,17 @@ def _worker(rank, world, port, beam, hash_bits, out_q):
         mv = np.tile(np.arange(pz.fanout, dtype=np.uint32), mine.shape[0])
         cand = sm.Candidates(children, bo.hash64(children), bo.fingerprint64(children),
                              bo.hamming(children, pz.solved), bo.pack_payload(pidx, np.full_like(pidx, rank), mv))
-        # exchange: bucket r goes to rank r
-        buckets = sm.route(cand, world)
-        recv = [None] * world
-        dist.all_to_all_object_list(recv, buckets) if hasattr(dist, "all_to_all_object_list") else None
-        if recv[0] is None:
+        def exchange(buckets):
+            """bucket r goes to rank r; returns the buckets sent here"""
             gathered = [None] * world
             dist.all_gather_object(gathered, buckets)
-            recv = [gathered[src][rank] for src in range(world)]
-        local = sm.Candidates(*(np.concatenate([getattr(b, f) for b in recv])
-                                for f in ("states", "h", "fp", "score", "payload")))
-        assert (bo.owner_rank(local.h, world) == rank).all()
+            return [gathered[src][rank] for src in range(world)]
+
+        if not band_routed:
+            recv = exchange(sm.route(cand, world))
+            local = sm.Candidates(*(np.concatenate([getattr(b, f) for b in recv])
+                                    for f in ("states", "h", "fp", "score", "payload")))
+            assert (bo.owner_rank(local.h, world) == rank).all()
 
         def allreduce_sum(a):
             t = torch.from_numpy(np.ascontiguousarray(a, dtype=np.int64))
@@ -66,8 +66,15 @@ def _worker(rank, world, port, beam, hash_bits, out_q):
         n_local = (beam + world - 1) // world
         pool_target = int(1.2 * n_local + 0.5)
         hash_capacity = max(1024, int(1.2 * 1.25 * n_local / 0.45 + 0.5))
-        keep, stats = sm.sharded_select(local, beam, world, pool_target, hash_capacity, allreduce_sum, allgather,
-                                        hash_bits=hash_bits)
+        if band_routed:
+            local, keep, stats = sm.sharded_select(cand, beam, world, pool_target, hash_capacity, allreduce_sum,
+                                                   allgather, hash_bits=hash_bits, band_exchange=exchange)
+            assert (bo.owner_rank(local.h, world) == rank).all()
+            stats["received"] = int(local.h.shape[0])
+            stats["generated"] = int(cand.h.shape[0])
+        else:
+            keep, stats = sm.sharded_select(local, beam, world, pool_target, hash_capacity, allreduce_sum, allgather,
+                                            hash_bits=hash_bits)
         survivors = allgather((local.states[keep], local.payload[keep]))
         if rank == 0:
             fronts = [rows[own == r] for r in range(world)]
@@ -96,3 +103,22 @@ def test_sharded_selection_equals_single_rank_oracle(world, beam, hash_bits):
     ok, stats, count = q.get(timeout=10)
     assert ok, (stats, count)
     assert stats["stalls"] == 0
+
+
+@pytest.mark.parametrize("world,beam,hash_bits", [(2, 300, 24), (2, 64, 2), (3, 500, 44)])
+def test_band_routed_selection_equals_single_rank_oracle(world, beam, hash_bits):
+    """The peer-exchange order of operations: histograms where the candidates were generated, then only the band
+    travels.  Same survivors as the single-rank oracle, and fewer records cross than were generated."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, beam, hash_bits, q, True)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+        assert p.exitcode == 0
+    ok, stats, count = q.get(timeout=10)
+    assert ok, (stats, count)
+    assert stats["stalls"] == 0
+    assert stats["received"] < stats["generated"]
