@@ -271,12 +271,17 @@ def run_ours(args):
     pinned_in = torch.empty((rows_dev.shape[0], n), dtype=torch.uint8).pin_memory()
     pinned_in.numpy()[:] = rows_dev
     depth0 = engine.status()["depth"]
+    pinned_out = torch.empty((sizes["k_work"], n), dtype=torch.uint8).pin_memory()
     e2e_steps = max(3, min(K, 10))
+    # untimed: the stage timers above ran eager steps and dropped the captured graphs; capture them again first
+    for i in range(2):
+        engine.load_frontier(pinned_in.numpy(), depth=(depth0 + i) % 2)
+        engine.step()
+        engine.frontier_into(pinned_out.numpy())
     barrier()
     t0 = time.perf_counter()
     e2e_cands = 0
     d2h = 0
-    pinned_out = torch.empty((sizes["k_work"], n), dtype=torch.uint8).pin_memory()
     for i in range(e2e_steps):
         engine.load_frontier(pinned_in.numpy(), depth=depth0 % 2)  # host rows -> device (syncs)
         engine.step()
