@@ -198,6 +198,175 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
 }
 
 // ------------------------------------------------------------------------------------------------
+// Layer 2 + scalar head on CTA pairs (thread-block clusters of two, tcgen05 cta_group::2).
+//
+// With one CTA per tile every 128 x 256 x 16 MMA reads 4 KB of A and 8 KB of B from shared memory in the 128
+// cycles it takes: 96 of the 128 bytes per clock the shared-memory port gives, and the TMA fills of the next
+// K-blocks need 48 KB per four MMAs on top.  The port, not the tensor core, then bounds the kernel at about two
+// thirds of the tensor peak.  A pair of CTAs shares B: each CTA loads its own 128 rows of A and HALF of the 256
+// weight rows of the chunk, the even CTA issues one MMA of M = 256 that reads both CTAs' shared memory and
+// writes each CTA's 128 accumulator rows into that CTA's TMEM.  Per CTA that is 8 KB of operand reads per MMA
+// and 32 KB of fills per K-block: two thirds of the traffic.
+//
+// q[row] (+)= sum_n relu(acc[row, n] * col_scale[n] + bias[n]) * w_out[n]  (col_scale for e4m3 operands only).
+// Warps of each CTA: 0 = TMA (own A rows, own half of B; completion bytes are counted on the even CTA's barrier),
+// 1 = TMEM allocation, and in the even CTA MMA issue; 2..5 = epilogue for the CTA's own 128 rows.
+// Barriers: full[s] lives in the even CTA (its TMA thread arms it with the bytes of both CTAs); empty[s] and
+// tmem_full[b] exist in both CTAs and are signalled by multicast commits; tmem_empty[b] lives in the even CTA and
+// counts the eight epilogue warps of the pair.
+// ------------------------------------------------------------------------------------------------
+
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_STAGE_BYTES = 2 * A_BYTES;  // 128 x 128-byte rows of A + 128 x 128-byte rows of B
+constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+
+template <int F8>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+k_mlp_head_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PAIR_STAGES * PAIR_STAGE_BYTES);
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * PAIR_STAGES + 5);
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (PAIR_STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * PAIR_STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * PAIR_STAGES + 2 + b); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * PAIR_STAGES + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t crank = cluster_ctarank();  // 0 = even CTA (issues the MMAs), 1 = its peer
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs_grid = gridDim.x >> 1;
+
+  int64_t rows = (int64_t)(*g.count_dev) - g.row_offset;
+  if (rows > g.row_limit) rows = g.row_limit;
+  if (rows < 0) rows = 0;
+  const int num_ptiles = (int)((rows + 2 * BM - 1) / (2 * BM));  // tiles of 256 rows
+  const int n_chunks = g.n_total / BN;
+  constexpr int BKE = F8 ? BK8 : BK;
+  const int k_blocks = g.k_total / BKE;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PAIR_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 8); }
+    mbar_init(drain_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    // both CTAs' warp 1 take part; each CTA finds the (same) base address in its own slot
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_base_slot);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int pt = pair_id; pt < num_ptiles && ok; pt += num_pairs_grid) {
+        const int row0 = (int)(g.row_offset + (int64_t)pt * 2 * BM + (int64_t)crank * BM);
+        for (int nc = 0; nc < n_chunks && ok; ++nc) {
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+            const uint32_t sa = smem_u32(smem + stage * PAIR_STAGE_BYTES);
+            if (crank == 0) mbar_expect_tx(full_bar(stage), 2 * PAIR_STAGE_BYTES);  // both CTAs' boxes
+            tma_load_2d_pair(sa, &tmA, kb * BKE, row0, full_bar(stage));
+            tma_load_2d_pair(sa + A_BYTES, &tmB, kb * BKE, nc * BN + (int)crank * (BN / 2), full_bar(stage));
+            if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && crank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_it = 0;
+      bool ok = true;
+      for (int pt = pair_id; pt < num_ptiles && ok; pt += num_pairs_grid) {
+        for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
+          const uint32_t b = acc_it & 1u;
+          if (!mbar_wait(tempty_bar(b), ((acc_it >> 1) & 1u) ^ 1u, g.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + b * BN;
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + stage * PAIR_STAGE_BYTES);
+            const uint64_t adesc = make_desc_sw128(sa);
+            const uint64_t bdesc = make_desc_sw128(sa + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              tc_mma_pair<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
+            tc_commit_pair(empty_bar(stage), (uint16_t)3);  // both CTAs may refill this stage
+            if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
+          }
+          if (ok) tc_commit_pair(tfull_bar(b), (uint16_t)3);  // both CTAs' epilogues may read their rows
+        }
+      }
+      tc_commit_pair(drain_bar, (uint16_t)1);
+      mbar_wait(drain_bar, 0, g.err, ERR_WAIT_DRAIN);
+    }
+  } else {
+    const int quad = warp & 3;
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int pt = pair_id; pt < num_ptiles && ok; pt += num_pairs_grid) {
+      const int64_t row_local = (int64_t)pt * 2 * BM + (int64_t)crank * BM + quad * 32 + lane;
+      const int64_t row = g.row_offset + row_local;
+      const bool row_ok = row_local < rows;
+      float rowsum = 0.f;
+      for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
+        const uint32_t b = acc_it & 1u;
+        if (!mbar_wait(tfull_bar(b), (acc_it >> 1) & 1u, g.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tc_ld32(taddr + c0, v);
+          tc_wait_ld();
+          const int n0 = nc * BN + c0;
+#pragma unroll
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 bq = __ldg(reinterpret_cast<const float4*>(g.bias + n0) + j4);
+            const float4 wq = __ldg(reinterpret_cast<const float4*>(g.w_out + n0) + j4);
+            float4 cq = make_float4(1.f, 1.f, 1.f, 1.f);
+            if (F8) cq = __ldg(reinterpret_cast<const float4*>(g.col_scale + n0) + j4);
+            rowsum = fmaf(fmaxf(fmaf(__uint_as_float(v[4 * j4]), cq.x, bq.x), 0.f), wq.x, rowsum);
+            rowsum = fmaf(fmaxf(fmaf(__uint_as_float(v[4 * j4 + 1]), cq.y, bq.y), 0.f), wq.y, rowsum);
+            rowsum = fmaf(fmaxf(fmaf(__uint_as_float(v[4 * j4 + 2]), cq.z, bq.z), 0.f), wq.z, rowsum);
+            rowsum = fmaf(fmaxf(fmaf(__uint_as_float(v[4 * j4 + 3]), cq.w, bq.w), 0.f), wq.w, rowsum);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_even_cta(tempty_bar(b));
+      }
+      if (row_ok && ok) {
+        if (g.accumulate_q) g.out_q[row] += rowsum;
+        else g.out_q[row] = rowsum;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still read its shared memory or signal its barriers
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // Layer 1 with the one-hot operand built in shared memory.
 //
 // out[row, :] = bf16(relu(onehot(child[row]) * W1^T + b1)).  The A operand is never materialised in global
@@ -212,6 +381,22 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
 //
 // Warps: 0 = TMA (W1), 1 = MMA + TMEM owner, then EW epilogue warps, then 12 - EW one-hot producer warps.
 // ------------------------------------------------------------------------------------------------
+
+// max(x, 0) rounded to bf16, two values per 32-bit word (lo in bits 0..15)
+__device__ __forceinline__ uint32_t pack_relu_bf16(float lo, float hi) {
+  uint32_t d;
+  asm("cvt.rn.relu.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+
+#ifdef MGBS_L1_PROBE
+__device__ unsigned long long g_l1_probe[8];
+#define PROBE_T0() const long long _p0 = clock64()
+#define PROBE_ADD(i) atomicAdd(&g_l1_probe[i], (unsigned long long)(clock64() - _p0))
+#else
+#define PROBE_T0()
+#define PROBE_ADD(i)
+#endif
 
 constexpr int L1_THREADS = 448;
 constexpr int L1_A_STAGES = 6;                           // 6 x 16 KB: a whole 128 x 384 one-hot tile when K <= 384
@@ -310,21 +495,30 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
   } else if (warp == 1) {
     // ---- MMA issue ----
     if (lane == 0) {
+#ifdef MGBS_L1_PROBE
+      const long long _pstart = clock64();
+#endif
       int sb = 0;
       uint32_t pb = 0, acc_it = 0, it_base = 0;
       bool ok = true;
       for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x, it_base += (uint32_t)blocks_per_tile) {
         for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
           const uint32_t b = acc_it & 1u;
+          { PROBE_T0();
           if (!mbar_wait(tempty_bar(b), ((acc_it >> 1) & 1u) ^ 1u, g.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          PROBE_ADD(0); }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + b * BN;
           for (int kb = 0; kb < k_blocks; ++kb) {
             const uint32_t it = it_base + (uint32_t)(resident ? kb : nc * k_blocks + kb);
             const int sa = (int)(it % L1_A_STAGES);
             // resident tile: N-chunks after the first find the phase already complete
+            { PROBE_T0();
             if (!mbar_wait(a_full(sa), (it / L1_A_STAGES) & 1u, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+            PROBE_ADD(1); }
+            { PROBE_T0();
             if (!mbar_wait(b_full(sb), pb, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+            PROBE_ADD(2); }
             tc_fence_after();
             const uint64_t adesc = make_desc_sw128(smem_u32(a_ring + sa * A_BYTES));
             const uint64_t bdesc = make_desc_sw128(smem_u32(b_ring + sb * B_BYTES));
@@ -340,6 +534,9 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
       }
       tc_commit(drain_bar);
       mbar_wait(drain_bar, 0, g.err, ERR_WAIT_DRAIN);
+#ifdef MGBS_L1_PROBE
+      atomicAdd(&g_l1_probe[3], (unsigned long long)(clock64() - _pstart));
+#endif
     }
   } else if (warp < 2 + EW) {
     // ---- epilogue: TMEM -> bias, ReLU, bf16 -> swizzled staging box -> TMA store ----
@@ -353,9 +550,71 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
       const int row0 = mt * BM;
       for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
         const uint32_t b = acc_it & 1u;
+        { PROBE_T0();
         if (!mbar_wait(tfull_bar(b), (acc_it >> 1) & 1u, g.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        if (warp == 2 && lane == 0) PROBE_ADD(4); }
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * BN;
+        if constexpr (EW == 4) {
+          // private staging: each warp owns two boxes of 32 rows x 64 bytes (64-byte swizzle) for its TMEM lane
+          // quadrant and alternates between them, so filling one overlaps the TMA store reading the other and
+          // no barrier between warps is needed.  (Storing straight from registers, 32 bytes per thread and row,
+          // measured 8 % slower for the whole scorer than these TMA stores of full rows.)
+          constexpr int SUBC = F8 ? 64 : 32;  // output columns per 64-byte box row
+          uint8_t* mybuf = staging + (warp - 2) * 4096;
+#pragma unroll 1
+          for (int gcol = 0; gcol < BN; gcol += SUBC, ++box_it) {
+            uint8_t* box = mybuf + (box_it & 1u) * 2048;
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
+            uint32_t packed[16];
+            if (F8) {
+#pragma unroll
+              for (int sub = 0; sub < 2; ++sub) {
+                uint32_t v[32];
+                tc_ld32(taddr + gcol + sub * 32, v);
+                tc_wait_ld();
+                const int n0 = nc * BN + gcol + sub * 32;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float4 cq = __ldg(reinterpret_cast<const float4*>(g.col_scale + n0) + j);
+                  const float4 bq = __ldg(reinterpret_cast<const float4*>(g.bias + n0) + j);
+                  float x[4];
+                  x[0] = fmaxf(fmaf(__uint_as_float(v[4 * j]), cq.x, bq.x), 0.f) * g.out_inv_scale;
+                  x[1] = fmaxf(fmaf(__uint_as_float(v[4 * j + 1]), cq.y, bq.y), 0.f) * g.out_inv_scale;
+                  x[2] = fmaxf(fmaf(__uint_as_float(v[4 * j + 2]), cq.z, bq.z), 0.f) * g.out_inv_scale;
+                  x[3] = fmaxf(fmaf(__uint_as_float(v[4 * j + 3]), cq.w, bq.w), 0.f) * g.out_inv_scale;
+                  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(x[0], x[1]), __NV_SATFINITE, __NV_E4M3);
+                  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(x[2], x[3]), __NV_SATFINITE, __NV_E4M3);
+                  packed[sub * 8 + j] = lo | (hi << 16);
+                }
+              }
+            } else {
+              uint32_t v[32];
+              tc_ld32(taddr + gcol, v);
+              tc_wait_ld();
+              const int n0 = nc * BN + gcol;
+#pragma unroll
+              for (int j4 = 0; j4 < 8; ++j4) {
+                const float4 bq = __ldg(reinterpret_cast<const float4*>(g.bias + n0) + j4);
+                packed[2 * j4] = pack_relu_bf16(__uint_as_float(v[4 * j4]) + bq.x, __uint_as_float(v[4 * j4 + 1]) + bq.y);
+                packed[2 * j4 + 1] = pack_relu_bf16(__uint_as_float(v[4 * j4 + 2]) + bq.z, __uint_as_float(v[4 * j4 + 3]) + bq.w);
+              }
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              // 64-byte swizzle: 16-byte chunk index ^= (row / 2) mod 4 inside 512-byte atoms
+              const uint32_t off = (uint32_t)lane * 64u + (((uint32_t)q ^ (((uint32_t)lane >> 1) & 3u)) << 4);
+              *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmOut, smem_u32(box), nc * BN + gcol, row0 + quad * 32);
+              asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            }
+          }
+        } else {
 #pragma unroll 1
         for (int gcol = 0; gcol < BN; gcol += BKE, ++box_it) {  // one box = 128 bytes per row
           uint8_t* box = staging;
@@ -373,12 +632,13 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
               uint32_t packed[8];
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
+                const float4 cq = __ldg(reinterpret_cast<const float4*>(g.col_scale + n0) + j);
+                const float4 bq = __ldg(reinterpret_cast<const float4*>(g.bias + n0) + j);
                 float x[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const int c = 4 * j + e;
-                  x[e] = fmaxf(__uint_as_float(v[c]) * __ldg(g.col_scale + n0 + c) + __ldg(g.bias + n0 + c), 0.f) * g.out_inv_scale;
-                }
+                x[0] = fmaxf(fmaf(__uint_as_float(v[4 * j]), cq.x, bq.x), 0.f) * g.out_inv_scale;
+                x[1] = fmaxf(fmaf(__uint_as_float(v[4 * j + 1]), cq.y, bq.y), 0.f) * g.out_inv_scale;
+                x[2] = fmaxf(fmaf(__uint_as_float(v[4 * j + 2]), cq.z, bq.z), 0.f) * g.out_inv_scale;
+                x[3] = fmaxf(fmaf(__uint_as_float(v[4 * j + 3]), cq.w, bq.w), 0.f) * g.out_inv_scale;
                 const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(x[0], x[1]), __NV_SATFINITE, __NV_E4M3);
                 const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(x[2], x[3]), __NV_SATFINITE, __NV_E4M3);
                 packed[j] = lo | (hi << 16);
@@ -391,11 +651,11 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
             } else {
               uint32_t packed[16];
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const float x0 = fmaxf(__uint_as_float(v[2 * j]) + __ldg(g.bias + n0 + 2 * j), 0.f);
-                const float x1 = fmaxf(__uint_as_float(v[2 * j + 1]) + __ldg(g.bias + n0 + 2 * j + 1), 0.f);
-                __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-                packed[j] = *reinterpret_cast<uint32_t*>(&h);
+              for (int j4 = 0; j4 < 8; ++j4) {
+                // four columns per bias load; ReLU rides in the packing conversion
+                const float4 bq = __ldg(reinterpret_cast<const float4*>(g.bias + n0) + j4);
+                packed[2 * j4] = pack_relu_bf16(__uint_as_float(v[4 * j4]) + bq.x, __uint_as_float(v[4 * j4 + 1]) + bq.y);
+                packed[2 * j4 + 1] = pack_relu_bf16(__uint_as_float(v[4 * j4 + 2]) + bq.z, __uint_as_float(v[4 * j4 + 3]) + bq.w);
               }
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
@@ -411,12 +671,13 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         }
+        }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty_bar(b));
       }
     }
-    if (et == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (EW == 4 ? lane == 0 : et == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else {
     // ---- one-hot producers: warp pw owns A stage pw and builds K-blocks pw, pw+4, pw+8, ... of the sequence ----
     constexpr int PROD_W = 12 - EW;          // producer warps
@@ -430,6 +691,9 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
     bool ok = true;
     for (int mt = blockIdx.x; mt < num_mtiles; mt += gridDim.x, it_base += (uint32_t)blocks_per_tile) {
       // all producer warps have finished reading the previous tile's child rows
+#ifdef MGBS_L1_PROBE
+      const long long _pc0 = clock64();
+#endif
       asm volatile("bar.sync 2, %0;" ::"n"(PROD_W * 32) : "memory");
       if (pt < BM) {
         const int64_t row = (int64_t)mt * BM + pt;
@@ -445,6 +709,9 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         }
       }
       asm volatile("bar.sync 2, %0;" ::"n"(PROD_W * 32) : "memory");
+#ifdef MGBS_L1_PROBE
+      if (warp == 2 + EW && lane == 0) atomicAdd(&g_l1_probe[7], (unsigned long long)(clock64() - _pc0));
+#endif
       if (!ok) continue;
       // first K-block of this tile that belongs to this warp
       const uint32_t first = (uint32_t)((pw - (int)(it_base & 3u)) & 3);
@@ -453,7 +720,10 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         const int kb = (int)(j % (uint32_t)k_blocks);
         const int slot = (int)(it % L1_A_STAGES);
         uint8_t* a_stage = a_ring + slot * A_BYTES;
+        { PROBE_T0();
         if (!mbar_wait(a_empty(slot), ((it / L1_A_STAGES) & 1u) ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+        if (warp == 2 + EW && lane == 0) PROBE_ADD(5); }
+        PROBE_T0();
         // zero this warp's 64 rows (8 KB, contiguous): consecutive lanes write consecutive 16-byte chunks
         uint4* a4 = reinterpret_cast<uint4*>(a_stage + half * (A_BYTES / WPG));
 #pragma unroll 8
@@ -464,22 +734,42 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         const int p_lo = p_lo_tab[kb];
         int p_hi = p_lo + (BKE + V - 1) / V;  // inclusive upper bound on positions that can reach this block
         if (p_hi > n - 1) p_hi = n - 1;
-#pragma unroll 4
-        for (int pos = p_lo; pos <= p_hi; ++pos) {
-          const int cbase = pos * V - c_lo;
+        // twelve positions at a time (a whole K-block for 64 one-hot columns of 6 values): their bytes sit in four
+        // aligned words of the child row, fetched with independent loads - one shared-memory latency per group;
+        // a load per position would be a chain of dependent loads, each queued behind the tensor cores' operand
+        // reads - then scattered
+#pragma unroll 1
+        for (int pg = p_lo; pg <= p_hi; pg += 12) {
+          const int w_lo = pg >> 2;
+          uint32_t cw[ROWS_W / 32][4];
 #pragma unroll
           for (int rr = 0; rr < ROWS_W / 32; ++rr) {
-            const uint32_t row = (uint32_t)(half * ROWS_W + lane + 32 * rr);
-            const int col = cbase + (int)child_s[row * L1_CHILD_PITCH + pos];
-            if (col >= 0 && col < BKE) {
-              if (F8) a_stage[swz128(row, (uint32_t)col)] = 0x38;  // e4m3 1.0
-              else *reinterpret_cast<uint16_t*>(a_stage + swz128(row, (uint32_t)col * 2u)) = 0x3f80;  // bf16 1.0
+            const uint32_t* crow = reinterpret_cast<const uint32_t*>(child_s + (half * ROWS_W + lane + 32 * rr) * L1_CHILD_PITCH);
+#pragma unroll
+            for (int w = 0; w < 4; ++w) cw[rr][w] = crow[w_lo + w];  // may run past the state bytes: those are not used
+          }
+#pragma unroll
+          for (int t = 0; t < 12; ++t) {
+            const int pos = pg + t;
+            if (pos > p_hi) break;
+            const int cbase = pos * V - c_lo;
+            const int byte = pos - 4 * w_lo;  // 0..14
+#pragma unroll
+            for (int rr = 0; rr < ROWS_W / 32; ++rr) {
+              const uint32_t row = (uint32_t)(half * ROWS_W + lane + 32 * rr);
+              const uint32_t word = (byte >> 2) == 0 ? cw[rr][0] : (byte >> 2) == 1 ? cw[rr][1] : (byte >> 2) == 2 ? cw[rr][2] : cw[rr][3];
+              const int col = cbase + (int)((word >> (8 * (byte & 3))) & 0xffu);
+              if (col >= 0 && col < BKE) {
+                if (F8) a_stage[swz128(row, (uint32_t)col)] = 0x38;  // e4m3 1.0
+                else *reinterpret_cast<uint16_t*>(a_stage + swz128(row, (uint32_t)col * 2u)) = 0x3f80;  // bf16 1.0
+              }
             }
           }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(a_full(slot));
+        if (warp == 2 + EW && lane == 0) PROBE_ADD(6);
       }
     }
   }
@@ -544,7 +834,11 @@ struct MgbsMlp {
   int sms = 148;
   int k1_pad = 0;
   CUtensorMap tm_x, tm_h1;
+  CUtensorMap tm_h1w;  // same tensor, store boxes of one warp: 32 rows x 64 bytes, 64-byte swizzle
   CUtensorMap tm_w1[MGBS_MAX_MODELS], tm_w2[MGBS_MAX_MODELS];
+  CUtensorMap tm_w2h[MGBS_MAX_MODELS];  // W2 in boxes of 128 rows: the half of a chunk one CTA of a pair loads
+  int pair_clusters = 0;                // CTA pairs that can be resident at once (0: pairs unavailable)
+  bool head_pair = true;
   bool fused_l1 = true;
   bool profile = false;
   cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -585,11 +879,13 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
   int rc = 0;
   if (!f8) rc = make_map(&m->tm_x, c.x, rows_pad, (uint64_t)k1_pad, mgbs::BM, eb);
   if (!rc) rc = make_map(&m->tm_h1, c.h1, rows_pad, (uint64_t)c.hidden, mgbs::BM, eb);
+  if (!rc) rc = mgbs::make_map_box(&m->tm_h1w, c.h1, rows_pad, (uint64_t)c.hidden, 32, 64 / eb, eb, 64);
   for (int i = 0; i < c.num_models && !rc; ++i) {
     if (!c.w1[i] || !c.b1[i] || !c.w2[i] || !c.b2[i] || !c.w3[i]) rc = MGBS_ERR_ARG;
     if (!rc && f8 && (!c.s1[i] || !c.s2[i])) rc = MGBS_ERR_ARG;
     if (!rc) rc = make_map(&m->tm_w1[i], c.w1[i], (uint64_t)c.hidden, (uint64_t)k1_pad, mgbs::BN, eb);
     if (!rc) rc = make_map(&m->tm_w2[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden, mgbs::BN, eb);
+    if (!rc) rc = make_map(&m->tm_w2h[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden, mgbs::BN / 2, eb);
   }
   if (f8) m->fused_l1 = true;
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
@@ -598,6 +894,27 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_head_pair<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::PAIR_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_head_pair<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::PAIR_SMEM);
+  if (!rc) {
+    // how many CTA pairs the device can hold at once: the grid of the pair kernel
+    cudaLaunchConfig_t lc;
+    memset(&lc, 0, sizeof(lc));
+    lc.gridDim = dim3(2 * (m->sms / 2));
+    lc.blockDim = dim3(mgbs::GEMM_THREADS);
+    lc.dynamicSmemBytes = mgbs::PAIR_SMEM;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    lc.attrs = at;
+    lc.numAttrs = 1;
+    int nclusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&nclusters, mgbs::k_mlp_head_pair<0>, &lc) == cudaSuccess && nclusters > 0)
+      m->pair_clusters = nclusters < m->sms / 2 ? nclusters : m->sms / 2;
+    else
+      (void)cudaGetLastError();
+    if (m->pair_clusters < 1) m->head_pair = false;
+  }
   if (rc) { delete m; return rc; }
   *out = m;
   return 0;
@@ -608,6 +925,13 @@ int mgbs_mlp_destroy(MgbsMlp* m) {
     for (int i = 0; i < 5; ++i)
       if (m->ev[i]) cudaEventDestroy(m->ev[i]);
   delete m;
+  return 0;
+}
+
+int mgbs_mlp_set_head_mode(MgbsMlp* m, int32_t pair) {
+  if (!m) return MGBS_ERR_ARG;
+  if (pair && m->pair_clusters < 1) return MGBS_ERR_UNSUPPORTED;
+  m->head_pair = pair != 0;
   return 0;
 }
 
@@ -687,11 +1011,11 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
       l.err = c.err;
       const bool resident = m->k1_pad / (c.dtype == 1 ? BK8 : BK) <= L1_A_STAGES;
       if (c.dtype == 1 && resident) k_mlp_l1<1, 8><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
-      else if (c.dtype == 1) k_mlp_l1<1, 4><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
+      else if (c.dtype == 1) k_mlp_l1<1, 4><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
       // bf16 builds six K-blocks per tile: eight producer warps are needed even with the resident tile (measured:
       // 0.69-0.76 ms with 4 epilogue + 8 producer warps against 0.82 ms with 8 + 4 on the 786 432-row case);
       // e4m3 builds three and gains from the wider epilogue
-      else k_mlp_l1<0, 4><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
+      else k_mlp_l1<0, 4><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
     } else {
       k_mlp_gemm<0, 0><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_x, m->tm_w1[i], g);
     }
@@ -703,8 +1027,26 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
     g.out_q = c.q;
     g.accumulate_q = i > 0 ? 1 : 0;
     g.col_scale = c.s2[i];
-    if (c.dtype == 1) k_mlp_gemm<1, 1><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h1, m->tm_w2[i], g);
-    else k_mlp_gemm<1, 0><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h1, m->tm_w2[i], g);
+    if (m->head_pair && m->pair_clusters > 0) {
+      cudaLaunchConfig_t lc;
+      memset(&lc, 0, sizeof(lc));
+      lc.gridDim = dim3(2 * m->pair_clusters);
+      lc.blockDim = dim3(GEMM_THREADS);
+      lc.dynamicSmemBytes = PAIR_SMEM;
+      lc.stream = st;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      lc.attrs = at;
+      lc.numAttrs = 1;
+      cudaError_t le = c.dtype == 1 ? cudaLaunchKernelEx(&lc, k_mlp_head_pair<1>, m->tm_h1, m->tm_w2h[i], g)
+                                    : cudaLaunchKernelEx(&lc, k_mlp_head_pair<0>, m->tm_h1, m->tm_w2h[i], g);
+      if (le != cudaSuccess) return (int)le;
+    } else if (c.dtype == 1) {
+      k_mlp_gemm<1, 1><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h1, m->tm_w2[i], g);
+    } else {
+      k_mlp_gemm<1, 0><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h1, m->tm_w2[i], g);
+    }
     if (prof) cudaEventRecord(m->ev[3], st);
   }
   {
@@ -846,3 +1188,11 @@ extern "C" int mgbs_mlp_score_noalloc(const MgbsMlpNoAllocArgs* a, const uint8_t
   }
   return 0;
 }
+
+#ifdef MGBS_L1_PROBE
+extern "C" int mgbs_l1_probe_read(unsigned long long* out8, int reset) {
+  cudaMemcpyFromSymbol(out8, mgbs::g_l1_probe, 64);
+  if (reset) { unsigned long long z[8] = {0}; cudaMemcpyToSymbol(mgbs::g_l1_probe, z, 64); }
+  return 0;
+}
+#endif

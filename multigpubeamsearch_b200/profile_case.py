@@ -23,6 +23,8 @@ def main() -> None:
     ap.add_argument("--repeat", type=int, default=3)
     ap.add_argument("--scorer", default="mlp", choices=["mlp", "mlp_fp8", "transformer", "transformer_fp8"])
     ap.add_argument("--micro-batch", type=int, default=32768)
+    ap.add_argument("--head", default="pair", choices=["pair", "single"],
+                    help="MLP layer 2 + head on CTA pairs (default) or single CTAs")
     args = ap.parse_args()
     pz = puzzles.puzzle54()
     rng = np.random.default_rng(0)
@@ -40,6 +42,7 @@ def main() -> None:
     else:
         sc = scorers.MLPValueScorer(puzzles.mlp_weights(324, 1024), 54, 64, 6, max_rows=args.rows,
                                     dtype="fp8" if args.scorer == "mlp_fp8" else "bf16")
+        sc.set_head_mode(args.head == "pair")
     times = []
     for _ in range(args.repeat):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -51,6 +51,7 @@ _SIGS = {
     "mgbs_mlp_destroy": (C.c_int, [C.c_void_p]),
     "mgbs_mlp_profile": (C.c_int, [C.c_void_p, C.c_int32]),
     "mgbs_mlp_set_l1_mode": (C.c_int, [C.c_void_p, C.c_int32]),
+    "mgbs_mlp_set_head_mode": (C.c_int, [C.c_void_p, C.c_int32]),
     "mgbs_mlp_profile_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
     "mgbs_mlp_enqueue": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
@@ -188,6 +189,10 @@ class MLPValueScorer:
     def set_l1_mode(self, fused: bool) -> None:
         """Layer 1 with the one-hot operand built in shared memory (default) or as one-hot kernel + plain GEMM."""
         _lib.check(self.lib.mgbs_mlp_set_l1_mode(self._h, int(bool(fused))), "set_l1_mode")
+
+    def set_head_mode(self, pair: bool) -> None:
+        """Layer 2 + head on CTA pairs sharing each weight block (default) or on single CTAs (for comparison)."""
+        _lib.check(self.lib.mgbs_mlp_set_head_mode(self._h, int(bool(pair))), "set_head_mode")
 
     def profile(self, on: bool) -> None:
         """Record CUDA events between the scorer's kernels (eager launches only)."""

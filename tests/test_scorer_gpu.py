@@ -118,6 +118,29 @@ def test_fused_layer1_equals_unfused_path():
     assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("dtype,count", [("bf16", 1000), ("bf16", 257), ("fp8", 513), ("bf16", 70000)])
+def test_head_on_cta_pairs_equals_single_cta_path(dtype, count):
+    """Layer 2 + head on CTA pairs (default) against the one-CTA-per-tile kernel: the same products summed in the
+    same order inside every output row, so the raw head outputs agree to float32 rounding of the row sums."""
+    pz = puzzles.puzzle54()
+    ws = [puzzles.mlp_weights(324, 1024, model_idx=i) for i in range(2)]
+    rng = np.random.default_rng(5)
+    for w in ws:
+        w["b1"] = (rng.standard_normal(1024) * 0.05).astype(np.float32)
+        w["b2"] = (rng.standard_normal(1024) * 0.05).astype(np.float32)
+    sc = scorers.MLPValueScorer(ws, 54, 64, 6, max_rows=count, score_offset=-150.0, dtype=dtype)
+    dev = torch.from_numpy(padded(children_of(pz, count, seed=9), 64)).cuda()
+    sc.set_head_mode(True)
+    k_pair = sc.score(dev).cpu().numpy()
+    q_pair = sc.last_q(count).cpu().numpy().copy()
+    sc.set_head_mode(False)
+    k_single = sc.score(dev).cpu().numpy()
+    q_single = sc.last_q(count).cpu().numpy().copy()
+    assert sc.error_code() == 0
+    assert np.abs(q_pair - q_single).max() <= 1e-5, np.abs(q_pair - q_single).max()
+    assert np.abs(k_pair.astype(np.int64) - k_single.astype(np.int64)).max() <= 1
+
+
 @pytest.mark.parametrize("name,count,models", [("rand54", 20000, 1), ("rand96", 5000, 2), ("rand54", 77, 1)])
 def test_fp8_scorer_within_tolerance(name, count, models):
     # FP8 E4M3 operands with per-channel weight scales: max-abs error of the network output <= 2e-2 (stated bound)
