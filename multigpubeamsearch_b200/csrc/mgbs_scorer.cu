@@ -423,28 +423,37 @@ struct L1Args {
 // EW = epilogue warps (4 or 8); the other 12 - EW warps of the 14 build the one-hot operand.  With the resident
 // tile (K <= 384) production is light and the epilogue is the bottleneck: EW = 8 (two warps per TMEM lane quadrant,
 // each taking every other 32-column group of a box).  With the ring (K > 384) production dominates: EW = 4.
-template <int F8, int EW>
+// PAIR = 1: thread-block clusters of two (see k_mlp_head_pair).  Each CTA builds the one-hot operand of its own 128
+// rows and loads half of each 256-row block of W1; the even CTA issues MMAs of M = 256 over both.  The weight ring
+// then holds six half blocks instead of three whole ones, and the shared-memory port carries a third less.
+template <int F8, int EW, int PAIR>
 __global__ void __launch_bounds__(L1_THREADS, 1)
 k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmOut, L1Args g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* a_ring = smem;                                   // 4 x 16 KB, 1024-aligned
-  uint8_t* b_ring = a_ring + L1_A_STAGES * A_BYTES;         // 3 x 32 KB
+  uint8_t* b_ring = a_ring + L1_A_STAGES * A_BYTES;         // 3 x 32 KB, or 6 x 16 KB for CTA pairs
+  constexpr int NBS = PAIR ? 2 * L1_B_STAGES : L1_B_STAGES; // stages of the weight ring
+  constexpr int BSB = PAIR ? B_BYTES / 2 : B_BYTES;         // bytes per stage
   uint8_t* staging = b_ring + L1_B_STAGES * B_BYTES;        // 2 x 16 KB
   uint8_t* child_s = staging + L1_STAGING;
   uint64_t* bars = reinterpret_cast<uint64_t*>(((uintptr_t)(child_s + BM * L1_CHILD_PITCH) + 7) & ~(uintptr_t)7);
   // barriers: a_full[4], a_empty[4], b_full[3], b_empty[3], tmem_full[2], tmem_empty[2], drain
-  constexpr int NB = 2 * L1_A_STAGES + 2 * L1_B_STAGES + 5;
+  constexpr int NB = 2 * L1_A_STAGES + 2 * NBS + 5;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + NB);
   int32_t* p_lo_tab = reinterpret_cast<int32_t*>(bars + NB + 1);  // first position of each K-block
   const uint32_t bar0 = smem_u32(bars);
   auto a_full = [&](int s) { return bar0 + 8u * s; };
   auto a_empty = [&](int s) { return bar0 + 8u * (L1_A_STAGES + s); };
   auto b_full = [&](int s) { return bar0 + 8u * (2 * L1_A_STAGES + s); };
-  auto b_empty = [&](int s) { return bar0 + 8u * (2 * L1_A_STAGES + L1_B_STAGES + s); };
-  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * L1_A_STAGES + 2 * L1_B_STAGES + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * L1_A_STAGES + 2 * L1_B_STAGES + 2 + b); };
-  const uint32_t drain_bar = bar0 + 8u * (2 * L1_A_STAGES + 2 * L1_B_STAGES + 4);
+  auto b_empty = [&](int s) { return bar0 + 8u * (2 * L1_A_STAGES + NBS + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * L1_A_STAGES + 2 * NBS + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * L1_A_STAGES + 2 * NBS + 2 + b); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * L1_A_STAGES + 2 * NBS + 4);
+  // tile schedule: CTA pairs walk tiles of 256 rows, each CTA taking its half; single CTAs walk tiles of 128 rows
+  const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
+  const int tile_first = PAIR ? 2 * (int)(blockIdx.x >> 1) + (int)crank : (int)blockIdx.x;
+  const int tile_step = PAIR ? (int)(gridDim.x & ~1u) : (int)gridDim.x;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -458,20 +467,27 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
   const int blocks_per_tile = resident ? k_blocks : n_chunks * k_blocks;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < L1_A_STAGES; ++s) { mbar_init(a_full(s), (12 - EW) / 4); mbar_init(a_empty(s), 1); }
-    for (int s = 0; s < L1_B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), EW); }
+    // pairs: a_full, b_full and tmem_empty are used in the even CTA only and count both CTAs' arrivals
+    for (int s = 0; s < L1_A_STAGES; ++s) { mbar_init(a_full(s), (PAIR ? 2 : 1) * (12 - EW) / 4); mbar_init(a_empty(s), 1); }
+    for (int s = 0; s < NBS; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), (PAIR ? 2 : 1) * EW); }
     mbar_init(drain_bar, 1);
     for (int kb = 0; kb < k_blocks && kb < L1_MAX_KBLOCKS; ++kb) p_lo_tab[kb] = (kb * BKE) / g.V;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_base_slot);
 
@@ -481,27 +497,33 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+      for (int mt = tile_first; mt - (int)crank < num_mtiles && ok; mt += tile_step) {
         for (int nc = 0; nc < n_chunks && ok; ++nc) {
           for (int kb = 0; kb < k_blocks; ++kb) {
             if (!mbar_wait(b_empty(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-            mbar_expect_tx(b_full(stage), B_BYTES);
-            tma_load_2d(smem_u32(b_ring + stage * B_BYTES), &tmB, kb * BKE, nc * BN, b_full(stage));
-            if (++stage == L1_B_STAGES) { stage = 0; phase ^= 1u; }
+            if (PAIR) {
+              // this CTA's half of the weight block; the bytes of both halves are counted in the even CTA
+              if (crank == 0) mbar_expect_tx(b_full(stage), 2 * BSB);
+              tma_load_2d_pair(smem_u32(b_ring + stage * BSB), &tmB, kb * BKE, nc * BN + (int)crank * (BN / 2), b_full(stage));
+            } else {
+              mbar_expect_tx(b_full(stage), B_BYTES);
+              tma_load_2d(smem_u32(b_ring + stage * B_BYTES), &tmB, kb * BKE, nc * BN, b_full(stage));
+            }
+            if (++stage == NBS) { stage = 0; phase ^= 1u; }
           }
         }
       }
     }
   } else if (warp == 1) {
     // ---- MMA issue ----
-    if (lane == 0) {
+    if (lane == 0 && crank == 0) {
 #ifdef MGBS_L1_PROBE
       const long long _pstart = clock64();
 #endif
       int sb = 0;
       uint32_t pb = 0, acc_it = 0, it_base = 0;
       bool ok = true;
-      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x, it_base += (uint32_t)blocks_per_tile) {
+      for (int mt = tile_first; mt < num_mtiles && ok; mt += tile_step, it_base += (uint32_t)blocks_per_tile) {
         for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
           const uint32_t b = acc_it & 1u;
           { PROBE_T0();
@@ -514,25 +536,41 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
             const int sa = (int)(it % L1_A_STAGES);
             // resident tile: N-chunks after the first find the phase already complete
             { PROBE_T0();
-            if (!mbar_wait(a_full(sa), (it / L1_A_STAGES) & 1u, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+            if (PAIR) {
+              if (!mbar_wait_cluster(a_full(sa), (it / L1_A_STAGES) & 1u, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+            } else {
+              if (!mbar_wait(a_full(sa), (it / L1_A_STAGES) & 1u, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+            }
             PROBE_ADD(1); }
             { PROBE_T0();
             if (!mbar_wait(b_full(sb), pb, g.err, ERR_WAIT_FULL)) { ok = false; break; }
             PROBE_ADD(2); }
             tc_fence_after();
             const uint64_t adesc = make_desc_sw128(smem_u32(a_ring + sa * A_BYTES));
-            const uint64_t bdesc = make_desc_sw128(smem_u32(b_ring + sb * B_BYTES));
+            const uint64_t bdesc = make_desc_sw128(smem_u32(b_ring + sb * BSB));
+            if (PAIR) {
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k)
-              tc_mma<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
-            if (!resident || nc == n_chunks - 1) tc_commit(a_empty(sa));
-            tc_commit(b_empty(sb));
-            if (++sb == L1_B_STAGES) { sb = 0; pb ^= 1u; }
+              for (int k = 0; k < BK / UMMA_K; ++k)
+                tc_mma_pair<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
+              if (!resident || nc == n_chunks - 1) tc_commit_pair(a_empty(sa), (uint16_t)3);
+              tc_commit_pair(b_empty(sb), (uint16_t)3);
+            } else {
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k)
+                tc_mma<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
+              if (!resident || nc == n_chunks - 1) tc_commit(a_empty(sa));
+              tc_commit(b_empty(sb));
+            }
+            if (++sb == NBS) { sb = 0; pb ^= 1u; }
           }
-          if (ok) tc_commit(tfull_bar(b));
+          if (ok) {
+            if (PAIR) tc_commit_pair(tfull_bar(b), (uint16_t)3);
+            else tc_commit(tfull_bar(b));
+          }
         }
       }
-      tc_commit(drain_bar);
+      if (PAIR) tc_commit_pair(drain_bar, (uint16_t)1);
+      else tc_commit(drain_bar);
       mbar_wait(drain_bar, 0, g.err, ERR_WAIT_DRAIN);
 #ifdef MGBS_L1_PROBE
       atomicAdd(&g_l1_probe[3], (unsigned long long)(clock64() - _pstart));
@@ -546,7 +584,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
     const uint32_t r = (uint32_t)(quad * 32 + lane);  // tile row owned by this thread
     uint32_t acc_it = 0, box_it = 0;
     bool ok = true;
-    for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+    for (int mt = tile_first; mt - (int)crank < num_mtiles && ok; mt += tile_step) {
       const int row0 = mt * BM;
       for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
         const uint32_t b = acc_it & 1u;
@@ -674,7 +712,10 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(b));
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_even_cta(tempty_bar(b));
+          else mbar_arrive(tempty_bar(b));
+        }
       }
     }
     if (EW == 4 ? lane == 0 : et == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -689,7 +730,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
     const int V = g.V, n = g.n;
     uint32_t it_base = 0;           // index of this tile's first K-block in the CTA's K-block sequence
     bool ok = true;
-    for (int mt = blockIdx.x; mt < num_mtiles; mt += gridDim.x, it_base += (uint32_t)blocks_per_tile) {
+    for (int mt = tile_first; mt - (int)crank < num_mtiles; mt += tile_step, it_base += (uint32_t)blocks_per_tile) {
       // all producer warps have finished reading the previous tile's child rows
 #ifdef MGBS_L1_PROBE
       const long long _pc0 = clock64();
@@ -766,18 +807,24 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
             }
           }
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (PAIR) asm volatile("fence.proxy.async;" ::: "memory");
+        else asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
-        if (lane == 0) mbar_arrive(a_full(slot));
+        if (lane == 0) {
+          if (PAIR) mbar_arrive_even_cta_release(a_full(slot));  // the even CTA's MMAs read this CTA's block too
+          else mbar_arrive(a_full(slot));
+        }
         if (warp == 2 + EW && lane == 0) PROBE_ADD(6);
       }
     }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // neither CTA leaves while its peer may still read its shared memory
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -837,7 +884,9 @@ struct MgbsMlp {
   CUtensorMap tm_h1w;  // same tensor, store boxes of one warp: 32 rows x 64 bytes, 64-byte swizzle
   CUtensorMap tm_w1[MGBS_MAX_MODELS], tm_w2[MGBS_MAX_MODELS];
   CUtensorMap tm_w2h[MGBS_MAX_MODELS];  // W2 in boxes of 128 rows: the half of a chunk one CTA of a pair loads
+  CUtensorMap tm_w1h[MGBS_MAX_MODELS];  // W1 likewise
   int pair_clusters = 0;                // CTA pairs that can be resident at once (0: pairs unavailable)
+  int l1_pair_clusters = 0;             // the same for the layer-1 kernel
   bool head_pair = true;
   bool fused_l1 = true;
   bool profile = false;
@@ -884,16 +933,21 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
     if (!c.w1[i] || !c.b1[i] || !c.w2[i] || !c.b2[i] || !c.w3[i]) rc = MGBS_ERR_ARG;
     if (!rc && f8 && (!c.s1[i] || !c.s2[i])) rc = MGBS_ERR_ARG;
     if (!rc) rc = make_map(&m->tm_w1[i], c.w1[i], (uint64_t)c.hidden, (uint64_t)k1_pad, mgbs::BN, eb);
+    if (!rc) rc = make_map(&m->tm_w1h[i], c.w1[i], (uint64_t)c.hidden, (uint64_t)k1_pad, mgbs::BN / 2, eb);
     if (!rc) rc = make_map(&m->tm_w2[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden, mgbs::BN, eb);
     if (!rc) rc = make_map(&m->tm_w2h[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden, mgbs::BN / 2, eb);
   }
   if (f8) m->fused_l1 = true;
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
-  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1<0, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
-  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1<1, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
+  auto l1_smem = [&](const void* fn) {
+    if (!rc) rc = (int)cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
+  };
+  l1_smem((const void*)mgbs::k_mlp_l1<0, 4, 0>);
+  l1_smem((const void*)mgbs::k_mlp_l1<1, 8, 0>);
+  l1_smem((const void*)mgbs::k_mlp_l1<1, 4, 0>);
+  l1_smem((const void*)mgbs::k_mlp_l1<1, 8, 1>);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
-  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_head_pair<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::PAIR_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_head_pair<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::PAIR_SMEM);
   if (!rc) {
@@ -914,6 +968,13 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
     else
       (void)cudaGetLastError();
     if (m->pair_clusters < 1) m->head_pair = false;
+    lc.blockDim = dim3(mgbs::L1_THREADS);
+    lc.dynamicSmemBytes = mgbs::L1_SMEM;
+    nclusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&nclusters, mgbs::k_mlp_l1<1, 8, 1>, &lc) == cudaSuccess && nclusters > 0)
+      m->l1_pair_clusters = nclusters < m->sms / 2 ? nclusters : m->sms / 2;
+    else
+      (void)cudaGetLastError();
   }
   if (rc) { delete m; return rc; }
   *out = m;
@@ -1010,12 +1071,33 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
       l.out_inv_scale = c.act_inv_scale;
       l.err = c.err;
       const bool resident = m->k1_pad / (c.dtype == 1 ? BK8 : BK) <= L1_A_STAGES;
-      if (c.dtype == 1 && resident) k_mlp_l1<1, 8><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
-      else if (c.dtype == 1) k_mlp_l1<1, 4><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
       // bf16 builds six K-blocks per tile: eight producer warps are needed even with the resident tile (measured:
       // 0.69-0.76 ms with 4 epilogue + 8 producer warps against 0.82 ms with 8 + 4 on the 786 432-row case);
       // e4m3 builds three and gains from the wider epilogue
-      else k_mlp_l1<0, 4><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
+      // CTA pairs for layer 1 only where they were measured faster: e4m3 operands with the resident tile (1.09 ms
+      // against 1.11 ms for the whole scorer on 786 432 rows).  With bf16 the pair was 0.05 ms slower than single
+      // CTAs: the even CTA's MMAs then wait for the slower of two sets of one-hot producers.
+      if (m->head_pair && m->l1_pair_clusters > 0 && c.dtype == 1 && resident) {
+        cudaLaunchConfig_t lc;
+        memset(&lc, 0, sizeof(lc));
+        lc.gridDim = dim3(2 * m->l1_pair_clusters);
+        lc.blockDim = dim3(L1_THREADS);
+        lc.dynamicSmemBytes = L1_SMEM;
+        lc.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        lc.attrs = at;
+        lc.numAttrs = 1;
+        cudaError_t le = cudaLaunchKernelEx(&lc, k_mlp_l1<1, 8, 1>, m->tm_w1h[i], m->tm_h1, l);
+        if (le != cudaSuccess) return (int)le;
+      } else if (c.dtype == 1 && resident) {
+        k_mlp_l1<1, 8, 0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
+      } else if (c.dtype == 1) {
+        k_mlp_l1<1, 4, 0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
+      } else {
+        k_mlp_l1<0, 4, 0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
+      }
     } else {
       k_mlp_gemm<0, 0><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_x, m->tm_w1[i], g);
     }

@@ -48,6 +48,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait that also acquires what other CTAs of the cluster released on this barrier
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* err, int code) {
+  for (uint32_t it = 0; it < (1u << 24); ++it) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (it > 1024) __nanosleep(64);
+  }
+  if (err) atomicCAS(err, 0, code);
+  return false;
+}
 // Bounded wait: about 1-2 s of polling at most, then report and give up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
   for (uint32_t it = 0; it < (1u << 24); ++it) {
@@ -122,6 +142,11 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) 
 // plain arrive on the even CTA's barrier at this offset (from either CTA of the pair)
 __device__ __forceinline__ void mbar_arrive_even_cta(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & kPeerBitMask) : "memory");
+}
+// the same with release semantics at cluster scope: what this thread (and, after a __syncwarp, its warp) wrote to
+// its CTA's shared memory is visible to whoever acquires the barrier in the even CTA
+__device__ __forceinline__ void mbar_arrive_even_cta_release(uint32_t bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar & kPeerBitMask) : "memory");
 }
 __device__ __forceinline__ void tc_mma_pair_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
