@@ -39,7 +39,7 @@ BEAM_PER_GPU = 65536
 SCORE_OFFSET = -150.0
 PREP_DEPTHS = 8  # untimed depths that grow the frontier from one state to the full beam
 CPU_SAMPLE_PARENTS = 4096
-GEMM2_DRAM_BYTES_PER_ROW = 2103.0
+GEMM2_DRAM_BYTES_PER_ROW = 2107.0
 
 
 def workload_name(n_gpus: int) -> str:
@@ -256,9 +256,9 @@ def run_ours(args):
     flops_per_row_l2 = 2 * (1024 * 1024 + 1024)  # layer 2 + scalar head
     achieved_tflops = rows_per_launch * flops_per_row_l2 / (gemm2_ms * 1e-3) / 1e12
     # DRAM bytes of the layer-2 GEMM per scored row, from one ncu capture of a 151 552-row case
-    # (dram__bytes_read.sum + dram__bytes_write.sum = 318.66 MB); traffic grows with the row count
+    # (dram__bytes_read.sum + dram__bytes_write.sum = 319.36 MB); traffic grows with the row count
     traffic = GEMM2_DRAM_BYTES_PER_ROW * rows_per_launch
-    roofline = {"bound": "tensor", "kernel": "k_mlp_gemm<1> (layer 2 GEMM + scalar head)", "achieved": achieved_tflops,
+    roofline = {"bound": "tensor", "kernel": "k_mlp_head_pair<0> (layer 2 GEMM + scalar head on CTA pairs)", "achieved": achieved_tflops,
                 "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                 "frac": achieved_tflops / peaks["bf16_tflops_sustained"], "peak_source": peaks["source"] + " (sustained bf16)",
                 "traffic": traffic,
