@@ -1,6 +1,6 @@
 """Timed runs of the other benchmark configurations (the default one lives in bench.py).
 
-    python -m multigpubeamsearch_b200.workloads --name c4|c5 [--steps K] [--beam-per-gpu B]
+    python -m multigpubeamsearch_b200.workloads --name c4|c5 [--steps K] [--beam-per-gpu B] [--dtype bf16|fp8]
     python -m torch.distributed.run --nproc-per-node N -m multigpubeamsearch_b200.workloads --name c5
 
 c4: state length 54, 12 generators, transformer ensemble (2 encoders x 4 layers, d 256, 8 heads, FFN 1024, bf16),
@@ -32,6 +32,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--beam-per-gpu", type=int, default=0)
     ap.add_argument("--prep", type=int, default=10)
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"], help="GEMM operand type of the scorer")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -56,12 +57,13 @@ def main() -> None:
     if args.name == "c4":
         sc = scorers.TransformerValueScorer([puzzles.transformer_weights(54, 6, model_idx=i) for i in range(2)],
                                             pz.state_len, cfg["state_size_bytes"], pz.num_values,
-                                            max_rows=sizes["cand_cap"], micro_batch=32768)
-        scorer_name = "transformer 2x(4 layers, d256, 8 heads, ffn 1024) bf16"
+                                            max_rows=sizes["cand_cap"], micro_batch=32768, dtype=args.dtype)
+        scorer_name = f"transformer 2x(4 layers, d256, 8 heads, ffn 1024) {args.dtype}"
     else:
         sc = scorers.MLPValueScorer([puzzles.mlp_weights(pz.state_len * pz.num_values, 1024, model_idx=i) for i in range(3)],
-                                    pz.state_len, cfg["state_size_bytes"], pz.num_values, max_rows=sizes["cand_cap"])
-        scorer_name = "3 x MLP 768-1024-1024-1 bf16"
+                                    pz.state_len, cfg["state_size_bytes"], pz.num_values, max_rows=sizes["cand_cap"],
+                                    dtype=args.dtype)
+        scorer_name = f"3 x MLP 768-1024-1024-1 {args.dtype}"
     _, cfg, buffers, engine = be.configure_engine(pz, cfg=cfg, scorer=sc)
     dev = torch.device("cuda", local_rank)
     stream = engine._stream
