@@ -501,7 +501,7 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
   int64_t items;
   if (W == 1) {
     a.cv.hash = c.cand_hash; a.cv.fp = c.cand_fp; a.cv.score = c.cand_score; a.cv.payload = c.cand_payload;
-    a.cv.states = c.children;
+    a.cv.states = nullptr;  // survivors are rebuilt from parent row + move (k_emit walks the table, not the candidates)
     a.cv.counts = &c.ctrl->cand_count;
     a.cv.nbuckets = 1;
     a.cv.cap = (uint32_t)c.cand_cap;
@@ -624,7 +624,7 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
   }
   a.hist = nullptr;
   a.hist_prev = fin + (int64_t)(Lf - 1) * MGBS_HIST_STRIDE;
-  MGBS_TRY(launch_emit(a, items, e->sms, st));
+  MGBS_TRY(launch_emit(a, a.cv.states ? items : c.hash_capacity, e->sms, st));
   MGBS_TRACE();  // emit
   if (W > 1) {
     MGBS_NCCL(g_nccl.AllGather(tie_buf + (int64_t)c.rank * kTieSegWords, tie_buf, kTieSegWords, ncclUint64, e->comm, st));

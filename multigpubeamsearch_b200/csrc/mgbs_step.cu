@@ -731,6 +731,47 @@ __global__ void __launch_bounds__(kStreamThreads) k_emit(StepArgs a) {
   const int hb = a.hash_bits;
   const int lane = threadIdx.x & 31;
   unsigned long long* seg = a.tie_buf + (int64_t)a.rank * kTieSegWords;
+  if (a.cv.states == nullptr) {
+    // Survivors are rebuilt from their back-pointers, so everything needed sits in the table entry itself (hash,
+    // fingerprint, score and back-pointer of the winner): walk the table's slots instead of the candidates - five
+    // times fewer items on one GPU and no lookups.  Tie records then carry the slot index.
+    const uint64_t rounded = (cap + 31ull) & ~31ull;
+    for (uint64_t j = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; j < rounded; j += (uint64_t)gridDim.x * blockDim.x) {
+      bool keep = false, tie = false;
+      uint32_t k = 0, payload = 0;
+      uint64_t h = 0, f = 0;
+      if (j < cap) {
+        const ulonglong2 hf = __ldcg(reinterpret_cast<const ulonglong2*>(table + j));
+        if (hf.x != 0ull && hf.y != 0ull) {
+          const uint64_t best = ~__ldcg(&table[j].best_inv);
+          h = hf.x; f = hf.y;
+          k = (uint32_t)(best >> 32);
+          payload = (uint32_t)best;
+          const uint64_t s = order_key(k, h, hb);
+          keep = s < T;
+          tie = !keep && ties && s == tie_key;
+        }
+      }
+      const unsigned km = __ballot_sync(0xffffffffu, keep);
+      if (km) {
+        uint32_t base = 0;
+        if (lane == 0) base = atomicAdd(&a.ctrl->next_count, (uint32_t)__popc(km));
+        base = __shfl_sync(0xffffffffu, base, 0);
+        if (keep) emit_row(a, j, k, h, payload, base + __popc(km & ((1u << lane) - 1u)));
+      }
+      if (tie) {
+        const unsigned long long t = atomicAdd(seg, 1ull);
+        if (t < MGBS_TIE_CAP) {
+          seg[1 + 3 * t] = h;
+          seg[2 + 3 * t] = f;
+          seg[3 + 3 * t] = j;
+        } else {
+          atomicOr(&a.ctrl->status, MGBS_ST_TIE_OVERFLOW);
+        }
+      }
+    }
+    return;
+  }
   for_each_candidate(a.cv, [&](uint64_t i, bool valid) {
     bool keep = false, tie = false;
     uint32_t k = 0, payload = 0;
@@ -791,7 +832,12 @@ __global__ void __launch_bounds__(kStreamThreads) k_finish(StepArgs a) {
       }
       if (before < need) {
         const uint32_t pos = atomicAdd(&a.ctrl->next_count, 1u);
-        emit_row(a, i, __ldg(a.cv.score + i), h, __ldg(a.cv.payload + i), pos);
+        if (a.cv.states == nullptr) {  // i is a table slot (see k_emit)
+          const uint64_t best = ~__ldcg(&reinterpret_cast<const Slot*>(a.table)[i].best_inv);
+          emit_row(a, i, (uint32_t)(best >> 32), h, (uint32_t)best, pos);
+        } else {
+          emit_row(a, i, __ldg(a.cv.score + i), h, __ldg(a.cv.payload + i), pos);
+        }
       }
     }
   }
