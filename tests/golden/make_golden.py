@@ -16,7 +16,9 @@ import numpy as np
 
 
 def main() -> None:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference").resolve()
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+    ref = Path(sys.argv[1]).resolve()
     sys.path.insert(0, str(ref))
     sys.dont_write_bytecode = True
     import data_loader  # type: ignore
