@@ -95,6 +95,7 @@ SIGNATURES = {
     "mgbs_engine_destroy": (C.c_int, [_P]),
     "mgbs_nccl_unique_id": (C.c_int, [C.c_char_p, _P]),
     "mgbs_engine_init_nccl": (C.c_int, [_P, C.c_char_p, _P]),
+    "mgbs_engine_set_parent_scorer": (C.c_int, [_P, _P, _P]),
     "mgbs_sym_bytes": (C.c_int, [C.POINTER(MgbsConfig), C.POINTER(_I64), C.POINTER(_I64)]),
     "mgbs_sym_frontier_offsets": (C.c_int, [C.POINTER(MgbsConfig), C.POINTER(_I64)]),
     "mgbs_engine_set_peers": (C.c_int, [_P, _P, C.POINTER(_I64)]),

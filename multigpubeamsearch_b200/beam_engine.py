@@ -366,7 +366,12 @@ class BeamEngine:
         """Attach a device scorer object (see scorers.MLPValueScorer): it supplies a C callback and its handle."""
         self._scorer = scorer
         fn, user = scorer.c_callback()
-        _lib.check(self.lib.mgbs_engine_set_scorer(self._h, fn, user), "set_scorer")
+        if getattr(scorer, "scores_parents", False):
+            # action values: one forward pass per frontier row gives the scores of all its children
+            _lib.check(self.lib.mgbs_engine_set_parent_scorer(self._h, fn, user), "set_scorer")
+        else:
+            _lib.check(self.lib.mgbs_engine_set_parent_scorer(self._h, None, None), "set_scorer")
+            _lib.check(self.lib.mgbs_engine_set_scorer(self._h, fn, user), "set_scorer")
 
     def begin_uniform_score(self, score: int) -> None:
         """Prepass fill: every child gets the same score (beam_engine.cpp:893-915)."""

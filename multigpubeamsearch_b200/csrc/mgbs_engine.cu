@@ -70,6 +70,8 @@ struct MgbsEngine {
   ncclComm_t comm = nullptr;
   mgbs_scorer_fn scorer = nullptr;
   void* scorer_user = nullptr;
+  mgbs_parent_scorer_fn parent_scorer = nullptr;
+  void* parent_scorer_user = nullptr;
   cudaGraphExec_t graph[2] = {nullptr, nullptr};
   MgbsCtrl host_ctrl;
   mgbs::SymLayout sym{};
@@ -283,6 +285,15 @@ int mgbs_engine_set_peers(MgbsEngine* e, const uint8_t* handles, const int64_t* 
   return 0;
 }
 
+int mgbs_engine_set_parent_scorer(MgbsEngine* e, mgbs_parent_scorer_fn fn, void* user) {
+  if (!e) return MGBS_ERR_ARG;
+  e->parent_scorer = fn;
+  e->parent_scorer_user = user;
+  for (int p = 0; p < 2; ++p)
+    if (e->graph[p]) { cudaGraphExecDestroy(e->graph[p]); e->graph[p] = nullptr; }
+  return 0;
+}
+
 int mgbs_engine_set_scorer(MgbsEngine* e, mgbs_scorer_fn fn, void* user) {
   if (!e) return MGBS_ERR_ARG;
   e->scorer = fn;
@@ -485,8 +496,14 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     MGBS_TRACE();  // expand
     if (prof) cudaEventRecord(e->ev[1], st);
     if (phase == 0 && c.score_mode == MGBS_SCORE_EXTERNAL) {
-      if (!e->scorer) return MGBS_ERR_STATE;
-      MGBS_TRY(e->scorer(e->scorer_user, c.children, &c.ctrl->cand_count, c.cand_score, stream));
+      if (e->parent_scorer) {
+        // action values: one forward pass per parent row gives the scores of all its children
+        MGBS_TRY(e->parent_scorer(e->parent_scorer_user, c.frontier[parity], &c.ctrl->frontier_count[parity],
+                                  c.cand_score, stream));
+      } else {
+        if (!e->scorer) return MGBS_ERR_STATE;
+        MGBS_TRY(e->scorer(e->scorer_user, c.children, &c.ctrl->cand_count, c.cand_score, stream));
+      }
     }
     if (phase == 1) return 0;
   }

@@ -36,11 +36,13 @@ struct GemmArgs {
   const float* w_out;         // EPI 1: [n_total] weights of the scalar head
   __nv_bfloat16* out_bf16;    // EPI 0: [rows, n_total]
   float* out_q;               // EPI 1: [rows]
-  int32_t accumulate_q;       // EPI 1: add to out_q instead of overwriting (ensemble members after the first)
+  int32_t accumulate_q;       // EPI 1, 2: add to out_q instead of overwriting (ensemble members after the first)
+  int32_t q_cols;             // EPI 2: output columns kept (the fan-out); out_q is [rows, q_cols]
   int* err;
 };
 
 // EPI 0: out = bf16(relu(acc + bias)).  EPI 1: q[row] (+)= sum_n relu(acc + bias[n]) * w_out[n].
+// EPI 2: q[row, n] (+)= acc + bias[n] for n < q_cols (output layer of an action-value network: one value per move).
 template <int EPI, int F8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs g) {
@@ -151,6 +153,7 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * BN;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
+          if (EPI == 2 && nc * BN + c0 >= g.q_cols) break;  // columns past the fan-out are padding
           uint32_t v[32];
           tc_ld32(taddr + c0, v);
           tc_wait_ld();
@@ -168,6 +171,18 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
               uint4* dst = reinterpret_cast<uint4*>(g.out_bf16 + row * g.n_total + n0);
 #pragma unroll
               for (int q = 0; q < 4; ++q) dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            }
+          } else if (EPI == 2) {
+            if (row_ok) {
+              float* qrow = g.out_q + row * g.q_cols;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (n0 + j < g.q_cols) {
+                  const float x = __uint_as_float(v[j]) + __ldg(g.bias + n0 + j);
+                  if (g.accumulate_q) qrow[n0 + j] += x;
+                  else qrow[n0 + j] = x;
+                }
+              }
             }
           } else {
 #pragma unroll
@@ -870,6 +885,18 @@ __global__ void __launch_bounds__(256) k_q_to_key(const float* __restrict__ q, c
   }
 }
 
+// Action values [parents, fanout] (summed over ensemble members) -> score keys of the candidates; candidate
+// c = parent * fanout + move reads q[c], so the two arrays share one index.
+__global__ void __launch_bounds__(256) k_qa_to_key(const float* __restrict__ q, const int32_t* parents_dev, int fanout,
+                                                   float inv_models, float offset, uint32_t* __restrict__ keys) {
+  const int64_t total = (int64_t)(*parents_dev) * fanout;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    float x = q[i] * inv_models - offset;
+    x = fminf(fmaxf(x, 0.f), 300.f);
+    keys[i] = (uint32_t)(x * 256.f + 0.5f);
+  }
+}
+
 }  // namespace mgbs
 
 // ------------------------------------------------------------------------------------------------
@@ -1140,6 +1167,117 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
     k_q_to_key<<<(int)g, 256, 0, st>>>(c.q, count_dev, 1.f / (float)c.num_models, c.score_offset - b3 / (float)c.num_models, scores);
   }
   if (prof) cudaEventRecord(m->ev[4], st);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Action-value scorer: one-hot -> hidden1 -> hidden2 -> fanout on the parent rows.
+// ------------------------------------------------------------------------------------------------
+
+struct MgbsQmlp {
+  MgbsQmlpConfig cfg;
+  int sms = 148;
+  CUtensorMap tm_h1, tm_h1w, tm_h2;
+  CUtensorMap tm_w1[MGBS_MAX_MODELS], tm_w2[MGBS_MAX_MODELS], tm_w3[MGBS_MAX_MODELS];
+};
+
+extern "C" {
+
+int mgbs_sizeof_qmlp_config(void) { return (int)sizeof(MgbsQmlpConfig); }
+
+int mgbs_qmlp_create(const MgbsQmlpConfig* cfg, MgbsQmlp** out) {
+  if (!cfg || !out) return MGBS_ERR_ARG;
+  const MgbsQmlpConfig& c = *cfg;
+  if (c.state_len < 1 || c.state_len > MGBS_MAX_STATE_LEN || c.num_values < 1 || c.num_values > 256) return MGBS_ERR_ARG;
+  if (c.fanout < 1 || c.fanout > MGBS_MAX_FANOUT) return MGBS_ERR_ARG;
+  if (c.hidden1 < mgbs::BN || c.hidden1 % mgbs::BN != 0 || c.hidden2 < mgbs::BN || c.hidden2 % mgbs::BN != 0) return MGBS_ERR_UNSUPPORTED;
+  if (c.num_models < 1 || c.num_models > MGBS_MAX_MODELS || c.max_parents < 1) return MGBS_ERR_ARG;
+  const int k1 = c.state_len * c.num_values;
+  const int k1_pad = (k1 + mgbs::BK - 1) / mgbs::BK * mgbs::BK;
+  if (c.k1_pad != k1_pad || k1_pad / mgbs::BK > mgbs::L1_MAX_KBLOCKS) return MGBS_ERR_ARG;
+  if (c.state_stride < c.state_len || c.state_stride % 16 != 0 || c.state_stride > MGBS_MAX_STATE_LEN) return MGBS_ERR_ARG;
+  if (!c.h1 || !c.h2 || !c.q || !c.err) return MGBS_ERR_ARG;
+  MgbsQmlp* m = new (std::nothrow) MgbsQmlp();
+  if (!m) return MGBS_ERR_STATE;
+  m->cfg = c;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) m->sms = sms;
+  }
+  const uint64_t rows_pad = (uint64_t)((c.max_parents + mgbs::BM - 1) / mgbs::BM * mgbs::BM);
+  int rc = make_map_bf16(&m->tm_h1, c.h1, rows_pad, (uint64_t)c.hidden1, mgbs::BM);
+  if (!rc) rc = mgbs::make_map_box(&m->tm_h1w, c.h1, rows_pad, (uint64_t)c.hidden1, 32, 32, 2, 64);
+  if (!rc) rc = make_map_bf16(&m->tm_h2, c.h2, rows_pad, (uint64_t)c.hidden2, mgbs::BM);
+  for (int i = 0; i < c.num_models && !rc; ++i) {
+    if (!c.w1[i] || !c.b1[i] || !c.w2[i] || !c.b2[i] || !c.w3[i] || !c.b3[i]) { rc = MGBS_ERR_ARG; break; }
+    rc = make_map_bf16(&m->tm_w1[i], c.w1[i], (uint64_t)c.hidden1, (uint64_t)k1_pad, mgbs::BN);
+    if (!rc) rc = make_map_bf16(&m->tm_w2[i], c.w2[i], (uint64_t)c.hidden2, (uint64_t)c.hidden1, mgbs::BN);
+    if (!rc) rc = make_map_bf16(&m->tm_w3[i], c.w3[i], (uint64_t)mgbs::BN, (uint64_t)c.hidden2, mgbs::BN);
+  }
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
+  if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_l1<0, 4, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
+  if (rc) { delete m; return rc; }
+  *out = m;
+  return 0;
+}
+
+int mgbs_qmlp_destroy(MgbsQmlp* m) {
+  delete m;
+  return 0;
+}
+
+int mgbs_qmlp_enqueue(void* user, const uint8_t* parents, const int32_t* parent_count_dev, uint32_t* cand_scores,
+                      void* stream) {
+  MgbsQmlp* m = static_cast<MgbsQmlp*>(user);
+  if (!m || !parents || !parent_count_dev || !cand_scores) return MGBS_ERR_ARG;
+  using namespace mgbs;
+  const MgbsQmlpConfig& c = m->cfg;
+  cudaStream_t st = (cudaStream_t)stream;
+  const uint32_t* count_dev = reinterpret_cast<const uint32_t*>(parent_count_dev);  // never negative
+  const int grid = m->sms;
+  for (int i = 0; i < c.num_models; ++i) {
+    L1Args l;
+    l.children = parents;
+    l.count_dev = count_dev;
+    l.row_limit = c.max_parents;
+    l.n = c.state_len; l.stride = c.state_stride; l.V = c.num_values;
+    l.n_total = c.hidden1;
+    l.k_total = c.k1_pad;
+    l.bias = c.b1[i];
+    l.col_scale = nullptr;
+    l.out_inv_scale = 1.f;
+    l.err = c.err;
+    k_mlp_l1<0, 4, 0><<<grid, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
+    GemmArgs g;
+    g.count_dev = count_dev;
+    g.row_offset = 0;
+    g.row_limit = c.max_parents;
+    g.n_total = c.hidden2;
+    g.k_total = c.hidden1;
+    g.bias = c.b2[i];
+    g.col_scale = nullptr;
+    g.w_out = nullptr;
+    g.out_bf16 = reinterpret_cast<__nv_bfloat16*>(c.h2);
+    g.out_q = nullptr;
+    g.accumulate_q = 0;
+    g.q_cols = 0;
+    g.err = c.err;
+    k_mlp_gemm<0, 0><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h1, m->tm_w2[i], g);
+    g.n_total = BN;  // output layer padded to one 256-column chunk
+    g.k_total = c.hidden2;
+    g.bias = c.b3[i];
+    g.out_bf16 = nullptr;
+    g.out_q = c.q;
+    g.accumulate_q = i > 0 ? 1 : 0;
+    g.q_cols = c.fanout;
+    k_mlp_gemm<2, 0><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h2, m->tm_w3[i], g);
+  }
+  k_qa_to_key<<<m->sms * 4, 256, 0, st>>>(c.q, parent_count_dev, c.fanout, 1.f / (float)c.num_models, c.score_offset,
+                                          cand_scores);
   return (int)cudaGetLastError();
 }
 

@@ -120,6 +120,20 @@ def mlp_weights(in_features: int, hidden: int = 1024, seed: int = 7000, model_id
     }
 
 
+def q_mlp_weights(in_features: int, fanout: int, hidden1: int = 1024, hidden2: int = 512, seed: int = 7500,
+                  model_idx: int = 0, std: float = 0.02) -> Dict[str, np.ndarray]:
+    """Random-init action-value MLP in_features -> hidden1 -> hidden2 -> fanout (Gaussian std 0.02, zero biases)."""
+    rng = np.random.default_rng(seed + model_idx)
+    return {
+        "w1": (rng.standard_normal((hidden1, in_features)) * std).astype(np.float32),
+        "b1": np.zeros((hidden1,), dtype=np.float32),
+        "w2": (rng.standard_normal((hidden2, hidden1)) * std).astype(np.float32),
+        "b2": np.zeros((hidden2,), dtype=np.float32),
+        "w3": (rng.standard_normal((fanout, hidden2)) * std).astype(np.float32),
+        "b3": np.zeros((fanout,), dtype=np.float32),
+    }
+
+
 def transformer_weights(tokens: int, vocab: int, d_model: int = 256, layers: int = 4, ffn: int = 1024,
                         seed: int = 8000, model_idx: int = 0, std: float = 0.02) -> Dict:
     """Random-init pre-LayerNorm encoder: Gaussian std 0.02 matrices and embeddings, zero biases, LayerNorm 1/0."""

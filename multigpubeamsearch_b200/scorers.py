@@ -241,6 +241,131 @@ class MLPValueScorer:
 
 
 # ----------------------------------------------------------------------------------------------
+# Action-value scorer (the reference's scorer contract: parents in, one value per move out)
+# ----------------------------------------------------------------------------------------------
+
+
+class MgbsQmlpConfig(C.Structure):
+    _fields_ = [
+        ("state_len", C.c_int32), ("state_stride", C.c_int32), ("num_values", C.c_int32), ("fanout", C.c_int32),
+        ("hidden1", C.c_int32), ("hidden2", C.c_int32), ("num_models", C.c_int32), ("k1_pad", C.c_int32),
+        ("max_parents", C.c_int64), ("score_offset", C.c_float), ("pad0", C.c_int32),
+        ("h1", C.c_void_p), ("h2", C.c_void_p), ("q", C.c_void_p), ("err", C.c_void_p),
+        ("w1", C.c_void_p * MAX_MODELS), ("b1", C.c_void_p * MAX_MODELS), ("w2", C.c_void_p * MAX_MODELS),
+        ("b2", C.c_void_p * MAX_MODELS), ("w3", C.c_void_p * MAX_MODELS), ("b3", C.c_void_p * MAX_MODELS),
+    ]
+
+
+_Q_SIGS = {
+    "mgbs_sizeof_qmlp_config": (C.c_int, []),
+    "mgbs_qmlp_create": (C.c_int, [C.POINTER(MgbsQmlpConfig), C.POINTER(C.c_void_p)]),
+    "mgbs_qmlp_destroy": (C.c_int, [C.c_void_p]),
+    "mgbs_qmlp_enqueue": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+}
+_lib.SIGNATURES.update(_Q_SIGS)
+
+
+class MLPActionValueScorer:
+    """Ensemble of action-value MLPs one-hot(n x V) -> hidden1 -> hidden2 -> fanout (ReLU between layers), evaluated
+    once per PARENT row: candidate ``parent * fanout + move`` takes ``q[parent, move]``.  This is the reference's
+    scorer contract (scorers.MLPActionScorer, scorers.py:21-36: uint8 [B, n] in, [B, fanout] out; the static
+    FullBeamNice backend has the same shape, beam_engine.cpp:621-667); it costs 1/fanout of the value scorers' forward
+    passes.  Weights: dicts with w1 [H1, n*V], b1, w2 [H2, H1], b2, w3 [fanout, H2], b3 [fanout]; bf16 operands, float32
+    accumulation; members are averaged; keys as in the value scorers."""
+
+    scores_parents = True
+
+    def __init__(self, weights, state_len: int, state_stride: int, num_values: int, fanout: int, max_parents: int,
+                 score_offset: float = -150.0, device=None):
+        self.lib = _lib.load()
+        for name, (res, args) in _Q_SIGS.items():
+            fn = getattr(self.lib, name)
+            fn.restype, fn.argtypes = res, args
+        if self.lib.mgbs_sizeof_qmlp_config() != C.sizeof(MgbsQmlpConfig):
+            raise RuntimeError("structure layout mismatch between scorers.py and libmgbs_b200.so")
+        if isinstance(weights, dict):
+            weights = [weights]
+        if not 1 <= len(weights) <= MAX_MODELS:
+            raise RuntimeError(f"1..{MAX_MODELS} ensemble members supported")
+        dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        k1 = state_len * num_values
+        k1_pad = (k1 + 63) // 64 * 64
+        h1, h2 = int(weights[0]["w1"].shape[0]), int(weights[0]["w2"].shape[0])
+        rows_pad = (int(max_parents) + 127) // 128 * 128
+        self.state_len, self.state_stride, self.num_values, self.fanout = state_len, state_stride, num_values, fanout
+        self.hidden1, self.hidden2, self.num_models, self.max_parents = h1, h2, len(weights), int(max_parents)
+        self._keep: List[torch.Tensor] = []
+        cfg = MgbsQmlpConfig()
+        cfg.state_len, cfg.state_stride, cfg.num_values, cfg.fanout = state_len, state_stride, num_values, fanout
+        cfg.hidden1, cfg.hidden2, cfg.num_models, cfg.k1_pad = h1, h2, len(weights), k1_pad
+        cfg.max_parents, cfg.score_offset = int(max_parents), float(score_offset)
+
+        def keep(t):
+            self._keep.append(t)
+            return t.data_ptr()
+
+        for i, w in enumerate(weights):
+            if w["w1"].shape != (h1, k1) or w["w2"].shape != (h2, h1) or w["w3"].shape != (fanout, h2):
+                raise RuntimeError("weight shapes do not match the puzzle")
+            w1 = torch.zeros((h1, k1_pad), dtype=torch.bfloat16, device=dev)
+            w1[:, :k1] = torch.from_numpy(np.ascontiguousarray(w["w1"], dtype=np.float32)).to(dev).to(torch.bfloat16)
+            w3 = torch.zeros((256, h2), dtype=torch.bfloat16, device=dev)
+            w3[:fanout] = torch.from_numpy(np.ascontiguousarray(w["w3"], dtype=np.float32)).to(dev).to(torch.bfloat16)
+            b3 = torch.zeros((256,), dtype=torch.float32, device=dev)
+            b3[:fanout] = torch.from_numpy(np.ascontiguousarray(w["b3"], dtype=np.float32)).to(dev)
+            cfg.w1[i], cfg.w3[i], cfg.b3[i] = keep(w1), keep(w3), keep(b3)
+            cfg.w2[i] = keep(torch.from_numpy(np.ascontiguousarray(w["w2"], dtype=np.float32)).to(dev).to(torch.bfloat16).contiguous())
+            cfg.b1[i] = keep(torch.from_numpy(np.ascontiguousarray(w["b1"], dtype=np.float32)).to(dev))
+            cfg.b2[i] = keep(torch.from_numpy(np.ascontiguousarray(w["b2"], dtype=np.float32)).to(dev))
+        self.h1 = torch.zeros((rows_pad, h1), dtype=torch.bfloat16, device=dev)
+        self.h2 = torch.zeros((rows_pad, h2), dtype=torch.bfloat16, device=dev)
+        self.q = torch.zeros((rows_pad, fanout), dtype=torch.float32, device=dev)
+        self.err = torch.zeros((1,), dtype=torch.int32, device=dev)
+        self._count = torch.zeros((1,), dtype=torch.int32, device=dev)
+        cfg.h1, cfg.h2, cfg.q, cfg.err = self.h1.data_ptr(), self.h2.data_ptr(), self.q.data_ptr(), self.err.data_ptr()
+        self._cfg = cfg
+        h = C.c_void_p()
+        _lib.check(self.lib.mgbs_qmlp_create(C.byref(cfg), C.byref(h)), "MLPActionValueScorer")
+        self._h = h
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            self.lib.mgbs_qmlp_destroy(h)
+            self._h = None
+
+    def c_callback(self):
+        return C.cast(self.lib.mgbs_qmlp_enqueue, C.c_void_p), self._h
+
+    def flops_per_state(self) -> int:
+        """Per CANDIDATE: one parent pass serves fanout candidates."""
+        k1 = self.state_len * self.num_values
+        per_parent = 2 * (k1 * self.hidden1 + self.hidden1 * self.hidden2 + self.hidden2 * self.fanout)
+        return self.num_models * per_parent // self.fanout
+
+    def score(self, parents: torch.Tensor) -> torch.Tensor:
+        """Keys [P * fanout] of all children of ``parents`` ([P, state_stride] uint8 on the device)."""
+        if parents.dtype != torch.uint8 or parents.dim() != 2 or parents.shape[1] != self.state_stride:
+            raise RuntimeError("parents must be [P, state_stride] uint8")
+        if parents.shape[0] > self.max_parents:
+            raise RuntimeError("more rows than the scorer was sized for")
+        parents = parents.contiguous()
+        self._count.fill_(parents.shape[0])
+        keys = torch.zeros((parents.shape[0] * self.fanout,), dtype=torch.int32, device=parents.device)
+        _lib.check(self.lib.mgbs_qmlp_enqueue(self._h, parents.data_ptr(), self._count.data_ptr(), keys.data_ptr(),
+                                              C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                   "MLPActionValueScorer.score")
+        return keys
+
+    def last_q(self, count: int) -> torch.Tensor:
+        """Action values [count, fanout] of the last call, summed over ensemble members."""
+        return self.q[:count]
+
+    def error_code(self) -> int:
+        return int(self.err.item())
+
+
+# ----------------------------------------------------------------------------------------------
 # Transformer value scorer
 # ----------------------------------------------------------------------------------------------
 

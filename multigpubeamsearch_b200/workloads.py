@@ -1,10 +1,12 @@
 """Timed runs of the other benchmark configurations (the default one lives in bench.py).
 
-    python -m multigpubeamsearch_b200.workloads --name c4|c5 [--steps K] [--beam-per-gpu B] [--dtype bf16|fp8]
+    python -m multigpubeamsearch_b200.workloads --name c4|c5|c2q [--steps K] [--beam-per-gpu B] [--dtype bf16|fp8]
     python -m torch.distributed.run --nproc-per-node N -m multigpubeamsearch_b200.workloads --name c5
 
 c4: state length 54, 12 generators, transformer ensemble (2 encoders x 4 layers, d 256, 8 heads, FFN 1024, bf16),
     scoring micro-batch 32 768, global beam 65 536 over all ranks.
+c2q: the benchmark's puzzle and beam (65 536 per rank) with an action-value MLP 324 -> 1024 -> 1024 -> 12 evaluated once
+    per parent row (the reference's own scorer contract) instead of a value MLP evaluated on every child.
 c5: state length 96, 18 generators, ensemble of 3 MLPs 768 -> 1024 -> 1024 -> 1 (bf16 here; the block-scaled 4-bit
     format is not built), global beam 2^22 on 8 ranks = 524 288 per rank, BETA 1.2, load 0.45, probe limit 256,
     depth loop through CUDA graphs.
@@ -27,7 +29,7 @@ from . import puzzles, scorers
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--name", choices=["c4", "c5"], required=True)
+    ap.add_argument("--name", choices=["c4", "c5", "c2q"], required=True)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--beam-per-gpu", type=int, default=0)
@@ -41,6 +43,10 @@ def main() -> None:
     if args.name == "c4":
         pz = puzzles.puzzle54()
         per_gpu = args.beam_per_gpu or max(65536 // world, 1)
+        scramble_len = 40
+    elif args.name == "c2q":
+        pz = puzzles.puzzle54()
+        per_gpu = args.beam_per_gpu or 65536
         scramble_len = 40
     else:
         pz = puzzles.puzzle96()
@@ -59,6 +65,11 @@ def main() -> None:
                                             pz.state_len, cfg["state_size_bytes"], pz.num_values,
                                             max_rows=sizes["cand_cap"], micro_batch=32768, dtype=args.dtype)
         scorer_name = f"transformer 2x(4 layers, d256, 8 heads, ffn 1024) {args.dtype}"
+    elif args.name == "c2q":
+        sc = scorers.MLPActionValueScorer(puzzles.q_mlp_weights(pz.state_len * pz.num_values, pz.fanout, 1024, 1024),
+                                          pz.state_len, cfg["state_size_bytes"], pz.num_values, pz.fanout,
+                                          max_parents=sizes["k_work"])
+        scorer_name = "action-value MLP 324-1024-1024-12 bf16 on parent rows"
     else:
         sc = scorers.MLPValueScorer([puzzles.mlp_weights(pz.state_len * pz.num_values, 1024, model_idx=i) for i in range(3)],
                                     pz.state_len, cfg["state_size_bytes"], pz.num_values, max_rows=sizes["cand_cap"],

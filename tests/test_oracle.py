@@ -175,3 +175,18 @@ def test_search_lrx_world_invariance(world):
         assert np.array_equal(a, b)
     if r.found:
         assert np.array_equal(bo.replay(start, pz.generators, r.path), pz.solved)
+
+
+def test_action_value_network_reduces_to_the_value_network_for_one_move():
+    """mlp_action_values with an output layer of width 1 is mlp_forward; wider outputs are independent columns."""
+    rng = np.random.default_rng(4)
+    states = rng.integers(0, 6, size=(37, 20)).astype(np.uint8)
+    w = {"w1": rng.standard_normal((64, 120)).astype(np.float32) * 0.1, "b1": rng.standard_normal(64).astype(np.float32) * 0.1,
+         "w2": rng.standard_normal((32, 64)).astype(np.float32) * 0.1, "b2": rng.standard_normal(32).astype(np.float32) * 0.1}
+    w3 = rng.standard_normal((5, 32)).astype(np.float32) * 0.1
+    b3 = rng.standard_normal(5).astype(np.float32) * 0.1
+    q = bo.mlp_action_values(states, [dict(w, w3=w3, b3=b3)], 6)
+    assert q.shape == (37, 5)
+    for m in range(5):
+        v = bo.mlp_forward(states, [dict(w, w3=w3[m], b3=b3[m])], 6)
+        assert np.allclose(q[:, m], v, atol=1e-6)

@@ -170,3 +170,60 @@ def test_fp8_scorer_within_tolerance(name, count, models):
     perm = np.random.default_rng(1).permutation(count)
     keys2 = sc.score(dev[torch.from_numpy(perm).cuda()].contiguous())
     assert np.array_equal(keys.cpu().numpy()[perm], keys2.cpu().numpy())
+
+
+def _q_weights(pz, models, h1=1024, h2=512):
+    ws = [puzzles.q_mlp_weights(pz.state_len * pz.num_values, pz.fanout, h1, h2, model_idx=i) for i in range(models)]
+    rng = np.random.default_rng(17)
+    for w in ws:  # non-zero biases so that every epilogue term is exercised
+        w["b1"] = (rng.standard_normal(h1) * 0.05).astype(np.float32)
+        w["b2"] = (rng.standard_normal(h2) * 0.05).astype(np.float32)
+        w["b3"] = (rng.standard_normal(pz.fanout) * 0.1).astype(np.float32)
+    return ws
+
+
+@pytest.mark.parametrize("name,count,models,h2", [("rand54", 1000, 1, 512), ("rand96", 4097, 2, 256), ("rand54", 1, 1, 1024)])
+def test_action_value_scorer_matches_fp32(name, count, models, h2):
+    """One forward pass per parent, one value per move (the reference's scorer contract) against float32."""
+    pz = puzzles.by_name(name)
+    stride = (pz.state_len + 15) // 16 * 16
+    ws = _q_weights(pz, models, 1024, h2)
+    sc = scorers.MLPActionValueScorer(ws, pz.state_len, stride, pz.num_values, pz.fanout, max_parents=count)
+    rows = children_of(pz, count, seed=count + 5)
+    keys = sc.score(torch.from_numpy(padded(rows, stride)).cuda())
+    torch.cuda.synchronize()
+    assert sc.error_code() == 0
+    q_ref = bo.mlp_action_values(rows, ws, pz.num_values)  # [P, G], mean over members
+    q_dev = sc.last_q(count).cpu().numpy() / models
+    assert q_dev.shape == q_ref.shape
+    # bf16 operands and bf16 activations between layers, fp32 accumulation
+    assert np.abs(q_dev - q_ref).max() <= 5e-3, np.abs(q_dev - q_ref).max()
+    assert np.array_equal(keys.cpu().numpy().astype(np.uint32),
+                          bo.q_to_score_key(q_dev.reshape(-1).astype(np.float32), -150.0))
+
+
+def test_engine_with_action_value_scorer_matches_oracle_on_device_scores():
+    """Engine step with the parent scorer: candidate p*G + m takes q[p, m]; selection is exact given those keys."""
+    pz = puzzles.puzzle54()
+    beam = 700
+    ws = _q_weights(pz, 2)
+    cfg = be.config_for_puzzle(pz, global_beam_width=beam, max_depth=6, beta=1.2, hash_load_factor=0.45,
+                               probe_limit=256, band_rounds=8, inference_backend="mlp")
+    ext = be.build_extension()
+    be.init_distributed_if_needed(cfg)
+    sizes = ext.derive_sizes(cfg)
+    sc = scorers.MLPActionValueScorer(ws, 54, cfg["state_size_bytes"], 6, pz.fanout, max_parents=sizes["k_work"])
+    _, cfg, buffers, engine = be.configure_engine(pz, cfg=cfg, scorer=sc)
+    frontier = np.unique(children_of(pz, 400, seed=3), axis=0)
+    for graph in (False, True):
+        engine.load_frontier(frontier)
+        engine.enable_cuda_graphs(graph)
+        engine.step()
+        st = engine.status()
+        assert st["status_bits"] == 0 and sc.error_code() == 0
+        ncand = frontier.shape[0] * pz.fanout
+        dev_scores = buffers["cand_score"][:ncand].cpu().numpy().astype(np.uint32)
+        q_ref = bo.mlp_action_values(frontier, ws, 6).reshape(-1)
+        assert np.abs(dev_scores.astype(np.int64) - bo.q_to_score_key(q_ref, -150.0).astype(np.int64)).max() <= 2
+        want = bo.depth_step([frontier], pz.generators, pz.solved, None, beam, score_override=[dev_scores])
+        assert np.array_equal(bo.sorted_rows(engine.frontier()), bo.sorted_rows(want.states))
