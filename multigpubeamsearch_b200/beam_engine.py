@@ -167,7 +167,9 @@ def allocate_buffers(ext: _Ext, cfg: Dict[str, Any]) -> Dict[str, torch.Tensor]:
         "hash_table": z((sizes["hash_capacity"] * 32,), torch.uint8),
         "hist": z((sizes["hist_words"],), torch.int32),
         "tie_buf": z((world * _lib.TIE_SEG_WORDS,), torch.int64),
-        "history_payload": z((max(1, int(cfg["max_depth"])), k_work), torch.int32),
+        # back-pointer rows, written round-robin by depth: max_depth rows keep a whole search on the device,
+        # "history_rows" = 1 or 2 is enough when a CPUHistoryArchive copies every layer after its step
+        "history_payload": z((max(1, int(cfg.get("history_rows") or cfg["max_depth"])), k_work), torch.int32),
         "score_current": z((k_work,), torch.int32),
         "score_next": z((k_work,), torch.int32),
         "ctrl": z((C.sizeof(_lib.MgbsCtrl),), torch.uint8),
@@ -536,6 +538,12 @@ class BeamEngine:
         c = self._read_ctrl()
         k = int(c.frontier_count[c.depth & 1])
         return self.buffers["history_payload"][c.depth - 1, :k].cpu().numpy().astype(np.uint32)
+
+    def history_layer(self, depth: int, count: int) -> np.ndarray:
+        """Packed back-pointers of the first ``count`` rows of the depth ``depth``+1 frontier (valid until the ring of
+        history rows wraps past it)."""
+        h = self.buffers["history_payload"]
+        return h[depth % h.shape[0], :count].cpu().numpy().astype(np.uint32)
 
     def current_state_bytes(self, i: int) -> bytes:
         c = self._read_ctrl()

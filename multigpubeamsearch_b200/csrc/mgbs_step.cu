@@ -708,7 +708,9 @@ __device__ __forceinline__ void emit_row(const StepArgs& a, uint64_t i, uint32_t
   if (a.next_score) a.next_score[pos] = k;
   if (a.next_hash) a.next_hash[pos] = h;
   const int32_t depth = a.ctrl->depth;
-  if (a.history && depth < a.history_depths) a.history[(int64_t)depth * a.frontier_cap + pos] = payload;
+  // the rows form a ring: hosts that archive every layer after its step need one row, the others size it to
+  // the deepest search
+  if (a.history && a.history_depths > 0) a.history[(int64_t)(depth % a.history_depths) * a.frontier_cap + pos] = payload;
 }
 
 

@@ -71,15 +71,47 @@ def reconstruct_path(engine: BeamEngine) -> Optional[List[int]]:
     return moves[::-1]
 
 
+def reconstruct_path_from_archive(engine: BeamEngine, archive) -> Optional[List[int]]:
+    """The same walk-back over a CPUHistoryArchive (the device then keeps only a small ring of history rows)."""
+    c = engine._read_ctrl()
+    if not c.found:
+        return None
+    if c.found_depth == 0:
+        return []
+    world = _world(engine)
+    payloads: List[Any] = [int(c.found_payload)]
+    if world > 1:
+        payloads = [None] * world
+        dist.all_gather_object(payloads, int(c.found_payload))
+    finders = [p for p in payloads if p != NO_PAYLOAD]
+    if not finders:
+        return None
+    parent, prank, move = unpack_payload(finders[0])
+
+    def exchange(value, src):
+        box = [value]
+        dist.broadcast_object_list(box, src=int(src))
+        return box[0]
+
+    head = archive.path_to(int(c.found_depth) - 1, int(parent), int(prank), exchange if world > 1 else None)
+    return head + [int(move)]
+
+
 def solve_one(engine: BeamEngine, puzzle: Puzzle, start: np.ndarray, max_depth: int, sample_id: int = 0,
-              prepass: bool = True, depth_log: Optional[List[Dict[str, Any]]] = None) -> Dict[str, Any]:
-    """Search one start state; returns {id, found, depth, path, valid, status_bits, wall_ms, depths_prepass}."""
+              prepass: bool = True, depth_log: Optional[List[Dict[str, Any]]] = None, archive=None) -> Dict[str, Any]:
+    """Search one start state; returns {id, found, depth, path, valid, status_bits, wall_ms, depths_prepass}.
+
+    With ``archive`` (a history_archive.CPUHistoryArchive over this engine) every depth's back-pointers are copied
+    to the host after its step - and checkpointed, if the archive was built with checkpoint=True - and the path is
+    rebuilt from the archive."""
     start = np.ascontiguousarray(start, dtype=np.uint8)
     world, rank = _world(engine), int(engine.cfg["rank"])
     n = int(engine.cfg["state_len"])
     owner = int(engine.lib.mgbs_hash64_host(start.ctypes.data_as(C.c_void_p), n) % world)
     t0 = time.perf_counter()
     engine.reset_search(bytes(start), active_on_this_rank=(owner == rank))
+    if archive is not None:
+        archive.start_new()
     beam = int(engine.cfg["global_beam_width"])
     fanout = int(engine.cfg["fanout"])
     st = engine.status()
@@ -105,6 +137,8 @@ def solve_one(engine: BeamEngine, puzzle: Puzzle, start: np.ndarray, max_depth: 
         engine.step()
         st = engine.status()
         bits |= st["status_bits"]
+        if archive is not None:
+            archive.after_step(st["depth"], st["current_size"])
         depths_prepass += int(in_prepass)
         if depth_log is not None and rank == 0:
             depth_log.append({
@@ -115,7 +149,11 @@ def solve_one(engine: BeamEngine, puzzle: Puzzle, start: np.ndarray, max_depth: 
             })
     if in_prepass:
         engine.end_uniform_score()
-    path = reconstruct_path(engine) if st["found"] else None
+    if archive is not None:
+        archive.finish_pending()
+    path = None
+    if st["found"]:
+        path = reconstruct_path_from_archive(engine, archive) if archive is not None else reconstruct_path(engine)
     valid = bool(path is not None and np.array_equal(replay(start, puzzle.generators, path), puzzle.solved))
     return {
         "id": sample_id, "found": bool(st["found"]), "depth": int(st["found_depth"] if st["found"] else st["depth"]),

@@ -288,3 +288,44 @@ def test_solver_loop_with_prepass_matches_oracle(tmp_path):
     # same answers without the prepass
     r2 = solver.solve_one(engine, pz, starts[0], 40, prepass=False)
     assert (r2["found"], r2["depth"]) == (summary["results"][0]["found"], summary["results"][0]["depth"])
+
+
+def test_history_archive_with_one_device_row_and_resume(tmp_path):
+    """The device keeps a ring of ONE history row; the host archive collects every layer, checkpoints it, and a
+    second engine resumes from the files and finishes the search with the same answer and a valid path."""
+    from multigpubeamsearch_b200 import solver
+    from multigpubeamsearch_b200.history_archive import CPUHistoryArchive
+    pz = puzzles.lrx(16)
+    start = pz.scramble(9, 30)
+    want = bo.search(start, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam=1024, max_depth=40)
+    assert want.found and want.depth > 6
+    # whole search through the archive
+    engine = make_engine(pz, global_beam_width=1024, max_depth=40, history_rows=1)
+    assert engine.buffers["history_payload"].shape[0] == 1
+    arch = CPUHistoryArchive(engine, str(tmp_path / "full"), sample_id=1, checkpoint=True)
+    r = solver.solve_one(engine, pz, start, 40, prepass=False, archive=arch)
+    arch.finish()
+    assert r["found"] and r["depth"] == want.depth and r["valid"] and len(r["path"]) == want.depth
+    # stop after 5 depths, resume in a fresh engine
+    e1 = make_engine(pz, global_beam_width=1024, max_depth=40, history_rows=1)
+    a1 = CPUHistoryArchive(e1, str(tmp_path / "cut"), sample_id=1, checkpoint=True)
+    e1.reset_search(bytes(start))
+    a1.start_new()
+    for _ in range(5):
+        e1.step()
+        st = e1.status()
+        a1.after_step(st["depth"], st["current_size"])
+    a1.finish()
+    e2 = make_engine(pz, global_beam_width=1024, max_depth=40, history_rows=1)
+    a2 = CPUHistoryArchive(e2, str(tmp_path / "cut"), sample_id=1, checkpoint=True)
+    assert a2.try_resume() == 5
+    st = e2.status()
+    assert st["depth"] == 5
+    while not st["found"] and st["depth"] < 40:
+        e2.step()
+        st = e2.status()
+        a2.after_step(st["depth"], st["current_size"])
+    a2.finish()
+    assert st["found"] and st["found_depth"] == want.depth and st["status_bits"] == 0
+    path = solver.reconstruct_path_from_archive(e2, a2)
+    assert len(path) == want.depth and np.array_equal(solver.replay(start, pz.generators, path), pz.solved)
