@@ -80,7 +80,7 @@ class MgbsConfig(C.Structure):
         ("recv_hash", _P), ("recv_fp", _P), ("recv_score", _P), ("recv_payload", _P), ("recv_states", _P),
         ("send_counts", _P), ("recv_counts", _P),
         ("exchange_mode", C.c_int32), ("pad1", C.c_int32), ("sym", _P), ("sym_bytes", C.c_int64), ("tickets", _P),
-        ("io_stage", _P),
+        ("io_stage", _P), ("hash_mode", C.c_int32), ("zobrist_values", C.c_int32), ("zobrist", _P),
     ]
 
 

@@ -272,6 +272,17 @@ class BeamEngine:
         c.frontier_score[0], c.frontier_score[1] = p("score_current"), p("score_next")
         c.ctrl = p("ctrl")
         c.io_stage = p("io_stage")
+        hash_mode = str(cfg.get("hash_mode", "fnv")).lower()
+        if hash_mode not in {"fnv", "zobrist128"}:
+            raise RuntimeError(f"unknown hash_mode {hash_mode!r}")
+        if hash_mode == "zobrist128":
+            # the v6 128-bit Zobrist hash (production_v6_dispatcher.py:109-113): table [state_len, num_values, 2] u64
+            from .puzzles import zobrist_table
+            nv = int(cfg["num_values"])
+            tab = zobrist_table(int(cfg["state_len"]), nv)
+            self._zobrist_host = tab
+            buffers["zobrist"] = torch.from_numpy(tab.view(np.int64)).to(buffers["ctrl"].device)
+            c.hash_mode, c.zobrist_values, c.zobrist = 1, nv, buffers["zobrist"].data_ptr()
         for side in ("send", "recv"):
             setattr(c, f"{side}_hash", p(f"{side}_hash"))
             setattr(c, f"{side}_fp", p(f"{side}_fingerprint"))
@@ -363,6 +374,20 @@ class BeamEngine:
             raise RuntimeError(f"central state must be {n} bytes, got {len(state)}")
         self._central = np.frombuffer(state, dtype=np.uint8).copy()
         self.buffers["central_state"].copy_(torch.from_numpy(self._central))
+
+    def owner_of(self, state: np.ndarray) -> int:
+        """Rank that owns ``state`` (where reset_search must be active): hash mod world, or the Zobrist owner rule."""
+        world = int(self.cfg["world_size"])
+        s = np.ascontiguousarray(state, dtype=np.uint8)
+        if getattr(self, "_zobrist_host", None) is not None:
+            lo = hi = 0
+            for pos in range(int(self.cfg["state_len"])):
+                lo ^= int(self._zobrist_host[pos, int(s[pos]), 0])
+                hi ^= int(self._zobrist_host[pos, int(s[pos]), 1])
+            lo = lo + 4 if lo <= 2 else lo
+            hi = 4 if hi == 0 else hi
+            return int((hi ^ ((lo * 0x9E3779B97F4A7C15) & 0xFFFFFFFFFFFFFFFF)) % world)
+        return int(self.lib.mgbs_hash64_host(s.ctypes.data_as(C.c_void_p), int(self.cfg["state_len"])) % world)
 
     def set_scorer(self, scorer) -> None:
         """Attach a device scorer object (see scorers.MLPValueScorer): it supplies a C callback and its handle."""
@@ -617,6 +642,6 @@ def run_one_search(engine: BeamEngine, state: np.ndarray, max_depth: int) -> Dic
     state = np.ascontiguousarray(state, dtype=np.uint8)
     world, rank = int(engine.cfg["world_size"]), int(engine.cfg["rank"])
     n = int(engine.cfg["state_len"])
-    owner = int(engine.lib.mgbs_hash64_host(state.ctypes.data_as(C.c_void_p), n) % world)
+    owner = engine.owner_of(state)
     engine.reset_search(bytes(state), active_on_this_rank=(owner == rank))
     return engine.search(max_depth)

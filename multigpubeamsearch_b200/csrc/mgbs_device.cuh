@@ -39,6 +39,19 @@ MGBS_HD uint64_t finish_fingerprint(uint64_t f) {
   return f;
 }
 
+// 128-bit Zobrist hash mode (hash_state128_zobrist, beam_kernels_stream2.cu:28-38): the XOR over positions of a
+// 128-bit table entry per (position, value).  Its low word takes the place of the 64-bit hash and its high word that
+// of the fingerprint; both get the same sentinel remap as above because the dedup table uses 0 as "empty".
+MGBS_HD uint64_t finish_zobrist_lo(uint64_t lo) { return lo <= 2ull ? lo + 4ull : lo; }
+MGBS_HD uint64_t finish_zobrist_hi(uint64_t hi) { return hi == 0ull ? 4ull : hi; }
+
+// destination rank of a candidate: hash mod world (beam_kernels.cu:582), or for the Zobrist mode
+// (hi ^ lo * golden) mod world (owner_from_hash128, beam_kernels_stream3.cu:29-35)
+MGBS_HD uint32_t owner_of(uint64_t h, uint64_t f, uint32_t world, int hash_mode) {
+  if (hash_mode == MGBS_HASH_ZOBRIST128) return (uint32_t)((f ^ (h * kGolden)) % (uint64_t)world);
+  return (uint32_t)(h % (uint64_t)world);
+}
+
 // back-pointer: parent row (23 bits) | source rank (4 bits) | move (5 bits); integer order = the duplicate
 // tie-break order (parent_idx, source_rank, move) of candidate_better (beam_kernels_stream4.cu:25-33)
 constexpr int kMoveBits = 5;

@@ -152,6 +152,8 @@ int mgbs_engine_create(const MgbsConfig* cfg, MgbsEngine** out) {
       !c.cand_payload || !c.table || !c.hist || !c.tie_buf || !c.ctrl)
     return MGBS_ERR_ARG;
   if (c.exchange_mode != MGBS_EXCHANGE_NCCL && c.exchange_mode != MGBS_EXCHANGE_PEER) return MGBS_ERR_ARG;
+  if (c.hash_mode != MGBS_HASH_FNV && c.hash_mode != MGBS_HASH_ZOBRIST128) return MGBS_ERR_ARG;
+  if (c.hash_mode == MGBS_HASH_ZOBRIST128 && (!c.zobrist || c.zobrist_values < 1 || c.zobrist_values > 256)) return MGBS_ERR_ARG;
   if (c.world_size > 1 && c.exchange_mode == MGBS_EXCHANGE_PEER) {
     if (!c.children || c.bucket_cap < 1 || !c.send_counts || !c.sym || !c.tickets) return MGBS_ERR_ARG;
   } else if (c.world_size > 1) {
@@ -491,6 +493,8 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     x.children = c.children;
     x.cand_hash = c.cand_hash; x.cand_fp = c.cand_fp; x.cand_score = c.cand_score; x.cand_payload = c.cand_payload;
     x.ctrl = c.ctrl;
+    x.zobrist = c.hash_mode == MGBS_HASH_ZOBRIST128 ? c.zobrist : nullptr;
+    x.zobrist_values = c.zobrist_values;
     MGBS_TRACE();  // depth_begin + clears
     MGBS_TRY(launch_expand(x, c.frontier_cap, e->sms, st));
     MGBS_TRACE();  // expand
@@ -541,6 +545,7 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     pr.off_hash = L.hash[parity]; pr.off_fp = L.fp[parity]; pr.off_score = L.score[parity];
     pr.off_payload = L.payload[parity]; pr.off_counts = L.counts[parity];
     pr.off_route_flag = L.route_flag;
+    pr.hash_mode = c.hash_mode;
     a.cvh.hash = c.cand_hash; a.cvh.fp = c.cand_fp; a.cvh.score = c.cand_score; a.cvh.payload = c.cand_payload;
     a.cvh.states = nullptr;
     a.cvh.counts = &c.ctrl->cand_count;
@@ -570,6 +575,7 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     r.send_counts = c.send_counts;
     r.ctrl = c.ctrl;
     r.world = W; r.stride = c.state_stride; r.bucket_cap = (uint32_t)c.bucket_cap;
+    r.hash_mode = c.hash_mode;
     MGBS_TRY(launch_route(r, c.cand_cap, e->sms, st));
     MGBS_TRY(exchange(e, st));
     MGBS_TRY(launch_clamp_counts(c.recv_counts, W, (uint32_t)c.bucket_cap, st));
@@ -713,6 +719,7 @@ int mgbs_launch_expand(const uint8_t* frontier, const int32_t* count_dev, int64_
   x.score_mode = score_mode; x.uniform_score = uniform_score;
   x.children = children; x.cand_hash = cand_hash; x.cand_fp = cand_fp; x.cand_score = cand_score;
   x.cand_payload = cand_payload; x.ctrl = ctrl;
+  x.zobrist = nullptr; x.zobrist_values = 0;
   int sms = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   return mgbs::launch_expand(x, count_dev ? (int64_t)1 << 22 : count, sms, (cudaStream_t)stream);

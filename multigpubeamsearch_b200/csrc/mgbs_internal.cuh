@@ -47,6 +47,8 @@ struct ExpandArgs {
   uint32_t* cand_score;
   uint32_t* cand_payload;
   MgbsCtrl* ctrl;
+  const uint64_t* zobrist;  // MGBS_HASH_ZOBRIST128: [n, zobrist_values, 2]; null = FNV hash + fingerprint
+  int32_t zobrist_values;
 };
 
 // Candidate view: one or more buckets of `cap` entries with device-side fill counts.
@@ -102,6 +104,7 @@ struct RouteArgs {
   // peer mode: records go straight into the owner's receive buckets; offsets of the bucket arrays of this parity
   PeerCtx peer;
   int64_t off_hash, off_fp, off_score, off_payload, off_counts, off_route_flag;
+  int32_t hash_mode;
   int32_t rank;
 };
 

@@ -31,7 +31,7 @@ namespace mgbs {
 // ------------------------------------------------------------------------------------------------
 
 
-template <int WORDS>
+template <int WORDS, int ZOB>
 __global__ void __launch_bounds__(kExpandThreads, 3) k_expand(ExpandArgs a) {
   constexpr int PITCH_W = WORDS + 1;
   __shared__ uint32_t par_s[kExpandTile * PITCH_W];
@@ -69,7 +69,8 @@ __global__ void __launch_bounds__(kExpandThreads, 3) k_expand(ExpandArgs a) {
       const int64_t p = p0 + pl;
       if (p >= P) continue;
       const uint8_t* row = reinterpret_cast<const uint8_t*>(par_s + pl * PITCH_W);
-      uint64_t h = kFnvOffset, f = kGolden;
+      uint64_t h = ZOB ? 0ull : kFnvOffset, f = ZOB ? 0ull : kGolden;
+      const ulonglong2* ztab = reinterpret_cast<const ulonglong2*>(a.zobrist);
       int ham = 0;
       const int64_t c = p * G + g;
       uint4* child_dst = a.children ? reinterpret_cast<uint4*>(a.children + c * (int64_t)a.stride) : nullptr;
@@ -88,8 +89,14 @@ __global__ void __launch_bounds__(kExpandThreads, 3) k_expand(ExpandArgs a) {
           for (int j = 0; j < 4; ++j) {
             if (wi * 4 + j < n) {
               const uint32_t v = row[(gi >> (8 * j)) & 0xffu];
-              h = (h ^ (uint64_t)v) * kFnvPrime;
-              f ^= (uint64_t)v + kGolden + (f << 6) + (f >> 2);
+              if (ZOB) {
+                const ulonglong2 z = __ldg(ztab + (wi * 4 + j) * a.zobrist_values + (int)v);
+                h ^= z.x;
+                f ^= z.y;
+              } else {
+                h = (h ^ (uint64_t)v) * kFnvPrime;
+                f ^= (uint64_t)v + kGolden + (f << 6) + (f >> 2);
+              }
               ham += (v != ((sv >> (8 * j)) & 0xffu));
               acc |= v << (8 * j);
             }
@@ -98,8 +105,13 @@ __global__ void __launch_bounds__(kExpandThreads, 3) k_expand(ExpandArgs a) {
         }
         if (child_dst) child_dst[q] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
       }
-      h = finish_hash(h);
-      f = finish_fingerprint(f);
+      if (ZOB) {
+        h = finish_zobrist_lo(h);
+        f = finish_zobrist_hi(f);
+      } else {
+        h = finish_hash(h);
+        f = finish_fingerprint(f);
+      }
       const uint32_t payload = pack_payload((uint32_t)p, (uint32_t)a.rank, (uint32_t)g);
       a.cand_hash[c] = h;
       a.cand_fp[c] = f;
@@ -902,11 +914,12 @@ __global__ void __launch_bounds__(kStreamThreads) k_route(RouteArgs a) {
   const int vecs = a.stride >> 4;
   for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < rounded; i += gridDim.x * blockDim.x) {
     const bool valid = i < cnt;
-    uint64_t h = 0;
+    uint64_t h = 0, f = 0;
     uint32_t owner = 0;
     if (valid) {
       h = __ldg(a.hash + i);
-      owner = (uint32_t)(h % (uint64_t)a.world);
+      f = __ldg(a.fp + i);
+      owner = owner_of(h, f, (uint32_t)a.world, a.hash_mode);
     }
     const unsigned vm = __ballot_sync(0xffffffffu, valid);
     if (!valid) continue;
@@ -922,7 +935,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_route(RouteArgs a) {
     }
     const uint64_t d = (uint64_t)owner * a.bucket_cap + pos;
     a.s_hash[d] = h;
-    a.s_fp[d] = __ldg(a.fp + i);
+    a.s_fp[d] = f;
     a.s_score[d] = __ldg(a.score + i);
     a.s_payload[d] = __ldg(a.payload + i);
     const uint4* src = reinterpret_cast<const uint4*>(a.states + (uint64_t)i * a.stride);
@@ -958,12 +971,16 @@ __global__ void __launch_bounds__(kStreamThreads) k_route_band(StepArgs a, Route
     bool in = false;
     uint64_t h = 0;
     uint32_t k = 0, owner = 0;
+    uint64_t f = 0;
     if (i < cnt) {
       h = __ldg(r.hash + i);
       k = __ldg(r.score + i);
       const uint64_t s = order_key(k, h, hb);
       in = s >= D && s < E;
-      owner = (uint32_t)(h % (uint64_t)r.world);
+      if (in) {
+        f = __ldg(r.fp + i);
+        owner = owner_of(h, f, (uint32_t)r.world, r.hash_mode);
+      }
     }
     const unsigned vm = __ballot_sync(0xffffffffu, in);
     if (!in) continue;
@@ -980,7 +997,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_route_band(StepArgs a, Route
     uint8_t* ob = r.peer.base[owner];
     const uint64_t d = (uint64_t)r.rank * r.bucket_cap + pos;
     reinterpret_cast<uint64_t*>(ob + r.off_hash)[d] = h;
-    reinterpret_cast<uint64_t*>(ob + r.off_fp)[d] = __ldg(r.fp + i);
+    reinterpret_cast<uint64_t*>(ob + r.off_fp)[d] = f;
     reinterpret_cast<uint32_t*>(ob + r.off_score)[d] = k;
     reinterpret_cast<uint32_t*>(ob + r.off_payload)[d] = __ldg(r.payload + i);
   }
@@ -1072,12 +1089,23 @@ int launch_expand(const ExpandArgs& a, int64_t max_parents, int sms, cudaStream_
   const int words = a.stride / 4;
   int64_t tiles = (max_parents + kExpandTile - 1) / kExpandTile;
   int grid = (int)(tiles < (int64_t)sms * 6 ? (tiles < 1 ? 1 : tiles) : (int64_t)sms * 6);
+  if (a.zobrist) {
+    switch (words) {
+      case 4: k_expand<4, 1><<<grid, kExpandThreads, 0, st>>>(a); break;
+      case 8: k_expand<8, 1><<<grid, kExpandThreads, 0, st>>>(a); break;
+      case 16: k_expand<16, 1><<<grid, kExpandThreads, 0, st>>>(a); break;
+      case 24: k_expand<24, 1><<<grid, kExpandThreads, 0, st>>>(a); break;
+      case 32: k_expand<32, 1><<<grid, kExpandThreads, 0, st>>>(a); break;
+      default: return MGBS_ERR_UNSUPPORTED;
+    }
+    return (int)cudaGetLastError();
+  }
   switch (words) {
-    case 4: k_expand<4><<<grid, kExpandThreads, 0, st>>>(a); break;
-    case 8: k_expand<8><<<grid, kExpandThreads, 0, st>>>(a); break;
-    case 16: k_expand<16><<<grid, kExpandThreads, 0, st>>>(a); break;
-    case 24: k_expand<24><<<grid, kExpandThreads, 0, st>>>(a); break;
-    case 32: k_expand<32><<<grid, kExpandThreads, 0, st>>>(a); break;
+    case 4: k_expand<4, 0><<<grid, kExpandThreads, 0, st>>>(a); break;
+    case 8: k_expand<8, 0><<<grid, kExpandThreads, 0, st>>>(a); break;
+    case 16: k_expand<16, 0><<<grid, kExpandThreads, 0, st>>>(a); break;
+    case 24: k_expand<24, 0><<<grid, kExpandThreads, 0, st>>>(a); break;
+    case 32: k_expand<32, 0><<<grid, kExpandThreads, 0, st>>>(a); break;
     default: return MGBS_ERR_UNSUPPORTED;
   }
   return (int)cudaGetLastError();

@@ -104,6 +104,15 @@ def by_name(name: str) -> Puzzle:
     raise ValueError(f"unknown puzzle {name!r}")
 
 
+def zobrist_table(state_len: int, num_values: int) -> np.ndarray:
+    """[state_len, num_values, 2] uint64 Zobrist table {lo, hi} for the 128-bit hash mode: the corner of the
+    reference's production table (production_v6_dispatcher.py:109-113, numpy default_rng(0xC0DEC0DE), shape
+    (128, 128, 2)) that this puzzle indexes."""
+    rng = np.random.default_rng(0xC0DEC0DE)
+    z = rng.integers(0, np.iinfo(np.uint64).max, size=(128, 128, 2), dtype=np.uint64)
+    return np.ascontiguousarray(z[:state_len, :num_values, :])
+
+
 def mlp_weights(in_features: int, hidden: int = 1024, seed: int = 7000, model_idx: int = 0,
                 std: float = 0.02) -> Dict[str, np.ndarray]:
     """Random-init value MLP in_features -> hidden -> hidden -> 1 (Gaussian std 0.02, zero biases), float32.

@@ -107,7 +107,7 @@ def solve_one(engine: BeamEngine, puzzle: Puzzle, start: np.ndarray, max_depth: 
     start = np.ascontiguousarray(start, dtype=np.uint8)
     world, rank = _world(engine), int(engine.cfg["rank"])
     n = int(engine.cfg["state_len"])
-    owner = int(engine.lib.mgbs_hash64_host(start.ctypes.data_as(C.c_void_p), n) % world)
+    owner = engine.owner_of(start)
     t0 = time.perf_counter()
     engine.reset_search(bytes(start), active_on_this_rank=(owner == rank))
     if archive is not None:

@@ -22,12 +22,21 @@ def gather_rows(rows):
     return out
 
 
-def run_case(name, beam, scramble_len, depths, backend, graph, exchange="peer"):
+def run_case(name, beam, scramble_len, depths, backend, graph, exchange="peer", hash_mode="fnv"):
     world, rank = dist.get_world_size(), dist.get_rank()
     pz = puzzles.by_name(name)
     cfg = be.config_for_puzzle(pz, world_size=world, rank=rank, global_beam_width=beam, max_depth=depths + 2,
                                beta=1.2, gamma=1.25, hash_load_factor=0.45, probe_limit=256, band_rounds=8,
-                               inference_backend=backend, use_cuda_graphs=graph, exchange=exchange)
+                               inference_backend=backend, use_cuda_graphs=graph, exchange=exchange, hash_mode=hash_mode)
+    table = bo.zobrist_table(pz.state_len, pz.num_values) if hash_mode == "zobrist128" else None
+    hasher = (lambda c: bo.hash128_zobrist(c, table)) if table is not None else None
+
+    def owners(rows):
+        if table is not None:
+            lo, hi = bo.hash128_zobrist(rows, table)
+            return bo.owner_from_hash128(hi, lo, world)
+        return bo.owner_rank(bo.hash64(rows), world)
+
     sc = None
     weights = None
     if backend == "mlp":
@@ -39,7 +48,8 @@ def run_case(name, beam, scramble_len, depths, backend, graph, exchange="peer"):
     _, cfg, buffers, engine = be.configure_engine(pz, cfg=cfg, scorer=sc)
     start = pz.scramble(3, scramble_len)
     n = pz.state_len
-    owner = int(bo.owner_rank(bo.hash64(start[None, :]), world)[0])
+    owner = int(owners(start[None, :])[0])
+    assert engine.owner_of(start) == owner
     engine.reset_search(bytes(start), active_on_this_rank=(owner == rank))
     fronts = [start[None, :] if r == owner else start[:0][None, :].reshape(0, n) for r in range(world)]
     for depth in range(depths):
@@ -57,16 +67,16 @@ def run_case(name, beam, scramble_len, depths, backend, graph, exchange="peer"):
         all_rows = gather_rows((rows, pay, sco))
         # every row lives on its hash owner
         if rows.shape[0]:
-            assert (bo.owner_rank(bo.hash64(rows), world) == rank).all()
+            assert (owners(rows) == rank).all()
         if backend == "mlp":
             # expected set from the device's own scores: gather (child bytes -> key) of all candidates of all ranks
             ncand = fronts[rank].shape[0] * pz.fanout
             dev_scores = buffers["cand_score"][:ncand].cpu().numpy().astype(np.uint32)
             sc_all = [None] * world
             dist.all_gather_object(sc_all, dev_scores)
-            want = bo.depth_step(fronts, pz.generators, pz.solved, None, beam, score_override=sc_all)
+            want = bo.depth_step(fronts, pz.generators, pz.solved, None, beam, score_override=sc_all, hasher=hasher)
         else:
-            want = bo.depth_step(fronts, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam)
+            want = bo.depth_step(fronts, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam, hasher=hasher)
         got = np.concatenate([r for r, _, _ in all_rows]) if any(r.shape[0] for r, _, _ in all_rows) else rows[:0]
         assert got.shape[0] == want.states.shape[0], (depth, got.shape, want.states.shape)
         assert np.array_equal(bo.sorted_rows(got), bo.sorted_rows(want.states)), f"depth {depth}"
@@ -79,7 +89,7 @@ def run_case(name, beam, scramble_len, depths, backend, graph, exchange="peer"):
         if st["found"]:
             break
     if rank == 0:
-        print(f"CASE_OK {name} beam={beam} backend={backend} graph={graph} exchange={exchange} depths={depth + 1} "
+        print(f"CASE_OK {name} beam={beam} backend={backend} graph={graph} exchange={exchange} hash={hash_mode} depths={depth + 1} "
               f"frontier={sum(f.shape[0] for f in fronts)}", flush=True)
     engine.close()
     dist.barrier()
@@ -94,6 +104,7 @@ def main():
         run_case("lrx16", 1024, 30, 12, "central_hamming", False, exchange)
         run_case("rand54", 4096, 12, 6, "central_hamming", True, exchange)
         run_case("rand54", 2048, 30, 5, "mlp", True, exchange)
+        run_case("rand54", 4096, 12, 5, "central_hamming", True, exchange, hash_mode="zobrist128")
     # the engine's own depth loop: all ranks stop at the same depth with the same answer
     pz = puzzles.puzzle54()
     world, rank = dist.get_world_size(), dist.get_rank()

@@ -329,3 +329,35 @@ def test_history_archive_with_one_device_row_and_resume(tmp_path):
     assert st["found"] and st["found_depth"] == want.depth and st["status_bits"] == 0
     path = solver.reconstruct_path_from_archive(e2, a2)
     assert len(path) == want.depth and np.array_equal(solver.replay(start, pz.generators, path), pz.solved)
+
+
+@pytest.mark.parametrize("name,count,beam", [("rand54", 500, 1024), ("rand96", 300, 700), ("lrx16", 200, 64)])
+def test_zobrist_hash_mode_matches_oracle(name, count, beam):
+    """The v6 128-bit Zobrist hash instead of FNV + fingerprint: candidate hashes are the oracle's (lo, hi) pairs and
+    a step keeps exactly the oracle's survivors under the (score, lo, hi) order."""
+    pz = puzzles.by_name(name)
+    engine = make_engine(pz, global_beam_width=beam, hash_mode="zobrist128")
+    table = bo.zobrist_table(pz.state_len, pz.num_values)
+    frontier = random_frontier(pz, count, seed=count + 3)[: engine.sizes()["k_work"]]
+    hasher = lambda c: bo.hash128_zobrist(c, table)
+    for graph in (False, True):
+        engine.load_frontier(frontier, depth=0)
+        engine.enable_cuda_graphs(graph)
+        engine.step()
+        st = engine.status()
+        assert st["status_bits"] == 0, st["status_names"]
+        ncand = frontier.shape[0] * pz.fanout
+        lo, hi = hasher(bo.expand(frontier, pz.generators))
+        assert np.array_equal(engine.buffers["cand_hash"][:ncand].cpu().numpy().view(np.uint64), lo)
+        assert np.array_equal(engine.buffers["cand_fingerprint"][:ncand].cpu().numpy().view(np.uint64), hi)
+        want = bo.depth_step([frontier], pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam, hasher=hasher)
+        got = engine.frontier()
+        assert np.array_equal(bo.sorted_rows(got), bo.sorted_rows(want.states))
+        assert {bytes(r): int(p) for r, p in zip(got, engine.frontier_payloads())} == \
+            {bytes(r): int(p) for r, p in zip(want.states, want.payload)}
+    # the start state's owner under the Zobrist rule, as the host computes it
+    lo0, hi0 = hasher(frontier[:1])
+    for w in (2, 3, 8):
+        engine.cfg["world_size"] = w
+        assert engine.owner_of(frontier[0]) == int(bo.owner_from_hash128(hi0, lo0, w)[0])
+    engine.cfg["world_size"] = 1

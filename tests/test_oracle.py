@@ -190,3 +190,32 @@ def test_action_value_network_reduces_to_the_value_network_for_one_move():
     for m in range(5):
         v = bo.mlp_forward(states, [dict(w, w3=w3[m], b3=b3[m])], 6)
         assert np.allclose(q[:, m], v, atol=1e-6)
+
+
+def test_zobrist_hash_is_the_xor_of_table_entries_and_owner_rule():
+    """hash128_zobrist against a scalar restatement of the reference's CPU mirror (tests/stream2_reference_smoke.py:41-48)
+    and owner_from_hash128 against the Python rule (production_v6_dispatcher.py:116-119)."""
+    table = bo.zobrist_table(54, 6)
+    assert table.shape == (54, 6, 2) and table.dtype == np.uint64
+    # the table is the corner of the (128, 128, 2) production table drawn from default_rng(0xC0DEC0DE)
+    full = np.random.default_rng(0xC0DEC0DE).integers(0, np.iinfo(np.uint64).max, size=(128, 128, 2), dtype=np.uint64)
+    assert np.array_equal(table, full[:54, :6])
+    rng = np.random.default_rng(12)
+    states = rng.integers(0, 6, size=(40, 54)).astype(np.uint8)
+    lo, hi = bo.hash128_zobrist(states, table)
+    for i in (0, 17, 39):
+        l = h = 0
+        for p in range(54):
+            l ^= int(table[p, states[i, p], 0])
+            h ^= int(table[p, states[i, p], 1])
+        assert (int(lo[i]), int(hi[i])) == (l, h)
+        for w in (2, 3, 8):
+            assert int(bo.owner_from_hash128(hi[i:i + 1], lo[i:i + 1], w)[0]) == \
+                (h ^ ((l * 0x9E3779B97F4A7C15) & 0xFFFFFFFFFFFFFFFF)) % w
+    # a different hash only reorders equal scores: the kept set has the same size and the same score multiset
+    pz = puzzles.puzzle54()
+    frontier = np.unique(np.stack([pz.scramble(j, 12) for j in range(60)]), axis=0)
+    a = bo.depth_step([frontier], pz.generators, pz.solved, bo.hamming_scorer(pz.solved), 200)
+    b = bo.depth_step([frontier], pz.generators, pz.solved, bo.hamming_scorer(pz.solved), 200,
+                      hasher=lambda c: bo.hash128_zobrist(c, table))
+    assert a.states.shape == b.states.shape and np.array_equal(np.sort(a.score), np.sort(b.score))
