@@ -155,9 +155,12 @@ def allocate_buffers(ext: _Ext, cfg: Dict[str, Any]) -> Dict[str, torch.Tensor]:
     def z(shape, dtype):
         return torch.zeros(shape, dtype=dtype, device=device)
 
-    buffers = {
+    peer_mode = world > 1 and str(cfg.get("exchange", "peer")) == "peer"
+    buffers = {} if peer_mode else {  # peer mode: the frontiers are views into the symmetric region (below)
         "beam_current": z((k_work, stride), torch.uint8),
         "beam_next": z((k_work, stride), torch.uint8),
+    }
+    buffers.update({
         "action_table": z((int(cfg["fanout"]), int(cfg["state_len"])), torch.uint8),
         "central_state": z((int(cfg["state_len"]),), torch.uint8),
         "cand_hash": z((cand_cap,), torch.int64),
@@ -174,10 +177,10 @@ def allocate_buffers(ext: _Ext, cfg: Dict[str, Any]) -> Dict[str, torch.Tensor]:
         "score_next": z((k_work,), torch.int32),
         "ctrl": z((C.sizeof(_lib.MgbsCtrl),), torch.uint8),
         "io_stage": z((k_work * int(cfg["state_len"]),), torch.uint8),
-    }
+    })
     if need_children:
         buffers["next_state_pool"] = z((cand_cap, stride), torch.uint8)
-    if world > 1 and str(cfg.get("exchange", "peer")) == "peer":
+    if peer_mode:
         tmp = _lib.MgbsConfig()
         tmp.world_size, tmp.state_stride, tmp.bucket_cap = world, stride, sizes["bucket_cap_per_peer"]
         tmp.band_rounds, tmp.band_levels = int(cfg["band_rounds"]), int(cfg["band_levels"])

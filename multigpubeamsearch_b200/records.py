@@ -19,7 +19,7 @@ def unpack_payload(payload):
     return parent, rank, move
 
 
-def order_key(score: int, h: int, hash_bits: int = 44) -> int:
+def order_key(score: int, h: int, hash_bits: int = 24) -> int:
     """The 64-bit selection key of the engine: score above the top ``hash_bits`` bits of the 64-bit hash."""
     k = min(int(score), 0xFFFFF)
     return ((k << hash_bits) | (int(h) >> (64 - hash_bits))) if hash_bits else k
