@@ -490,7 +490,11 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     x.solved = c.solved;
     x.n = c.state_len; x.stride = c.state_stride; x.fanout = c.fanout; x.rank = c.rank;
     x.score_mode = c.score_mode; x.uniform_score = c.uniform_score;
-    x.children = c.children;
+    // child rows are needed by a child scorer and by the NCCL exchange; with a parent scorer and survivors rebuilt
+    // from back-pointers nobody reads them
+    const bool rows_unused = c.score_mode == MGBS_SCORE_EXTERNAL && e->parent_scorer != nullptr &&
+                             (W == 1 || c.exchange_mode == MGBS_EXCHANGE_PEER);
+    x.children = rows_unused ? nullptr : c.children;
     x.cand_hash = c.cand_hash; x.cand_fp = c.cand_fp; x.cand_score = c.cand_score; x.cand_payload = c.cand_payload;
     x.ctrl = c.ctrl;
     x.zobrist = c.hash_mode == MGBS_HASH_ZOBRIST128 ? c.zobrist : nullptr;

@@ -35,6 +35,7 @@ def main() -> None:
     ap.add_argument("--beam-per-gpu", type=int, default=0)
     ap.add_argument("--prep", type=int, default=10)
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"], help="GEMM operand type of the scorer")
+    ap.add_argument("--hash-mode", default="fnv", choices=["fnv", "zobrist128"])
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -56,7 +57,7 @@ def main() -> None:
     depths = args.prep + args.warmup + args.steps + 4
     cfg = be.config_for_puzzle(pz, world_size=world, rank=rank, global_beam_width=beam, max_depth=depths, beta=1.2,
                                gamma=1.05, hash_load_factor=0.45, probe_limit=256, band_rounds=3, band_levels=3,
-                               inference_backend="mlp", use_cuda_graphs=True)
+                               inference_backend="mlp", use_cuda_graphs=True, hash_mode=args.hash_mode)
     ext = be.build_extension()
     be.init_distributed_if_needed(cfg)
     sizes = ext.derive_sizes(cfg)
