@@ -63,15 +63,20 @@ class ClockSampler:
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_indices):
+        """One nvidia-smi process for all listed GPUs (an empty list = no sampling: with several ranks only rank 0
+        samples, for every GPU of the job - eight pollers at once were seen to stall the GPUs for milliseconds)."""
         self.proc = None
-        self.gpu_index = gpu_index
+        self.gpu_indices = list(gpu_indices)
 
     def start(self):
+        if not self.gpu_indices:
+            return
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
-                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", ",".join(str(i) for i in self.gpu_indices)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
@@ -84,7 +89,7 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
+        sm, mx, reasons, per_gpu = [], [], set(), {}
         for line in out.strip().splitlines():
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 9:
@@ -92,13 +97,15 @@ class ClockSampler:
             try:
                 sm.append(float(parts[1]))
                 mx.append(float(parts[2]))
+                per_gpu.setdefault(parts[0], []).append(float(parts[1]))
             except ValueError:
                 continue
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons),
+                "per_gpu_sm_mhz": {k: statistics.median(v) for k, v in sorted(per_gpu.items())}}
 
 
 def cpu_baseline_step_rate(threads: int, steps: int = 3, parents: int = CPU_SAMPLE_PARENTS):
@@ -209,7 +216,7 @@ def run_ours(args):
         torch.cuda.synchronize()
         return [a.elapsed_time(b) for a, b in evs]
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler([local_rank] if world == 1 else (list(range(world)) if rank == 0 else []))
     sampler.start()  # nvidia-smi needs a moment to start: it samples the warm-up, the timed steps and the passes after
     timed_steps(W)  # warm-up (captures the graphs)
     cand_before = engine.status()["total_candidates"]
@@ -351,7 +358,8 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": total_ms / K, "p50_ms_per_step": statistics.median(ms),
             "p90_ms_per_step": sorted(ms)[min(len(ms) - 1, int(0.9 * len(ms)))], "max_ms_per_step": max(ms),
-            "rank_ms_per_step": rank_means, "higher_is_better": True,
+            "rank_ms_per_step": rank_means,
+            "slow_steps": sum(1 for x in ms if x > 1.5 * statistics.median(ms)), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
             "config": {"workload": workload_name(world), "global_beam": beam, "beam_per_gpu": BEAM_PER_GPU,
                        "candidates_per_step": total_cands / K, "l2": "256 MB buffer written between timed steps",
