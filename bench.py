@@ -74,7 +74,8 @@ class ClockSampler:
             return
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms",
+                 "100" if len(self.gpu_indices) == 1 else "200",
                  "-i", ",".join(str(i) for i in self.gpu_indices)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
