@@ -105,3 +105,77 @@ def test_archive_rejects_a_checkpoint_of_another_configuration(tmp_path):
         a2 = CPUHistoryArchive(e, str(tmp_path / "x"), checkpoint=False)
         a2.start_new()
         a2.after_step(3, 10)
+
+
+def _archive_rank(rank, world, port, root, out_q):
+    """One gloo rank: every rank runs the same oracle steps over the per-rank frontiers and keeps its own share."""
+    import os
+
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        pz = puzzles.puzzle54()
+        start = pz.scramble(5, 25)
+
+        class ShardEngine(OracleEngine):
+            def __init__(self):
+                super().__init__(pz, 96, rank=rank, world_size=world)
+                self.fronts = None
+
+            def reset_search(self, s):
+                owner = int(bo.owner_rank(bo.hash64(s[None, :]), world)[0])
+                self.fronts = [s[None, :].copy() if r == owner else s[:0][None, :].reshape(0, pz.state_len) for r in range(world)]
+                self.rows, self.depth = self.fronts[rank], 0
+
+            def step(self):
+                res = bo.depth_step(self.fronts, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), self.beam)
+                own = bo.owner_rank(res.h, world)
+                self.fronts = [res.states[own == r] for r in range(world)]
+                self.rows, self.last_layer = self.fronts[rank], res.payload[own == rank].astype(np.uint32)
+                self.depth += 1
+
+        e = ShardEngine()
+        e.reset_search(start)
+        a = CPUHistoryArchive(e, root, sample_id=0, checkpoint=True, barrier=dist.barrier)
+        a.start_new()
+        _run(e, a, 6)
+        a.finish()
+
+        def exchange(value, src):
+            box = [value]
+            dist.broadcast_object_list(box, src=int(src))
+            return box[0]
+
+        # walk back from row 0 of the LAST rank's frontier: every rank takes part, all get the same moves
+        target_rank = world - 1
+        target = exchange(e.fronts[target_rank][0] if rank == target_rank else None, target_rank)
+        moves = a.path_to(6, 0, rank=target_rank, exchange=exchange)
+        ok = len(moves) == 6 and np.array_equal(replay(start, pz.generators, moves), target)
+        out_q.put((rank, ok, len(a.layers)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_archive_walk_back_across_two_gloo_ranks(tmp_path):
+    import socket
+
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_archive_rank, args=(r, 2, port, str(tmp_path), q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+        assert p.exitcode == 0
+    got = sorted(q.get(timeout=10) for _ in range(2))
+    assert got == [(0, True, 6), (1, True, 6)], got
+    m = json.loads((tmp_path / "sample_0" / MANIFEST).read_text())
+    assert m["depth"] == 6 and m["world_size"] == 2
+    assert (tmp_path / "sample_0" / "layer_00005_rank1.npy").exists()
