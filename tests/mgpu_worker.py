@@ -45,6 +45,14 @@ def run_case(name, beam, scramble_len, depths, backend, graph, exchange="peer", 
         weights = puzzles.mlp_weights(pz.state_len * pz.num_values, 1024)
         sc = scorers.MLPValueScorer(weights, pz.state_len, cfg["state_size_bytes"], pz.num_values,
                                     max_rows=sizes["cand_cap"])
+    if backend == "qmlp":
+        # action values on the parent rows (the expansion then writes no child rows in peer mode)
+        cfg["inference_backend"] = "mlp"
+        ext = be.build_extension()
+        sizes = ext.derive_sizes(cfg)
+        weights = puzzles.q_mlp_weights(pz.state_len * pz.num_values, pz.fanout, 1024, 512)
+        sc = scorers.MLPActionValueScorer(weights, pz.state_len, cfg["state_size_bytes"], pz.num_values, pz.fanout,
+                                          max_parents=sizes["k_work"])
     _, cfg, buffers, engine = be.configure_engine(pz, cfg=cfg, scorer=sc)
     start = pz.scramble(3, scramble_len)
     n = pz.state_len
@@ -68,7 +76,7 @@ def run_case(name, beam, scramble_len, depths, backend, graph, exchange="peer", 
         # every row lives on its hash owner
         if rows.shape[0]:
             assert (owners(rows) == rank).all()
-        if backend == "mlp":
+        if backend in ("mlp", "qmlp"):
             # expected set from the device's own scores: gather (child bytes -> key) of all candidates of all ranks
             ncand = fronts[rank].shape[0] * pz.fanout
             dev_scores = buffers["cand_score"][:ncand].cpu().numpy().astype(np.uint32)
@@ -105,6 +113,7 @@ def main():
         run_case("rand54", 4096, 12, 6, "central_hamming", True, exchange)
         run_case("rand54", 2048, 30, 5, "mlp", True, exchange)
         run_case("rand54", 4096, 12, 5, "central_hamming", True, exchange, hash_mode="zobrist128")
+        run_case("rand54", 2048, 30, 5, "qmlp", True, exchange)
     # the engine's own depth loop: all ranks stop at the same depth with the same answer
     pz = puzzles.puzzle54()
     world, rank = dist.get_world_size(), dist.get_rank()

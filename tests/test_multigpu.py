@@ -22,4 +22,4 @@ def test_sharded_search_matches_oracle(world):
            "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), str(ROOT / "tests" / "mgpu_worker.py")]
     out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
-    assert out.stdout.count("CASE_OK") == 8 and "SEARCH_OK" in out.stdout, out.stdout[-2000:]
+    assert out.stdout.count("CASE_OK") == 10 and "SEARCH_OK" in out.stdout, out.stdout[-2000:]
