@@ -69,6 +69,24 @@ def test_host_hash_matches_oracle():
             assert lib.mgbs_fingerprint64_host(row.ctypes.data_as(C.c_void_p), n) == int(want_f[i])
 
 
+def test_host_hash_matches_reference_device_functions():
+    """The library's host helpers against vectors produced by the reference's own hash_state_120 /
+    fingerprint_state_120 (beam_kernels.cu:38-59) compiled as host C++ (tests/golden/make_scalar_golden.py)."""
+    import json
+    lib = _lib.load()
+    data = json.loads((ROOT / "tests" / "golden" / "scalar_reference.json").read_text())
+    for c in data["state_cases"]:
+        if c["kind"] == "arange":
+            s = np.arange(120, dtype=np.uint8)
+        elif c["kind"] == "zeros":
+            s = np.zeros(120, dtype=np.uint8)
+        else:
+            s = np.random.default_rng(c["seed"]).integers(0, int(c["kind"][7:]), size=120, dtype=np.uint8)
+        s = np.ascontiguousarray(s)
+        assert lib.mgbs_hash64_host(s.ctypes.data_as(C.c_void_p), 120) == c["hash64"]
+        assert lib.mgbs_fingerprint64_host(s.ctypes.data_as(C.c_void_p), 120) == c["fingerprint64"]
+
+
 def test_engine_create_rejects_bad_configs_without_a_gpu():
     lib = _lib.load()
     c = _lib.MgbsConfig()

@@ -85,6 +85,51 @@ def test_expand_kernel_bit_exact(n, fanout):
     assert lib.mgbs_fingerprint64_host(row.ctypes.data_as(C.c_void_p), n) == int(bo.fingerprint64(row)[0])
 
 
+def test_expand_kernel_matches_reference_device_functions():
+    """The expansion kernel at the reference's native shape (120 bytes, 24 moves) against vectors produced by
+    the reference's own apply_move_table / hash_state_120 / fingerprint_state_120 / hamming_to_central
+    (beam_kernels.cu:38-94) compiled as host C++ - no oracle in between."""
+    import importlib.util
+    import json
+    from pathlib import Path
+    golden = Path(__file__).resolve().parent / "golden"
+    spec = importlib.util.spec_from_file_location("make_scalar_golden", golden / "make_scalar_golden.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    data = json.loads((golden / "scalar_reference.json").read_text())["legacy_expand"]
+    table, central = mod.legacy_tables(data["table_seed"])
+    parents = np.stack([central if c["parent_seed"] is None else
+                        np.random.default_rng(c["parent_seed"]).integers(0, 120, size=120, dtype=np.uint8)
+                        for c in data["cases"]])
+    lib = _lib.load()
+    n, stride, fanout, P = 120, 128, 24, parents.shape[0]
+    dev = torch.device("cuda", 0)
+    f_pad = np.zeros((P, stride), np.uint8)
+    f_pad[:, :n] = parents
+    t_f, t_g, t_s = (torch.from_numpy(x).to(dev) for x in (f_pad, table, central))
+    Cn = P * fanout
+    t_children = torch.zeros((Cn, stride), dtype=torch.uint8, device=dev)
+    t_h = torch.zeros(Cn, dtype=torch.int64, device=dev)
+    t_fp = torch.zeros(Cn, dtype=torch.int64, device=dev)
+    t_k = torch.zeros(Cn, dtype=torch.int32, device=dev)
+    t_p = torch.zeros(Cn, dtype=torch.int32, device=dev)
+    rc = lib.mgbs_launch_expand(t_f.data_ptr(), None, P, t_g.data_ptr(), t_s.data_ptr(), n, stride, fanout, 0,
+                                _lib.SCORE_HAMMING, 0, t_children.data_ptr(), t_h.data_ptr(), t_fp.data_ptr(),
+                                t_k.data_ptr(), t_p.data_ptr(), None,
+                                C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    h = t_h.cpu().numpy().view(np.uint64).reshape(P, fanout)
+    fp = t_fp.cpu().numpy().view(np.uint64).reshape(P, fanout)
+    ham = t_k.cpu().numpy().reshape(P, fanout)
+    rows = t_children.cpu().numpy().reshape(P, fanout, stride)
+    for i, c in enumerate(data["cases"]):
+        assert [int(x) for x in h[i]] == c["child_hash64"]
+        assert [int(x) for x in fp[i]] == c["child_fingerprint64"]
+        assert ham[i].tolist() == c["child_hamming"]
+        assert rows[i, 0, :n].tolist() == c["child_bytes_move0"]
+
+
 def check_step(engine, pz, frontier, beam, mode="exact_k", graph=False):
     engine.load_frontier(frontier, depth=0)
     engine.enable_cuda_graphs(graph)

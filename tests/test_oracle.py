@@ -31,6 +31,105 @@ def test_hash64_matches_reference_cpu_helper():
         assert bo.owner_rank(h, w).tolist() == [c[f"owner_w{w}"] for c in data["cases"]]
 
 
+def _scalar_golden():
+    """Vectors produced by the reference's own scalar functions compiled as host C++ (oracle/Makefile,
+    tests/golden/make_scalar_golden.py) and the seeded input generators of that script."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_scalar_golden", GOLDEN / "make_scalar_golden.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return json.loads((GOLDEN / "scalar_reference.json").read_text()), mod
+
+
+def _scalar_state(case):
+    if case["kind"] == "arange":
+        return np.arange(120, dtype=np.uint8)
+    if case["kind"] == "zeros":
+        return np.zeros(120, dtype=np.uint8)
+    hi = int(case["kind"][len("uniform"):])
+    return np.random.default_rng(case["seed"]).integers(0, hi, size=120, dtype=np.uint8)
+
+
+def test_fingerprint_hash_and_best_key_match_reference_device_functions():
+    """hash_state_120, fingerprint_state_120, tie16, make_best_key, mix64 (beam_kernels.cu:29-67)."""
+    data, _ = _scalar_golden()
+    assert data["state_size"] == 120 and data["fanout"] == 24
+    for c in data["mix64"]:
+        assert int(bo.mix64(np.array([c["x"]], dtype=np.uint64))[0]) == c["y"]
+    cases = data["state_cases"]
+    states = np.stack([_scalar_state(c) for c in cases])
+    assert [int(x) for x in bo.hash64(states)] == [c["hash64"] for c in cases]
+    fp = bo.fingerprint64(states)
+    assert [int(x) for x in fp] == [c["fingerprint64"] for c in cases]
+    assert [int(x) for x in bo.tie16(fp)] == [c["tie16"] for c in cases]
+    score_q = np.array([c["score_q"] for c in cases], dtype=np.uint32)
+    assert [int(x) for x in bo.make_best_key(score_q, fp)] == [c["best_key"] for c in cases]
+
+
+def test_expansion_and_hamming_match_reference_device_functions():
+    """apply_move_table, hamming_to_central, is_central_state (beam_kernels.cu:69-103) on a seeded table."""
+    data, mod = _scalar_golden()
+    table, central = mod.legacy_tables(data["legacy_expand"]["table_seed"])
+    for c in data["legacy_expand"]["cases"]:
+        parent = central.copy() if c["parent_seed"] is None else \
+            np.random.default_rng(c["parent_seed"]).integers(0, 120, size=120, dtype=np.uint8)
+        children = bo.expand(parent[None, :], table)
+        assert children[0].tolist() == c["child_bytes_move0"]
+        assert [int(x) for x in bo.hash64(children)] == c["child_hash64"]
+        assert [int(x) for x in bo.fingerprint64(children)] == c["child_fingerprint64"]
+        assert bo.hamming(children, central).tolist() == c["child_hamming"]
+        assert int(bo.hamming(parent[None, :], central)[0]) == c["parent_hamming"]
+        assert int(np.array_equal(parent, central)) == c["parent_is_central"]
+        # the legacy u16 score of kernel_dummy_inference follows from the Hamming distance (beam_kernels.cu:133-143)
+        assert bo.legacy_hamming_q(np.array(c["child_hamming"])).tolist() == \
+            [65535 if h == 0 else max(65535 - 512 * h, 1) for h in c["child_hamming"]]
+
+
+def test_v6_expansion_zobrist_and_owner_match_reference_device_functions():
+    """apply_move_state128, is_goal_state128, hash_state128_zobrist (beam_kernels_stream2.cu:8-38),
+    owner_from_hash128 (beam_kernels_stream3.cu:29-35)."""
+    data, mod = _scalar_golden()
+    gens, central, zob = mod.v6_tables(data["v6_expand"]["seed"])
+    for c in data["v6_expand"]["cases"]:
+        parent = np.zeros(128, dtype=np.uint8)
+        parent[:120] = central[:120] if c["parent_seed"] is None else \
+            np.random.default_rng(c["parent_seed"]).integers(0, 120, size=120, dtype=np.uint8)
+        children = bo.expand(parent[None, :], gens)
+        assert children[0].tolist() == c["child_bytes_move0"]
+        lo, hi = bo.hash128_zobrist(children, zob)
+        assert [[int(a), int(b)] for a, b in zip(lo, hi)] == c["child_lo_hi"]
+        for k, w in enumerate((1, 2, 3, 8)):
+            assert bo.owner_from_hash128(hi, lo, w).tolist() == [o[k] for o in c["owner_w1_2_3_8"]]
+        assert [(int(np.array_equal(ch, central))) for ch in children] == c["child_is_goal"]
+        assert int(np.array_equal(parent, central)) == c["parent_is_goal"]
+
+
+def test_duplicate_winner_order_matches_reference_candidate_better():
+    """candidate_better (beam_kernels_stream4.cu:25-33): (score, parent, route) lexicographic; the packed
+    back-pointer of this build orders (parent, rank, move) the same way for equal owners."""
+    data, _ = _scalar_golden()
+    for c in data["pack_route"]:
+        r, o, m = c["args"]
+        assert (r << 16) | (o << 8) | m == c["packed"]
+    for c in data["candidate_better"]:
+        a, b = tuple(c["a"]), tuple(c["b"])
+        assert int(a < b) == c["a_better"]
+        # dedup_by_key keeps the minimum sort value: the winner of a two-element group is the better candidate
+        won = bo.dedup_by_key(["k", "k"], [a, b])["k"]
+        assert won == (a if c["a_better"] or a == b else b)
+
+
+def test_score_key_and_monotone_threshold_match_reference_host_helpers():
+    """q_to_score_key_host, threshold_update (beam_types.hpp:103-106, 125-134)."""
+    data, _ = _scalar_golden()
+    for c in data["q_to_score_key"]:
+        assert int(bo.q_to_score_key(np.array([c["q"]], dtype=np.float32))[0]) == c["key"]
+    cur, init = bo.UINT32_MAX, False
+    for c in data["threshold_update"]:
+        cur, init = bo.v6_threshold_update(cur, init, c["total"], c["beam"], c["new"])
+        assert cur == c["threshold"] and int(init) == c["initialised"]
+
+
 def test_hash64_scalar_definition():
     # independent scalar restatement with Python ints
     rng = np.random.default_rng(5)
