@@ -55,13 +55,15 @@ extern "C" {
 #define MGBS_ST_FRONTIER_OVERFLOW 8u /* survivors beyond the frontier capacity were dropped */
 #define MGBS_ST_BUCKET_OVERFLOW 16u /* exchange bucket full, candidate dropped */
 #define MGBS_ST_ROUNDS_EXHAUSTED 32u /* fewer than beam unique entries after the last band round */
-#define MGBS_ST_PEER_TIMEOUT 64u     /* a bounded wait for another rank's data gave up */
+#define MGBS_ST_PEER_TIMEOUT 64u     /* a bounded wait for another rank's data gave up (here or, by its notice, on a peer) */
+#define MGBS_ST_GRID_TIMEOUT 128u    /* a bounded wait between the blocks of the selection kernel gave up */
 
 #define MGBS_ERR_ARG (-1)
 #define MGBS_ERR_UNSUPPORTED (-2)
 #define MGBS_ERR_NCCL (-3)
 #define MGBS_ERR_STATE (-4)
 #define MGBS_ERR_TOO_LARGE (-5)
+#define MGBS_ERR_PEER_TIMEOUT (-6) /* the depth loop stopped because a cross-rank wait gave up (status has MGBS_ST_PEER_TIMEOUT) */
 
 /* Progress of one radix descent (band threshold or final cut). */
 typedef struct MgbsRadix {
@@ -97,12 +99,20 @@ typedef struct MgbsCtrl {
   uint32_t rounds_used;
   uint32_t bands_done;       /* 1 when band rounds are complete */
   uint32_t epoch;            /* depth steps taken since the engine was created; tags cross-rank flags */
-  uint32_t pad0;
+  int32_t active_rows;       /* frontier rows this depth expands: min(frontier_count, logical active limit) */
   uint64_t band_lo[MGBS_MAX_ROUNDS + 1];
   uint64_t threshold_key;    /* last final cut: every key below survives */
   uint64_t rho_num;          /* candidates inserted / unique entries of the last depth: the duplicate ratio that */
   uint64_t rho_den;          /* sizes the first band of the next depth */
   uint64_t total_candidates; /* running sum over depths (this rank) */
+  uint32_t halt;             /* 1 while a depth runs that opened on a finished search (a failed wait; inside the depth
+                              * loop also: found, or nothing left to expand): every kernel of that depth returns at
+                              * once and the block stays as it was, so a host that enqueues one depth ahead of what it
+                              * has read loses nothing.  exhausted: the last depth produced no state at all */
+  uint32_t exhausted;
+  uint32_t grid_bar;         /* arrival counter of the selection kernel's block barrier (reset when a depth opens) */
+  uint32_t pad0;
+  uint64_t launch_seq;       /* depth launches finished since the last reset, halted ones included */
   MgbsRadix band[MGBS_MAX_ROUNDS][MGBS_MAX_LEVELS + 1];
   MgbsRadix fin[MGBS_MAX_LEVELS + 1];
 } MgbsCtrl;
@@ -173,7 +183,29 @@ typedef struct MgbsConfig {
   int32_t hash_mode;
   int32_t zobrist_values;
   const uint64_t* zobrist;
+  /* Optional pinned host memory, sizeof(MgbsMirror) bytes, device-accessible at the same address (cudaHostAlloc /
+   * torch pin_memory): the last kernel of every depth writes a summary of the control block there, so that the
+   * depth loop (mgbs_engine_search) reads host memory instead of copying the control block and synchronising the
+   * stream after every depth (the reference's status() synchronises every stream and makes three device-to-host
+   * copies per depth, beam_engine.cpp:1173-1198). */
+  struct MgbsMirror* host_mirror;
+  /* Bounded waits of the cross-rank kernels give up after this many polls (0 = default 2^22, about a second). */
+  int64_t peer_poll_limit;
+  /* 0 (default) = selection as one persistent kernel (band rounds, final cut, emit and finish with block barriers
+   * in between; world 1 and MGBS_EXCHANGE_PEER); 1 = one launch per stage (always used with MGBS_EXCHANGE_NCCL,
+   * whose collectives sit between the stages). */
+  int32_t staged_select;
+  int32_t pad2;
 } MgbsConfig;
+
+/* Summary of the control block written to MgbsConfig.host_mirror by the last kernel of a depth; seq is written
+ * last (after a system-wide fence) and equals MgbsCtrl.launch_seq: one more per enqueued depth, halted or not. */
+typedef struct MgbsMirror {
+  int32_t depth, found, found_depth, frontier_next; /* frontier_next: rows of the frontier the depth produced (this rank) */
+  uint32_t found_payload, status, unique_total, epoch;
+  uint64_t total_candidates;
+  volatile uint64_t seq;
+} MgbsMirror;
 
 #define MGBS_HASH_FNV 0
 #define MGBS_HASH_ZOBRIST128 1
@@ -212,6 +244,10 @@ int mgbs_sym_frontier_offsets(const MgbsConfig* cfg, int64_t* out2);
  * rank's region), offsets = byte offset of the region inside that allocation.  The reference has no counterpart
  * (it exchanges through NCCL only, beam_engine.cpp:1368-1400). */
 int mgbs_engine_set_peers(MgbsEngine* e, const uint8_t* handles, const int64_t* offsets);
+/* The same for ranks that live in ONE process (threads, or one thread driving several GPUs with peer access
+ * enabled): bases[r] = device pointer of rank r's symmetric region as this GPU addresses it.  No reference
+ * counterpart. */
+int mgbs_engine_set_peer_pointers(MgbsEngine* e, uint8_t* const* bases);
 /* CUDA IPC handle (64 bytes) of the device allocation containing ptr and ptr's offset inside it: what each rank
  * publishes to the others for mgbs_engine_set_peers.  No reference counterpart. */
 int mgbs_ipc_export(const void* ptr, uint8_t* handle64, int64_t* offset);
@@ -233,6 +269,13 @@ int mgbs_engine_set_parent_scorer(MgbsEngine* e, mgbs_parent_scorer_fn fn, void*
 /* Switch the scorer used by the expansion (MGBS_SCORE_*); drops captured graphs.  Covers begin_uniform_score /
  * set_uniform_score / end_uniform_score (beam_engine.cpp:893-915): the uniform mode is the reference's prepass fill. */
 int mgbs_engine_set_score_mode(MgbsEngine* e, int32_t score_mode, int32_t uniform_score);
+
+/* Logical limits of the reference's prepass (set_active_limit / set_next_limit / clear_logical_limits,
+ * beam_engine.cpp:1064-1090): active_limit > 0 makes a depth expand at most that many rows of the current frontier;
+ * next_limit > 0 caps the next frontier at that many rows and the dedup table at next_limit / load + 1024 slots
+ * (load = frontier_cap / hash_capacity), with the pool target scaled alike.  -1 clears a limit.  Drops captured
+ * graphs, as the reference invalidates its graph. */
+int mgbs_engine_set_logical_limits(MgbsEngine* e, int64_t active_limit, int64_t next_limit);
 
 /* Reset to a one-state frontier on the owning rank (reset_search, beam_engine.cpp:995-1021).  start_is_solved = 1
  * marks the search as found at depth 0 (kernel_check_current_solved, beam_kernels.cu:857-875).  Synchronises. */
@@ -276,7 +319,10 @@ int mgbs_engine_trace_read(MgbsEngine* e, float* ms, int32_t capacity);
 int mgbs_engine_read_ctrl(MgbsEngine* e, MgbsCtrl* out_host, void* stream);
 
 /* Depth loop: step until found, max_depth or an empty frontier (BeamEngine::search, beam_engine.cpp:1147-1171).
- * out_host receives the final control block. */
+ * out_host receives the final control block.  With MgbsConfig.host_mirror the loop enqueues one depth ahead of the
+ * last summary it has read and never synchronises the stream between depths (a depth that opens on a finished
+ * search halts on the device).  Returns MGBS_ERR_PEER_TIMEOUT when a cross-rank wait gave up: the status bit is set
+ * on every rank that took part, each rank's loop returns, and nothing is left waiting. */
 int mgbs_engine_search(MgbsEngine* e, int32_t max_depth, int32_t use_graph, MgbsCtrl* out_host, void* stream);
 
 /* Stage launchers, usable on their own (reference convention: extern "C" launch_<stage>(ptrs, sizes, stream),

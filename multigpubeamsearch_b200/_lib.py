@@ -31,10 +31,11 @@ ST_FRONTIER_OVERFLOW = 8
 ST_BUCKET_OVERFLOW = 16
 ST_ROUNDS_EXHAUSTED = 32
 ST_PEER_TIMEOUT = 64
+ST_GRID_TIMEOUT = 128
 STATUS_NAMES = {
     ST_HASH_OVERFLOW: "hash_overflow", ST_BAND_STALL: "band_stall", ST_TIE_OVERFLOW: "tie_overflow",
     ST_FRONTIER_OVERFLOW: "frontier_overflow", ST_BUCKET_OVERFLOW: "bucket_overflow",
-    ST_ROUNDS_EXHAUSTED: "rounds_exhausted", ST_PEER_TIMEOUT: "peer_timeout",
+    ST_ROUNDS_EXHAUSTED: "rounds_exhausted", ST_PEER_TIMEOUT: "peer_timeout", ST_GRID_TIMEOUT: "grid_timeout",
 }
 
 
@@ -53,9 +54,11 @@ class MgbsCtrl(C.Structure):
         ("table_count", C.c_uint32), ("next_count", C.c_uint32), ("tie_count", C.c_uint32),
         ("cand_count", C.c_uint32), ("unique_total", C.c_uint32), ("inserted_total", C.c_uint32),
         ("hash_overflow", C.c_uint32), ("rounds_used", C.c_uint32), ("bands_done", C.c_uint32),
-        ("epoch", C.c_uint32), ("pad0", C.c_uint32),
+        ("epoch", C.c_uint32), ("active_rows", C.c_int32),
         ("band_lo", C.c_uint64 * (MAX_ROUNDS + 1)), ("threshold_key", C.c_uint64),
         ("rho_num", C.c_uint64), ("rho_den", C.c_uint64), ("total_candidates", C.c_uint64),
+        ("halt", C.c_uint32), ("exhausted", C.c_uint32), ("grid_bar", C.c_uint32), ("pad0", C.c_uint32),
+        ("launch_seq", C.c_uint64),
         ("band", (MgbsRadix * (MAX_LEVELS + 1)) * MAX_ROUNDS), ("fin", MgbsRadix * (MAX_LEVELS + 1)),
     ]
 
@@ -81,6 +84,15 @@ class MgbsConfig(C.Structure):
         ("send_counts", _P), ("recv_counts", _P),
         ("exchange_mode", C.c_int32), ("pad1", C.c_int32), ("sym", _P), ("sym_bytes", C.c_int64), ("tickets", _P),
         ("io_stage", _P), ("hash_mode", C.c_int32), ("zobrist_values", C.c_int32), ("zobrist", _P),
+        ("host_mirror", _P), ("peer_poll_limit", C.c_int64), ("staged_select", C.c_int32), ("pad2", C.c_int32),
+    ]
+
+
+class MgbsMirror(C.Structure):
+    _fields_ = [
+        ("depth", C.c_int32), ("found", C.c_int32), ("found_depth", C.c_int32), ("frontier_next", C.c_int32),
+        ("found_payload", C.c_uint32), ("status", C.c_uint32), ("unique_total", C.c_uint32), ("epoch", C.c_uint32),
+        ("total_candidates", C.c_uint64), ("seq", C.c_uint64),
     ]
 
 
@@ -99,6 +111,8 @@ SIGNATURES = {
     "mgbs_sym_bytes": (C.c_int, [C.POINTER(MgbsConfig), C.POINTER(_I64), C.POINTER(_I64)]),
     "mgbs_sym_frontier_offsets": (C.c_int, [C.POINTER(MgbsConfig), C.POINTER(_I64)]),
     "mgbs_engine_set_peers": (C.c_int, [_P, _P, C.POINTER(_I64)]),
+    "mgbs_engine_set_peer_pointers": (C.c_int, [_P, C.POINTER(_P)]),
+    "mgbs_engine_set_logical_limits": (C.c_int, [_P, _I64, _I64]),
     "mgbs_ipc_export": (C.c_int, [_P, _P, C.POINTER(_I64)]),
     "mgbs_engine_set_scorer": (C.c_int, [_P, _P, _P]),
     "mgbs_engine_set_score_mode": (C.c_int, [_P, _I32, _I32]),
@@ -149,7 +163,8 @@ def check(rc: int, what: str) -> None:
     """C++ errors become RuntimeError, as CUDA_CHECK / NCCL_CHECK do in the reference (beam_engine.cpp:34-46)."""
     if rc == 0:
         return
-    names = {-1: "bad argument", -2: "unsupported shape", -3: "NCCL error", -4: "bad engine state"}
+    names = {-1: "bad argument", -2: "unsupported shape", -3: "NCCL error", -4: "bad engine state",
+             -5: "request too large", -6: "a cross-rank wait gave up (peer timeout)"}
     if rc < 0:
         raise RuntimeError(f"{what}: {names.get(rc, rc)}")
     raise RuntimeError(f"{what}: CUDA error {rc}")

@@ -70,6 +70,16 @@ def make_default_config() -> Dict[str, Any]:
         # world > 1: "peer" = candidates stored straight into the owner's buckets over NVLink peer mappings and
         # histograms reduced in-kernel; "nccl" = grouped send/recv + all-reduce (the reference's scheme)
         "exchange": os.environ.get("MGBS_EXCHANGE", "peer"),
+        # Knobs of the reference's tile pipeline (beam_engine.py:44-58, 68-109).  They are accepted so that a
+        # reference configuration loads unchanged; this engine has no expand tiles, score ring or net ring (one
+        # depth is one fixed-shape launch sequence), so they do not change what runs:
+        "k_expand_tile": int(os.environ.get("K_EXPAND_TILE", "0")),
+        "score_ring_depth": int(os.environ.get("SCORE_RING_DEPTH", "2")),
+        "net_ring_depth": int(os.environ.get("NET_RING_DEPTH", "2")),
+        "inference_parallelism": int(os.environ.get("INFERENCE_PARALLELISM", "1")),
+        "histogram_period_micro": int(os.environ.get("HISTOGRAM_PERIOD_MICRO", "4")),
+        # bounded waits of the cross-rank kernels give up after this many polls (about a second by default)
+        "peer_poll_limit": int(os.environ.get("MGBS_PEER_POLL_LIMIT", str(1 << 22))),
     }
 
 
@@ -231,6 +241,9 @@ class BeamEngine:
         self._uniform: Optional[int] = None
         self._events = None
         self._timing: Dict[str, float] = {}
+        self._limits = [-1, -1]
+        self._debug = (False, False, 1)
+        self._light_solved_scan = False
         c = _lib.MgbsConfig()
         c.state_len = int(cfg["state_len"])
         c.state_stride = int(cfg["state_size_bytes"])
@@ -301,6 +314,16 @@ class BeamEngine:
             c.sym = p("sym")
             c.sym_bytes = int(b["sym"].numel())
             c.tickets = p("tickets")
+        c.peer_poll_limit = int(cfg.get("peer_poll_limit", 0) or 0)
+        pipeline = str(cfg.get("select_pipeline", "persistent"))
+        if pipeline not in ("persistent", "staged"):
+            raise RuntimeError("select_pipeline must be 'persistent' or 'staged'")
+        c.staged_select = int(pipeline == "staged")
+        # pinned host summary of the control block, written by the last kernel of every depth: the depth loop
+        # reads it instead of copying the control block and synchronising after every depth
+        if bool(cfg.get("host_mirror", True)):
+            self._mirror = torch.zeros((C.sizeof(_lib.MgbsMirror),), dtype=torch.uint8).pin_memory()
+            c.host_mirror = self._mirror.data_ptr()
         if c.score_mode == _lib.SCORE_EXTERNAL and not c.children:
             raise RuntimeError("a neural backend needs the next_state_pool buffer (materialised children)")
         self._c = c
@@ -405,13 +428,20 @@ class BeamEngine:
 
     def begin_uniform_score(self, score: int) -> None:
         """Prepass fill: every child gets the same score (beam_engine.cpp:893-915)."""
+        if self._uniform is not None:
+            raise RuntimeError("uniform score phase already active")
         self._uniform = int(score)
         _lib.check(self.lib.mgbs_engine_set_score_mode(self._h, _lib.SCORE_UNIFORM, int(score)), "begin_uniform_score")
 
     def set_uniform_score(self, score: int) -> None:
-        self.begin_uniform_score(score)
+        if self._uniform is None:
+            raise RuntimeError("uniform score phase is not active")
+        self._uniform = int(score)
+        _lib.check(self.lib.mgbs_engine_set_score_mode(self._h, _lib.SCORE_UNIFORM, int(score)), "set_uniform_score")
 
     def end_uniform_score(self) -> None:
+        if self._uniform is None:
+            raise RuntimeError("uniform score phase is not active")
         self._uniform = None
         _lib.check(self.lib.mgbs_engine_set_score_mode(self._h, self._c.score_mode, 0), "end_uniform_score")
 
@@ -440,6 +470,93 @@ class BeamEngine:
             n = self.lib.mgbs_engine_trace_read(self._h, tr, 96)
             out["trace_ms"] = [round(float(tr[i]), 4) for i in range(n)]
         return out
+
+    # -- reference methods around the scorer and the prepass -------------------------------------
+    def warmup_inference(self, repeats: int = 2) -> None:
+        """Run the attached scorer ``repeats`` times on the current frontier's capacity worth of rows
+        (warmup_inference, beam_engine.cpp:917-929); no effect on the search state."""
+        if self._scorer is None:
+            return
+        for _ in range(max(1, int(repeats))):
+            self.benchmark_inference(min(int(self.cfg.get("b_micro", 32768)), self._sizes["k_work"]), 1, 0)
+
+    def benchmark_inference(self, micro_size: int, repeats: int = 50, warmup: int = 10) -> List[float]:
+        """Milliseconds of ``repeats`` scorer passes over ``micro_size`` rows (benchmark_inference,
+        beam_engine.cpp:931-977): the value scorers score that many child rows, the action-value scorer that many
+        parent rows.  Rows are whatever the buffers hold; timing does not depend on their content."""
+        if self._scorer is None:
+            raise RuntimeError("benchmark_inference needs a scorer (set_scorer)")
+        parents = bool(getattr(self._scorer, "scores_parents", False))
+        pool = self.buffers["beam_current"] if parents else self.buffers["next_state_pool"]
+        micro = max(1, min(int(micro_size), int(pool.shape[0]), int(self.cfg.get("b_micro", micro_size) or micro_size)))
+        rows = pool[:micro]
+        out: List[float] = []
+        with torch.cuda.stream(self._stream):
+            self._stream.wait_stream(torch.cuda.current_stream())
+            for i in range(max(0, int(warmup)) + max(1, int(repeats))):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(self._stream)
+                self._scorer.score(rows)
+                e1.record(self._stream)
+                e1.synchronize()
+                if i >= max(0, int(warmup)):
+                    out.append(float(e0.elapsed_time(e1)))
+        return out
+
+    def load_torchscript_ensemble(self, module_paths: List[str]) -> None:
+        """The reference runs TorchScript modules as a scorer backend (beam_engine.cpp:479-554).  This engine's
+        scorers are its own tensor-core kernels over plain weight arrays: export the weights and attach a scorer
+        object with set_scorer (scorers.MLPValueScorer, MLPActionValueScorer, TransformerValueScorer)."""
+        raise RuntimeError("load_torchscript_ensemble: TorchScript modules are not executed by this engine; "
+                           "attach a scorers.* object with set_scorer")
+
+    def load_fullbeamnice_static(self, weights: Dict[str, Any]) -> None:
+        """Attach the reference's static Q-network (load_fullbeamnice_static, beam_engine.cpp:887-891) from its
+        weight dictionary (keys embed_w_t ... out_bias, action_perm; scripts/static_fullbeamnice_inference.py:59-185).
+        See scorers.fullbeamnice_scorer_from_static_weights."""
+        from . import scorers
+        sc = scorers.fullbeamnice_scorer_from_static_weights(weights, self.cfg, self._sizes)
+        self.set_scorer(sc)
+
+    def enable_debug(self, verbose: bool = False, print_counters: bool = False, log_period: int = 0) -> None:
+        """Debug printing knobs (enable_debug, beam_engine.cpp:1092-1102): with print_counters the status
+        dictionary is printed after every ``log_period``-th step."""
+        self._debug = (bool(verbose), bool(print_counters), max(1, int(log_period or 1)))
+
+    def set_prepass_light_solved_scan(self, enable: bool) -> None:
+        """The reference can skip its separate solved-state scan during the prepass
+        (set_prepass_light_solved_scan, beam_engine.cpp:1141-1145).  Here the goal test is part of the expansion
+        kernel and costs nothing extra, so the flag is recorded and changes nothing."""
+        self._light_solved_scan = bool(enable)
+
+    def set_active_limit(self, active_limit: int) -> None:
+        """Process at most ``active_limit`` rows of the current frontier (set_active_limit,
+        beam_engine.cpp:1064-1070); drops the captured graphs."""
+        self._limits[0] = max(1, min(int(active_limit), self._sizes["k_work"]))
+        self._apply_limits()
+
+    def set_next_limit(self, next_limit: int) -> None:
+        """Cap the next frontier at ``next_limit`` rows and the dedup table at next_limit / load + 1024 slots
+        (set_next_limit, beam_engine.cpp:1072-1083); drops the captured graphs."""
+        self._limits[1] = max(1, min(int(next_limit), self._sizes["k_work"]))
+        self._apply_limits()
+
+    def clear_logical_limits(self) -> None:
+        """beam_engine.cpp:1085-1090."""
+        self._limits = [-1, -1]
+        self._apply_limits()
+
+    def _apply_limits(self) -> None:
+        _lib.check(self.lib.mgbs_engine_set_logical_limits(self._h, int(self._limits[0]), int(self._limits[1])),
+                   "set logical limits")
+
+    def step_prepass_fast(self, score: int = 0) -> None:
+        """One eager depth with a constant score (step_prepass_fast, beam_engine.cpp:1136-1140)."""
+        self.begin_uniform_score(score)
+        try:
+            self.step_current(1)
+        finally:
+            self.end_uniform_score()
 
     # -- search ---------------------------------------------------------------------------------
     def reset_search(self, state: bytes, active_on_this_rank: bool = True) -> None:
@@ -495,12 +612,24 @@ class BeamEngine:
 
     def search(self, max_depth: int, histogram_period_micro: int = 8) -> Dict[str, Any]:
         """Depth loop until found / max_depth / empty frontier (beam_engine.cpp:1147-1171)."""
-        _lib.check(self.lib.mgbs_engine_search(self._h, int(max_depth), int(self._use_graph), C.byref(self._ctrl),
-                                               self._sp()), "search")
+        rows = int(self.buffers["history_payload"].shape[0])
+        rc = self.lib.mgbs_engine_search(self._h, int(max_depth), int(self._use_graph), C.byref(self._ctrl), self._sp())
         self._graph_used = self._graph_used or self._use_graph
+        if rc == -6:
+            # every rank's loop has returned (each wait is bounded and a rank that gives up tells the others): the
+            # ranks no longer agree on their frontiers, so the search cannot go on; status() names the bit
+            raise RuntimeError("search: a cross-rank wait gave up (peer timeout); status bit peer_timeout is set")
+        _lib.check(rc, "search")
         st = self.status()
+        # capacity problems are counted, not raised (the reference counts COUNTER_HASH_OVERFLOW / BUCKET_OVERFLOW and
+        # its driver asserts on them, scripts/solve_testcsv_2gpu.py:414-415): say so next to the answer
+        truncated = [n for n in st["status_names"] if n not in ("peer_timeout", "grid_timeout")]
+        if truncated:
+            import warnings
+            warnings.warn(f"beam search ran with a truncated beam: {', '.join(truncated)}", RuntimeWarning)
         return {"found": bool(st["found"]), "depth": int(st["found_depth"] if st["found"] else st["depth"]),
-                "status": st}
+                "status": st, "beam_truncated": bool(truncated), "status_names": st["status_names"],
+                "history_rows": rows}
 
     def status(self) -> Dict[str, Any]:
         """Keys of the reference's status() (beam_engine.cpp:1173-1198) plus this engine's own counters."""
@@ -565,7 +694,8 @@ class BeamEngine:
         """Back-pointers (parent, rank, move packed) of the current frontier rows; depth must be >= 1."""
         c = self._read_ctrl()
         k = int(c.frontier_count[c.depth & 1])
-        return self.buffers["history_payload"][c.depth - 1, :k].cpu().numpy().astype(np.uint32)
+        h = self.buffers["history_payload"]
+        return h[(c.depth - 1) % h.shape[0], :k].cpu().numpy().astype(np.uint32)
 
     def history_layer(self, depth: int, count: int) -> np.ndarray:
         """Packed back-pointers of the first ``count`` rows of the depth ``depth``+1 frontier (valid until the ring of
@@ -584,9 +714,11 @@ class BeamEngine:
         """Back-pointer of row ``local_index`` of the depth ``depth``+1 frontier (beam_engine.cpp:1200-1219)."""
         from .records import unpack_payload
         h = self.buffers["history_payload"]
-        if depth < 0 or depth >= h.shape[0] or local_index < 0 or local_index >= h.shape[1]:
+        # the device keeps the last h.shape[0] layers as a ring (row = depth mod rows): older layers were overwritten
+        newest = int(self._ctrl.depth) - 1
+        if depth < 0 or depth > newest or depth <= newest - h.shape[0] or local_index < 0 or local_index >= h.shape[1]:
             return {"valid": 0, "parent_idx": -1, "parent_rank": -1, "action": -1}
-        payload = int(h[depth, local_index].item()) & 0xFFFFFFFF
+        payload = int(h[depth % h.shape[0], local_index].item()) & 0xFFFFFFFF
         p, r, m = unpack_payload(payload)
         return {"valid": 1, "parent_idx": int(p), "parent_rank": int(r), "action": int(m)}
 
@@ -604,8 +736,11 @@ class BeamEngine:
         moves = [int(m)]
         idx = int(p)
         hist = self.buffers["history_payload"]
+        if c.found_depth - 1 > hist.shape[0]:
+            raise RuntimeError(f"the device keeps {hist.shape[0]} history layers but the path has {c.found_depth - 1}: "
+                               "walk back through CPUHistoryArchive.path_to, or size history_rows / max_depth to the search")
         for d in range(c.found_depth - 2, -1, -1):
-            pp, _, mm = unpack_payload(int(hist[d, idx].item()) & 0xFFFFFFFF)
+            pp, _, mm = unpack_payload(int(hist[d % hist.shape[0], idx].item()) & 0xFFFFFFFF)
             moves.append(int(mm))
             idx = int(pp)
         return moves[::-1]
@@ -638,6 +773,15 @@ def configure_engine(puzzle: Puzzle, cfg: Optional[Dict[str, Any]] = None, score
         engine.map_peers()
     engine.enable_cuda_graphs(bool(cfg.get("use_cuda_graphs", True)))
     return ext, cfg, buffers, engine
+
+
+def make_shallow_scramble(puzzle: Puzzle, actions) -> np.ndarray:
+    """The solved state with ``actions`` (move indices) applied in order (make_shallow_scramble,
+    beam_engine.py:2627-2631)."""
+    state = puzzle.solved.copy()
+    for a in actions:
+        state = state[puzzle.generators[int(a)].astype(np.int64)]
+    return state.astype(np.uint8)
 
 
 def run_one_search(engine: BeamEngine, state: np.ndarray, max_depth: int) -> Dict[str, Any]:

@@ -72,7 +72,10 @@ struct MgbsEngine {
   void* scorer_user = nullptr;
   mgbs_parent_scorer_fn parent_scorer = nullptr;
   void* parent_scorer_user = nullptr;
-  cudaGraphExec_t graph[2] = {nullptr, nullptr};
+  cudaGraphExec_t graph[2][2] = {{nullptr, nullptr}, {nullptr, nullptr}};  // [parity][inside the depth loop]
+  int64_t active_limit = -1, next_limit = -1;
+  MgbsMirror* mirror_dev = nullptr;  // device address of cfg.host_mirror
+  bool coop_ok = true;               // cooperative launch of the selection kernel works (also inside capture)
   MgbsCtrl host_ctrl;
   mgbs::SymLayout sym{};
   uint8_t* peer_base[MGBS_MAX_WORLD] = {nullptr};
@@ -83,6 +86,12 @@ struct MgbsEngine {
   cudaEvent_t tev[96] = {nullptr};  // per-launch trace (profile mode)
   int trace_n = 0;
 };
+
+static void drop_graphs(MgbsEngine* e) {
+  for (int p = 0; p < 2; ++p)
+    for (int h = 0; h < 2; ++h)
+      if (e->graph[p][h]) { cudaGraphExecDestroy(e->graph[p][h]); e->graph[p][h] = nullptr; }
+}
 
 #define MGBS_TRY(expr)            \
   do {                            \
@@ -182,15 +191,43 @@ int mgbs_engine_create(const MgbsConfig* cfg, MgbsEngine** out) {
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) e->sms = sms;
   }
+  if (c.host_mirror) {
+    // pinned host memory: the kernels write through the device alias of the same allocation
+    void* dptr = nullptr;
+    if (cudaHostGetDevicePointer(&dptr, c.host_mirror, 0) != cudaSuccess || !dptr) { cudaGetLastError(); delete e; return MGBS_ERR_ARG; }
+    e->mirror_dev = static_cast<MgbsMirror*>(dptr);
+    memset(c.host_mirror, 0, sizeof(MgbsMirror));
+  }
   memset(&e->host_ctrl, 0, sizeof(MgbsCtrl));
   *out = e;
   return 0;
 }
 
+int mgbs_engine_set_logical_limits(MgbsEngine* e, int64_t active_limit, int64_t next_limit) {
+  if (!e) return MGBS_ERR_ARG;
+  if (active_limit == 0 || next_limit == 0) return MGBS_ERR_ARG;
+  e->active_limit = active_limit < 0 ? -1 : (active_limit > e->cfg.frontier_cap ? e->cfg.frontier_cap : active_limit);
+  e->next_limit = next_limit < 0 ? -1 : (next_limit > e->cfg.frontier_cap ? e->cfg.frontier_cap : next_limit);
+  drop_graphs(e);
+  return 0;
+}
+
+int mgbs_engine_set_peer_pointers(MgbsEngine* e, uint8_t* const* bases) {
+  if (!e || !bases) return MGBS_ERR_ARG;
+  const MgbsConfig& c = e->cfg;
+  if (c.world_size == 1 || c.exchange_mode != MGBS_EXCHANGE_PEER) return 0;
+  for (int r = 0; r < c.world_size; ++r) {
+    if (!bases[r]) return MGBS_ERR_ARG;
+    e->peer_base[r] = r == c.rank ? c.sym : bases[r];
+  }
+  e->peers_ready = true;
+  drop_graphs(e);
+  return 0;
+}
+
 int mgbs_engine_destroy(MgbsEngine* e) {
   if (!e) return 0;
-  for (int p = 0; p < 2; ++p)
-    if (e->graph[p]) cudaGraphExecDestroy(e->graph[p]);
+  drop_graphs(e);
   if (e->comm && g_nccl.ok) g_nccl.CommDestroy(e->comm);
   for (int i = 0; i < 6; ++i)
     if (e->ev[i]) cudaEventDestroy(e->ev[i]);
@@ -291,8 +328,7 @@ int mgbs_engine_set_parent_scorer(MgbsEngine* e, mgbs_parent_scorer_fn fn, void*
   if (!e) return MGBS_ERR_ARG;
   e->parent_scorer = fn;
   e->parent_scorer_user = user;
-  for (int p = 0; p < 2; ++p)
-    if (e->graph[p]) { cudaGraphExecDestroy(e->graph[p]); e->graph[p] = nullptr; }
+  drop_graphs(e);
   return 0;
 }
 
@@ -300,8 +336,7 @@ int mgbs_engine_set_scorer(MgbsEngine* e, mgbs_scorer_fn fn, void* user) {
   if (!e) return MGBS_ERR_ARG;
   e->scorer = fn;
   e->scorer_user = user;
-  for (int p = 0; p < 2; ++p)
-    if (e->graph[p]) { cudaGraphExecDestroy(e->graph[p]); e->graph[p] = nullptr; }
+  drop_graphs(e);
   return 0;
 }
 
@@ -314,8 +349,7 @@ int mgbs_engine_profile(MgbsEngine* e, int32_t on) {
     for (int i = 0; i < 96; ++i)
       if (!e->tev[i]) MGBS_TRY(cudaEventCreate(&e->tev[i]));
   e->profile = on != 0;
-  for (int p = 0; p < 2; ++p)
-    if (e->graph[p]) { cudaGraphExecDestroy(e->graph[p]); e->graph[p] = nullptr; }
+  drop_graphs(e);
   return 0;
 }
 
@@ -341,8 +375,7 @@ int mgbs_engine_set_score_mode(MgbsEngine* e, int32_t score_mode, int32_t unifor
   if (!e || score_mode < MGBS_SCORE_EXTERNAL || score_mode > MGBS_SCORE_UNIFORM) return MGBS_ERR_ARG;
   e->cfg.score_mode = score_mode;
   e->cfg.uniform_score = uniform_score;
-  for (int p = 0; p < 2; ++p)
-    if (e->graph[p]) { cudaGraphExecDestroy(e->graph[p]); e->graph[p] = nullptr; }
+  drop_graphs(e);
   return 0;
 }
 
@@ -370,6 +403,7 @@ int mgbs_engine_reset(MgbsEngine* e, const uint8_t* start_state_host, int32_t ac
     MGBS_TRY(cudaMemcpyAsync(c.frontier[0], row, (size_t)c.state_stride, cudaMemcpyHostToDevice, st));
   }
   MGBS_TRY(cudaStreamSynchronize(st));
+  if (c.host_mirror) memset(c.host_mirror, 0, sizeof(MgbsMirror));  // launch_seq restarts at 0 with the control block
   return 0;
 }
 
@@ -401,6 +435,7 @@ int mgbs_engine_load_frontier(MgbsEngine* e, const uint8_t* rows_host, int64_t c
                                (size_t)c.state_len, (size_t)count, cudaMemcpyHostToDevice, st));
   }
   MGBS_TRY(cudaStreamSynchronize(st));
+  if (c.host_mirror) memset(c.host_mirror, 0, sizeof(MgbsMirror));
   return 0;
 }
 
@@ -461,7 +496,7 @@ static int exchange(MgbsEngine* e, cudaStream_t st) {
   return 0;
 }
 
-int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void* stream) {
+static int enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, int auto_halt, void* stream) {
   if (!e || phase < 0 || phase > 2) return MGBS_ERR_ARG;
   using namespace mgbs;
   cudaStream_t st = (cudaStream_t)stream;
@@ -470,6 +505,16 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
   const int W = c.world_size;
   const int Lb = c.band_levels, R = c.band_rounds, Lf = e->final_levels;
   unsigned long long* tie_buf = reinterpret_cast<unsigned long long*>(c.tie_buf);
+  // logical limits (set_next_limit, beam_engine.cpp:1072-1083): fewer frontier rows, a smaller table and pool
+  int64_t frontier_cap_eff = c.frontier_cap, hash_capacity_eff = c.hash_capacity, pool_target_eff = c.pool_target;
+  if (e->next_limit > 0 && e->next_limit < c.frontier_cap) {
+    frontier_cap_eff = e->next_limit;
+    const double inv_load = (double)c.hash_capacity / (double)c.frontier_cap;
+    hash_capacity_eff = (int64_t)((double)e->next_limit * inv_load) + 1024;
+    if (hash_capacity_eff > c.hash_capacity) hash_capacity_eff = c.hash_capacity;
+    pool_target_eff = (int64_t)((double)c.pool_target * (double)e->next_limit / (double)c.frontier_cap);
+    if (pool_target_eff < 1) pool_target_eff = 1;
+  }
 
   const bool prof = e->profile && phase == 0;
   if (prof) { cudaEventRecord(e->ev[0], st); e->trace_n = 0; }
@@ -479,12 +524,14 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     const bool peer_mode = W > 1 && c.exchange_mode == MGBS_EXCHANGE_PEER;
     MGBS_TRY(launch_depth_begin(c.ctrl, parity, c.fanout, c.cand_cap, tie_buf + (int64_t)c.rank * kTieSegWords,
                                 W > 1 ? c.send_counts : nullptr,
-                                peer_mode ? reinterpret_cast<uint32_t*>(c.sym + e->sym.counts[parity]) : nullptr, W, st));
-    MGBS_TRY(cudaMemsetAsync(c.table, 0, (size_t)c.hash_capacity * 32, st));
+                                peer_mode ? reinterpret_cast<uint32_t*>(c.sym + e->sym.counts[parity]) : nullptr, W,
+                                e->active_limit, auto_halt,
+                                peer_mode ? reinterpret_cast<const uint32_t*>(c.sym + e->sym.abort_word) : nullptr, st));
+    MGBS_TRY(cudaMemsetAsync(c.table, 0, (size_t)hash_capacity_eff * 32, st));
     MGBS_TRY(cudaMemsetAsync(c.hist, 0, (size_t)(R * Lb + MGBS_MAX_LEVELS) * MGBS_HIST_STRIDE * sizeof(uint32_t), st));
     ExpandArgs x;
     x.frontier = c.frontier[parity];
-    x.count_dev = &c.ctrl->frontier_count[parity];
+    x.count_dev = &c.ctrl->active_rows;
     x.count = 0;
     x.gens = c.gens;
     x.solved = c.solved;
@@ -506,7 +553,7 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     if (phase == 0 && c.score_mode == MGBS_SCORE_EXTERNAL) {
       if (e->parent_scorer) {
         // action values: one forward pass per parent row gives the scores of all its children
-        MGBS_TRY(e->parent_scorer(e->parent_scorer_user, c.frontier[parity], &c.ctrl->frontier_count[parity],
+        MGBS_TRY(e->parent_scorer(e->parent_scorer_user, c.frontier[parity], &c.ctrl->active_rows,
                                   c.cand_score, stream));
       } else {
         if (!e->scorer) return MGBS_ERR_STATE;
@@ -570,6 +617,13 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     a.peer.tickets = c.tickets;
     a.peer.off_hx = L.hx;
     a.peer.off_hflag = L.hflag;
+    a.peer.off_tie = L.tie;
+    a.peer.off_tie_flag = L.tie_flag;
+    a.peer.off_abort = L.abort_word;
+    const uint32_t poll = c.peer_poll_limit > 0 ? (uint32_t)(c.peer_poll_limit > 0x7fffffffll ? 0x7fffffffll : c.peer_poll_limit) : (1u << 22);
+    a.peer.poll_limit = poll;
+    pr.peer.poll_limit = poll;
+    pr.peer.off_abort = L.abort_word;
   } else {
     RouteArgs r;
     memset(&r, 0, sizeof(r));
@@ -596,10 +650,17 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
   a.ctrl = c.ctrl;
   a.table = c.table;
   a.tie_buf = tie_buf;
-  a.hash_capacity = c.hash_capacity;
+  a.hash_capacity = hash_capacity_eff;
   a.beam = c.global_beam_width;
-  a.pool_target = c.pool_target;
+  a.pool_target = pool_target_eff;
   a.frontier_cap = c.frontier_cap;
+  a.next_cap = frontier_cap_eff;
+  a.mirror = e->mirror_dev;
+  a.hist_base = c.hist;
+  a.band_levels = Lb;
+  a.final_levels = Lf;
+  // the block barrier must outlast a cross-rank wait that one block is in
+  a.grid_poll_limit = (peer ? a.peer.poll_limit : 0u) * 2u + (1u << 22);
   a.world = W; a.rank = c.rank;
   a.key_bits = e->key_bits; a.hash_bits = c.hash_bits;
   a.rounds = R;
@@ -613,6 +674,23 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
   a.next_hash = c.frontier_hash[parity ^ 1];
   a.n = c.state_len; a.stride = c.state_stride; a.fanout = c.fanout; a.parity = parity;
 
+  if (!c.staged_select && (W == 1 || peer)) {
+    // band rounds, final cut, emit, ties and finish as phases of one co-resident kernel
+    a.levels = Lf;
+    a.hist_stats = c.hist + (int64_t)(R * Lb) * MGBS_HIST_STRIDE;
+    int rc = launch_select(a, pr, e->sms, e->coop_ok, st);
+    if (rc != 0 && e->coop_ok) {
+      // a runtime that refuses the cooperative launch here (e.g. inside stream capture): the grid is sized to be
+      // co-resident anyway and every block barrier wait is bounded, so a plain launch is used from now on
+      cudaGetLastError();
+      e->coop_ok = false;
+      rc = launch_select(a, pr, e->sms, false, st);
+    }
+    MGBS_TRY(rc);
+    MGBS_TRACE();  // selection
+    if (prof) { cudaEventRecord(e->ev[4], st); cudaEventRecord(e->ev[5], st); }
+    return 0;
+  }
   // band rounds: place a threshold by histogram levels, then insert that band into the table
   for (int r = 0; r < R; ++r) {
     a.round = r;
@@ -645,15 +723,16 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
     a.hist = fin + (int64_t)l * MGBS_HIST_STRIDE;
     a.peer.slot = R * Lb + l;
     a.hist_prev = l > 0 ? fin + (int64_t)(l - 1) * MGBS_HIST_STRIDE : nullptr;
-    MGBS_TRY(launch_final_hist(a, c.hash_capacity, e->sms, st));
+    MGBS_TRY(launch_final_hist(a, hash_capacity_eff, e->sms, st));
     MGBS_TRY(allreduce_hist(e, a.hist, st));
     MGBS_TRACE();  // final histogram (+ reduction)
   }
   a.hist = nullptr;
   a.hist_prev = fin + (int64_t)(Lf - 1) * MGBS_HIST_STRIDE;
-  MGBS_TRY(launch_emit(a, a.cv.states ? items : c.hash_capacity, e->sms, st));
+  MGBS_TRY(launch_emit(a, a.cv.states ? items : hash_capacity_eff, e->sms, st));
   MGBS_TRACE();  // emit
   if (W > 1) {
+    if (!e->comm) return MGBS_ERR_STATE;
     MGBS_NCCL(g_nccl.AllGather(tie_buf + (int64_t)c.rank * kTieSegWords, tie_buf, kTieSegWords, ncclUint64, e->comm, st));
   }
   MGBS_TRY(launch_finish(a, st));
@@ -663,26 +742,42 @@ int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void
   return 0;
 }
 
+int mgbs_engine_enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, void* stream) {
+  return enqueue_depth(e, parity, phase, 0, stream);
+}
+
 // One depth step through a captured CUDA graph (one graph per frontier parity; captured on first use).
 // Replaces BeamEngine::step with capture_cuda_graph (beam_engine.cpp:1104-1116, 1658-1672).
-int mgbs_engine_step_graph(MgbsEngine* e, int32_t parity, void* stream) {
+static int step_graph(MgbsEngine* e, int32_t parity, int auto_halt, void* stream) {
   if (!e) return MGBS_ERR_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   parity &= 1;
+  auto_halt = auto_halt ? 1 : 0;
   if (e->profile) return MGBS_ERR_STATE;  // stage events cannot be timed from inside a graph
-  if (!e->graph[parity]) {
+  for (int attempt = 0; attempt < 2 && !e->graph[parity][auto_halt]; ++attempt) {
+    const bool coop_before = e->coop_ok;
     cudaGraph_t g = nullptr;
     MGBS_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-    int rc = mgbs_engine_enqueue_depth(e, parity, 0, stream);
+    int rc = enqueue_depth(e, parity, 0, auto_halt, stream);
     cudaError_t ce = cudaStreamEndCapture(st, &g);
-    if (rc != 0) { if (g) cudaGraphDestroy(g); return rc; }
-    if (ce != cudaSuccess) return (int)ce;
-    ce = cudaGraphInstantiate(&e->graph[parity], g, 0);
-    cudaGraphDestroy(g);
-    if (ce != cudaSuccess) return (int)ce;
+    if (rc == 0 && ce == cudaSuccess) {
+      ce = cudaGraphInstantiate(&e->graph[parity][auto_halt], g, 0);
+      cudaGraphDestroy(g);
+      if (ce == cudaSuccess) break;
+      e->graph[parity][auto_halt] = nullptr;
+    } else if (g) {
+      cudaGraphDestroy(g);
+    }
+    cudaGetLastError();
+    // a runtime that cannot capture or instantiate the cooperative selection launch: capture once more with a
+    // plain launch (the grid is sized to be co-resident and every block-barrier wait is bounded)
+    if (attempt == 0 && coop_before && !e->cfg.staged_select) { e->coop_ok = false; continue; }
+    return rc != 0 ? rc : (int)ce;
   }
-  return (int)cudaGraphLaunch(e->graph[parity], st);
+  return (int)cudaGraphLaunch(e->graph[parity][auto_halt], st);
 }
+
+int mgbs_engine_step_graph(MgbsEngine* e, int32_t parity, void* stream) { return step_graph(e, parity, 0, stream); }
 
 int mgbs_engine_read_ctrl(MgbsEngine* e, MgbsCtrl* out_host, void* stream) {
   if (!e || !out_host) return MGBS_ERR_ARG;
@@ -693,20 +788,67 @@ int mgbs_engine_read_ctrl(MgbsEngine* e, MgbsCtrl* out_host, void* stream) {
 }
 
 // Depth loop on the host: step until found, max_depth or an empty frontier (BeamEngine::search,
-// beam_engine.cpp:1147-1171).  The control block is read once per depth (one small copy, one stream sync);
-// world > 1 ranks see the same found flag and global frontier size because both ride in all-reduced statistics.
+// beam_engine.cpp:1147-1171).  Every launch of the loop is made with auto_halt: a depth that opens on a finished
+// search returns at once on the device and leaves the control block as it was.  That lets the host run ahead: with a
+// pinned mirror it enqueues depth d + 1 before it has seen the summary of depth d and reads summaries from host
+// memory, so between depths there is neither a copy nor a stream synchronisation; without a mirror it reads the
+// control block once per depth.  world > 1: all ranks see the same found flag and the same global counts (both ride
+// in summed statistics), so they stop together; a cross-rank wait that gave up ends the loop with an error on
+// every rank (the rank that gave up tells the others, and every wait is bounded).
+static const uint32_t kFatalBits = MGBS_ST_PEER_TIMEOUT | MGBS_ST_GRID_TIMEOUT;
+
+static int launch_one(MgbsEngine* e, int parity, int use_graph, void* stream) {
+  if (use_graph) return step_graph(e, parity, 1, stream);
+  return enqueue_depth(e, parity, 0, 1, stream);
+}
+
 int mgbs_engine_search(MgbsEngine* e, int32_t max_depth, int32_t use_graph, MgbsCtrl* out_host, void* stream) {
   if (!e || !out_host) return MGBS_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
   MGBS_TRY(mgbs_engine_read_ctrl(e, out_host, stream));
-  while (!out_host->found && out_host->depth < max_depth) {
-    const int parity = out_host->depth & 1;
-    if (e->cfg.world_size == 1 && out_host->frontier_count[parity] == 0) break;
-    if (use_graph) MGBS_TRY(mgbs_engine_step_graph(e, parity, stream));
-    else MGBS_TRY(mgbs_engine_enqueue_depth(e, parity, 0, stream));
-    MGBS_TRY(mgbs_engine_read_ctrl(e, out_host, stream));
-    if (e->cfg.world_size > 1 && out_host->unique_total == 0) break;
+  const int W = e->cfg.world_size;
+  volatile MgbsMirror* m = e->profile ? nullptr : e->cfg.host_mirror;
+  if (!m) {
+    while (!out_host->found && out_host->depth < max_depth && !out_host->exhausted && !(out_host->status & kFatalBits)) {
+      const int parity = out_host->depth & 1;
+      if (W == 1 && out_host->frontier_count[parity] == 0) break;
+      MGBS_TRY(launch_one(e, parity, use_graph && !e->profile, stream));
+      MGBS_TRY(mgbs_engine_read_ctrl(e, out_host, stream));
+    }
+    return (out_host->status & kFatalBits) ? MGBS_ERR_PEER_TIMEOUT : 0;
   }
-  return 0;
+  // run-ahead loop over the pinned summaries.  Every launch that is not halted advances the depth by one, and once
+  // one launch halts all later ones do (found, nothing left and a failed wait are sticky), so the frontier parity
+  // of launch k is that of depth0 + k without waiting for anything.
+  const uint64_t seq0 = out_host->launch_seq;
+  const int depth0 = out_host->depth;
+  bool stop = out_host->found || out_host->exhausted || (out_host->status & kFatalBits) ||
+              (W == 1 && out_host->frontier_count[depth0 & 1] == 0);
+  uint64_t issued = 0, seen = 0;
+  for (;;) {
+    // keep one depth in flight beyond the last summary read, never past max_depth
+    while (!stop && issued - seen < 2 && depth0 + (int64_t)issued < (int64_t)max_depth) {
+      MGBS_TRY(launch_one(e, (int)((depth0 + issued) & 1), use_graph, stream));
+      ++issued;
+    }
+    if (seen == issued) break;
+    // wait for the next summary: host memory only; now and then ask the runtime whether the stream failed
+    const uint64_t want = seq0 + seen + 1;
+    uint32_t spins = 0;
+    while (m->seq < want) {
+      if ((++spins & 0xfffu) == 0u) {
+        cudaError_t q = cudaStreamQuery(st);
+        if (q != cudaSuccess && q != cudaErrorNotReady) return (int)q;
+        if (q == cudaSuccess && m->seq < want) return MGBS_ERR_STATE;  // the stream is idle and nothing arrived
+      }
+    }
+    ++seen;
+    // the launch after this one may be rewriting the summary right now; every field only ever moves towards
+    // "stop" (found, status and exhaustion are sticky), so a mixed read is still a correct reason to stop
+    if (m->found || (m->status & kFatalBits) || m->unique_total == 0 || (W == 1 && m->frontier_next == 0)) stop = true;
+  }
+  MGBS_TRY(mgbs_engine_read_ctrl(e, out_host, stream));
+  return (out_host->status & kFatalBits) ? MGBS_ERR_PEER_TIMEOUT : 0;
 }
 
 int mgbs_launch_expand(const uint8_t* frontier, const int32_t* count_dev, int64_t count, const uint8_t* gens,

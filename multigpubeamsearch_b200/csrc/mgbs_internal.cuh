@@ -22,6 +22,9 @@ struct SymLayout {
   int64_t route_flag;   // [world] u32: sender r finished routing a band (value = epoch * 16 + round)
   int64_t hx;          // [slots][world][MGBS_HIST_STRIDE] u32 histogram exchange
   int64_t hflag;       // [slots][world] u32
+  int64_t tie;         // [world][kTieSegWords] u64: tie records of every rank at the cut key (persistent selection)
+  int64_t tie_flag;    // [world] u32: rank r's tie records have arrived (value = epoch)
+  int64_t abort_word;  // u32: epoch in which some rank gave up a wait and told everybody (0 = never)
   int64_t total;
   int32_t slots;
 };
@@ -29,9 +32,11 @@ struct SymLayout {
 struct PeerCtx {
   uint8_t* base[MGBS_MAX_WORLD];
   int64_t off_hx, off_hflag;
+  int64_t off_tie, off_tie_flag, off_abort;
   uint32_t* tickets;
   int32_t enabled;
   int32_t slot;  // histogram slot of this launch
+  uint32_t poll_limit;  // polls before a wait for another rank gives up
 };
 
 struct ExpandArgs {
@@ -77,7 +82,8 @@ struct StepArgs {
   int64_t hash_capacity;
   int64_t beam;
   int64_t pool_target;
-  int64_t frontier_cap;
+  int64_t frontier_cap;  // row capacity (and history row pitch) of a frontier buffer
+  int64_t next_cap;      // rows the next frontier may take: frontier_cap, or the logical next limit
   int32_t world, rank;
   int32_t key_bits, hash_bits;
   int32_t level, levels, round, rounds;
@@ -92,6 +98,11 @@ struct StepArgs {
   int32_t n, stride, fanout, parity;
   PeerCtx peer;
   int64_t off_frontier_cur;  // peer mode: offset of the current frontier inside every rank's symmetric region
+  // persistent selection kernel (k_select): all histograms of the depth and the level counts
+  uint32_t* hist_base;       // [(rounds * band_levels + final_levels)][MGBS_HIST_STRIDE]
+  int32_t band_levels, final_levels;
+  uint32_t grid_poll_limit;  // polls before the block barrier gives up
+  MgbsMirror* mirror;        // pinned host summary, or null
 };
 
 struct RouteArgs {
@@ -110,7 +121,10 @@ struct RouteArgs {
 
 int launch_expand(const ExpandArgs& a, int64_t max_parents, int sms, cudaStream_t st);
 int launch_depth_begin(MgbsCtrl* c, int parity, int fanout, int64_t cand_cap, unsigned long long* tie_seg,
-                       uint32_t* send_counts, uint32_t* recv_counts, int world, cudaStream_t st);
+                       uint32_t* send_counts, uint32_t* recv_counts, int world, int64_t active_limit, int auto_halt,
+                       const uint32_t* abort_word, cudaStream_t st);
+int launch_select(const StepArgs& a, const RouteArgs& r, int sms, bool cooperative, cudaStream_t st);
+int select_blocks_per_sm();
 int launch_band_hist(const StepArgs& a, int64_t items, int sms, cudaStream_t st);
 int launch_band_insert(const StepArgs& a, int64_t items, int sms, cudaStream_t st);
 int launch_final_hist(const StepArgs& a, int64_t slots, int sms, cudaStream_t st);

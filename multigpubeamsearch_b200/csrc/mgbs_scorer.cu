@@ -404,14 +404,6 @@ __device__ __forceinline__ uint32_t pack_relu_bf16(float lo, float hi) {
   return d;
 }
 
-#ifdef MGBS_L1_PROBE
-__device__ unsigned long long g_l1_probe[8];
-#define PROBE_T0() const long long _p0 = clock64()
-#define PROBE_ADD(i) atomicAdd(&g_l1_probe[i], (unsigned long long)(clock64() - _p0))
-#else
-#define PROBE_T0()
-#define PROBE_ADD(i)
-#endif
 
 constexpr int L1_THREADS = 448;
 constexpr int L1_A_STAGES = 6;                           // 6 x 16 KB: a whole 128 x 384 one-hot tile when K <= 384
@@ -532,34 +524,25 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
   } else if (warp == 1) {
     // ---- MMA issue ----
     if (lane == 0 && crank == 0) {
-#ifdef MGBS_L1_PROBE
-      const long long _pstart = clock64();
-#endif
       int sb = 0;
       uint32_t pb = 0, acc_it = 0, it_base = 0;
       bool ok = true;
       for (int mt = tile_first; mt < num_mtiles && ok; mt += tile_step, it_base += (uint32_t)blocks_per_tile) {
         for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
           const uint32_t b = acc_it & 1u;
-          { PROBE_T0();
           if (!mbar_wait(tempty_bar(b), ((acc_it >> 1) & 1u) ^ 1u, g.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
-          PROBE_ADD(0); }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + b * BN;
           for (int kb = 0; kb < k_blocks; ++kb) {
             const uint32_t it = it_base + (uint32_t)(resident ? kb : nc * k_blocks + kb);
             const int sa = (int)(it % L1_A_STAGES);
             // resident tile: N-chunks after the first find the phase already complete
-            { PROBE_T0();
             if (PAIR) {
               if (!mbar_wait_cluster(a_full(sa), (it / L1_A_STAGES) & 1u, g.err, ERR_WAIT_FULL)) { ok = false; break; }
             } else {
               if (!mbar_wait(a_full(sa), (it / L1_A_STAGES) & 1u, g.err, ERR_WAIT_FULL)) { ok = false; break; }
             }
-            PROBE_ADD(1); }
-            { PROBE_T0();
             if (!mbar_wait(b_full(sb), pb, g.err, ERR_WAIT_FULL)) { ok = false; break; }
-            PROBE_ADD(2); }
             tc_fence_after();
             const uint64_t adesc = make_desc_sw128(smem_u32(a_ring + sa * A_BYTES));
             const uint64_t bdesc = make_desc_sw128(smem_u32(b_ring + sb * BSB));
@@ -587,9 +570,6 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
       if (PAIR) tc_commit_pair(drain_bar, (uint16_t)1);
       else tc_commit(drain_bar);
       mbar_wait(drain_bar, 0, g.err, ERR_WAIT_DRAIN);
-#ifdef MGBS_L1_PROBE
-      atomicAdd(&g_l1_probe[3], (unsigned long long)(clock64() - _pstart));
-#endif
     }
   } else if (warp < 2 + EW) {
     // ---- epilogue: TMEM -> bias, ReLU, bf16 -> swizzled staging box -> TMA store ----
@@ -603,9 +583,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
       const int row0 = mt * BM;
       for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
         const uint32_t b = acc_it & 1u;
-        { PROBE_T0();
         if (!mbar_wait(tfull_bar(b), (acc_it >> 1) & 1u, g.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
-        if (warp == 2 && lane == 0) PROBE_ADD(4); }
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * BN;
         if constexpr (EW == 4) {
@@ -747,9 +725,6 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
     bool ok = true;
     for (int mt = tile_first; mt - (int)crank < num_mtiles; mt += tile_step, it_base += (uint32_t)blocks_per_tile) {
       // all producer warps have finished reading the previous tile's child rows
-#ifdef MGBS_L1_PROBE
-      const long long _pc0 = clock64();
-#endif
       asm volatile("bar.sync 2, %0;" ::"n"(PROD_W * 32) : "memory");
       if (pt < BM) {
         const int64_t row = (int64_t)mt * BM + pt;
@@ -765,9 +740,6 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         }
       }
       asm volatile("bar.sync 2, %0;" ::"n"(PROD_W * 32) : "memory");
-#ifdef MGBS_L1_PROBE
-      if (warp == 2 + EW && lane == 0) atomicAdd(&g_l1_probe[7], (unsigned long long)(clock64() - _pc0));
-#endif
       if (!ok) continue;
       // first K-block of this tile that belongs to this warp
       const uint32_t first = (uint32_t)((pw - (int)(it_base & 3u)) & 3);
@@ -776,10 +748,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         const int kb = (int)(j % (uint32_t)k_blocks);
         const int slot = (int)(it % L1_A_STAGES);
         uint8_t* a_stage = a_ring + slot * A_BYTES;
-        { PROBE_T0();
         if (!mbar_wait(a_empty(slot), ((it / L1_A_STAGES) & 1u) ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-        if (warp == 2 + EW && lane == 0) PROBE_ADD(5); }
-        PROBE_T0();
         // zero this warp's 64 rows (8 KB, contiguous): consecutive lanes write consecutive 16-byte chunks
         uint4* a4 = reinterpret_cast<uint4*>(a_stage + half * (A_BYTES / WPG));
 #pragma unroll 8
@@ -829,7 +798,6 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
           if (PAIR) mbar_arrive_even_cta_release(a_full(slot));  // the even CTA's MMAs read this CTA's block too
           else mbar_arrive(a_full(slot));
         }
-        if (warp == 2 + EW && lane == 0) PROBE_ADD(6);
       }
     }
   }
@@ -1409,10 +1377,3 @@ extern "C" int mgbs_mlp_score_noalloc(const MgbsMlpNoAllocArgs* a, const uint8_t
   return 0;
 }
 
-#ifdef MGBS_L1_PROBE
-extern "C" int mgbs_l1_probe_read(unsigned long long* out8, int reset) {
-  cudaMemcpyFromSymbol(out8, mgbs::g_l1_probe, 64);
-  if (reset) { unsigned long long z[8] = {0}; cudaMemcpyToSymbol(mgbs::g_l1_probe, z, 64); }
-  return 0;
-}
-#endif

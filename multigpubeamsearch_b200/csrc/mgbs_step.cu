@@ -24,26 +24,47 @@ namespace mgbs {
 // Replaces apply_move_table / hash_state_120 / fingerprint_state_120 / hamming_to_central and the expansion
 // half of kernel_process_score_slot (beam_kernels.cu:29-103, 528-580).
 //
-// One thread per candidate because both hashes are serial byte chains.  A block stages 64 parent rows in
-// shared memory with a row pitch of stride+4 bytes (odd word pitch: the 32 lanes of a warp read 32 different
-// rows at the same byte offset without bank conflicts) and the generator tables next to them; a warp handles
-// one move for 32 parents, so the table lookups are broadcasts.
+// Both hashes are serial byte chains, so the work is one chain pair per candidate and the kernel is bound by
+// instruction issue, not by memory.  A block stages 64 parent rows in shared memory with a row pitch of stride+4
+// bytes (odd word pitch: the 32 lanes of a warp read 32 different rows at the same byte offset without bank
+// conflicts) and the generator tables next to them; a warp handles 32 parents and TWO moves per pass - two
+// independent chain pairs per thread, which the scheduler interleaves - so the table lookups are broadcasts.  The
+// 24-byte records of the tile's 64 x fanout candidates are staged in shared memory and copied out afterwards with
+// consecutive lanes on consecutive candidates (the candidate index is parent-major, so a warp's own candidates
+// lie fanout entries apart).
 // ------------------------------------------------------------------------------------------------
 
+template <int WORDS>
+struct ExpandSmem {
+  static constexpr int kPitchW = WORDS + 1;
+  // byte offsets inside the dynamic shared memory block
+  static __host__ __device__ constexpr int par() { return 0; }
+  static __host__ __device__ constexpr int gen() { return par() + kExpandTile * kPitchW * 4; }
+  static __host__ __device__ constexpr int sol() { return gen() + MGBS_MAX_FANOUT * WORDS * 4; }
+  static __host__ __device__ constexpr int rec() { return (sol() + WORDS * 4 + 15) / 16 * 16; }
+  static __host__ __device__ constexpr int total(int fanout) { return rec() + kExpandTile * fanout * 24; }
+};
 
 template <int WORDS, int ZOB>
 __global__ void __launch_bounds__(kExpandThreads, 3) k_expand(ExpandArgs a) {
-  constexpr int PITCH_W = WORDS + 1;
-  __shared__ uint32_t par_s[kExpandTile * PITCH_W];
-  __shared__ uint32_t gen_s[MGBS_MAX_FANOUT * WORDS];
-  __shared__ uint32_t sol_s[WORDS];
+  using L = ExpandSmem<WORDS>;
+  constexpr int PITCH_W = L::kPitchW;
+  extern __shared__ __align__(16) uint8_t expand_smem[];
+  uint32_t* par_s = reinterpret_cast<uint32_t*>(expand_smem + L::par());
+  uint32_t* gen_s = reinterpret_cast<uint32_t*>(expand_smem + L::gen());
+  uint32_t* sol_s = reinterpret_cast<uint32_t*>(expand_smem + L::sol());
+  const int G = a.fanout;
+  const int tile_cands = kExpandTile * G;
+  uint64_t* rec_h = reinterpret_cast<uint64_t*>(expand_smem + L::rec());
+  uint64_t* rec_f = rec_h + tile_cands;
+  uint32_t* rec_k = reinterpret_cast<uint32_t*>(rec_f + tile_cands);
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const int n = a.n;
-  const int G = a.fanout;
   const int64_t P = a.count_dev ? (int64_t)(*a.count_dev) : a.count;
+  if (P <= 0) return;
 
   // generator tables and solved state, padded to WORDS*4 bytes per row
   for (int i = tid; i < G * WORDS * 4; i += kExpandThreads) {
@@ -52,73 +73,105 @@ __global__ void __launch_bounds__(kExpandThreads, 3) k_expand(ExpandArgs a) {
   }
   for (int i = tid; i < WORDS * 4; i += kExpandThreads) reinterpret_cast<uint8_t*>(sol_s)[i] = i < n ? a.solved[i] : 0;
 
+  const bool want_score = a.score_mode != MGBS_SCORE_EXTERNAL;
   const int64_t ntiles = (P + kExpandTile - 1) / kExpandTile;
   const uint32_t* fw = reinterpret_cast<const uint32_t*>(a.frontier);
+  const ulonglong2* ztab = reinterpret_cast<const ulonglong2*>(a.zobrist);
+  const int pairs = (G + 1) >> 1;
   for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
     const int64_t p0 = tile * kExpandTile;
-    __syncthreads();
+    __syncthreads();  // the previous tile's records have been copied out
     for (int i = tid; i < kExpandTile * WORDS; i += kExpandThreads) {
       int r = i / WORDS, w = i - r * WORDS;
       int64_t p = p0 + r;
       par_s[r * PITCH_W + w] = p < P ? fw[p * WORDS + w] : 0u;
     }
     __syncthreads();
-    for (int u = warp; u < 2 * G; u += kExpandThreads / 32) {
-      const int g = u >> 1;
+    for (int u = warp; u < 2 * pairs; u += kExpandThreads / 32) {
+      const int g0 = (u >> 1) << 1;
+      const bool two = g0 + 1 < G;
+      const int g1 = two ? g0 + 1 : g0;  // an odd fan-out: the last pass repeats its move and drops the copy
       const int pl = ((u & 1) << 5) + lane;
       const int64_t p = p0 + pl;
       if (p >= P) continue;
       const uint8_t* row = reinterpret_cast<const uint8_t*>(par_s + pl * PITCH_W);
-      uint64_t h = ZOB ? 0ull : kFnvOffset, f = ZOB ? 0ull : kGolden;
-      const ulonglong2* ztab = reinterpret_cast<const ulonglong2*>(a.zobrist);
-      int ham = 0;
-      const int64_t c = p * G + g;
-      uint4* child_dst = a.children ? reinterpret_cast<uint4*>(a.children + c * (int64_t)a.stride) : nullptr;
-      // 16 bytes of the child at a time: the four words are stored as soon as they are complete, so that only
-      // four of them are live (the register count decides how many warps hide the shared-memory latency)
+      uint64_t h0 = ZOB ? 0ull : kFnvOffset, f0 = ZOB ? 0ull : kGolden;
+      uint64_t h1 = h0, f1 = f0;
+      int ham0 = 0, ham1 = 0;
+      const int64_t c0 = p * G + g0;
+      uint4* dst0 = a.children ? reinterpret_cast<uint4*>(a.children + c0 * (int64_t)a.stride) : nullptr;
+      uint4* dst1 = (a.children && two) ? reinterpret_cast<uint4*>(a.children + (c0 + 1) * (int64_t)a.stride) : nullptr;
+      // 16 bytes of each child at a time: the words are stored as soon as they are complete, so that only
+      // eight of them are live (the register count decides how many warps hide the shared-memory latency)
 #pragma unroll
       for (int q = 0; q < WORDS / 4; ++q) {
-        uint32_t cw[4];
+        uint32_t cw0[4], cw1[4];
 #pragma unroll
         for (int w4 = 0; w4 < 4; ++w4) {
           const int wi = q * 4 + w4;
-          const uint32_t gi = gen_s[g * WORDS + wi];
+          const uint32_t gi0 = gen_s[g0 * WORDS + wi];
+          const uint32_t gi1 = gen_s[g1 * WORDS + wi];
           const uint32_t sv = sol_s[wi];
-          uint32_t acc = 0;
+          uint32_t acc0 = 0, acc1 = 0;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             if (wi * 4 + j < n) {
-              const uint32_t v = row[(gi >> (8 * j)) & 0xffu];
+              const uint32_t v0 = row[(gi0 >> (8 * j)) & 0xffu];
+              const uint32_t v1 = row[(gi1 >> (8 * j)) & 0xffu];
               if (ZOB) {
-                const ulonglong2 z = __ldg(ztab + (wi * 4 + j) * a.zobrist_values + (int)v);
-                h ^= z.x;
-                f ^= z.y;
+                const ulonglong2 z0 = __ldg(ztab + (wi * 4 + j) * a.zobrist_values + (int)v0);
+                const ulonglong2 z1 = __ldg(ztab + (wi * 4 + j) * a.zobrist_values + (int)v1);
+                h0 ^= z0.x; f0 ^= z0.y;
+                h1 ^= z1.x; f1 ^= z1.y;
               } else {
-                h = (h ^ (uint64_t)v) * kFnvPrime;
-                f ^= (uint64_t)v + kGolden + (f << 6) + (f >> 2);
+                h0 = (h0 ^ (uint64_t)v0) * kFnvPrime;
+                h1 = (h1 ^ (uint64_t)v1) * kFnvPrime;
+                f0 ^= (uint64_t)v0 + kGolden + (f0 << 6) + (f0 >> 2);
+                f1 ^= (uint64_t)v1 + kGolden + (f1 << 6) + (f1 >> 2);
               }
-              ham += (v != ((sv >> (8 * j)) & 0xffu));
-              acc |= v << (8 * j);
+              const uint32_t s8 = (sv >> (8 * j)) & 0xffu;
+              ham0 += (v0 != s8);
+              ham1 += (v1 != s8);
+              acc0 |= v0 << (8 * j);
+              acc1 |= v1 << (8 * j);
             }
           }
-          cw[w4] = acc;
+          cw0[w4] = acc0;
+          cw1[w4] = acc1;
         }
-        if (child_dst) child_dst[q] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+        if (dst0) dst0[q] = make_uint4(cw0[0], cw0[1], cw0[2], cw0[3]);
+        if (dst1) dst1[q] = make_uint4(cw1[0], cw1[1], cw1[2], cw1[3]);
       }
       if (ZOB) {
-        h = finish_zobrist_lo(h);
-        f = finish_zobrist_hi(f);
+        h0 = finish_zobrist_lo(h0); f0 = finish_zobrist_hi(f0);
+        h1 = finish_zobrist_lo(h1); f1 = finish_zobrist_hi(f1);
       } else {
-        h = finish_hash(h);
-        f = finish_fingerprint(f);
+        h0 = finish_hash(h0); f0 = finish_fingerprint(f0);
+        h1 = finish_hash(h1); f1 = finish_fingerprint(f1);
       }
-      const uint32_t payload = pack_payload((uint32_t)p, (uint32_t)a.rank, (uint32_t)g);
-      a.cand_hash[c] = h;
-      a.cand_fp[c] = f;
-      a.cand_payload[c] = payload;
-      if (a.score_mode == MGBS_SCORE_HAMMING) a.cand_score[c] = (uint32_t)ham;
-      else if (a.score_mode == MGBS_SCORE_UNIFORM) a.cand_score[c] = (uint32_t)a.uniform_score;
-      if (ham == 0 && a.ctrl) atomicMin(&a.ctrl->found_payload, payload);
+      const int s0 = pl * G + g0;
+      rec_h[s0] = h0;
+      rec_f[s0] = f0;
+      if (want_score) rec_k[s0] = a.score_mode == MGBS_SCORE_HAMMING ? (uint32_t)ham0 : (uint32_t)a.uniform_score;
+      if (ham0 == 0 && a.ctrl) atomicMin(&a.ctrl->found_payload, pack_payload((uint32_t)p, (uint32_t)a.rank, (uint32_t)g0));
+      if (two) {
+        rec_h[s0 + 1] = h1;
+        rec_f[s0 + 1] = f1;
+        if (want_score) rec_k[s0 + 1] = a.score_mode == MGBS_SCORE_HAMMING ? (uint32_t)ham1 : (uint32_t)a.uniform_score;
+        if (ham1 == 0 && a.ctrl) atomicMin(&a.ctrl->found_payload, pack_payload((uint32_t)p, (uint32_t)a.rank, (uint32_t)g1));
+      }
+    }
+    __syncthreads();
+    // copy-out: consecutive lanes, consecutive candidates; the back-pointer is a function of the index
+    const int64_t rows_here = P - p0 < kExpandTile ? P - p0 : kExpandTile;
+    const int cnt = (int)rows_here * G;
+    const int64_t cbase = p0 * G;
+    for (int i = tid; i < cnt; i += kExpandThreads) {
+      a.cand_hash[cbase + i] = rec_h[i];
+      a.cand_fp[cbase + i] = rec_f[i];
+      const int pl = i / G;
+      a.cand_payload[cbase + i] = pack_payload((uint32_t)(p0 + pl), (uint32_t)a.rank, (uint32_t)(i - pl * G));
+      if (want_score) a.cand_score[cbase + i] = rec_k[i];
     }
   }
 }
@@ -370,31 +423,31 @@ __device__ __forceinline__ void hist_flush(const uint32_t* sh, uint32_t* hist) {
 
 __device__ __forceinline__ void publish_stats(const StepArgs& a) {
   if (blockIdx.x == 0 && threadIdx.x == 0) {
-    a.hist[MGBS_RADIX_BINS + a.rank] = a.ctrl->table_count;
-    a.hist[MGBS_RADIX_BINS + 16 + a.rank] = a.ctrl->inserted_total;
-    a.hist[MGBS_RADIX_BINS + 32] = (a.ctrl->found_payload != 0xffffffffu) ? 1u : 0u;
+    // read past the L1 cache: inside the persistent selection kernel other blocks' atomics updated these words
+    a.hist[MGBS_RADIX_BINS + a.rank] = __ldcg(&a.ctrl->table_count);
+    a.hist[MGBS_RADIX_BINS + 16 + a.rank] = __ldcg(&a.ctrl->inserted_total);
+    a.hist[MGBS_RADIX_BINS + 32] = (__ldcg(&a.ctrl->found_payload) != 0xffffffffu) ? 1u : 0u;
   }
 }
 
-// One-shot all-reduce of a finished histogram over peer-mapped memory.  Called by every thread of every block
-// after its contribution was added to the local histogram; the block that arrives last pushes the local
-// histogram into slot [rank] of every rank's exchange area, raises its flag there (value = epoch), waits - with a
-// limit - for the flags of all ranks in its own area, and replaces the local histogram by the sum.  Consumers then
-// read the local histogram exactly as in the NCCL mode.
-__device__ void peer_allreduce_hist(const StepArgs& a) {
-  __shared__ int s_last;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned t = atomicAdd(&a.peer.tickets[a.peer.slot], 1u);
-    s_last = ((t + 1u) % gridDim.x) == 0u;
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
+// A wait for another rank ran out: record it here and tell every rank (their abort words take this depth's epoch),
+// so that ranks which never time out themselves - because this rank's flags did arrive - learn that the sums they
+// used were partial.
+__device__ __forceinline__ void peer_give_up(const StepArgs& a) {
+  atomicOr(&a.ctrl->status, MGBS_ST_PEER_TIMEOUT);
+  const uint32_t epoch = a.ctrl->epoch;
+  for (int r = 0; r < a.world; ++r)
+    *reinterpret_cast<volatile uint32_t*>(a.peer.base[r] + a.peer.off_abort) = epoch;
+  __threadfence_system();
+}
+
+// Sum of one histogram over all ranks through peer-mapped memory, executed by every thread of ONE block: push the
+// local histogram into slot [rank] of every rank's exchange area, raise this rank's flag there (value = epoch),
+// wait - with a limit - for the flags of all ranks in the own area, and replace the local histogram by the sum.
+__device__ void peer_allreduce_block(const StepArgs& a, uint32_t* hist, int slot) {
   const uint32_t epoch = a.ctrl->epoch;
   const int W = a.world;
-  const int64_t slot_words = (int64_t)a.peer.slot * W * MGBS_HIST_STRIDE;
+  const int64_t slot_words = (int64_t)slot * W * MGBS_HIST_STRIDE;
   // every thread keeps its words of the local histogram in registers (independent loads, issued together) and
   // stores them to all peers: stores do not stall, so the push costs one load latency instead of one per word
   constexpr int PER = (MGBS_HIST_STRIDE + kStreamThreads - 1) / kStreamThreads;
@@ -402,7 +455,7 @@ __device__ void peer_allreduce_hist(const StepArgs& a) {
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
     const int i = threadIdx.x + j * kStreamThreads;
-    mine_v[j] = i < MGBS_HIST_STRIDE ? __ldcg(a.hist + i) : 0u;
+    mine_v[j] = i < MGBS_HIST_STRIDE ? __ldcg(hist + i) : 0u;
   }
   for (int r = 0; r < W; ++r) {
     uint32_t* dst = reinterpret_cast<uint32_t*>(a.peer.base[r] + a.peer.off_hx) + slot_words + (int64_t)a.rank * MGBS_HIST_STRIDE;
@@ -416,17 +469,15 @@ __device__ void peer_allreduce_hist(const StepArgs& a) {
   __syncthreads();
   if ((int)threadIdx.x < W) {
     const int r = threadIdx.x;
-    volatile uint32_t* f = reinterpret_cast<volatile uint32_t*>(a.peer.base[r] + a.peer.off_hflag) +
-                           (int64_t)a.peer.slot * W + a.rank;
+    volatile uint32_t* f = reinterpret_cast<volatile uint32_t*>(a.peer.base[r] + a.peer.off_hflag) + (int64_t)slot * W + a.rank;
     *f = epoch;
-    volatile uint32_t* mine = reinterpret_cast<volatile uint32_t*>(a.peer.base[a.rank] + a.peer.off_hflag) +
-                              (int64_t)a.peer.slot * W + r;
+    volatile uint32_t* mine = reinterpret_cast<volatile uint32_t*>(a.peer.base[a.rank] + a.peer.off_hflag) + (int64_t)slot * W + r;
     bool ok = false;
-    for (uint32_t it = 0; it < (1u << 22); ++it) {
+    for (uint32_t it = 0; it < a.peer.poll_limit; ++it) {
       if ((int32_t)(*mine - epoch) >= 0) { ok = true; break; }
       if (it > 1024) __nanosleep(100);
     }
-    if (!ok) atomicOr(&a.ctrl->status, MGBS_ST_PEER_TIMEOUT);
+    if (!ok) peer_give_up(a);
   }
   __threadfence_system();
   __syncthreads();
@@ -445,8 +496,28 @@ __device__ void peer_allreduce_hist(const StepArgs& a) {
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
     const int i = threadIdx.x + j * kStreamThreads;
-    if (i < MGBS_HIST_STRIDE) a.hist[i] = sum[j];
+    if (i < MGBS_HIST_STRIDE) hist[i] = sum[j];
   }
+  __threadfence();
+}
+
+// One-shot all-reduce of a finished histogram over peer-mapped memory.  Called by every thread of every block
+// after its contribution was added to the local histogram; the block that arrives last pushes the local
+// histogram into slot [rank] of every rank's exchange area, raises its flag there (value = epoch), waits - with a
+// limit - for the flags of all ranks in its own area, and replaces the local histogram by the sum.  Consumers then
+// read the local histogram exactly as in the NCCL mode.
+__device__ void peer_allreduce_hist(const StepArgs& a) {
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned t = atomicAdd(&a.peer.tickets[a.peer.slot], 1u);
+    s_last = ((t + 1u) % gridDim.x) == 0u;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  peer_allreduce_block(a, a.hist, a.peer.slot);
 }
 
 // Band histogram of one level.  Level 0 needs only the lower bound D; deeper levels first consume the previous
@@ -456,7 +527,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_band_hist(StepArgs a) {
   for (int b = threadIdx.x; b < MGBS_RADIX_BINS; b += blockDim.x) sh[b] = 0;
   // an earlier round found the pool complete (from summed statistics, so every rank agrees): nothing left to do,
   // not even the reduction
-  if (a.ctrl->bands_done) return;
+  if (a.ctrl->halt || a.ctrl->bands_done) return;
   const uint64_t D = a.ctrl->band_lo[a.round];
   MgbsRadix st = radix_zero();
   if (a.level == 0) {
@@ -558,6 +629,7 @@ __device__ __forceinline__ const Slot* table_find(const Slot* table, uint64_t ca
 
 // Insert the band [D, E) of candidates.  The prologue consumes the last band-level histogram to get E.
 __global__ void __launch_bounds__(kStreamThreads) k_band_insert(StepArgs a) {
+  if (a.ctrl->halt) return;
   const uint64_t D = a.ctrl->band_lo[a.round];
   if (a.ctrl->bands_done) {  // set by an earlier round of this depth
     if (blockIdx.x == 0 && threadIdx.x == 0) a.ctrl->band_lo[a.round + 1] = D;
@@ -611,6 +683,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_band_insert(StepArgs a) {
 // Final-cut histogram over the occupied table slots.
 __global__ void __launch_bounds__(kStreamThreads) k_final_hist(StepArgs a) {
   __shared__ uint32_t sh[MGBS_RADIX_BINS];
+  if (a.ctrl->halt) return;
   for (int b = threadIdx.x; b < MGBS_RADIX_BINS; b += blockDim.x) sh[b] = 0;
   MgbsRadix st = radix_zero();
   if (a.level == 0) {
@@ -657,7 +730,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_final_hist(StepArgs a) {
 
 // Write one survivor into the next frontier.
 __device__ __forceinline__ void emit_row(const StepArgs& a, uint64_t i, uint32_t k, uint64_t h, uint32_t payload, uint32_t pos) {
-  if ((int64_t)pos >= a.frontier_cap) {
+  if ((int64_t)pos >= a.next_cap) {
     atomicOr(&a.ctrl->status, MGBS_ST_FRONTIER_OVERFLOW);
     return;
   }
@@ -729,6 +802,7 @@ __device__ __forceinline__ void emit_row(const StepArgs& a, uint64_t i, uint32_t
 // Survivors: every candidate below the cut that is the winner of its table entry.  Winners whose key equals the
 // cut key go to the tie list; k_finish keeps the smallest (hash, fingerprint) among them.
 __global__ void __launch_bounds__(kStreamThreads) k_emit(StepArgs a) {
+  if (a.ctrl->halt) return;
   MgbsRadix st;
   if (a.levels == 1) st = final_initial(a, a.hist_prev);
   else st = a.ctrl->fin[a.levels - 1];
@@ -826,63 +900,121 @@ __global__ void __launch_bounds__(kStreamThreads) k_emit(StepArgs a) {
   });
 }
 
-// One block: resolve ties at the cut key against the tie records of all ranks, then close the depth.
-__global__ void __launch_bounds__(kStreamThreads) k_finish(StepArgs a) {
-  const MgbsRadix st = a.ctrl->fin[a.levels];
+// Summary of the control block for the host (pinned memory), written by the last kernel of every depth launch,
+// halted or not; seq goes last, after a system-wide fence.
+__device__ __forceinline__ void write_mirror(const StepArgs& a) {
+  MgbsCtrl* c = a.ctrl;
+  c->launch_seq += 1;
+  MgbsMirror* m = a.mirror;
+  if (!m) return;
+  m->depth = c->depth;
+  m->found = c->found;
+  m->found_depth = c->found_depth;
+  m->frontier_next = c->frontier_count[c->depth & 1];
+  m->found_payload = c->found_payload;
+  m->status = c->status;
+  m->unique_total = c->unique_total;
+  m->epoch = c->epoch;
+  m->total_candidates = c->total_candidates;
+  __threadfence_system();
+  m->seq = c->launch_seq;
+}
+
+// Resolve ties at the cut key against the tie records of all ranks (tie_all: world segments), one block.
+__device__ void resolve_ties(const StepArgs& a, const MgbsRadix& st, const unsigned long long* tie_all) {
   const uint64_t need = st.tie_need;
-  if (need > 0) {
-    const unsigned long long* mine = a.tie_buf + (int64_t)a.rank * kTieSegWords;
-    uint64_t my_n = mine[0] < MGBS_TIE_CAP ? mine[0] : MGBS_TIE_CAP;
-    for (uint64_t t = threadIdx.x; t < my_n; t += blockDim.x) {
-      const uint64_t h = mine[1 + 3 * t], f = mine[2 + 3 * t], i = mine[3 + 3 * t];
-      uint64_t before = 0;
-      for (int r = 0; r < a.world; ++r) {
-        const unsigned long long* seg = a.tie_buf + (int64_t)r * kTieSegWords;
-        const uint64_t n_r = seg[0] < MGBS_TIE_CAP ? seg[0] : MGBS_TIE_CAP;
-        for (uint64_t j = 0; j < n_r; ++j) {
-          const uint64_t hj = seg[1 + 3 * j], fj = seg[2 + 3 * j];
-          before += (hj < h || (hj == h && fj < f)) ? 1 : 0;
-        }
-      }
-      if (before < need) {
-        const uint32_t pos = atomicAdd(&a.ctrl->next_count, 1u);
-        if (a.cv.states == nullptr) {  // i is a table slot (see k_emit)
-          const uint64_t best = ~__ldcg(&reinterpret_cast<const Slot*>(a.table)[i].best_inv);
-          emit_row(a, i, (uint32_t)(best >> 32), h, (uint32_t)best, pos);
-        } else {
-          emit_row(a, i, __ldg(a.cv.score + i), h, __ldg(a.cv.payload + i), pos);
-        }
+  if (need == 0) return;
+  const unsigned long long* mine = tie_all + (int64_t)a.rank * kTieSegWords;
+  uint64_t my_n = mine[0] < MGBS_TIE_CAP ? mine[0] : MGBS_TIE_CAP;
+  for (uint64_t t = threadIdx.x; t < my_n; t += blockDim.x) {
+    const uint64_t h = mine[1 + 3 * t], f = mine[2 + 3 * t], i = mine[3 + 3 * t];
+    uint64_t before = 0;
+    for (int r = 0; r < a.world; ++r) {
+      const unsigned long long* seg = tie_all + (int64_t)r * kTieSegWords;
+      const uint64_t n_r = seg[0] < MGBS_TIE_CAP ? seg[0] : MGBS_TIE_CAP;
+      for (uint64_t j = 0; j < n_r; ++j) {
+        const uint64_t hj = seg[1 + 3 * j], fj = seg[2 + 3 * j];
+        before += (hj < h || (hj == h && fj < f)) ? 1 : 0;
       }
     }
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    MgbsCtrl* c = a.ctrl;
-    uint64_t u_tot, u_max, i_tot;
-    uint32_t found_any;
-    read_stats(a.hist_stats, a.world, u_tot, u_max, i_tot, found_any);
-    uint32_t nc = c->next_count;
-    if ((int64_t)nc > a.frontier_cap) nc = (uint32_t)a.frontier_cap;
-    c->frontier_count[a.parity ^ 1] = (int32_t)nc;
-    c->unique_total = (uint32_t)u_tot;
-    if (u_tot > 0 && i_tot >= u_tot) { c->rho_num = i_tot; c->rho_den = u_tot; }
-    if (u_tot < (uint64_t)a.beam && c->band_lo[a.rounds] != ~0ull)
-      atomicOr(&c->status, MGBS_ST_ROUNDS_EXHAUSTED);
-    if (found_any && !c->found) {
-      c->found = 1;
-      c->found_depth = c->depth + 1;
+    if (before < need) {
+      const uint32_t pos = atomicAdd(&a.ctrl->next_count, 1u);
+      if (a.cv.states == nullptr) {  // i is a table slot (see k_emit)
+        const uint64_t best = ~__ldcg(&reinterpret_cast<const Slot*>(a.table)[i].best_inv);
+        emit_row(a, i, (uint32_t)(best >> 32), h, (uint32_t)best, pos);
+      } else {
+        emit_row(a, i, __ldg(a.cv.score + i), h, __ldg(a.cv.payload + i), pos);
+      }
     }
-    c->total_candidates += c->cand_count;
-    c->depth += 1;
   }
 }
 
-// One thread: open the depth.
+// Thread 0 of one block: close the depth.
+__device__ void close_depth(const StepArgs& a, const uint32_t* hist_stats) {
+  MgbsCtrl* c = a.ctrl;
+  uint64_t u_tot, u_max, i_tot;
+  uint32_t found_any;
+  read_stats(hist_stats, a.world, u_tot, u_max, i_tot, found_any);
+  uint32_t nc = *reinterpret_cast<volatile uint32_t*>(&c->next_count);
+  if ((int64_t)nc > a.next_cap) nc = (uint32_t)a.next_cap;
+  c->frontier_count[a.parity ^ 1] = (int32_t)nc;
+  c->unique_total = (uint32_t)u_tot;
+  c->exhausted = u_tot == 0 ? 1u : 0u;
+  if (u_tot > 0 && i_tot >= u_tot) { c->rho_num = i_tot; c->rho_den = u_tot; }
+  if (u_tot < (uint64_t)a.beam && c->band_lo[a.rounds] != ~0ull)
+    atomicOr(&c->status, MGBS_ST_ROUNDS_EXHAUSTED);
+  // some rank gave up a wait during this depth and said so: this rank's sums may be partial as well
+  if (a.peer.enabled) {
+    const uint32_t ab = *reinterpret_cast<volatile uint32_t*>(a.peer.base[a.rank] + a.peer.off_abort);
+    if (ab != 0u && (int32_t)(ab - c->epoch) >= 0) atomicOr(&c->status, MGBS_ST_PEER_TIMEOUT);
+  }
+  if (found_any && !c->found) {
+    c->found = 1;
+    c->found_depth = c->depth + 1;
+  }
+  c->total_candidates += c->cand_count;
+  c->depth += 1;
+  write_mirror(a);
+}
+
+// One block: resolve ties at the cut key against the tie records of all ranks, then close the depth.
+__global__ void __launch_bounds__(kStreamThreads) k_finish(StepArgs a) {
+  if (a.ctrl->halt) {
+    if (threadIdx.x == 0) write_mirror(a);
+    return;
+  }
+  const MgbsRadix st = a.ctrl->fin[a.levels];
+  resolve_ties(a, st, a.tie_buf);
+  __syncthreads();
+  if (threadIdx.x == 0) close_depth(a, a.hist_stats);
+}
+
+// One thread: open the depth.  auto_halt = the launch belongs to a depth loop that must not run past the end of
+// the search (found, nothing left); a failed cross-rank wait halts every later depth in any case, because the ranks
+// no longer agree on what they hold.
 __global__ void k_depth_begin(MgbsCtrl* c, int parity, int fanout, int64_t cand_cap, unsigned long long* tie_seg,
-                              uint32_t* send_counts, uint32_t* recv_counts, int world) {
+                              uint32_t* send_counts, uint32_t* recv_counts, int world, int64_t active_limit,
+                              int auto_halt, const uint32_t* abort_word) {
   if (blockIdx.x != 0 || threadIdx.x != 0) return;
-  int64_t cand = (int64_t)c->frontier_count[parity] * fanout;
-  if (cand > cand_cap) cand = cand_cap;
+  if (abort_word) {
+    const uint32_t ab = *reinterpret_cast<const volatile uint32_t*>(abort_word);
+    if (ab != 0u && (int32_t)(ab - c->epoch) >= 0 && c->epoch != 0u) atomicOr(&c->status, MGBS_ST_PEER_TIMEOUT);
+  }
+  const bool broken = (c->status & (MGBS_ST_PEER_TIMEOUT | MGBS_ST_GRID_TIMEOUT)) != 0u;
+  const bool finished = c->found != 0 || c->exhausted != 0u;
+  c->grid_bar = 0;
+  if (broken || (auto_halt && finished)) {
+    c->halt = 1;
+    c->active_rows = 0;
+    c->cand_count = 0;
+    return;
+  }
+  c->halt = 0;
+  int64_t rows = c->frontier_count[parity];
+  if (active_limit > 0 && rows > active_limit) rows = active_limit;
+  int64_t cand = rows * fanout;
+  if (cand > cand_cap) { cand = cand_cap; rows = cand_cap / fanout; }
+  c->active_rows = (int32_t)rows;
   c->cand_count = (uint32_t)cand;
   c->table_count = 0;
   c->next_count = 0;
@@ -908,6 +1040,7 @@ __global__ void k_depth_begin(MgbsCtrl* c, int parity, int fanout, int64_t cand_
 // Replaces the remote branch of kernel_process_score_slot (beam_kernels.cu:592-608); the local share goes through
 // its own bucket as well, so that the owner sees one uniform set of receive buckets.
 __global__ void __launch_bounds__(kStreamThreads) k_route(RouteArgs a) {
+  if (a.ctrl->halt) return;
   const uint32_t cnt = a.ctrl->cand_count;
   const uint32_t rounded = (cnt + 31u) & ~31u;
   const int lane = threadIdx.x & 31;
@@ -955,7 +1088,7 @@ __global__ void __launch_bounds__(kStreamThreads) k_route(RouteArgs a) {
 // that when the kernel ends the receive buckets hold the whole band.
 __global__ void __launch_bounds__(kStreamThreads) k_route_band(StepArgs a, RouteArgs r) {
   __shared__ int s_last;
-  if (a.ctrl->bands_done) return;
+  if (a.ctrl->halt || a.ctrl->bands_done) return;
   const uint64_t D = a.ctrl->band_lo[a.round];
   MgbsRadix st;
   if (a.levels == 1) st = band_initial(a, a.hist_prev, D);
@@ -1021,13 +1154,388 @@ __global__ void __launch_bounds__(kStreamThreads) k_route_band(StepArgs a, Route
     *reinterpret_cast<volatile uint32_t*>(r.peer.base[q] + r.off_route_flag + 4 * r.rank) = want;
     volatile uint32_t* mine = reinterpret_cast<volatile uint32_t*>(r.peer.base[r.rank] + r.off_route_flag + 4 * q);
     bool ok = false;
-    for (uint32_t it = 0; it < (1u << 22); ++it) {
+    for (uint32_t it = 0; it < a.peer.poll_limit; ++it) {
       if ((int32_t)(*mine - want) >= 0) { ok = true; break; }
       if (it > 256) __nanosleep(200);
     }
-    if (!ok) atomicOr(&a.ctrl->status, MGBS_ST_PEER_TIMEOUT);
+    if (!ok) peer_give_up(a);
   }
   __threadfence_system();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Persistent selection kernel: everything after scoring in ONE launch (world 1 and MGBS_EXCHANGE_PEER).
+//
+// The staged form above needs about twenty launches per depth (per band round: histogram levels + insert; final
+// histogram levels; emit; finish), most of them a few microseconds of work behind a launch, and in peer mode every
+// cross-rank reduction sits at the end of a launch.  Here the same steps run as phases of one co-resident grid
+// (cooperative launch, at most select_blocks_per_sm() blocks per SM) with a block barrier between them; block 0
+// does the cross-rank work (histogram sums, band-route handshake, tie exchange) between two barriers.  Every
+// decision is taken from histograms in global memory that all blocks read after a barrier, so the blocks agree;
+// the arithmetic (band_initial / band_advance / final_initial / final_advance, table_insert, emit_row) is the same
+// code the staged kernels call.
+//
+// The barrier is an arrival counter in the control block, reset when the depth opens; generation g is complete
+// when the counter reaches g * gridDim.x.  Its wait is bounded: after grid_poll_limit polls the block sets
+// MGBS_ST_GRID_TIMEOUT, and from then on no block waits any more (the depth ends with that status; the host stops).
+// ------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ void grid_barrier(const StepArgs& a, uint32_t& gen) {
+  __syncthreads();
+  gen += 1u;
+  if (threadIdx.x == 0) {
+    MgbsCtrl* c = a.ctrl;
+    __threadfence();
+    atomicAdd(&c->grid_bar, 1u);
+    const uint32_t target = gen * gridDim.x;
+    volatile uint32_t* bar = &c->grid_bar;
+    volatile uint32_t* status = &c->status;
+    uint32_t it = 0;
+    while ((int32_t)(*bar - target) < 0) {
+      if (*status & MGBS_ST_GRID_TIMEOUT) break;
+      if (++it > a.grid_poll_limit) { atomicOr(&c->status, MGBS_ST_GRID_TIMEOUT); break; }
+      if (it > 32) __nanosleep(40);
+    }
+    __threadfence();
+  }
+  __syncthreads();
+}
+
+// Count one radix level of the candidates in view cv into the shared histogram and add it to `hist`.
+__device__ void count_candidates_level(const CandView& cv, const MgbsRadix& st, uint64_t D, int key_bits, int hash_bits,
+                                       uint32_t* sh, uint32_t* hist) {
+  for (int b = threadIdx.x; b < MGBS_RADIX_BINS; b += blockDim.x) sh[b] = 0;
+  __syncthreads();
+  const int db = digit_bits_at(key_bits, (int)st.bits_done);
+  const int shift = key_bits - (int)st.bits_done - db;
+  const uint32_t mask = (1u << db) - 1u;
+  const int pshift = key_bits - (int)st.bits_done;
+  const bool any_prefix = st.bits_done != 0;
+  const uint64_t pfx = any_prefix ? (st.prefix >> pshift) : 0;
+  for_each_candidate(cv, [&](uint64_t i, bool valid) {
+    bool in = false;
+    uint32_t digit = 0;
+    if (valid) {
+      const uint64_t s = order_key(__ldg(cv.score + i), __ldg(cv.hash + i), hash_bits);
+      in = s >= D && (!any_prefix || (s >> pshift) == pfx);
+      digit = (uint32_t)(s >> shift) & mask;
+    }
+    hist_add(sh, in, digit);
+  });
+  hist_flush(sh, hist);
+}
+
+__device__ void count_table_level(const StepArgs& a, const MgbsRadix& st, uint32_t* sh, uint32_t* hist) {
+  for (int b = threadIdx.x; b < MGBS_RADIX_BINS; b += blockDim.x) sh[b] = 0;
+  __syncthreads();
+  const int db = digit_bits_at(a.key_bits, (int)st.bits_done);
+  const int shift = a.key_bits - (int)st.bits_done - db;
+  const uint32_t mask = (1u << db) - 1u;
+  const int pshift = a.key_bits - (int)st.bits_done;
+  const bool any_prefix = st.bits_done != 0;
+  const uint64_t pfx = any_prefix ? (st.prefix >> pshift) : 0;
+  const Slot* table = reinterpret_cast<const Slot*>(a.table);
+  const uint64_t cap = (uint64_t)a.hash_capacity;
+  const uint64_t rounded = (cap + 31ull) & ~31ull;
+  for (uint64_t j = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; j < rounded; j += (uint64_t)gridDim.x * blockDim.x) {
+    bool in = false;
+    uint32_t digit = 0;
+    if (j < cap) {
+      const ulonglong2 hf = __ldcg(reinterpret_cast<const ulonglong2*>(table + j));
+      if (hf.x != 0ull && hf.y != 0ull) {
+        const uint64_t best = ~__ldcg(&table[j].best_inv);
+        const uint64_t s = order_key((uint32_t)(best >> 32), hf.x, a.hash_bits);
+        in = !any_prefix || (s >> pshift) == pfx;
+        digit = (uint32_t)(s >> shift) & mask;
+      }
+    }
+    hist_add(sh, in, digit);
+  }
+  hist_flush(sh, hist);
+}
+
+// Route this rank's candidates of the band [D, E) to their owners' receive buckets (the loop of k_route_band).
+__device__ void route_band_body(const StepArgs& a, const RouteArgs& r, uint64_t D, uint64_t E) {
+  const uint32_t cnt = a.ctrl->cand_count;
+  const uint32_t rounded = (cnt + 31u) & ~31u;
+  const int lane = threadIdx.x & 31;
+  const int hb = a.hash_bits;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < rounded; i += gridDim.x * blockDim.x) {
+    bool in = false;
+    uint64_t h = 0, f = 0;
+    uint32_t k = 0, owner = 0;
+    if (i < cnt) {
+      h = __ldg(r.hash + i);
+      k = __ldg(r.score + i);
+      const uint64_t s = order_key(k, h, hb);
+      in = s >= D && s < E;
+      if (in) {
+        f = __ldg(r.fp + i);
+        owner = owner_of(h, f, (uint32_t)r.world, r.hash_mode);
+      }
+    }
+    const unsigned vm = __ballot_sync(0xffffffffu, in);
+    if (!in) continue;
+    const unsigned peers = __match_any_sync(vm, owner);
+    const int leader = __ffs(peers) - 1;
+    uint32_t base = 0;
+    if (lane == leader) base = atomicAdd(&r.send_counts[owner], (uint32_t)__popc(peers));
+    base = __shfl_sync(peers, base, leader);
+    const uint32_t pos = base + __popc(peers & ((1u << lane) - 1u));
+    if (pos >= r.bucket_cap) {
+      atomicOr(&a.ctrl->status, MGBS_ST_BUCKET_OVERFLOW);
+      continue;
+    }
+    uint8_t* ob = r.peer.base[owner];
+    const uint64_t d = (uint64_t)r.rank * r.bucket_cap + pos;
+    reinterpret_cast<uint64_t*>(ob + r.off_hash)[d] = h;
+    reinterpret_cast<uint64_t*>(ob + r.off_fp)[d] = f;
+    reinterpret_cast<uint32_t*>(ob + r.off_score)[d] = k;
+    reinterpret_cast<uint32_t*>(ob + r.off_payload)[d] = __ldg(r.payload + i);
+  }
+  __threadfence_system();
+}
+
+// One block, after every block's routed records are fenced: publish the cursors and this rank's flag to every
+// owner and wait (bounded) until every sender has flagged this rank.
+__device__ void route_handshake_block(const StepArgs& a, const RouteArgs& r, int round) {
+  const uint32_t want = a.ctrl->epoch * 16u + (uint32_t)round;
+  if ((int)threadIdx.x < r.world) {
+    const int q = threadIdx.x;
+    uint32_t fill = *reinterpret_cast<volatile uint32_t*>(&r.send_counts[q]);
+    if (fill > r.bucket_cap) fill = r.bucket_cap;
+    *reinterpret_cast<volatile uint32_t*>(r.peer.base[q] + r.off_counts + 4 * r.rank) = fill;
+    __threadfence_system();
+    *reinterpret_cast<volatile uint32_t*>(r.peer.base[q] + r.off_route_flag + 4 * r.rank) = want;
+    volatile uint32_t* mine = reinterpret_cast<volatile uint32_t*>(r.peer.base[r.rank] + r.off_route_flag + 4 * q);
+    bool ok = false;
+    for (uint32_t it = 0; it < a.peer.poll_limit; ++it) {
+      if ((int32_t)(*mine - want) >= 0) { ok = true; break; }
+      if (it > 256) __nanosleep(200);
+    }
+    if (!ok) peer_give_up(a);
+  }
+  __threadfence_system();
+  __syncthreads();
+}
+
+// Insert the band [D, E) of the candidates this rank owns (the loop of k_band_insert).
+__device__ void insert_band_body(const StepArgs& a, uint64_t D, uint64_t E) {
+  Slot* table = reinterpret_cast<Slot*>(a.table);
+  const uint64_t cap = (uint64_t)a.hash_capacity;
+  const int hb = a.hash_bits;
+  uint32_t fresh_total = 0, ins_total = 0, drop_total = 0;
+  for_each_candidate(a.cv, [&](uint64_t i, bool valid) {
+    int res = -2;  // -2 = not in the band, -1 = dropped, >= 0 = slots claimed
+    if (valid) {
+      const uint32_t k = __ldcg(a.cv.score + i);
+      const uint64_t h = __ldcg(a.cv.hash + i);
+      const uint64_t s = order_key(k, h, hb);
+      if (s >= D && s < E) {
+        const uint64_t val = ((uint64_t)k << 32) | (uint64_t)__ldcg(a.cv.payload + i);
+        res = table_insert(table, cap, a.probe_limit, h, __ldcg(a.cv.fp + i), val);
+      }
+    }
+    fresh_total += __reduce_add_sync(0xffffffffu, (uint32_t)(res > 0 ? res : 0));
+    ins_total += __popc(__ballot_sync(0xffffffffu, res != -2));
+    drop_total += __popc(__ballot_sync(0xffffffffu, res == -1));
+  });
+  if ((threadIdx.x & 31) == 0) {
+    if (fresh_total) atomicAdd(&a.ctrl->table_count, fresh_total);
+    if (ins_total) atomicAdd(&a.ctrl->inserted_total, ins_total);
+    if (drop_total) {
+      atomicAdd(&a.ctrl->hash_overflow, drop_total);
+      atomicOr(&a.ctrl->status, MGBS_ST_HASH_OVERFLOW);
+    }
+  }
+}
+
+// Survivors below the cut straight from the table slots (the table-walk branch of k_emit); ties go to `seg`.
+__device__ void emit_table_body(const StepArgs& a, const MgbsRadix& st, unsigned long long* seg) {
+  const uint64_t T = st.result;
+  const bool ties = st.tie_need > 0;
+  const uint64_t tie_key = st.tie_key;
+  const Slot* table = reinterpret_cast<const Slot*>(a.table);
+  const uint64_t cap = (uint64_t)a.hash_capacity;
+  const int hb = a.hash_bits;
+  const int lane = threadIdx.x & 31;
+  const uint64_t rounded = (cap + 31ull) & ~31ull;
+  for (uint64_t j = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; j < rounded; j += (uint64_t)gridDim.x * blockDim.x) {
+    bool keep = false, tie = false;
+    uint32_t k = 0, payload = 0;
+    uint64_t h = 0, f = 0;
+    if (j < cap) {
+      const ulonglong2 hf = __ldcg(reinterpret_cast<const ulonglong2*>(table + j));
+      if (hf.x != 0ull && hf.y != 0ull) {
+        const uint64_t best = ~__ldcg(&table[j].best_inv);
+        h = hf.x; f = hf.y;
+        k = (uint32_t)(best >> 32);
+        payload = (uint32_t)best;
+        const uint64_t s = order_key(k, h, hb);
+        keep = s < T;
+        tie = !keep && ties && s == tie_key;
+      }
+    }
+    const unsigned km = __ballot_sync(0xffffffffu, keep);
+    if (km) {
+      uint32_t base = 0;
+      if (lane == 0) base = atomicAdd(&a.ctrl->next_count, (uint32_t)__popc(km));
+      base = __shfl_sync(0xffffffffu, base, 0);
+      if (keep) emit_row(a, j, k, h, payload, base + __popc(km & ((1u << lane) - 1u)));
+    }
+    if (tie) {
+      const unsigned long long t = atomicAdd(seg, 1ull);
+      if (t < MGBS_TIE_CAP) {
+        seg[1 + 3 * t] = h;
+        seg[2 + 3 * t] = f;
+        seg[3 + 3 * t] = j;
+      } else {
+        atomicOr(&a.ctrl->status, MGBS_ST_TIE_OVERFLOW);
+      }
+    }
+  }
+}
+
+// One block: bring every rank's tie records at the cut key together (peer stores + flags, bounded wait).  Only
+// called when the cut needs a tie-break, which every rank derives from the same summed histogram.
+__device__ void tie_exchange_block(const StepArgs& a, const unsigned long long* my_seg) {
+  const uint32_t epoch = a.ctrl->epoch;
+  const int W = a.world;
+  for (int r = 0; r < W; ++r) {
+    unsigned long long* dst = reinterpret_cast<unsigned long long*>(a.peer.base[r] + a.peer.off_tie) + (int64_t)a.rank * kTieSegWords;
+    for (int i = threadIdx.x; i < kTieSegWords; i += blockDim.x) dst[i] = my_seg[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if ((int)threadIdx.x < W) {
+    const int r = threadIdx.x;
+    *(reinterpret_cast<volatile uint32_t*>(a.peer.base[r] + a.peer.off_tie_flag) + a.rank) = epoch;
+    volatile uint32_t* mine = reinterpret_cast<volatile uint32_t*>(a.peer.base[a.rank] + a.peer.off_tie_flag) + r;
+    bool ok = false;
+    for (uint32_t it = 0; it < a.peer.poll_limit; ++it) {
+      if ((int32_t)(*mine - epoch) >= 0) { ok = true; break; }
+      if (it > 256) __nanosleep(200);
+    }
+    if (!ok) peer_give_up(a);
+  }
+  __threadfence_system();
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kStreamThreads, 2) k_select(StepArgs a, RouteArgs pr) {
+  __shared__ uint32_t sh[MGBS_RADIX_BINS];
+  MgbsCtrl* c = a.ctrl;
+  if (c->halt) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) write_mirror(a);
+    return;
+  }
+  const bool peer = a.peer.enabled != 0;
+  const bool lead = blockIdx.x == 0 && threadIdx.x == 0;
+  const int Lb = a.band_levels, Lf = a.final_levels, R = a.rounds;
+  uint32_t gen = 0;
+
+  // ---------------- band rounds: dedup the best-scoring candidates into the table ----------------
+  uint64_t D = 0;
+  int rounds_run = 0;
+  while (rounds_run < R) {
+    const int round = rounds_run;
+    a.round = round;
+    uint32_t* hist0 = a.hist_base + (int64_t)(round * Lb) * MGBS_HIST_STRIDE;
+    a.hist = hist0;
+    // level 0 counts every remaining candidate by its top digit and carries the per-rank statistics
+    MgbsRadix st = radix_zero();
+    st.done = (D == ~0ull) ? 1u : 0u;
+    publish_stats(a);
+    if (!st.done) count_candidates_level(a.cvh, st, D, a.key_bits, a.hash_bits, sh, hist0);
+    grid_barrier(a, gen);
+    if (peer) {
+      if (blockIdx.x == 0) peer_allreduce_block(a, hist0, round * Lb);
+      grid_barrier(a, gen);
+    }
+    st = band_initial(a, hist0, D);
+    for (int l = 1; l < Lb; ++l) {
+      uint32_t* hist = hist0 + (int64_t)l * MGBS_HIST_STRIDE;
+      st = band_advance(st, hist - MGBS_HIST_STRIDE, a.key_bits, false, D);
+      if (st.done) break;  // the same on every block and every rank
+      count_candidates_level(a.cvh, st, D, a.key_bits, a.hash_bits, sh, hist);
+      grid_barrier(a, gen);
+      if (peer) {
+        if (blockIdx.x == 0) peer_allreduce_block(a, hist, round * Lb + l);
+        grid_barrier(a, gen);
+      }
+    }
+    if (!st.done) st = band_advance(st, hist0 + (int64_t)(Lb - 1) * MGBS_HIST_STRIDE, a.key_bits, true, D);
+    const uint64_t E = st.result;
+    const bool complete = (st.flag & kFlagComplete) != 0u;
+    if (lead) {
+      c->band[round][Lb] = st;
+      c->band_lo[round + 1] = E > D ? E : D;
+      if (complete) {
+        c->bands_done = 1;
+      } else {
+        c->rounds_used = round + 1;
+        if (E <= D) atomicOr(&c->status, MGBS_ST_BAND_STALL);
+      }
+    }
+    ++rounds_run;
+    if (complete) break;
+    if (E > D) {
+      if (peer) {
+        route_band_body(a, pr, D, E);
+        grid_barrier(a, gen);
+        if (blockIdx.x == 0) route_handshake_block(a, pr, round);
+        grid_barrier(a, gen);
+      }
+      insert_band_body(a, D, E);
+      grid_barrier(a, gen);  // table_count / inserted_total are final before the next statistics are published
+      D = E;
+    }
+  }
+  // later entries keep the last bound, so that close_depth sees where the bands stopped
+  if (lead)
+    for (int r = rounds_run + 1; r <= R; ++r) c->band_lo[r] = D;
+
+  // ---------------- final cut: the key of the beam-th unique entry, by radix select over the table ----------------
+  uint32_t* fin0 = a.hist_base + (int64_t)(R * Lb) * MGBS_HIST_STRIDE;
+  a.hist = fin0;
+  publish_stats(a);
+  MgbsRadix fs = radix_zero();
+  count_table_level(a, fs, sh, fin0);
+  grid_barrier(a, gen);
+  if (peer) {
+    if (blockIdx.x == 0) peer_allreduce_block(a, fin0, R * Lb);
+    grid_barrier(a, gen);
+  }
+  fs = final_initial(a, fin0);
+  for (int l = 1; l < Lf; ++l) {
+    uint32_t* hist = fin0 + (int64_t)l * MGBS_HIST_STRIDE;
+    fs = final_advance(fs, hist - MGBS_HIST_STRIDE, a.key_bits, a.select_mode);
+    if (fs.done) break;
+    count_table_level(a, fs, sh, hist);
+    grid_barrier(a, gen);
+    if (peer) {
+      if (blockIdx.x == 0) peer_allreduce_block(a, hist, R * Lb + l);
+      grid_barrier(a, gen);
+    }
+  }
+  if (!fs.done) fs = final_advance(fs, fin0 + (int64_t)(Lf - 1) * MGBS_HIST_STRIDE, a.key_bits, a.select_mode);
+  if (lead) {
+    c->fin[Lf] = fs;
+    c->threshold_key = fs.result;
+  }
+  unsigned long long* seg = a.tie_buf + (int64_t)a.rank * kTieSegWords;
+  emit_table_body(a, fs, seg);
+  grid_barrier(a, gen);
+  if (blockIdx.x != 0) return;
+  // ---------------- one block: ties at the cut key, then close the depth ----------------
+  const unsigned long long* tie_all = a.tie_buf;
+  if (fs.tie_need > 0 && peer) {
+    tie_exchange_block(a, seg);
+    tie_all = reinterpret_cast<const unsigned long long*>(a.peer.base[a.rank] + a.peer.off_tie);
+  }
+  resolve_ties(a, fs, tie_all);
+  __syncthreads();
+  if (threadIdx.x == 0) close_depth(a, fin0);
 }
 
 // Copy rows of n bytes between a packed and a padded layout (bytes n..pitch of a padded destination row are zeroed).
@@ -1073,6 +1581,9 @@ SymLayout sym_layout(const MgbsConfig& c, int band_levels_effective) {
   L.slots = c.band_rounds * band_levels_effective + MGBS_MAX_LEVELS;
   L.hx = off;         off += align256((int64_t)L.slots * W * MGBS_HIST_STRIDE * 4);
   L.hflag = off;      off += align256((int64_t)L.slots * W * 4);
+  L.tie = off;        off += align256(W * (int64_t)kTieSegWords * 8);
+  L.tie_flag = off;   off += align256(W * 4);
+  L.abort_word = off; off += 256;
   L.total = off;
   return L;
 }
@@ -1085,35 +1596,46 @@ static inline int grid_for(int64_t items, int sms) {
   return (int)g;
 }
 
+template <int WORDS, int ZOB>
+static int launch_expand_t(const ExpandArgs& a, int grid, cudaStream_t st) {
+  const int smem = ExpandSmem<WORDS>::total(a.fanout);
+  if (smem > 48 * 1024) {
+    cudaError_t ce = cudaFuncSetAttribute(k_expand<WORDS, ZOB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (ce != cudaSuccess) return (int)ce;
+  }
+  k_expand<WORDS, ZOB><<<grid, kExpandThreads, smem, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
 int launch_expand(const ExpandArgs& a, int64_t max_parents, int sms, cudaStream_t st) {
   const int words = a.stride / 4;
   int64_t tiles = (max_parents + kExpandTile - 1) / kExpandTile;
   int grid = (int)(tiles < (int64_t)sms * 6 ? (tiles < 1 ? 1 : tiles) : (int64_t)sms * 6);
   if (a.zobrist) {
     switch (words) {
-      case 4: k_expand<4, 1><<<grid, kExpandThreads, 0, st>>>(a); break;
-      case 8: k_expand<8, 1><<<grid, kExpandThreads, 0, st>>>(a); break;
-      case 16: k_expand<16, 1><<<grid, kExpandThreads, 0, st>>>(a); break;
-      case 24: k_expand<24, 1><<<grid, kExpandThreads, 0, st>>>(a); break;
-      case 32: k_expand<32, 1><<<grid, kExpandThreads, 0, st>>>(a); break;
+      case 4: return launch_expand_t<4, 1>(a, grid, st);
+      case 8: return launch_expand_t<8, 1>(a, grid, st);
+      case 16: return launch_expand_t<16, 1>(a, grid, st);
+      case 24: return launch_expand_t<24, 1>(a, grid, st);
+      case 32: return launch_expand_t<32, 1>(a, grid, st);
       default: return MGBS_ERR_UNSUPPORTED;
     }
-    return (int)cudaGetLastError();
   }
   switch (words) {
-    case 4: k_expand<4, 0><<<grid, kExpandThreads, 0, st>>>(a); break;
-    case 8: k_expand<8, 0><<<grid, kExpandThreads, 0, st>>>(a); break;
-    case 16: k_expand<16, 0><<<grid, kExpandThreads, 0, st>>>(a); break;
-    case 24: k_expand<24, 0><<<grid, kExpandThreads, 0, st>>>(a); break;
-    case 32: k_expand<32, 0><<<grid, kExpandThreads, 0, st>>>(a); break;
+    case 4: return launch_expand_t<4, 0>(a, grid, st);
+    case 8: return launch_expand_t<8, 0>(a, grid, st);
+    case 16: return launch_expand_t<16, 0>(a, grid, st);
+    case 24: return launch_expand_t<24, 0>(a, grid, st);
+    case 32: return launch_expand_t<32, 0>(a, grid, st);
     default: return MGBS_ERR_UNSUPPORTED;
   }
-  return (int)cudaGetLastError();
 }
 
 int launch_depth_begin(MgbsCtrl* c, int parity, int fanout, int64_t cand_cap, unsigned long long* tie_seg,
-                       uint32_t* send_counts, uint32_t* recv_counts, int world, cudaStream_t st) {
-  k_depth_begin<<<1, 32, 0, st>>>(c, parity, fanout, cand_cap, tie_seg, send_counts, recv_counts, world);
+                       uint32_t* send_counts, uint32_t* recv_counts, int world, int64_t active_limit, int auto_halt,
+                       const uint32_t* abort_word, cudaStream_t st) {
+  k_depth_begin<<<1, 32, 0, st>>>(c, parity, fanout, cand_cap, tie_seg, send_counts, recv_counts, world, active_limit,
+                                  auto_halt, abort_word);
   return (int)cudaGetLastError();
 }
 
@@ -1139,6 +1661,23 @@ int launch_emit(const StepArgs& a, int64_t items, int sms, cudaStream_t st) {
 
 int launch_finish(const StepArgs& a, cudaStream_t st) {
   k_finish<<<1, kStreamThreads, 0, st>>>(a);
+  return (int)cudaGetLastError();
+}
+
+int select_blocks_per_sm() {
+  int occ = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_select, kStreamThreads, 0) != cudaSuccess) return 1;
+  if (occ > 2) occ = 2;
+  return occ < 1 ? 1 : occ;
+}
+
+int launch_select(const StepArgs& a, const RouteArgs& r, int sms, bool cooperative, cudaStream_t st) {
+  const int grid = sms * select_blocks_per_sm();
+  if (cooperative) {
+    void* args[2] = {const_cast<StepArgs*>(&a), const_cast<RouteArgs*>(&r)};
+    return (int)cudaLaunchCooperativeKernel(reinterpret_cast<void*>(k_select), dim3(grid), dim3(kStreamThreads), args, 0, st);
+  }
+  k_select<<<grid, kStreamThreads, 0, st>>>(a, r);
   return (int)cudaGetLastError();
 }
 

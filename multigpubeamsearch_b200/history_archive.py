@@ -9,6 +9,14 @@ to ``root/sample_<id>/`` and then a manifest (atomic rename) that names the last
 every rank; ``try_resume`` validates the manifest against the running configuration, reloads the layers and uploads
 the frontier, and the search continues from that depth.
 
+On-disk layout = the reference's (cpu_history_archive.py:243-318), so checkpoints can be exchanged with it:
+  frontier_depthNNNN_rankNNNN.bin    raw rows of state_size_bytes bytes     + .json {"depth", "rank", "count"}
+  transition_depthNNNN_rankNNNN.parent_idx.bin (int32), .parent_rank.bin (uint8), .action.bin (uint8),
+                                .valid.bin (uint8)                          + .json {"depth", "rank", "count"}
+  manifest.json  {sample_id, depth, rank_count, world_size, n_local, global_beam_width, max_depth, config_hash,
+                  complete_layer_depth, complete}; config_hash = sha256 of the reference's payload
+                  (cpu_history_archive.py:199-211).
+
 The archive talks to the engine through five members only - ``cfg``, ``status()``, ``frontier()``,
 ``history_layer(depth, count)``, ``load_frontier(rows, depth)`` - so the same code runs over the CUDA engine and over
 the CPU model of it used in the tests.
@@ -25,7 +33,7 @@ from typing import Any, Dict, List, Optional
 
 import numpy as np
 
-from .records import unpack_payload
+from .records import pack_payload, unpack_payload
 
 MANIFEST = "manifest.json"
 
@@ -37,11 +45,10 @@ def _atomic_write_json(path: Path, payload: Dict[str, Any]) -> None:
     os.replace(tmp, path)
 
 
-def _atomic_save(path: Path, array: np.ndarray) -> None:
+def _atomic_tofile(path: Path, array: np.ndarray) -> None:
     path.parent.mkdir(parents=True, exist_ok=True)
     tmp = path.with_suffix(path.suffix + ".tmp")
-    with open(tmp, "wb") as fh:
-        np.save(fh, array)
+    np.ascontiguousarray(array).tofile(tmp)
     os.replace(tmp, path)
 
 
@@ -52,7 +59,15 @@ class CPUHistoryArchive:
         self.rank = int(engine.cfg["rank"])
         self.world = int(engine.cfg["world_size"])
         self.checkpoint = bool(checkpoint)
+        self.sample_id = str(sample_id)
         self.root = Path(root) / f"sample_{sample_id}"
+        cfg = engine.cfg
+        self.state_len = int(cfg["state_len"])
+        self.state_size = int(cfg.get("state_size_bytes", self.state_len))
+        beam = int(cfg["global_beam_width"])
+        sizes = engine.sizes() if hasattr(engine, "sizes") else {}
+        self.n_local = int(sizes.get("n_local", (beam + self.world - 1) // self.world))
+        self.max_depth = int(cfg.get("max_depth", 0))
         self.layers: List[np.ndarray] = []   # layers[d][i] = packed back-pointer of row i of the depth d+1 frontier
         self.depth = 0
         self.keep_frontiers = max(1, int(keep_frontiers))
@@ -64,18 +79,65 @@ class CPUHistoryArchive:
 
     # -- identity of a run: a checkpoint is only valid for the configuration that wrote it ------------------------
     def _make_config_hash(self) -> str:
-        keys = ("state_len", "state_size_bytes", "fanout", "world_size", "global_beam_width", "beta", "gamma",
-                "select_mode", "hash_bits", "inference_backend")
+        """The reference's payload and serialisation (cpu_history_archive.py:199-211)."""
         c = self.engine.cfg
-        text = json.dumps({k: str(c.get(k)) for k in keys}, sort_keys=True)
-        return hashlib.sha256(text.encode()).hexdigest()[:16]
+        payload = {
+            "backend": "cpu",
+            "beta": float(c.get("beta", 0.0)),
+            "fanout": int(c["fanout"]),
+            "global_beam_width": int(c["global_beam_width"]),
+            "hash_load_factor": float(c.get("hash_load_factor", 0.0)),
+            "n_local": int(self.n_local),
+            "state_size_bytes": int(self.state_size),
+            "world_size": int(self.world),
+        }
+        raw = json.dumps(payload, sort_keys=True, separators=(",", ":")).encode("utf-8")
+        return hashlib.sha256(raw).hexdigest()
 
     # -- files -----------------------------------------------------------------------------------------------------
-    def _layer_path(self, depth: int, rank: int) -> Path:
-        return self.root / f"layer_{depth:05d}_rank{rank}.npy"
-
     def _frontier_path(self, depth: int, rank: int) -> Path:
-        return self.root / f"frontier_{depth:05d}_rank{rank}.npy"
+        return self.root / f"frontier_depth{depth:04d}_rank{rank:04d}.bin"
+
+    def _frontier_meta_path(self, depth: int, rank: int) -> Path:
+        return self.root / f"frontier_depth{depth:04d}_rank{rank:04d}.json"
+
+    def _transition_prefix(self, depth: int, rank: int) -> str:
+        return str(self.root / f"transition_depth{depth:04d}_rank{rank:04d}")
+
+    def _write_frontier(self, depth: int, rows: np.ndarray) -> None:
+        """Rows padded with zeros to state_size_bytes, as the reference's frontier files hold them."""
+        n = int(rows.shape[0])
+        padded = np.zeros((n, self.state_size), dtype=np.uint8)
+        padded[:, : self.state_len] = rows[:, : self.state_len]
+        _atomic_tofile(self._frontier_path(depth, self.rank), padded)
+        _atomic_write_json(self._frontier_meta_path(depth, self.rank), {"depth": depth, "rank": self.rank, "count": n})
+
+    def _read_frontier(self, depth: int, rank: int) -> np.ndarray:
+        meta = json.loads(self._frontier_meta_path(depth, rank).read_text(encoding="utf-8"))
+        count = int(meta["count"])
+        arr = np.fromfile(self._frontier_path(depth, rank), dtype=np.uint8, count=count * self.state_size)
+        return arr.reshape(count, self.state_size)[:, : self.state_len].copy()
+
+    def _write_transition(self, depth: int, layer: np.ndarray) -> None:
+        """One layer as the reference's four arrays (cpu_history_archive.py:290-303)."""
+        p, r, m = unpack_payload(layer)
+        prefix = self._transition_prefix(depth, self.rank)
+        n = int(layer.shape[0])
+        for suffix, arr in (("parent_idx", np.asarray(p, dtype=np.int32)), ("parent_rank", np.asarray(r, dtype=np.uint8)),
+                            ("action", np.asarray(m, dtype=np.uint8)), ("valid", np.ones((n,), dtype=np.uint8))):
+            _atomic_tofile(Path(prefix + f".{suffix}.bin"), arr)
+        _atomic_write_json(Path(prefix + ".json"), {"depth": depth, "rank": self.rank, "count": n})
+
+    def _read_transition(self, depth: int, rank: int) -> np.ndarray:
+        prefix = self._transition_prefix(depth, rank)
+        n = int(json.loads(Path(prefix + ".json").read_text(encoding="utf-8"))["count"])
+        p = np.fromfile(Path(prefix + ".parent_idx.bin"), dtype=np.int32, count=n).astype(np.uint32)
+        r = np.fromfile(Path(prefix + ".parent_rank.bin"), dtype=np.uint8, count=n).astype(np.uint32)
+        m = np.fromfile(Path(prefix + ".action.bin"), dtype=np.uint8, count=n).astype(np.uint32)
+        v = np.fromfile(Path(prefix + ".valid.bin"), dtype=np.uint8, count=n)
+        if not v.all():
+            raise ValueError(f"transition layer {depth} of rank {rank} holds invalid rows")
+        return pack_payload(p, r, m)
 
     # -- life cycle ------------------------------------------------------------------------------------------------
     def start_new(self) -> None:
@@ -104,13 +166,23 @@ class CPUHistoryArchive:
             self._pending_depth = depth
 
     def finish_pending(self) -> None:
-        """Wait for the background write, then (all ranks) publish its depth in the manifest."""
+        """Wait for the background write, then (all ranks) publish its depth in the manifest, and only after the
+        manifest names the new depth drop the frontier files it no longer needs: a crash at any point leaves a
+        manifest whose files exist on every rank."""
         if self._pending is not None:
             self._pending.result()
             depth = self._pending_depth
             self._pending, self._pending_depth = None, None
             self._barrier()
             self._write_manifest(depth)
+            self._barrier()
+            old = depth - self.keep_frontiers
+            if old >= 0:
+                for path in (self._frontier_path(old, self.rank), self._frontier_meta_path(old, self.rank)):
+                    try:
+                        path.unlink()
+                    except FileNotFoundError:
+                        pass
 
     def finish(self) -> None:
         self.finish_pending()
@@ -120,21 +192,24 @@ class CPUHistoryArchive:
 
     def _write_files(self, depth: int, layer: Optional[np.ndarray], frontier: np.ndarray) -> None:
         if layer is not None:
-            _atomic_save(self._layer_path(depth - 1, self.rank), layer)
-        _atomic_save(self._frontier_path(depth, self.rank), frontier)
-        old = depth - self.keep_frontiers
-        if old >= 0:
-            try:
-                self._frontier_path(old, self.rank).unlink()
-            except FileNotFoundError:
-                pass
+            self._write_transition(depth - 1, layer)
+        self._write_frontier(depth, frontier)
 
     def _write_manifest(self, depth: int) -> None:
+        """Keys of the reference's manifest (cpu_history_archive.py:305-318)."""
         if self.rank != 0:
             return
         _atomic_write_json(self.root / MANIFEST, {
-            "depth": int(depth), "world_size": self.world, "config_hash": self.config_hash,
-            "global_beam_width": int(self.engine.cfg["global_beam_width"]), "complete": True,
+            "sample_id": self.sample_id,
+            "depth": int(depth),
+            "rank_count": self.world,
+            "world_size": self.world,
+            "n_local": self.n_local,
+            "global_beam_width": int(self.engine.cfg["global_beam_width"]),
+            "max_depth": self.max_depth,
+            "config_hash": self.config_hash,
+            "complete_layer_depth": int(depth),
+            "complete": True,
         })
 
     # -- resume ----------------------------------------------------------------------------------------------------
@@ -147,15 +222,17 @@ class CPUHistoryArchive:
         m = json.loads(path.read_text(encoding="utf-8"))
         if not m.get("complete", False):
             raise ValueError("checkpoint manifest is not complete")
-        if int(m.get("world_size", -1)) != self.world:
+        if int(m.get("rank_count", m.get("world_size", -1))) != self.world:
             raise ValueError("checkpoint world size mismatch")
+        if int(m.get("n_local", -1)) != self.n_local:
+            raise ValueError("checkpoint n_local mismatch")
         if int(m.get("global_beam_width", -1)) != int(self.engine.cfg["global_beam_width"]):
             raise ValueError("checkpoint global_beam_width mismatch")
         if str(m.get("config_hash", "")) != self.config_hash:
             raise ValueError("checkpoint config_hash mismatch")
         depth = int(m["depth"])
-        self.layers = [np.load(self._layer_path(d, self.rank)).astype(np.uint32) for d in range(depth)]
-        frontier = np.load(self._frontier_path(depth, self.rank))
+        self.layers = [self._read_transition(d, self.rank) for d in range(depth)]
+        frontier = self._read_frontier(depth, self.rank)
         self.engine.load_frontier(frontier, depth=depth)
         self.depth = depth
         self._barrier()

@@ -6,8 +6,12 @@ MOVE_BITS = 5
 RANK_BITS = 4
 
 
-def pack_payload(parent: int, rank: int, move: int) -> int:
-    """Back-pointer word: parent row (23 bits) | source rank (4 bits) | move (5 bits)."""
+def pack_payload(parent, rank, move):
+    """Back-pointer word: parent row (23 bits) | source rank (4 bits) | move (5 bits); ints or numpy arrays."""
+    import numpy as np
+    if isinstance(parent, np.ndarray):
+        p, r, m = (np.asarray(x, dtype=np.uint32) for x in (parent, rank, move))
+        return (p << np.uint32(RANK_BITS + MOVE_BITS)) | (r << np.uint32(MOVE_BITS)) | m
     return ((int(parent) << (RANK_BITS + MOVE_BITS)) | (int(rank) << MOVE_BITS) | int(move)) & 0xFFFFFFFF
 
 

@@ -61,10 +61,13 @@ def reconstruct_path(engine: BeamEngine) -> Optional[List[int]]:
     parent, prank, move = unpack_payload(payloads[finders[0]])
     moves = [int(move)]
     hist = engine.buffers["history_payload"]
+    if c.found_depth - 1 > hist.shape[0]:
+        raise RuntimeError(f"the device keeps {hist.shape[0]} history layers but the path has {c.found_depth - 1}: "
+                           "pass a CPUHistoryArchive to solve_one, or size history_rows / max_depth to the search")
     for d in range(c.found_depth - 2, -1, -1):
         box = [None]
         if rank == prank:
-            box[0] = int(hist[d, int(parent)].item()) & 0xFFFFFFFF
+            box[0] = int(hist[d % hist.shape[0], int(parent)].item()) & 0xFFFFFFFF
         dist.broadcast_object_list(box, src=int(prank))
         parent, prank, move = unpack_payload(box[0])
         moves.append(int(move))

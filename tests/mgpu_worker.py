@@ -104,10 +104,88 @@ def run_case(name, beam, scramble_len, depths, backend, graph, exchange="peer", 
     del engine, buffers
 
 
+def run_scale_case(beam, exchange, pipeline="persistent"):
+    """The sharded benchmark configuration: 54-byte states, 12 moves, global beam `beam` (262 144 = the reference
+    configuration's beam) over all ranks, benchmark knobs.  The frontier is saturated by the engine's own depth loop
+    (unchecked), then ONE depth is compared with the oracle: survivors, back-pointers, scores, owner placement."""
+    world, rank = dist.get_world_size(), dist.get_rank()
+    pz = puzzles.puzzle54()
+    cfg = be.config_for_puzzle(pz, world_size=world, rank=rank, global_beam_width=beam, max_depth=16, beta=1.2,
+                               gamma=1.05, hash_load_factor=0.45, probe_limit=256, band_rounds=3, band_levels=3,
+                               inference_backend="central_hamming", use_cuda_graphs=True, exchange=exchange,
+                               select_pipeline=pipeline)
+    _, cfg, buffers, engine = be.configure_engine(pz, cfg=cfg)
+    res = be.run_one_search(engine, pz.scramble(0, 40), 8)
+    assert not res["found"] and res["status"]["status_bits"] == 0, res["status_names"]
+    fronts = gather_rows(engine.frontier())
+    assert sum(f.shape[0] for f in fronts) == beam, [f.shape for f in fronts]
+    engine.step()
+    st = engine.status()
+    assert st["status_bits"] == 0, st["status_names"]
+    rows, pay, sco = engine.frontier(), engine.frontier_payloads(), engine.frontier_scores()
+    if rows.shape[0]:
+        assert (bo.owner_rank(bo.hash64(rows), world) == rank).all()
+    parts = gather_rows((rows, pay, sco))
+    if rank == 0:
+        want = bo.depth_step(fronts, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam)
+        got = np.concatenate([r for r, _, _ in parts])
+        assert got.shape[0] == want.states.shape[0] == beam, (got.shape, want.states.shape)
+        assert np.array_equal(bo.sorted_rows(got), bo.sorted_rows(want.states))
+        got_pay = np.concatenate([p for _, p, _ in parts])
+        got_sco = np.concatenate([k for _, _, k in parts])
+        assert {bytes(r): (int(p), int(k)) for r, p, k in zip(got, got_pay, got_sco)} == \
+            {bytes(r): (int(p), int(k)) for r, p, k in zip(want.states, want.payload, want.score)}
+        print(f"SCALE_OK beam={beam} world={world} exchange={exchange} pipeline={pipeline} candidates={want.candidates} "
+              f"unique={want.unique}", flush=True)
+    engine.close()
+    dist.barrier()
+    del engine, buffers
+
+
+def run_late_rank_case():
+    """Failure detection without any GPU fault: the last rank is late on the HOST (it sleeps before it starts its
+    depth loop) and the poll limit is short, so the other ranks' waits run out.  Every rank must come back from
+    search() with an error and the peer_timeout bit: the early ranks because their waits gave up, the late rank
+    because the others told it so (its own waits find their flags already there).  Nothing hangs, no collective is
+    left unmatched (peer mode has no NCCL call inside the step)."""
+    import time
+    world, rank = dist.get_world_size(), dist.get_rank()
+    pz = puzzles.puzzle54()
+    cfg = be.config_for_puzzle(pz, world_size=world, rank=rank, global_beam_width=2048, max_depth=12, beta=1.2,
+                               gamma=1.25, hash_load_factor=0.45, probe_limit=256, band_rounds=3, exchange="peer",
+                               peer_poll_limit=100000)
+    _, cfg, buffers, engine = be.configure_engine(pz, cfg=cfg)
+    start = pz.scramble(1, 30)
+    engine.reset_search(bytes(start), active_on_this_rank=(engine.owner_of(start) == rank))
+    dist.barrier()
+    if rank == world - 1:
+        time.sleep(4.0)
+    t0 = time.perf_counter()
+    failed = False
+    try:
+        engine.search(10)
+    except RuntimeError as exc:
+        failed = "peer timeout" in str(exc)
+    took = time.perf_counter() - t0
+    st = engine.status()
+    ok = failed and bool(st["status_bits"] & 64) and took < 30.0
+    flags = [None] * world
+    dist.all_gather_object(flags, (ok, round(took, 2), st["depth"]))
+    assert all(f[0] for f in flags), flags
+    if rank == 0:
+        print(f"LATE_RANK_OK world={world} per-rank (ok, seconds, depth) = {flags}", flush=True)
+    engine.close()
+    dist.barrier()
+    del engine, buffers
+
+
 def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    if os.environ.get("MGBS_TEST_SCALE", "1") != "0":
+        run_scale_case(262144, "peer")
+        run_scale_case(262144, "nccl")
     for exchange in ("peer", "nccl"):
         run_case("lrx16", 1024, 30, 12, "central_hamming", False, exchange)
         run_case("rand54", 4096, 12, 6, "central_hamming", True, exchange)
@@ -135,6 +213,9 @@ def main():
     if rank == 0:
         print(f"SEARCH_OK found={res['found']} depth={res['depth']} solved={summary['solved']}", flush=True)
     engine.close()
+    dist.barrier()
+    del engine, buffers
+    run_late_rank_case()
     dist.barrier()
     dist.destroy_process_group()
 

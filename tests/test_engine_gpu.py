@@ -153,11 +153,12 @@ def check_step(engine, pz, frontier, beam, mode="exact_k", graph=False):
     return st, want
 
 
+@pytest.mark.parametrize("pipeline", ["persistent", "staged"])
 @pytest.mark.parametrize("name,count,beam", [("lrx16", 300, 256), ("rand54", 500, 1024), ("rand96", 400, 2048),
                                              ("rand54", 40, 100000), ("rand54", 1, 16)])
-def test_single_step_matches_oracle(name, count, beam):
+def test_single_step_matches_oracle(name, count, beam, pipeline):
     pz = puzzles.by_name(name)
-    engine = make_engine(pz, global_beam_width=beam)
+    engine = make_engine(pz, global_beam_width=beam, select_pipeline=pipeline)
     frontier = random_frontier(pz, count, seed=count + beam)[: engine.sizes()["k_work"]]
     for graph in (False, True):
         st, want = check_step(engine, pz, frontier, beam, graph=graph)
@@ -239,6 +240,156 @@ def test_full_search_lrx16_matches_oracle(scramble):
     res = be.run_one_search(engine, start, 40)
     assert res["found"] == want.found and res["depth"] == want.depth
     assert engine.cuda_graph_captured()
+
+
+def test_all_64_lrx16_scrambles_through_the_depth_loop():
+    """The reference's CPU-runnable configuration in full: S_16 under L, R, X, 64 seeded scrambles of 30 moves,
+    beam 1024, depth 40, Hamming scorer.  The engine's own depth loop (graph replay, the host one depth ahead of the
+    device summaries) must stop at the oracle's depth with a path that replays to the solved state, or, when the
+    oracle does not solve within 40, end on the oracle's frontier."""
+    pz = puzzles.lrx(16)
+    engine = make_engine(pz, global_beam_width=1024, max_depth=40)
+    engine.enable_cuda_graphs(True)
+    solved = 0
+    for j in range(64):
+        start = pz.scramble(j, 30)
+        want = bo.search(start, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam=1024, max_depth=40,
+                         keep_frontiers=True)
+        res = be.run_one_search(engine, start, 40)
+        assert res["status"]["status_bits"] == 0, (j, res["status_names"])
+        assert (res["found"], res["depth"]) == (want.found, want.depth), (j, res["found"], res["depth"], want.depth)
+        if want.found:
+            solved += 1
+            path = engine.reconstruct_path()
+            assert len(path) == want.depth and np.array_equal(bo.replay(start, pz.generators, path), pz.solved), j
+        else:
+            assert np.array_equal(bo.sorted_rows(engine.frontier()), want.frontiers[-1]), j
+    assert solved > 0
+
+
+def test_saturated_step_at_benchmark_scale_matches_oracle():
+    """One depth at the benchmark's exact knobs: 54-byte states, 12 moves, global beam 65 536 with a saturated
+    frontier (65 536 rows, 786 432 candidates), BETA 1.2, GAMMA 1.05, load 0.45, probe limit 256, three band rounds of
+    three levels - where the band sizing from the duplicate ratio, the 17 % insertion and the 183 k-slot table
+    actually operate.  Hamming scores make the oracle's expectation exact; eager launch and graph replay."""
+    pz = puzzles.puzzle54()
+    beam = 65536
+    engine = make_engine(pz, global_beam_width=beam, max_depth=24, beta=1.2, gamma=1.05, hash_load_factor=0.45,
+                         probe_limit=256, band_rounds=3, band_levels=3)
+    # saturate the frontier with the engine's own search, as the benchmark does
+    be.run_one_search(engine, pz.scramble(0, 40), 8)
+    frontier = engine.frontier()
+    assert frontier.shape[0] == beam
+    for graph in (False, True):
+        st, want = check_step(engine, pz, frontier, beam, graph=graph)
+        assert want.candidates == beam * pz.fanout and st["counters"][3] >= beam
+    # and two more depths in sequence from there: duplicates concentrate as the search goes on
+    engine.load_frontier(frontier, depth=0)
+    rows = frontier
+    for _ in range(2):
+        want = bo.depth_step([rows], pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam)
+        engine.step()
+        assert engine.status()["status_bits"] == 0
+        rows = engine.frontier()
+        assert np.array_equal(bo.sorted_rows(rows), bo.sorted_rows(want.states))
+
+
+def test_logical_limits_clamp_the_step():
+    """set_active_limit / set_next_limit / clear_logical_limits (beam_engine.cpp:1064-1090)."""
+    pz = puzzles.puzzle54()
+    engine = make_engine(pz, global_beam_width=2048)
+    frontier = random_frontier(pz, 400, seed=21)
+    # active limit: only the first rows of the frontier are expanded
+    engine.set_active_limit(100)
+    engine.load_frontier(frontier)
+    engine.step()
+    st = engine.status()
+    want = bo.depth_step([frontier[:100]], pz.generators, pz.solved, bo.hamming_scorer(pz.solved), 2048)
+    assert st["counters"][2] == 100 * pz.fanout and st["status_bits"] == 0
+    assert np.array_equal(bo.sorted_rows(engine.frontier()), bo.sorted_rows(want.states))
+    # next limit below what the step keeps: rows beyond it are dropped and the drop is reported
+    engine.clear_logical_limits()
+    engine.set_next_limit(300)
+    engine.load_frontier(frontier)
+    engine.step()
+    st = engine.status()
+    assert st["current_size"] == 300 and st["status_bits"] & _lib.ST_FRONTIER_OVERFLOW
+    # cleared: the full step again
+    engine.clear_logical_limits()
+    check_step(engine, pz, frontier, 2048)
+    # the prepass helper: one eager depth with a constant score
+    engine.load_frontier(frontier[:50])
+    engine.step_prepass_fast(3)
+    want = bo.depth_step([frontier[:50]], pz.generators, pz.solved, lambda c: np.full(c.shape[0], 3, np.uint32), 2048)
+    assert np.array_equal(bo.sorted_rows(engine.frontier()), bo.sorted_rows(want.states))
+
+
+def test_depth_loop_halts_on_the_device_and_mirror_matches_control_block():
+    """The depth loop runs one depth ahead of the summaries it reads; the depth that was already enqueued when the
+    solved state turned up must not change anything (it halts on the device)."""
+    pz = puzzles.puzzle54()
+    engine = make_engine(pz, global_beam_width=2048, max_depth=16)
+    start = be.make_shallow_scramble(pz, [3, 7, 1, 9])
+    for graph in (True, False):
+        engine.enable_cuda_graphs(graph)
+        res = be.run_one_search(engine, start, 12)
+        want = bo.search(start, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam=2048, max_depth=12)
+        assert res["found"] and res["depth"] == want.depth
+        st = engine.status()
+        assert st["depth"] == want.depth and st["status_bits"] == 0  # no extra depth was taken after the find
+        mirror = _lib.MgbsMirror.from_buffer_copy(bytes(engine._mirror.numpy()))
+        assert mirror.found == 1 and mirror.found_depth == want.depth and mirror.depth == st["depth"]
+        path = engine.reconstruct_path()
+        assert np.array_equal(bo.replay(start, pz.generators, path), pz.solved)
+    # a search that runs out of depth stops exactly at max_depth
+    far = pz.scramble(5, 40)
+    res = be.run_one_search(engine, far, 7)
+    assert not res["found"] and res["depth"] == 7 and engine.status()["depth"] == 7
+
+
+def test_history_ring_smaller_than_the_search():
+    """Two device history rows: entries older than the ring are reported invalid and the walk-back refuses."""
+    pz = puzzles.puzzle54()
+    engine = make_engine(pz, global_beam_width=512, max_depth=16, history_rows=2)
+    start = be.make_shallow_scramble(pz, [2, 5, 8, 11, 0])
+    res = be.run_one_search(engine, start, 10)
+    assert res["found"] and res["depth"] >= 4
+    d = res["depth"]
+    assert engine.history_entry(d - 1, 0)["valid"] in (0, 1)  # the finding depth wrote no layer: found before select
+    assert engine.history_entry(0, 0)["valid"] == 0            # overwritten long ago
+    with pytest.raises(RuntimeError, match="history"):
+        engine.reconstruct_path()
+
+
+def test_bounded_peer_wait_gives_up_and_reports():
+    """A two-rank engine in peer mode whose peer never answers: rank 1's region is a zeroed buffer on the same GPU
+    that nothing writes.  With a short poll limit every cross-rank wait runs out, the step ends by itself with the
+    peer_timeout bit, the depth loop returns an error instead of stepping on, and the GPU stays usable."""
+    pz = puzzles.puzzle54()
+    cfg = be.config_for_puzzle(pz, world_size=2, rank=0, global_beam_width=1024, max_depth=8, beta=1.2, gamma=1.25,
+                               hash_load_factor=0.45, probe_limit=256, band_rounds=3, exchange="peer",
+                               peer_poll_limit=2000)
+    ext = be.build_extension()
+    buffers = be.allocate_buffers(ext, cfg)
+    engine = ext.BeamEngine(cfg, buffers, "central_hamming")
+    engine.set_action_permutation_table(pz.action_table_bytes())
+    engine.set_central_state(bytes(pz.solved))
+    dead_peer = torch.zeros_like(buffers["sym"])
+    bases = (C.c_void_p * 2)(buffers["sym"].data_ptr(), dead_peer.data_ptr())
+    _lib.check(engine.lib.mgbs_engine_set_peer_pointers(engine._h, bases), "set_peer_pointers")
+    start = pz.scramble(2, 20)
+    engine.reset_search(bytes(start), active_on_this_rank=True)
+    with pytest.raises(RuntimeError, match="peer timeout"):
+        engine.search(6)
+    st = engine.status()
+    assert st["status_bits"] & _lib.ST_PEER_TIMEOUT and "peer_timeout" in st["status_names"]
+    assert st["depth"] <= 1  # the loop did not step on after the failed wait
+    # a later launch on the broken engine halts at once and changes nothing
+    engine.step()
+    assert engine.status()["depth"] == st["depth"]
+    engine.close()
+    # the context is intact: an ordinary engine on the same GPU works
+    check_step(make_engine(pz, global_beam_width=512), pz, random_frontier(pz, 100, seed=8), 512)
 
 
 def test_known_shallow_scrambles_rand54():

@@ -69,7 +69,7 @@ def test_archive_checkpoint_resume_and_walk_back(tmp_path):
     a1.finish()
     root = tmp_path / "b" / "sample_7"
     assert json.loads((root / MANIFEST).read_text())["depth"] == 5
-    (root / "layer_00005_rank0.npy.tmp").write_bytes(b"torn write of a run that died")  # must be ignored
+    (root / "transition_depth0005_rank0000.parent_idx.bin.tmp").write_bytes(b"torn write of a run that died")  # must be ignored
     e2 = OracleEngine(pz, 64)
     a2 = CPUHistoryArchive(e2, str(tmp_path / "b"), sample_id=7, checkpoint=True)
     assert a2.try_resume() == 5 and e2.depth == 5
@@ -86,7 +86,75 @@ def test_archive_checkpoint_resume_and_walk_back(tmp_path):
     assert entry["valid"] == 1 and entry["action"] == a2.path_to(8, 0)[-1]
     assert a2.history_entry(8, 0)["valid"] == 0
     # old frontier files are dropped, layers are all kept
-    assert not (root / "frontier_00003_rank0.npy").exists() and (root / "layer_00000_rank0.npy").exists()
+    assert not (root / "frontier_depth0003_rank0000.bin").exists()
+    assert not (root / "frontier_depth0003_rank0000.json").exists()
+    assert (root / "transition_depth0000_rank0000.parent_idx.bin").exists()
+    # the manifest is published before the frontier it replaces is dropped: the last two frontiers are there
+    assert (root / "frontier_depth0008_rank0000.bin").exists() and (root / "frontier_depth0007_rank0000.bin").exists()
+
+
+def _write_reference_layout(root, sample_id, cfg, n_local, max_depth, frontiers, layers):
+    """A checkpoint directory written the way the reference's CPUHistoryArchive writes it
+    (cpu_history_archive.py:199-211, 243-318): raw .bin arrays beside small .json files, manifest last."""
+    import hashlib
+    d = root / f"sample_{sample_id}"
+    d.mkdir(parents=True)
+    size = cfg["state_size_bytes"]
+    depth = len(layers)
+    rows = frontiers[depth]
+    padded = np.zeros((rows.shape[0], size), np.uint8)
+    padded[:, : rows.shape[1]] = rows
+    padded.tofile(d / f"frontier_depth{depth:04d}_rank0000.bin")
+    (d / f"frontier_depth{depth:04d}_rank0000.json").write_text(json.dumps({"depth": depth, "rank": 0, "count": int(rows.shape[0])}))
+    for t, layer in enumerate(layers):
+        parent, rank, move = bo.unpack_payload(layer)
+        prefix = str(d / f"transition_depth{t:04d}_rank0000")
+        parent.astype(np.int32).tofile(prefix + ".parent_idx.bin")
+        rank.astype(np.uint8).tofile(prefix + ".parent_rank.bin")
+        move.astype(np.uint8).tofile(prefix + ".action.bin")
+        np.ones(layer.shape[0], np.uint8).tofile(prefix + ".valid.bin")
+        (d / f"transition_depth{t:04d}_rank0000.json").write_text(json.dumps({"depth": t, "rank": 0, "count": int(layer.shape[0])}))
+    payload = {"backend": "cpu", "beta": float(cfg["beta"]), "fanout": int(cfg["fanout"]),
+               "global_beam_width": int(cfg["global_beam_width"]), "hash_load_factor": float(cfg["hash_load_factor"]),
+               "n_local": int(n_local), "state_size_bytes": int(size), "world_size": 1}
+    config_hash = hashlib.sha256(json.dumps(payload, sort_keys=True, separators=(",", ":")).encode("utf-8")).hexdigest()
+    (d / MANIFEST).write_text(json.dumps({
+        "sample_id": str(sample_id), "depth": depth, "rank_count": 1, "world_size": 1, "n_local": n_local,
+        "global_beam_width": int(cfg["global_beam_width"]), "max_depth": max_depth, "config_hash": config_hash,
+        "complete_layer_depth": depth, "complete": True}, indent=2))
+
+
+def test_resume_from_a_directory_in_the_reference_layout(tmp_path):
+    pz = puzzles.puzzle54()
+    start = pz.scramble(4, 30)
+    extra = {"hash_load_factor": 0.45, "max_depth": 12, "state_size_bytes": 64}
+    # ground truth: an uninterrupted run
+    e0 = OracleEngine(pz, 64, **extra)
+    e0.reset_search(start)
+    a0 = CPUHistoryArchive(e0, str(tmp_path / "truth"), sample_id=1, checkpoint=False)
+    a0.start_new()
+    frontiers = {0: e0.frontier()}
+    while e0.depth < 7:
+        e0.step()
+        a0.after_step(e0.depth, e0.status()["current_size"])
+        frontiers[e0.depth] = e0.frontier()
+    # a checkpoint at depth 4 written by hand in the reference's layout, then resumed and run on
+    _write_reference_layout(tmp_path / "ref", 1, e0.cfg, 64, 12, frontiers, a0.layers[:4])
+    e1 = OracleEngine(pz, 64, **extra)
+    a1 = CPUHistoryArchive(e1, str(tmp_path / "ref"), sample_id=1, checkpoint=True)
+    assert a1.try_resume() == 4 and e1.depth == 4
+    assert np.array_equal(e1.frontier(), frontiers[4])
+    _run(e1, a1, 7)
+    a1.finish()
+    assert np.array_equal(e1.frontier(), frontiers[7])
+    assert all(np.array_equal(x, y) for x, y in zip(a1.layers, a0.layers)) and len(a1.layers) == 7
+    moves = a1.path_to(7, 0)
+    assert np.array_equal(replay(start, pz.generators, moves), frontiers[7][0])
+    # and what this archive wrote afterwards carries the reference's manifest keys
+    m = json.loads((tmp_path / "ref" / "sample_1" / MANIFEST).read_text())
+    assert {"sample_id", "depth", "rank_count", "world_size", "n_local", "global_beam_width", "max_depth",
+            "config_hash", "complete_layer_depth", "complete"} <= set(m)
+    assert m["depth"] == 7 and m["n_local"] == 64 and len(m["config_hash"]) == 64
 
 
 def test_archive_rejects_a_checkpoint_of_another_configuration(tmp_path):
@@ -178,4 +246,5 @@ def test_archive_walk_back_across_two_gloo_ranks(tmp_path):
     assert got == [(0, True, 6), (1, True, 6)], got
     m = json.loads((tmp_path / "sample_0" / MANIFEST).read_text())
     assert m["depth"] == 6 and m["world_size"] == 2
-    assert (tmp_path / "sample_0" / "layer_00005_rank1.npy").exists()
+    assert m["rank_count"] == 2 and m["complete_layer_depth"] == 6
+    assert (tmp_path / "sample_0" / "transition_depth0005_rank0001.action.bin").exists()
