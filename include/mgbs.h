@@ -111,7 +111,8 @@ typedef struct MgbsCtrl {
                               * has read loses nothing.  exhausted: the last depth produced no state at all */
   uint32_t exhausted;
   uint32_t grid_bar;         /* arrival counter of the selection kernel's block barrier (reset when a depth opens) */
-  uint32_t pad0;
+  uint32_t win_lo;           /* lowest score of the 2046-score window the next depth's band histogram is taken over
+                              * (the cut score of this depth minus 1023, not below 0) */
   uint64_t launch_seq;       /* depth launches finished since the last reset, halted ones included */
   MgbsRadix band[MGBS_MAX_ROUNDS][MGBS_MAX_LEVELS + 1];
   MgbsRadix fin[MGBS_MAX_LEVELS + 1];

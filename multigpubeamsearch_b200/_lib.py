@@ -57,7 +57,7 @@ class MgbsCtrl(C.Structure):
         ("epoch", C.c_uint32), ("active_rows", C.c_int32),
         ("band_lo", C.c_uint64 * (MAX_ROUNDS + 1)), ("threshold_key", C.c_uint64),
         ("rho_num", C.c_uint64), ("rho_den", C.c_uint64), ("total_candidates", C.c_uint64),
-        ("halt", C.c_uint32), ("exhausted", C.c_uint32), ("grid_bar", C.c_uint32), ("pad0", C.c_uint32),
+        ("halt", C.c_uint32), ("exhausted", C.c_uint32), ("grid_bar", C.c_uint32), ("win_lo", C.c_uint32),
         ("launch_seq", C.c_uint64),
         ("band", (MgbsRadix * (MAX_LEVELS + 1)) * MAX_ROUNDS), ("fin", MgbsRadix * (MAX_LEVELS + 1)),
     ]

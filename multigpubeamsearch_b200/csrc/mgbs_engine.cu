@@ -127,7 +127,8 @@ int mgbs_derive_sizes(int64_t global_beam_width, int32_t world_size, double gamm
   out6[2] = k_work;
   out6[3] = hash_capacity;
   out6[4] = round_half_up(beta * (double)n_local);
-  out6[5] = (int64_t)(band_rounds * band_levels + MGBS_MAX_LEVELS) * MGBS_HIST_STRIDE;
+  // the persistent selection kernel uses up to three histograms per band round whatever band_levels says
+  out6[5] = (int64_t)(band_rounds * (band_levels < 3 ? 3 : band_levels) + MGBS_MAX_LEVELS) * MGBS_HIST_STRIDE;
   return 0;
 }
 
@@ -528,7 +529,7 @@ static int enqueue_depth(MgbsEngine* e, int32_t parity, int32_t phase, int auto_
                                 e->active_limit, auto_halt,
                                 peer_mode ? reinterpret_cast<const uint32_t*>(c.sym + e->sym.abort_word) : nullptr, st));
     MGBS_TRY(cudaMemsetAsync(c.table, 0, (size_t)hash_capacity_eff * 32, st));
-    MGBS_TRY(cudaMemsetAsync(c.hist, 0, (size_t)(R * Lb + MGBS_MAX_LEVELS) * MGBS_HIST_STRIDE * sizeof(uint32_t), st));
+    MGBS_TRY(cudaMemsetAsync(c.hist, 0, (size_t)(R * (Lb < 3 ? 3 : Lb) + MGBS_MAX_LEVELS) * MGBS_HIST_STRIDE * sizeof(uint32_t), st));
     ExpandArgs x;
     x.frontier = c.frontier[parity];
     x.count_dev = &c.ctrl->active_rows;

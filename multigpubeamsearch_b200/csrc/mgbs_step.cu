@@ -405,6 +405,32 @@ __device__ __forceinline__ void for_each_candidate(const CandView& cv, F f) {
   }
 }
 
+// The same walk with four items in flight per thread: `load(index)` fetches what an item needs (the loads of a batch
+// are independent and issued together), `f(index, valid, item)` consumes it and may use warp-wide operations.
+template <class Item, class L, class F>
+__device__ __forceinline__ void for_each_candidate_batched(const CandView& cv, L load, F f) {
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (int b = 0; b < cv.nbuckets; ++b) {
+    uint32_t cnt = __ldcg(cv.counts + b);
+    if (cnt > cv.cap) cnt = cv.cap;
+    const uint32_t rounded = (cnt + 31u) & ~31u;
+    const uint64_t base = (uint64_t)b * cv.cap;
+    for (uint32_t i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < rounded; i0 += 4u * stride) {
+      Item it[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t i = i0 + (uint32_t)u * stride;
+        if (i < cnt) it[u] = load(base + i);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t i = i0 + (uint32_t)u * stride;
+        if (i < rounded) f(base + i, i < cnt, it[u]);  // i < rounded is uniform over a warp
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void hist_add(uint32_t* sh, bool in, uint32_t digit) {
   const unsigned m = __ballot_sync(0xffffffffu, in);
   if (in) {
@@ -1225,13 +1251,14 @@ __device__ void count_candidates_level(const CandView& cv, const MgbsRadix& st, 
   hist_flush(sh, hist);
 }
 
-__device__ void count_table_level(const StepArgs& a, const MgbsRadix& st, uint32_t* sh, uint32_t* hist) {
+__device__ void count_table_level(const StepArgs& a, const MgbsRadix& st, uint64_t base, int key_bits, uint32_t* sh,
+                                  uint32_t* hist) {
   for (int b = threadIdx.x; b < MGBS_RADIX_BINS; b += blockDim.x) sh[b] = 0;
   __syncthreads();
-  const int db = digit_bits_at(a.key_bits, (int)st.bits_done);
-  const int shift = a.key_bits - (int)st.bits_done - db;
+  const int db = digit_bits_at(key_bits, (int)st.bits_done);
+  const int shift = key_bits - (int)st.bits_done - db;
   const uint32_t mask = (1u << db) - 1u;
-  const int pshift = a.key_bits - (int)st.bits_done;
+  const int pshift = key_bits - (int)st.bits_done;
   const bool any_prefix = st.bits_done != 0;
   const uint64_t pfx = any_prefix ? (st.prefix >> pshift) : 0;
   const Slot* table = reinterpret_cast<const Slot*>(a.table);
@@ -1244,7 +1271,7 @@ __device__ void count_table_level(const StepArgs& a, const MgbsRadix& st, uint32
       const ulonglong2 hf = __ldcg(reinterpret_cast<const ulonglong2*>(table + j));
       if (hf.x != 0ull && hf.y != 0ull) {
         const uint64_t best = ~__ldcg(&table[j].best_inv);
-        const uint64_t s = order_key((uint32_t)(best >> 32), hf.x, a.hash_bits);
+        const uint64_t s = order_key((uint32_t)(best >> 32), hf.x, a.hash_bits) - base;
         in = !any_prefix || (s >> pshift) == pfx;
         digit = (uint32_t)(s >> shift) & mask;
       }
@@ -1325,21 +1352,28 @@ __device__ void insert_band_body(const StepArgs& a, uint64_t D, uint64_t E) {
   const uint64_t cap = (uint64_t)a.hash_capacity;
   const int hb = a.hash_bits;
   uint32_t fresh_total = 0, ins_total = 0, drop_total = 0;
-  for_each_candidate(a.cv, [&](uint64_t i, bool valid) {
-    int res = -2;  // -2 = not in the band, -1 = dropped, >= 0 = slots claimed
-    if (valid) {
-      const uint32_t k = __ldcg(a.cv.score + i);
-      const uint64_t h = __ldcg(a.cv.hash + i);
-      const uint64_t s = order_key(k, h, hb);
-      if (s >= D && s < E) {
-        const uint64_t val = ((uint64_t)k << 32) | (uint64_t)__ldcg(a.cv.payload + i);
-        res = table_insert(table, cap, a.probe_limit, h, __ldcg(a.cv.fp + i), val);
-      }
-    }
-    fresh_total += __reduce_add_sync(0xffffffffu, (uint32_t)(res > 0 ? res : 0));
-    ins_total += __popc(__ballot_sync(0xffffffffu, res != -2));
-    drop_total += __popc(__ballot_sync(0xffffffffu, res == -1));
-  });
+  struct Item { uint32_t k; uint64_t h; };
+  for_each_candidate_batched<Item>(
+      a.cv,
+      [&](uint64_t i) {
+        Item it;  // past the L1 cache: in peer mode other ranks appended these records during this kernel
+        it.k = __ldcg(a.cv.score + i);
+        it.h = __ldcg(a.cv.hash + i);
+        return it;
+      },
+      [&](uint64_t i, bool valid, const Item& it) {
+        int res = -2;  // -2 = not in the band, -1 = dropped, >= 0 = slots claimed
+        if (valid) {
+          const uint64_t s = order_key(it.k, it.h, hb);
+          if (s >= D && s < E) {
+            const uint64_t val = ((uint64_t)it.k << 32) | (uint64_t)__ldcg(a.cv.payload + i);
+            res = table_insert(table, cap, a.probe_limit, it.h, __ldcg(a.cv.fp + i), val);
+          }
+        }
+        fresh_total += __reduce_add_sync(0xffffffffu, (uint32_t)(res > 0 ? res : 0));
+        ins_total += __popc(__ballot_sync(0xffffffffu, res != -2));
+        drop_total += __popc(__ballot_sync(0xffffffffu, res == -1));
+      });
   if ((threadIdx.x & 31) == 0) {
     if (fresh_total) atomicAdd(&a.ctrl->table_count, fresh_total);
     if (ins_total) atomicAdd(&a.ctrl->inserted_total, ins_total);
@@ -1351,7 +1385,7 @@ __device__ void insert_band_body(const StepArgs& a, uint64_t D, uint64_t E) {
 }
 
 // Survivors below the cut straight from the table slots (the table-walk branch of k_emit); ties go to `seg`.
-__device__ void emit_table_body(const StepArgs& a, const MgbsRadix& st, unsigned long long* seg) {
+__device__ void emit_table_body(const StepArgs& a, const MgbsRadix& st, uint64_t base, unsigned long long* seg) {
   const uint64_t T = st.result;
   const bool ties = st.tie_need > 0;
   const uint64_t tie_key = st.tie_key;
@@ -1371,17 +1405,17 @@ __device__ void emit_table_body(const StepArgs& a, const MgbsRadix& st, unsigned
         h = hf.x; f = hf.y;
         k = (uint32_t)(best >> 32);
         payload = (uint32_t)best;
-        const uint64_t s = order_key(k, h, hb);
+        const uint64_t s = order_key(k, h, hb) - base;  // the cut was selected on keys relative to base
         keep = s < T;
         tie = !keep && ties && s == tie_key;
       }
     }
     const unsigned km = __ballot_sync(0xffffffffu, keep);
     if (km) {
-      uint32_t base = 0;
-      if (lane == 0) base = atomicAdd(&a.ctrl->next_count, (uint32_t)__popc(km));
-      base = __shfl_sync(0xffffffffu, base, 0);
-      if (keep) emit_row(a, j, k, h, payload, base + __popc(km & ((1u << lane) - 1u)));
+      uint32_t pos0 = 0;
+      if (lane == 0) pos0 = atomicAdd(&a.ctrl->next_count, (uint32_t)__popc(km));
+      pos0 = __shfl_sync(0xffffffffu, pos0, 0);
+      if (keep) emit_row(a, j, k, h, payload, pos0 + __popc(km & ((1u << lane) - 1u)));
     }
     if (tie) {
       const unsigned long long t = atomicAdd(seg, 1ull);
@@ -1422,6 +1456,100 @@ __device__ void tie_exchange_block(const StepArgs& a, const unsigned long long* 
   __syncthreads();
 }
 
+// Band histogram over SCORES.  The selection key is the score above the top hash bits, and hashes are uniform, so the
+// number of candidates below a key (s, hash prefix x) is count(score < s) + x * count(score == s) up to a binomial
+// deviation far inside the tolerance of a band (any pool between the beam and the table's hard limit will do, and
+// the statistics after the insert verify it).  One histogram over scores therefore places a band, where a radix
+// descent over the whole key needs one pass per 11 bits.  Fine bins: bin 0 = score below the window, bin b in
+// 1..2046 = score win_lo + b - 1, bin 2047 = above.  Coarse bins (to find a window when the previous depth's does
+// not fit): score >> 9.
+__device__ __forceinline__ uint32_t clamp_score(uint32_t k) { return k > 0xfffffu ? 0xfffffu : k; }
+
+__device__ void count_score_window(const CandView& cv, uint64_t D, uint32_t win_lo, bool coarse, int hash_bits,
+                                   uint32_t* sh, uint32_t* hist) {
+  for (int b = threadIdx.x; b < MGBS_RADIX_BINS; b += blockDim.x) sh[b] = 0;
+  __syncthreads();
+  struct Item { uint32_t k; uint64_t h; };
+  const bool need_hash = D != 0ull && hash_bits != 0;
+  for_each_candidate_batched<Item>(
+      cv,
+      [&](uint64_t i) {
+        Item it;
+        it.k = __ldg(cv.score + i);
+        it.h = need_hash ? __ldg(cv.hash + i) : 0ull;
+        return it;
+      },
+      [&](uint64_t, bool valid, const Item& it) {
+        bool in = false;
+        uint32_t bin = 0;
+        if (valid) {
+          const uint32_t k = clamp_score(it.k);
+          in = D == 0ull || order_key(k, it.h, hash_bits) >= D;
+          if (coarse) {
+            bin = k >> 9;
+          } else {
+            const uint32_t rel = k < win_lo ? 0u : k - win_lo + 1u;
+            bin = rel > (uint32_t)(MGBS_RADIX_BINS - 1) ? (uint32_t)(MGBS_RADIX_BINS - 1) : rel;
+          }
+        }
+        hist_add(sh, in, bin);
+      });
+  hist_flush(sh, hist);
+}
+
+// First and last non-empty bin of a 2048-bin histogram (-1, -1 when empty); same answer on every thread.
+__device__ void hist_extent(const uint32_t* hist, int& first, int& last) {
+  __shared__ int s_first, s_last;
+  if (threadIdx.x == 0) { s_first = MGBS_RADIX_BINS; s_last = -1; }
+  __syncthreads();
+  constexpr int PER = MGBS_RADIX_BINS / kStreamThreads;
+  int lo = MGBS_RADIX_BINS, hi = -1;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int b = threadIdx.x * PER + j;
+    if (__ldcg(hist + b) != 0u) { lo = b < lo ? b : lo; hi = b; }
+  }
+  if (hi >= 0) { atomicMin(&s_first, lo); atomicMax(&s_last, hi); }
+  __syncthreads();
+  first = s_last >= 0 ? s_first : -1;
+  last = s_last;
+  __syncthreads();
+}
+
+// Band bound from a fine score histogram: true = st.result holds the bound, false = the cut score lies outside the
+// window (or in its open-ended first / last bin).
+__device__ bool band_from_window(MgbsRadix& st, const uint32_t* hist, uint32_t win_lo, int hash_bits, uint64_t D,
+                                 uint32_t& cut_score) {
+  const Cross c = find_crossing(hist, st.remaining, true);
+  if (c.bin < 0) {  // everything that is left fits
+    st.result = ~0ull;
+    st.done = 1;
+    cut_score = 0xffffffffu;
+    return true;
+  }
+  if (c.bin == 0 || c.bin == MGBS_RADIX_BINS - 1) return false;
+  const uint64_t sstar = (uint64_t)win_lo + (uint64_t)c.bin - 1ull;
+  cut_score = (uint32_t)sstar;
+  uint64_t E;
+  if (hash_bits == 0) {
+    E = sstar;  // score-only order: the level that does not fit whole stays out
+  } else {
+    const uint64_t full = 1ull << hash_bits;
+    const uint64_t lo = (D >> hash_bits) == sstar ? (D & (full - 1ull)) : 0ull;  // the level is partly inserted already
+    const uint64_t range = full - lo;
+    const uint64_t r = st.remaining - c.before, cnt = c.count;  // r < cnt
+    const uint64_t part = (range / cnt) * r + ((range % cnt) * r) / cnt;
+    E = (sstar << hash_bits) | (lo + part);
+  }
+  st.result = E > D ? E : D;
+  st.done = 1;
+  return true;
+}
+
+__device__ __forceinline__ int ceil_log2_u64(uint64_t x) {  // smallest b with 2^b >= x, x >= 1
+  return x <= 1ull ? 0 : 64 - __clzll((long long)(x - 1ull));
+}
+
 __global__ void __launch_bounds__(kStreamThreads, 2) k_select(StepArgs a, RouteArgs pr) {
   __shared__ uint32_t sh[MGBS_RADIX_BINS];
   MgbsCtrl* c = a.ctrl;
@@ -1431,44 +1559,77 @@ __global__ void __launch_bounds__(kStreamThreads, 2) k_select(StepArgs a, RouteA
   }
   const bool peer = a.peer.enabled != 0;
   const bool lead = blockIdx.x == 0 && threadIdx.x == 0;
-  const int Lb = a.band_levels, Lf = a.final_levels, R = a.rounds;
+  const int R = a.rounds;
+  constexpr int kBandSlots = 3;  // histograms a band round may use: score window, coarse scores, second window
   uint32_t gen = 0;
 
   // ---------------- band rounds: dedup the best-scoring candidates into the table ----------------
   uint64_t D = 0;
   int rounds_run = 0;
+  uint32_t win_lo = c->win_lo, next_win_lo = c->win_lo;
+  uint32_t score_min = 0, score_max = 0xfffffu;
+  bool range_known = false;
   while (rounds_run < R) {
     const int round = rounds_run;
     a.round = round;
-    uint32_t* hist0 = a.hist_base + (int64_t)(round * Lb) * MGBS_HIST_STRIDE;
+    uint32_t* hist0 = a.hist_base + (int64_t)(round * kBandSlots) * MGBS_HIST_STRIDE;
     a.hist = hist0;
-    // level 0 counts every remaining candidate by its top digit and carries the per-rank statistics
+    // one histogram over the scores of every remaining candidate; it also carries the per-rank statistics
     MgbsRadix st = radix_zero();
     st.done = (D == ~0ull) ? 1u : 0u;
     publish_stats(a);
-    if (!st.done) count_candidates_level(a.cvh, st, D, a.key_bits, a.hash_bits, sh, hist0);
+    if (!st.done) count_score_window(a.cvh, D, win_lo, false, a.hash_bits, sh, hist0);
     grid_barrier(a, gen);
     if (peer) {
-      if (blockIdx.x == 0) peer_allreduce_block(a, hist0, round * Lb);
+      if (blockIdx.x == 0) peer_allreduce_block(a, hist0, round * kBandSlots);
       grid_barrier(a, gen);
     }
     st = band_initial(a, hist0, D);
-    for (int l = 1; l < Lb; ++l) {
-      uint32_t* hist = hist0 + (int64_t)l * MGBS_HIST_STRIDE;
-      st = band_advance(st, hist - MGBS_HIST_STRIDE, a.key_bits, false, D);
-      if (st.done) break;  // the same on every block and every rank
-      count_candidates_level(a.cvh, st, D, a.key_bits, a.hash_bits, sh, hist);
+    const uint32_t* win_hist = hist0;
+    uint32_t cut_score = 0xffffffffu;
+    if (!st.done && !band_from_window(st, hist0, win_lo, a.hash_bits, D, cut_score)) {
+      // the window inherited from the previous depth misses the cut: find the cut's coarse score range, put a
+      // window around it and count once more (first depth of a search, or a jump of the scores between depths)
+      uint32_t* histc = hist0 + MGBS_HIST_STRIDE;
+      count_score_window(a.cvh, D, 0u, true, a.hash_bits, sh, histc);
       grid_barrier(a, gen);
       if (peer) {
-        if (blockIdx.x == 0) peer_allreduce_block(a, hist, round * Lb + l);
+        if (blockIdx.x == 0) peer_allreduce_block(a, histc, round * kBandSlots + 1);
         grid_barrier(a, gen);
       }
+      const Cross cc = find_crossing(histc, st.remaining, true);
+      const uint32_t cb = cc.bin < 0 ? 0u : (uint32_t)cc.bin;
+      win_lo = cb * 512u > 767u ? cb * 512u - 767u : 0u;
+      uint32_t* hist2 = histc + MGBS_HIST_STRIDE;
+      count_score_window(a.cvh, D, win_lo, false, a.hash_bits, sh, hist2);
+      grid_barrier(a, gen);
+      if (peer) {
+        if (blockIdx.x == 0) peer_allreduce_block(a, hist2, round * kBandSlots + 2);
+        grid_barrier(a, gen);
+      }
+      win_hist = hist2;
+      if (!band_from_window(st, hist2, win_lo, a.hash_bits, D, cut_score)) {
+        st.result = D;  // cannot happen (the window was placed around the cut); ends the round without a band
+        st.done = 1;
+      }
     }
-    if (!st.done) st = band_advance(st, hist0 + (int64_t)(Lb - 1) * MGBS_HIST_STRIDE, a.key_bits, true, D);
+    if (round == 0) {
+      // score range of everything generated this depth: bounds the keys of the final cut
+      int b_first, b_last;
+      hist_extent(win_hist, b_first, b_last);
+      if (b_first >= 1 && b_last >= b_first && b_last <= MGBS_RADIX_BINS - 2) {
+        score_min = win_lo + (uint32_t)b_first - 1u;
+        score_max = win_lo + (uint32_t)b_last - 1u;
+        range_known = true;
+      }
+      if (cut_score != 0xffffffffu) next_win_lo = cut_score > 1023u ? cut_score - 1023u : 0u;
+      else if (range_known) next_win_lo = (score_min + score_max) / 2u > 1023u ? (score_min + score_max) / 2u - 1023u : 0u;
+      else next_win_lo = win_lo;
+    }
     const uint64_t E = st.result;
     const bool complete = (st.flag & kFlagComplete) != 0u;
     if (lead) {
-      c->band[round][Lb] = st;
+      c->band[round][0] = st;
       c->band_lo[round + 1] = E > D ? E : D;
       if (complete) {
         c->bands_done = 1;
@@ -1496,35 +1657,55 @@ __global__ void __launch_bounds__(kStreamThreads, 2) k_select(StepArgs a, RouteA
     for (int r = rounds_run + 1; r <= R; ++r) c->band_lo[r] = D;
 
   // ---------------- final cut: the key of the beam-th unique entry, by radix select over the table ----------------
-  uint32_t* fin0 = a.hist_base + (int64_t)(R * Lb) * MGBS_HIST_STRIDE;
+  // Every table entry has a score inside [score_min, score_max] and a key below the last band bound, so the select
+  // runs on key - base with only as many bits as that range needs (three 11-bit levels where the whole 44-bit key
+  // would take four); base and bit count derive from summed histograms, so all blocks and ranks agree.
+  uint64_t base = 0;
+  int kb = a.key_bits;
+  if (range_known) {
+    uint64_t top_score = score_max;
+    if (D != ~0ull && a.hash_bits > 0 && (D >> a.hash_bits) < top_score) top_score = D >> a.hash_bits;  // keys < D only
+    if (D != ~0ull && a.hash_bits == 0 && D > 0 && D - 1 < top_score) top_score = D - 1;
+    if (top_score >= score_min) {
+      base = (uint64_t)score_min << a.hash_bits;
+      kb = ceil_log2_u64(top_score - score_min + 1ull) + a.hash_bits;
+      if (kb < 1) kb = 1;
+      if (kb > a.key_bits) { kb = a.key_bits; base = 0; }
+    }
+  }
+  const int Lf = (kb + MGBS_RADIX_BITS - 1) / MGBS_RADIX_BITS;
+  uint32_t* fin0 = a.hist_base + (int64_t)(R * kBandSlots) * MGBS_HIST_STRIDE;
   a.hist = fin0;
   publish_stats(a);
   MgbsRadix fs = radix_zero();
-  count_table_level(a, fs, sh, fin0);
+  count_table_level(a, fs, base, kb, sh, fin0);
   grid_barrier(a, gen);
   if (peer) {
-    if (blockIdx.x == 0) peer_allreduce_block(a, fin0, R * Lb);
+    if (blockIdx.x == 0) peer_allreduce_block(a, fin0, R * kBandSlots);
     grid_barrier(a, gen);
   }
   fs = final_initial(a, fin0);
   for (int l = 1; l < Lf; ++l) {
     uint32_t* hist = fin0 + (int64_t)l * MGBS_HIST_STRIDE;
-    fs = final_advance(fs, hist - MGBS_HIST_STRIDE, a.key_bits, a.select_mode);
+    fs = final_advance(fs, hist - MGBS_HIST_STRIDE, kb, a.select_mode);
     if (fs.done) break;
-    count_table_level(a, fs, sh, hist);
+    count_table_level(a, fs, base, kb, sh, hist);
     grid_barrier(a, gen);
     if (peer) {
-      if (blockIdx.x == 0) peer_allreduce_block(a, hist, R * Lb + l);
+      if (blockIdx.x == 0) peer_allreduce_block(a, hist, R * kBandSlots + l);
       grid_barrier(a, gen);
     }
   }
-  if (!fs.done) fs = final_advance(fs, fin0 + (int64_t)(Lf - 1) * MGBS_HIST_STRIDE, a.key_bits, a.select_mode);
+  if (!fs.done) fs = final_advance(fs, fin0 + (int64_t)(Lf - 1) * MGBS_HIST_STRIDE, kb, a.select_mode);
   if (lead) {
-    c->fin[Lf] = fs;
-    c->threshold_key = fs.result;
+    c->fin[0] = fs;
+    c->fin[1].prefix = base;
+    c->fin[1].bits_done = (uint32_t)kb;
+    c->threshold_key = fs.result == ~0ull ? ~0ull : base + fs.result;
+    c->win_lo = next_win_lo;
   }
   unsigned long long* seg = a.tie_buf + (int64_t)a.rank * kTieSegWords;
-  emit_table_body(a, fs, seg);
+  emit_table_body(a, fs, base, seg);
   grid_barrier(a, gen);
   if (blockIdx.x != 0) return;
   // ---------------- one block: ties at the cut key, then close the depth ----------------
@@ -1578,7 +1759,7 @@ SymLayout sym_layout(const MgbsConfig& c, int band_levels_effective) {
   }
   for (int p = 0; p < 2; ++p) { L.frontier[p] = off; off += align256(c.frontier_cap * (int64_t)c.state_stride); }
   L.route_flag = off; off += align256(W * 4);
-  L.slots = c.band_rounds * band_levels_effective + MGBS_MAX_LEVELS;
+  L.slots = c.band_rounds * (band_levels_effective < 3 ? 3 : band_levels_effective) + MGBS_MAX_LEVELS;
   L.hx = off;         off += align256((int64_t)L.slots * W * MGBS_HIST_STRIDE * 4);
   L.hflag = off;      off += align256((int64_t)L.slots * W * 4);
   L.tie = off;        off += align256(W * (int64_t)kTieSegWords * 8);

@@ -307,13 +307,19 @@ def test_logical_limits_clamp_the_step():
     want = bo.depth_step([frontier[:100]], pz.generators, pz.solved, bo.hamming_scorer(pz.solved), 2048)
     assert st["counters"][2] == 100 * pz.fanout and st["status_bits"] == 0
     assert np.array_equal(bo.sorted_rows(engine.frontier()), bo.sorted_rows(want.states))
-    # next limit below what the step keeps: rows beyond it are dropped and the drop is reported
+    # next limit below what the step would keep: the pool, the table and the next frontier shrink with it, the
+    # frontier stays within the limit and the truncation is reported
     engine.clear_logical_limits()
     engine.set_next_limit(300)
     engine.load_frontier(frontier)
     engine.step()
     st = engine.status()
-    assert st["current_size"] == 300 and st["status_bits"] & _lib.ST_FRONTIER_OVERFLOW
+    assert 0 < st["current_size"] <= 300
+    assert st["status_bits"] & (_lib.ST_FRONTIER_OVERFLOW | _lib.ST_BAND_STALL | _lib.ST_ROUNDS_EXHAUSTED)
+    # and the rows it kept are the best ones: a prefix of the full step's (score, hash) order
+    full = bo.depth_step([frontier], pz.generators, pz.solved, bo.hamming_scorer(pz.solved), 2048)
+    kept = {bytes(r) for r in engine.frontier()}
+    assert kept <= {bytes(r) for r in full.states}
     # cleared: the full step again
     engine.clear_logical_limits()
     check_step(engine, pz, frontier, 2048)
