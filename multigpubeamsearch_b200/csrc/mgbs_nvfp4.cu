@@ -1,0 +1,292 @@
+// NVFP4 path of the value MLP: second layer + scalar head with 4-bit operands and block scales.
+//
+// NVFP4 = E2M1 elements (1 sign, 2 exponent, 1 mantissa bit; magnitudes 0, 0.5, 1, 1.5, 2, 3, 4, 6), one unsigned
+// E4M3 scale factor per block of 16 consecutive K elements, and one float32 scale per tensor:
+//     x[k] ~ e2m1[k] * sf[k / 16] * tensor_scale.
+// The tensor core multiplies the block scales in (tcgen05.mma kind::mxf4nvf4, block16): one instruction covers
+// 128 x 256 x 64 and reads, besides the two shared-memory operands, 4 scale factors per A row and per B row from
+// tensor memory.  The two tensor scales are folded into the epilogue's per-column factor.
+//
+// Layouts.  Elements: two per byte, even K in the low nibble, row-major [rows, K / 2] bytes; a 128-byte row of a
+// TMA box (128-byte swizzle) therefore holds one K-block of 256 elements = four MMA steps.  Scale factors: the
+// tensor core wants, per MMA step and per group of 128 rows, a 512-byte chunk in which row r = r0 + 32 * r1 keeps
+// its four factors at byte r0 * 16 + r1 * 4 (32 "lanes" of 16 bytes: what tcgen05.cp 32x128b.warpx4 copies from
+// shared into tensor memory, lane r0, 32-bit column r1, replicated over the four lane quadrants).  Global memory
+// holds them in the order the kernel consumes them, so that one bulk copy per pipeline stage brings a K-block's
+// factors: A: [row tile of 128][K-block][step 0..3][512 B]; B: [column chunk of 256][K-block][step][half 0..1][512 B].
+//
+// First-layer activations are produced in e4m3 by the fused layer-1 kernel and re-quantised to NVFP4 by
+// k_quant_h1_nvfp4 (block maximum -> E4M3 scale, elements -> E2M1, written in the layouts above).
+//
+// Tensor memory: one accumulator of 256 columns (the two-buffer scheme of the 8- and 16-bit kernels would need all
+// 512 columns and leave none for the factors), then per pipeline stage 16 columns for A's and 32 for B's factors.
+// With one accumulator the epilogue cannot overlap the next tile's MMAs, so it is spread over eight warps (two
+// per lane quadrant, 128 columns each).
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "mgbs.h"
+#include "mgbs_nvfp4.cuh"
+#include "mgbs_tc.cuh"
+
+namespace mgbs {
+
+constexpr int F4_BK = 256;                   // elements per 128-byte K-block row
+constexpr int F4_STEPS = 4;                  // MMA steps (64 elements) per K-block
+constexpr int F4_SFA_BYTES = F4_STEPS * 512;             // 2 KB per stage
+constexpr int F4_SFB_BYTES = F4_STEPS * 2 * 512;         // 4 KB per stage
+constexpr int F4_STAGE_BYTES = A_BYTES + B_BYTES + F4_SFA_BYTES + F4_SFB_BYTES;  // 54 KB
+constexpr int F4_STAGES = 4;
+constexpr int F4_THREADS = 320;              // TMA warp, MMA warp, eight epilogue warps
+constexpr int F4_SMEM = F4_STAGES * F4_STAGE_BYTES + 1024 + 1024;
+constexpr uint32_t F4_SF_COLS = 48;          // tensor-memory columns of one stage's factors: 16 (A) + 32 (B)
+constexpr uint32_t F4_SF_BASE = BN;          // factors start after the accumulator
+
+// Instruction descriptor of kind::mxf4nvf4: A and B format E2M1 (code 1, bits 7-9 / 10-12), both K-major, N >> 3 in
+// bits 17-22, scale format UE4M3 (bit 23 = 0), M >> 4 in bits 24-28, scale-factor ids 0, K = 64 (bit 31 = 0).
+constexpr uint32_t kIdescNvfp4 = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void tc_mma_nvfp4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t sfa_tmem,
+                                             uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(kIdescNvfp4), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+
+// Shared-memory descriptor of one 512-byte scale-factor chunk: 32 rows of 16 bytes, no swizzle, 8-row groups 128
+// bytes apart (stride byte offset 128 >> 4 = 8), descriptor version 1.
+__device__ __forceinline__ uint64_t make_desc_sf(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3fffu) | (8ull << 32) | (1ull << 46);
+}
+
+// 32 lanes x 128 bits from shared memory into 4 tensor-memory columns, replicated into all four lane quadrants
+__device__ __forceinline__ void tc_cp_sf(uint32_t dst_tmem, uint64_t src_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(dst_tmem), "l"(src_desc) : "memory");
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// q[row] (+)= sum_n relu(acc[row, n] * col_scale[n] + bias[n]) * w_out[n],   acc = (A * sfA) (B * sfB)^T
+__global__ void __launch_bounds__(F4_THREADS, 1)
+k_mlp_head_nvfp4(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Nvfp4HeadArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + F4_STAGES * F4_STAGE_BYTES);
+  // bars[0..S) full, [S..2S) empty, [2S] tmem_full, [2S+1] tmem_empty, [2S+2] drain, then the tmem base word
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * F4_STAGES + 3);
+  float* partial = reinterpret_cast<float*>(bars + 2 * F4_STAGES + 4);  // [128] row sums of the second column half
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (F4_STAGES + s); };
+  const uint32_t tfull_bar = bar0 + 8u * (2 * F4_STAGES);
+  const uint32_t tempty_bar = bar0 + 8u * (2 * F4_STAGES + 1);
+  const uint32_t drain_bar = bar0 + 8u * (2 * F4_STAGES + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  int64_t rows = (int64_t)(*g.count_dev);
+  if (rows > g.row_limit) rows = g.row_limit;
+  if (rows < 0) rows = 0;
+  const int num_mtiles = (int)((rows + BM - 1) / BM);
+  const int n_chunks = g.n_total / BN;
+  const int k_blocks = g.k_total / F4_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < F4_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    mbar_init(tfull_bar, 1);
+    mbar_init(tempty_bar, 8);
+    mbar_init(drain_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_base_slot);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+        for (int nc = 0; nc < n_chunks && ok; ++nc) {
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait(empty_bar(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+            const uint32_t sa = smem_u32(smem + stage * F4_STAGE_BYTES);
+            mbar_expect_tx(full_bar(stage), F4_STAGE_BYTES);
+            tma_load_2d(sa, &tmA, kb * 128, mt * BM, full_bar(stage));               // x in bytes: 128 per K-block
+            tma_load_2d(sa + A_BYTES, &tmB, kb * 128, nc * BN, full_bar(stage));
+            bulk_load(sa + A_BYTES + B_BYTES, g.sfa + ((int64_t)mt * k_blocks + kb) * F4_SFA_BYTES, F4_SFA_BYTES, full_bar(stage));
+            bulk_load(sa + A_BYTES + B_BYTES + F4_SFA_BYTES, g.sfb + ((int64_t)nc * k_blocks + kb) * F4_SFB_BYTES, F4_SFB_BYTES,
+                      full_bar(stage));
+            if (++stage == F4_STAGES) { stage = 0; phase ^= 1u; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_it = 0;
+      bool ok = true;
+      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+        for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
+          if (!mbar_wait(tempty_bar, (acc_it & 1u) ^ 1u, g.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base;
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + stage * F4_STAGE_BYTES);
+            const uint32_t sf_s = sa + A_BYTES + B_BYTES;
+            const uint32_t sf_t = tmem_base + F4_SF_BASE + (uint32_t)stage * F4_SF_COLS;
+            // this stage's scale factors: 4 chunks for A (4 columns each), 8 for B
+#pragma unroll
+            for (int k = 0; k < F4_STEPS; ++k) {
+              tc_cp_sf(sf_t + 4u * k, make_desc_sf(sf_s + 512u * k));
+              tc_cp_sf(sf_t + 16u + 8u * k, make_desc_sf(sf_s + F4_SFA_BYTES + 1024u * k));
+              tc_cp_sf(sf_t + 16u + 8u * k + 4u, make_desc_sf(sf_s + F4_SFA_BYTES + 1024u * k + 512u));
+            }
+            const uint64_t adesc = make_desc_sw128(sa);
+            const uint64_t bdesc = make_desc_sw128(sa + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < F4_STEPS; ++k) {
+              // one step = 64 elements = 32 bytes inside the swizzle row: +2 in (address >> 4)
+              tc_mma_nvfp4(d_tmem, adesc + 2u * k, bdesc + 2u * k, sf_t + 4u * k, sf_t + 16u + 8u * k, (kb | k) != 0 ? 1u : 0u);
+            }
+            tc_commit(empty_bar(stage));
+            if (++stage == F4_STAGES) { stage = 0; phase ^= 1u; }
+          }
+          if (ok) tc_commit(tfull_bar);
+        }
+      }
+      tc_commit(drain_bar);
+      mbar_wait(drain_bar, 0, g.err, ERR_WAIT_DRAIN);
+    }
+  } else {
+    const int quad = warp & 3;            // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;     // which 128 accumulator columns
+    uint32_t acc_it = 0;
+    bool ok = true;
+    for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+      const int r = quad * 32 + lane;
+      const int64_t row = (int64_t)mt * BM + r;
+      const bool row_ok = row < rows;
+      float rowsum = 0.f;
+      for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
+        if (!mbar_wait(tfull_bar, acc_it & 1u, g.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)half * 128u;
+#pragma unroll 1
+        for (int c0 = 0; c0 < 128; c0 += 32) {
+          uint32_t v[32];
+          tc_ld32(taddr + c0, v);
+          tc_wait_ld();
+          const int n0 = nc * BN + half * 128 + c0;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float x = fmaxf(fmaf(__uint_as_float(v[j]), __ldg(g.col_scale + n0 + j), __ldg(g.bias + n0 + j)), 0.f);
+            rowsum = fmaf(x, __ldg(g.w_out + n0 + j), rowsum);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar);
+      }
+      // the two column halves of a row meet in shared memory (fixed order: deterministic sums)
+      if (half == 1) partial[r] = rowsum;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (half == 0 && row_ok && ok) {
+        const float total = rowsum + partial[r];
+        if (g.accumulate_q) g.out_q[row] += total;
+        else g.out_q[row] = total;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// e4m3 activations [rows, K] (value = e4m3 * in_scale) -> NVFP4: packed E2M1 [rows, K / 2] and E4M3 block factors in the
+// layout of the A operand above.  One thread per (row, block of 16).  factor = e4m3_rn(blockmax / 6 * inv_global),
+// element = e2m1_rn(x / (factor / inv_global)); a zero block keeps factor 0 and elements 0.
+__global__ void __launch_bounds__(256)
+k_quant_h1_nvfp4(const uint8_t* __restrict__ h1_e4m3, const uint32_t* count_dev, int64_t row_limit, int K, float in_scale,
+                 float inv_global, uint8_t* __restrict__ out_fp4, uint8_t* __restrict__ out_sf) {
+  int64_t rows = (int64_t)(*count_dev);
+  if (rows > row_limit) rows = row_limit;
+  const int blocks_per_row = K / 16;
+  const int k_blocks = K / F4_BK;
+  const int64_t total = rows * blocks_per_row;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / blocks_per_row;
+    const int blk = (int)(i - row * blocks_per_row);
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(h1_e4m3 + row * K + blk * 16));
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float x[16];
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const __nv_fp8_storage_t b = (__nv_fp8_storage_t)((w[j >> 2] >> (8 * (j & 3))) & 0xffu);
+      const __half_raw hr = __nv_cvt_fp8_to_halfraw(b, __NV_E4M3);
+      x[j] = __half2float(__half(hr)) * in_scale;
+      amax = fmaxf(amax, fabsf(x[j]));
+    }
+    const __nv_fp8_storage_t sf8 = __nv_cvt_float_to_fp8(amax * (1.f / 6.f) * inv_global, __NV_SATFINITE, __NV_E4M3);
+    const float sf = __half2float(__half(__nv_cvt_fp8_to_halfraw(sf8, __NV_E4M3)));
+    const float inv = sf > 0.f ? inv_global / sf : 0.f;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t p0 = __nv_cvt_float2_to_fp4x2(make_float2(x[2 * j] * inv, x[2 * j + 1] * inv), __NV_E2M1, cudaRoundNearest);
+      if (j < 4) lo |= (p0 & 0xffu) << (8 * j);
+      else hi |= (p0 & 0xffu) << (8 * (j - 4));
+    }
+    *reinterpret_cast<uint2*>(out_fp4 + row * (K / 2) + blk * 8) = make_uint2(lo, hi);
+    const int64_t mt = row >> 7;
+    const int r = (int)(row & 127);
+    const int col = blk * 16;
+    const int kb = col / F4_BK, step = (col % F4_BK) / 64, j4 = (col % 64) / 16;
+    out_sf[((mt * k_blocks + kb) * F4_STEPS + step) * 512 + (r & 31) * 16 + (r >> 5) * 4 + j4] = (uint8_t)sf8;
+  }
+}
+
+int nvfp4_head_smem() { return F4_SMEM; }
+
+int nvfp4_prepare() {
+  return (int)cudaFuncSetAttribute(k_mlp_head_nvfp4, cudaFuncAttributeMaxDynamicSharedMemorySize, F4_SMEM);
+}
+
+int launch_quant_h1_nvfp4(const uint8_t* h1_e4m3, const uint32_t* count_dev, int64_t row_limit, int K, float in_scale,
+                          float inv_global, uint8_t* out_fp4, uint8_t* out_sf, int sms, cudaStream_t st) {
+  if (K % F4_BK != 0) return MGBS_ERR_UNSUPPORTED;
+  k_quant_h1_nvfp4<<<sms * 8, 256, 0, st>>>(h1_e4m3, count_dev, row_limit, K, in_scale, inv_global, out_fp4, out_sf);
+  return (int)cudaGetLastError();
+}
+
+int launch_head_nvfp4(const CUtensorMap& tmA, const CUtensorMap& tmB, const Nvfp4HeadArgs& g, int sms, cudaStream_t st) {
+  if (g.k_total % F4_BK != 0 || g.n_total % BN != 0) return MGBS_ERR_UNSUPPORTED;
+  k_mlp_head_nvfp4<<<sms, F4_THREADS, F4_SMEM, st>>>(tmA, tmB, g);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace mgbs

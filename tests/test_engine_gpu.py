@@ -335,7 +335,8 @@ def test_depth_loop_halts_on_the_device_and_mirror_matches_control_block():
     solved state turned up must not change anything (it halts on the device)."""
     pz = puzzles.puzzle54()
     engine = make_engine(pz, global_beam_width=2048, max_depth=16)
-    start = be.make_shallow_scramble(pz, [3, 7, 1, 9])
+    start = be.make_shallow_scramble(pz, [3, 7, 2, 10, 0])  # no move undoes its predecessor
+    assert not np.array_equal(start, pz.solved)
     for graph in (True, False):
         engine.enable_cuda_graphs(graph)
         res = be.run_one_search(engine, start, 12)
