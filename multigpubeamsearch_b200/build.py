@@ -18,8 +18,8 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 ROOT = PKG.parent
 LIB = PKG / "libmgbs_b200.so"
-SOURCES = ["mgbs_step.cu", "mgbs_engine.cu", "mgbs_scorer.cu", "mgbs_transformer.cu"]
-HEADERS = ["mgbs_device.cuh", "mgbs_internal.cuh", "mgbs_tc.cuh"]
+SOURCES = ["mgbs_step.cu", "mgbs_engine.cu", "mgbs_scorer.cu", "mgbs_transformer.cu", "mgbs_nvfp4.cu"]
+HEADERS = ["mgbs_device.cuh", "mgbs_internal.cuh", "mgbs_tc.cuh", "mgbs_nvfp4.cuh"]
 
 
 def _nccl_include() -> str:

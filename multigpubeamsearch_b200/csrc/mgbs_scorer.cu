@@ -21,6 +21,7 @@
 #include <new>
 
 #include "mgbs.h"
+#include "mgbs_nvfp4.cuh"
 #include "mgbs_tc.cuh"
 
 namespace mgbs {
@@ -880,6 +881,7 @@ struct MgbsMlp {
   CUtensorMap tm_w1[MGBS_MAX_MODELS], tm_w2[MGBS_MAX_MODELS];
   CUtensorMap tm_w2h[MGBS_MAX_MODELS];  // W2 in boxes of 128 rows: the half of a chunk one CTA of a pair loads
   CUtensorMap tm_w1h[MGBS_MAX_MODELS];  // W1 likewise
+  CUtensorMap tm_h1q, tm_w2q[MGBS_MAX_MODELS];  // NVFP4: packed activations and weights as byte tensors
   int pair_clusters = 0;                // CTA pairs that can be resident at once (0: pairs unavailable)
   int l1_pair_clusters = 0;             // the same for the layer-1 kernel
   bool head_pair = true;
@@ -890,6 +892,12 @@ struct MgbsMlp {
 
 using mgbs::make_map;
 using mgbs::make_map_bf16;
+
+#define MGBS_SC_TRY(expr)       \
+  do {                          \
+    int _e = (int)(expr);       \
+    if (_e != 0) return _e;     \
+  } while (0)
 
 extern "C" {
 
@@ -902,8 +910,10 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
   if (c.hidden < mgbs::BN || c.hidden % mgbs::BN != 0) return MGBS_ERR_UNSUPPORTED;
   if (c.num_models < 1 || c.num_models > MGBS_MAX_MODELS || c.max_rows < 1) return MGBS_ERR_ARG;
   const int k1 = c.state_len * c.num_values;
-  if (c.dtype != 0 && c.dtype != 1) return MGBS_ERR_ARG;
-  const int f8 = c.dtype == 1;
+  if (c.dtype != 0 && c.dtype != 1 && c.dtype != 2) return MGBS_ERR_ARG;
+  const int f4 = c.dtype == 2;
+  const int f8 = c.dtype == 1 || f4;  // NVFP4 runs layer 1 on the e4m3 path
+  if (f4 && (!c.h1q || !c.sf_h1 || !(c.act4_inv_global > 0.f))) return MGBS_ERR_ARG;
   const int kblk = f8 ? mgbs::BK8 : mgbs::BK;
   const int eb = f8 ? 1 : 2;
   const int k1_pad = (k1 + kblk - 1) / kblk * kblk;
@@ -929,9 +939,16 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
     if (!rc && f8 && (!c.s1[i] || !c.s2[i])) rc = MGBS_ERR_ARG;
     if (!rc) rc = make_map(&m->tm_w1[i], c.w1[i], (uint64_t)c.hidden, (uint64_t)k1_pad, mgbs::BN, eb);
     if (!rc) rc = make_map(&m->tm_w1h[i], c.w1[i], (uint64_t)c.hidden, (uint64_t)k1_pad, mgbs::BN / 2, eb);
+    if (f4) {
+      if (!rc && !c.sf_w2[i]) rc = MGBS_ERR_ARG;
+      if (!rc) rc = make_map(&m->tm_w2q[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden / 2, mgbs::BN, 1);
+      continue;
+    }
     if (!rc) rc = make_map(&m->tm_w2[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden, mgbs::BN, eb);
     if (!rc) rc = make_map(&m->tm_w2h[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden, mgbs::BN / 2, eb);
   }
+  if (f4 && !rc) rc = make_map(&m->tm_h1q, c.h1q, rows_pad, (uint64_t)c.hidden / 2, mgbs::BM, 1);
+  if (f4 && !rc) rc = mgbs::nvfp4_prepare();
   if (f8) m->fused_l1 = true;
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<1, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
@@ -993,7 +1010,7 @@ int mgbs_mlp_set_head_mode(MgbsMlp* m, int32_t pair) {
 
 int mgbs_mlp_set_l1_mode(MgbsMlp* m, int32_t fused) {
   if (!m) return MGBS_ERR_ARG;
-  if (m->cfg.dtype == 1 && !fused) return MGBS_ERR_UNSUPPORTED;  // the e4m3 path has no separate one-hot matrix
+  if (m->cfg.dtype != 0 && !fused) return MGBS_ERR_UNSUPPORTED;  // the e4m3 path has no separate one-hot matrix
   m->fused_l1 = fused != 0;
   return 0;
 }
@@ -1030,6 +1047,8 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
   const int64_t rows_cap = c.max_rows;
   const int grid_gemm = m->sms;
   const bool prof = m->profile && c.num_models == 1;
+  const bool f4 = c.dtype == 2;
+  const bool e4 = c.dtype == 1 || f4;  // layer 1 on the e4m3 path
   if (prof) cudaEventRecord(m->ev[0], st);
   if (!m->fused_l1) {
     const int64_t chunks = rows_cap * (m->k1_pad / 8);
@@ -1065,14 +1084,14 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
       l.col_scale = c.s1[i];
       l.out_inv_scale = c.act_inv_scale;
       l.err = c.err;
-      const bool resident = m->k1_pad / (c.dtype == 1 ? BK8 : BK) <= L1_A_STAGES;
+      const bool resident = m->k1_pad / (e4 ? BK8 : BK) <= L1_A_STAGES;
       // bf16 builds six K-blocks per tile: eight producer warps are needed even with the resident tile (measured:
       // 0.69-0.76 ms with 4 epilogue + 8 producer warps against 0.82 ms with 8 + 4 on the 786 432-row case);
       // e4m3 builds three and gains from the wider epilogue
       // CTA pairs for layer 1 only where they were measured faster: e4m3 operands with the resident tile (1.09 ms
       // against 1.11 ms for the whole scorer on 786 432 rows).  With bf16 the pair was 0.05 ms slower than single
       // CTAs: the even CTA's MMAs then wait for the slower of two sets of one-hot producers.
-      if (m->head_pair && m->l1_pair_clusters > 0 && c.dtype == 1 && resident) {
+      if (m->head_pair && m->l1_pair_clusters > 0 && e4 && resident) {
         cudaLaunchConfig_t lc;
         memset(&lc, 0, sizeof(lc));
         lc.gridDim = dim3(2 * m->l1_pair_clusters);
@@ -1086,9 +1105,9 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
         lc.numAttrs = 1;
         cudaError_t le = cudaLaunchKernelEx(&lc, k_mlp_l1<1, 8, 1>, m->tm_w1h[i], m->tm_h1, l);
         if (le != cudaSuccess) return (int)le;
-      } else if (c.dtype == 1 && resident) {
+      } else if (e4 && resident) {
         k_mlp_l1<1, 8, 0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
-      } else if (c.dtype == 1) {
+      } else if (e4) {
         k_mlp_l1<1, 4, 0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
       } else {
         k_mlp_l1<0, 4, 0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
@@ -1104,7 +1123,26 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
     g.out_q = c.q;
     g.accumulate_q = i > 0 ? 1 : 0;
     g.col_scale = c.s2[i];
-    if (m->head_pair && m->pair_clusters > 0) {
+    if (f4) {
+      // e4m3 activations -> NVFP4 (packed elements + block factors), then the block-scaled 4-bit GEMM + head
+      MGBS_SC_TRY(launch_quant_h1_nvfp4(reinterpret_cast<const uint8_t*>(c.h1), count_dev, rows_cap, c.hidden,
+                                        1.f / c.act_inv_scale, c.act4_inv_global, reinterpret_cast<uint8_t*>(c.h1q),
+                                        c.sf_h1, m->sms, st));
+      Nvfp4HeadArgs h;
+      h.count_dev = count_dev;
+      h.row_limit = rows_cap;
+      h.n_total = c.hidden;
+      h.k_total = c.hidden;
+      h.sfa = c.sf_h1;
+      h.sfb = c.sf_w2[i];
+      h.bias = c.b2[i];
+      h.col_scale = c.s2[i];
+      h.w_out = c.w3[i];
+      h.out_q = c.q;
+      h.accumulate_q = i > 0 ? 1 : 0;
+      h.err = c.err;
+      MGBS_SC_TRY(launch_head_nvfp4(m->tm_h1q, m->tm_w2q[i], h, m->sms, st));
+    } else if (m->head_pair && m->pair_clusters > 0) {
       cudaLaunchConfig_t lc;
       memset(&lc, 0, sizeof(lc));
       lc.gridDim = dim3(2 * m->pair_clusters);

@@ -30,7 +30,44 @@ class MgbsMlpConfig(C.Structure):
         ("b2", C.c_void_p * MAX_MODELS), ("w3", C.c_void_p * MAX_MODELS),
         ("s1", C.c_void_p * MAX_MODELS), ("s2", C.c_void_p * MAX_MODELS),
         ("dtype", C.c_int32), ("act_inv_scale", C.c_float),
+        ("h1q", C.c_void_p), ("sf_h1", C.c_void_p), ("sf_w2", C.c_void_p * MAX_MODELS),
+        ("act4_inv_global", C.c_float), ("pad0", C.c_int32),
     ]
+
+
+E2M1_MIDPOINTS = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
+
+
+def e2m1_codes(x: np.ndarray) -> np.ndarray:
+    """4-bit E2M1 codes (sign in bit 3) of x rounded to the nearest representable value, ties to the even code."""
+    a = np.abs(np.asarray(x, dtype=np.float64))
+    code = np.searchsorted(E2M1_MIDPOINTS, a, side="left")
+    tie = (code < 7) & (a == E2M1_MIDPOINTS[np.minimum(code, 6)])
+    code = np.where(tie & (code % 2 == 1), code + 1, code).astype(np.uint8)
+    return code | (np.signbit(x).astype(np.uint8) << 3)
+
+
+def nvfp4_quantize_weights(w: np.ndarray):
+    """NVFP4 form of a weight matrix [N, K] (N a multiple of 256, K of 256) for the block-scaled tensor-core path:
+    (packed E2M1 bytes [N, K/2] with even K in the low nibble, block factors as bytes in the kernel's tile order
+    [N/256][K/256][4 steps][2 halves][512], tensor scale)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    n, k = w.shape
+    if n % 256 or k % 256:
+        raise RuntimeError("NVFP4 weights need dimensions that are multiples of 256")
+    tscale = np.float32(max(float(np.abs(w).max()), 1e-30) / (6.0 * 448.0))
+    blocks = w.reshape(n, k // 16, 16)
+    amax = np.abs(blocks).max(axis=2)
+    sf8 = torch.from_numpy((amax / np.float32(6.0) / tscale).astype(np.float32)).to(torch.float8_e4m3fn)
+    sf = sf8.to(torch.float32).numpy()
+    step = (sf * tscale)[:, :, None]
+    scaled = np.where(step > 0, blocks / np.where(step > 0, step, 1.0), 0.0)
+    codes = e2m1_codes(scaled).reshape(n, k)
+    packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).astype(np.uint8)
+    # factors: row r of chunk c, K-block kb, step st, block j -> tile (c, kb, st, half = r'//128) byte (r%32)*16 + ((r%128)//32)*4 + j
+    sfb = sf8.view(torch.uint8).numpy().reshape(n // 256, 2, 4, 32, k // 256, 4, 4)  # [c, half, r1, r0, kb, st, j]
+    sfb = np.ascontiguousarray(sfb.transpose(0, 4, 5, 1, 3, 2, 6))                    # [c, kb, st, half, r0, r1, j]
+    return np.ascontiguousarray(packed), sfb.reshape(-1).copy(), float(tscale)
 
 
 class MgbsMlpNoAllocArgs(C.Structure):
@@ -87,9 +124,12 @@ class MLPValueScorer:
         dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         hidden = int(weights[0]["w1"].shape[0])
         k1 = state_len * num_values
-        if dtype not in ("bf16", "fp8"):
-            raise RuntimeError("dtype must be 'bf16' or 'fp8'")
-        f8 = dtype == "fp8"
+        if dtype not in ("bf16", "fp8", "nvfp4"):
+            raise RuntimeError("dtype must be 'bf16', 'fp8' or 'nvfp4'")
+        f4 = dtype == "nvfp4"
+        f8 = dtype == "fp8" or f4  # NVFP4 runs the first layer on the e4m3 path
+        if f4 and hidden % 256:
+            raise RuntimeError("NVFP4 needs a hidden width that is a multiple of 256")
         self.dtype = dtype
         kblk = 128 if f8 else 64
         k1_pad = (k1 + kblk - 1) // kblk * kblk
@@ -97,7 +137,7 @@ class MLPValueScorer:
         self.state_len, self.state_stride, self.num_values = state_len, state_stride, num_values
         self.hidden, self.k1_pad, self.max_rows = hidden, k1_pad, int(max_rows)
         self.score_offset = float(score_offset)
-        self.t: Dict[str, List[torch.Tensor]] = {k: [] for k in ("w1", "b1", "w2", "b2", "w3", "s1", "s2")}
+        self.t: Dict[str, List[torch.Tensor]] = {k: [] for k in ("w1", "b1", "w2", "b2", "w3", "s1", "s2", "sf_w2")}
         cfg = MgbsMlpConfig()
         act_bound = 0.0
         if f8:
@@ -117,9 +157,17 @@ class MLPValueScorer:
                 w1 = torch.zeros((hidden, k1_pad), dtype=torch.uint8, device=dev)
                 w1[:, :k1] = (w1_f / s1[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
                 self.t["w1"].append(w1)
-                self.t["w2"].append((w2_f / s2w[:, None]).to(torch.float8_e4m3fn).view(torch.uint8).contiguous())
                 self.t["s1"].append(s1.contiguous())
-                self.t["s2"].append((s2w * act_scale).contiguous())
+                if f4:
+                    packed, sfb, w2_tscale = nvfp4_quantize_weights(np.asarray(w["w2"], dtype=np.float32))
+                    self.t["w2"].append(torch.from_numpy(packed).to(dev))
+                    self.t["sf_w2"].append(torch.from_numpy(sfb).to(dev))
+                    act4_scale = act_bound / (6.0 * 448.0)
+                    self.t["s2"].append(torch.full((hidden,), w2_tscale * act4_scale, dtype=torch.float32, device=dev))
+                    cfg.sf_w2[i] = self.t["sf_w2"][i].data_ptr()
+                else:
+                    self.t["w2"].append((w2_f / s2w[:, None]).to(torch.float8_e4m3fn).view(torch.uint8).contiguous())
+                    self.t["s2"].append((s2w * act_scale).contiguous())
                 cfg.s1[i] = self.t["s1"][i].data_ptr()
                 cfg.s2[i] = self.t["s2"][i].data_ptr()
             else:
@@ -144,9 +192,16 @@ class MLPValueScorer:
         cfg.score_offset = float(score_offset)
         cfg.x = None if f8 else self.x.data_ptr()
         cfg.h1, cfg.q, cfg.err = self.h1.data_ptr(), self.q.data_ptr(), self.err.data_ptr()
-        cfg.dtype = 1 if f8 else 0
+        cfg.dtype = 2 if f4 else (1 if f8 else 0)
         cfg.act_inv_scale = 1.0 / act_scale
         self.act_scale = act_scale
+        self.act_bound = act_bound
+        if f4:
+            # packed 4-bit activations and their block factors (tiles of 128 rows x 256 columns, 4 x 512 bytes each)
+            self.h1q = torch.zeros((rows_pad, hidden // 2), dtype=torch.uint8, device=dev)
+            self.sf_h1 = torch.zeros((rows_pad // 128 * (hidden // 256) * 4 * 512,), dtype=torch.uint8, device=dev)
+            cfg.h1q, cfg.sf_h1 = self.h1q.data_ptr(), self.sf_h1.data_ptr()
+            cfg.act4_inv_global = (6.0 * 448.0) / act_bound
         self._cfg = cfg
         h = C.c_void_p()
         _lib.check(self.lib.mgbs_mlp_create(C.byref(cfg), C.byref(h)), "MLPValueScorer")

@@ -172,6 +172,48 @@ def test_fp8_scorer_within_tolerance(name, count, models):
     assert np.array_equal(keys.cpu().numpy()[perm], keys2.cpu().numpy())
 
 
+@pytest.mark.parametrize("name,count,models,wscale", [("rand54", 20000, 1, 1.0), ("rand96", 5000, 2, 1.0),
+                                                      ("rand54", 77, 1, 1.0), ("rand54", 3000, 1, 6.0)])
+def test_nvfp4_scorer_within_tolerance(name, count, models, wscale):
+    """Second layer on the block-scaled 4-bit tensor-core path (E2M1 elements, E4M3 factor per 16, float32 tensor
+    scale; first layer e4m3).  Stated bound: max-abs error of the network output <= 5e-2 against the float32 network.
+    The random-init network's outputs are themselves only a few hundredths wide, so that bound alone would pass a
+    wrong operand layout; the device is therefore also held to 2e-3 against a float32 evaluation of the SAME rounded
+    operands (oracle.mlp_forward_nvfp4_model), and one case scales the weights up so that outputs are of order one."""
+    pz = puzzles.by_name(name)
+    stride = (pz.state_len + 15) // 16 * 16
+    ws = [puzzles.mlp_weights(pz.state_len * pz.num_values, 1024, model_idx=20 + i) for i in range(models)]
+    rng = np.random.default_rng(5)
+    for w in ws:
+        w["w1"] = (w["w1"] * wscale).astype(np.float32)
+        w["w2"] = (w["w2"] * wscale).astype(np.float32)
+        w["b1"] = (rng.standard_normal(1024) * 0.05).astype(np.float32)
+        w["b2"] = (rng.standard_normal(1024) * 0.05).astype(np.float32)
+        w["b3"] = np.float32(0.1)
+    sc = scorers.MLPValueScorer(ws, pz.state_len, stride, pz.num_values, max_rows=count, dtype="nvfp4")
+    rows = children_of(pz, count, seed=count + 2)
+    dev = torch.from_numpy(padded(rows, stride)).cuda()
+    keys = sc.score(dev)
+    torch.cuda.synchronize()
+    assert sc.error_code() == 0
+    q_dev = (sc.last_q(count).cpu().numpy() + sum(float(w["b3"]) for w in ws)) / models
+    q_model = bo.mlp_forward_nvfp4_model(rows, ws, pz.num_values, sc.act_bound)
+    q_ref = bo.mlp_forward(rows, ws, pz.num_values)
+    spread = float(q_ref.max() - q_ref.min())
+    err_model = np.abs(q_dev - q_model).max()
+    assert err_model <= 2e-3 * max(1.0, wscale ** 2), (err_model, spread)
+    if wscale == 1.0:
+        assert np.abs(q_dev - q_ref).max() <= 5e-2, np.abs(q_dev - q_ref).max()
+    else:
+        # outputs of order one: 4-bit operands keep the ranking signal (correlation with the float32 network)
+        assert spread > 0.3 and np.corrcoef(q_dev, q_ref)[0, 1] > 0.97, (spread, np.corrcoef(q_dev, q_ref)[0, 1])
+    rekey = bo.q_to_score_key(q_dev.astype(np.float32), -150.0).astype(np.int64)
+    assert np.abs(keys.cpu().numpy().astype(np.int64) - rekey).max() <= 1
+    perm = np.random.default_rng(1).permutation(count)
+    keys2 = sc.score(dev[torch.from_numpy(perm).cuda()].contiguous())
+    assert np.array_equal(keys.cpu().numpy()[perm], keys2.cpu().numpy())
+
+
 def _q_weights(pz, models, h1=1024, h2=512):
     ws = [puzzles.q_mlp_weights(pz.state_len * pz.num_values, pz.fanout, h1, h2, model_idx=i) for i in range(models)]
     rng = np.random.default_rng(17)
