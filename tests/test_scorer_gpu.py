@@ -172,46 +172,94 @@ def test_fp8_scorer_within_tolerance(name, count, models):
     assert np.array_equal(keys.cpu().numpy()[perm], keys2.cpu().numpy())
 
 
-@pytest.mark.parametrize("name,count,models,wscale", [("rand54", 20000, 1, 1.0), ("rand96", 5000, 2, 1.0),
-                                                      ("rand54", 77, 1, 1.0), ("rand54", 3000, 1, 6.0)])
-def test_nvfp4_scorer_within_tolerance(name, count, models, wscale):
+def _dequantize_nvfp4_activations(sc, count):
+    """Host view of the scorer's packed 4-bit activations: E2M1 codes x E4M3 block factors x tensor scale, read
+    back from the device buffers in the tile layout the tensor core consumes."""
+    vals = np.array([0, .5, 1, 1.5, 2, 3, 4, 6], np.float32)
+    hidden = sc.hidden
+    packed = sc.h1q[:count].cpu().numpy()
+    codes = np.empty((count, hidden), np.uint8)
+    codes[:, 0::2] = packed & 15
+    codes[:, 1::2] = packed >> 4
+    deq = np.where(codes & 8, -1.0, 1.0).astype(np.float32) * vals[codes & 7]
+    sf = sc.sf_h1.view(torch.float8_e4m3fn).to(torch.float32).cpu().numpy().reshape(-1, hidden // 256, 4, 32, 4, 4)
+    tscale = np.float32(sc.act_bound / (6.0 * 448.0))
+    out = np.zeros((count, hidden), np.float32)
+    for r in range(count):  # factors of row r: tile r // 128, lane (r % 128) % 32, column (r % 128) // 32
+        mt, rr = divmod(r, 128)
+        r1, r0 = divmod(rr, 32)
+        out[r] = deq[r] * np.repeat(sf[mt, :, :, r0, r1, :].reshape(-1), 16) * tscale
+    return out
+
+
+@pytest.mark.parametrize("name,count,wscale", [("rand54", 20000, 1.0), ("rand96", 5000, 1.0), ("rand54", 77, 1.0),
+                                               ("rand54", 3000, 6.0)])
+def test_nvfp4_scorer_within_tolerance(name, count, wscale):
     """Second layer on the block-scaled 4-bit tensor-core path (E2M1 elements, E4M3 factor per 16, float32 tensor
-    scale; first layer e4m3).  Stated bound: max-abs error of the network output <= 5e-2 against the float32 network.
-    The random-init network's outputs are themselves only a few hundredths wide, so that bound alone would pass a
-    wrong operand layout; the device is therefore also held to 2e-3 against a float32 evaluation of the SAME rounded
-    operands (oracle.mlp_forward_nvfp4_model), and one case scales the weights up so that outputs are of order one."""
+    scale; first layer e4m3).  Three checks: (1) the stated bound, max-abs error of the network output <= 5e-2
+    against the float32 network; (2) the tensor-core GEMM itself is exact: the device output equals a float32
+    evaluation on the host of the device's own packed activations and the host-packed weights to 1e-5 - any mistake
+    in the operand or scale-factor layouts would show here, while (1) alone would not notice (the random-init
+    network's outputs are only a few hundredths wide); (3) the activation quantiser agrees with the oracle's NVFP4
+    model except where the two float32 sums fall on different sides of a rounding boundary.  One case scales the
+    weights up so that outputs are of order one."""
     pz = puzzles.by_name(name)
     stride = (pz.state_len + 15) // 16 * 16
-    ws = [puzzles.mlp_weights(pz.state_len * pz.num_values, 1024, model_idx=20 + i) for i in range(models)]
+    w = puzzles.mlp_weights(pz.state_len * pz.num_values, 1024, model_idx=20)
     rng = np.random.default_rng(5)
-    for w in ws:
-        w["w1"] = (w["w1"] * wscale).astype(np.float32)
-        w["w2"] = (w["w2"] * wscale).astype(np.float32)
-        w["b1"] = (rng.standard_normal(1024) * 0.05).astype(np.float32)
-        w["b2"] = (rng.standard_normal(1024) * 0.05).astype(np.float32)
-        w["b3"] = np.float32(0.1)
-    sc = scorers.MLPValueScorer(ws, pz.state_len, stride, pz.num_values, max_rows=count, dtype="nvfp4")
+    w["w1"] = (w["w1"] * wscale).astype(np.float32)
+    w["w2"] = (w["w2"] * wscale).astype(np.float32)
+    w["b1"] = (rng.standard_normal(1024) * 0.05).astype(np.float32)
+    w["b2"] = (rng.standard_normal(1024) * 0.05).astype(np.float32)
+    w["b3"] = np.float32(0.1)
+    sc = scorers.MLPValueScorer([w], pz.state_len, stride, pz.num_values, max_rows=count, dtype="nvfp4")
     rows = children_of(pz, count, seed=count + 2)
     dev = torch.from_numpy(padded(rows, stride)).cuda()
     keys = sc.score(dev)
     torch.cuda.synchronize()
     assert sc.error_code() == 0
-    q_dev = (sc.last_q(count).cpu().numpy() + sum(float(w["b3"]) for w in ws)) / models
-    q_model = bo.mlp_forward_nvfp4_model(rows, ws, pz.num_values, sc.act_bound)
-    q_ref = bo.mlp_forward(rows, ws, pz.num_values)
-    spread = float(q_ref.max() - q_ref.min())
-    err_model = np.abs(q_dev - q_model).max()
-    assert err_model <= 2e-3 * max(1.0, wscale ** 2), (err_model, spread)
+    q_dev = sc.last_q(count).cpu().numpy() + float(w["b3"])
+    q_ref = bo.mlp_forward(rows, [w], pz.num_values)
+    # (2) exact GEMM on the device's own operands
+    n_chk = min(count, 2000)
+    h1q_dev = _dequantize_nvfp4_activations(sc, n_chk)
+    w2q = bo.quantize_nvfp4(w["w2"], bo.nvfp4_tensor_scale(float(np.abs(w["w2"]).max())))
+    q_host = np.maximum(h1q_dev @ w2q.T + w["b2"][None, :], 0.0) @ w["w3"] + float(w["b3"])
+    assert np.abs(q_dev[:n_chk] - q_host).max() <= 1e-5 * max(1.0, wscale ** 2), np.abs(q_dev[:n_chk] - q_host).max()
+    # (3) activation quantiser against the oracle's model
+    x = bo.one_hot(rows[:n_chk], pz.num_values)
+    w1q, s1 = bo._e4m3_rows(w["w1"])
+    h1 = np.maximum(x @ (w1q * s1[:, None]).T + w["b1"][None, :], 0.0).astype(np.float32)
+    h1q_model = bo.quantize_nvfp4(bo._e4m3_tensor(h1, sc.act_bound), bo.nvfp4_tensor_scale(sc.act_bound))
+    differs = np.abs(h1q_dev - h1q_model) > 1e-6
+    assert differs.mean() < 0.01, differs.mean()
+    assert np.abs(h1q_dev - h1q_model).max() <= 0.26 * float(h1.max()), np.abs(h1q_dev - h1q_model).max()
+    q_model = bo.mlp_forward_nvfp4_model(rows, [w], pz.num_values, sc.act_bound)
+    assert np.abs(q_dev - q_model).max() <= 2e-2 * max(1.0, wscale ** 2)
+    # (1) the stated bound
     if wscale == 1.0:
         assert np.abs(q_dev - q_ref).max() <= 5e-2, np.abs(q_dev - q_ref).max()
     else:
-        # outputs of order one: 4-bit operands keep the ranking signal (correlation with the float32 network)
+        spread = float(q_ref.max() - q_ref.min())
         assert spread > 0.3 and np.corrcoef(q_dev, q_ref)[0, 1] > 0.97, (spread, np.corrcoef(q_dev, q_ref)[0, 1])
     rekey = bo.q_to_score_key(q_dev.astype(np.float32), -150.0).astype(np.int64)
     assert np.abs(keys.cpu().numpy().astype(np.int64) - rekey).max() <= 1
     perm = np.random.default_rng(1).permutation(count)
     keys2 = sc.score(dev[torch.from_numpy(perm).cuda()].contiguous())
     assert np.array_equal(keys.cpu().numpy()[perm], keys2.cpu().numpy())
+
+
+def test_nvfp4_ensemble_within_tolerance():
+    """Three members (the large-frontier configuration's scorer): the members' head outputs add up in one buffer."""
+    pz = puzzles.puzzle96()
+    ws = [puzzles.mlp_weights(pz.state_len * pz.num_values, 1024, model_idx=30 + i) for i in range(3)]
+    sc = scorers.MLPValueScorer(ws, pz.state_len, 96, pz.num_values, max_rows=4000, dtype="nvfp4")
+    rows = children_of(pz, 4000, seed=9)
+    sc.score(torch.from_numpy(padded(rows, 96)).cuda())
+    torch.cuda.synchronize()
+    assert sc.error_code() == 0
+    q_dev = (sc.last_q(4000).cpu().numpy() + sum(float(w["b3"]) for w in ws)) / 3
+    assert np.abs(q_dev - bo.mlp_forward(rows, ws, pz.num_values)).max() <= 5e-2
 
 
 def _q_weights(pz, models, h1=1024, h2=512):
