@@ -20,6 +20,8 @@
 
 #include <new>
 
+#include <cuda_fp4.h>
+
 #include "mgbs.h"
 #include "mgbs_nvfp4.cuh"
 #include "mgbs_tc.cuh"
@@ -425,6 +427,8 @@ struct L1Args {
   const float* bias;
   const float* col_scale;    // fp8 only: [n_total] dequantisation factor of each W1 output channel
   float out_inv_scale;       // fp8 only: activations are stored as e4m3(value * out_inv_scale)
+  uint8_t* sf_out;           // NVFP4 output only: block factors, [row tile][column chunk][step][512 B]
+  float inv_global;          // NVFP4 output only: 1 / tensor scale of the activations
   int* err;
 };
 
@@ -434,7 +438,11 @@ struct L1Args {
 // PAIR = 1: thread-block clusters of two (see k_mlp_head_pair).  Each CTA builds the one-hot operand of its own 128
 // rows and loads half of each 256-row block of W1; the even CTA issues MMAs of M = 256 over both.  The weight ring
 // then holds six half blocks instead of three whole ones, and the shared-memory port carries a third less.
-template <int F8, int EW, int PAIR>
+// OUT4 = 1 (with F8 = 1, EW = 8): the activations leave as NVFP4 instead of e4m3 - per row and block of 16 columns
+// one E4M3 factor e4m3(blockmax / 6 * inv_global), elements E2M1(x * inv_global / factor), two per byte; tmOut is then
+// the packed tensor [rows, n_total / 2] bytes and the factors go to sf_out in the layout the block-scaled GEMM of the
+// second layer reads (row r of a 128-row tile at byte (r % 32) * 16 + (r / 32) * 4 of each 512-byte step chunk).
+template <int F8, int EW, int PAIR, int OUT4 = 0>
 __global__ void __launch_bounds__(L1_THREADS, 1)
 k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmOut, L1Args g) {
   extern __shared__ uint8_t smem_raw[];
@@ -645,6 +653,57 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
               tma_store_2d(&tmOut, smem_u32(box), nc * BN + gcol, row0 + quad * 32);
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
+          }
+        } else if constexpr (OUT4 != 0) {
+          // one box = the chunk's 256 columns, 128 bytes per row
+          uint8_t* box = staging;
+          if (et == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");
+          uint8_t* sf_row = g.sf_out + (((int64_t)mt * n_chunks + nc) * 4) * 512 + (r & 31u) * 16u + (r >> 5) * 4u;
+#pragma unroll
+          for (int sub0 = 0; sub0 < BN / 32; sub0 += EW / 4) {
+            const int sub = sub0 + sg;
+            uint32_t v[32];
+            tc_ld32(taddr + sub * 32, v);
+            tc_wait_ld();
+            const int n0 = nc * BN + sub * 32;
+            float x[32];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 cq = __ldg(reinterpret_cast<const float4*>(g.col_scale + n0) + j);
+              const float4 bq = __ldg(reinterpret_cast<const float4*>(g.bias + n0) + j);
+              x[4 * j] = fmaxf(fmaf(__uint_as_float(v[4 * j]), cq.x, bq.x), 0.f);
+              x[4 * j + 1] = fmaxf(fmaf(__uint_as_float(v[4 * j + 1]), cq.y, bq.y), 0.f);
+              x[4 * j + 2] = fmaxf(fmaf(__uint_as_float(v[4 * j + 2]), cq.z, bq.z), 0.f);
+              x[4 * j + 3] = fmaxf(fmaf(__uint_as_float(v[4 * j + 3]), cq.w, bq.w), 0.f);
+            }
+            uint32_t packed[4] = {0u, 0u, 0u, 0u};
+            uint32_t sf_pair = 0;
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+              float amax = 0.f;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) amax = fmaxf(amax, x[16 * blk + j]);
+              const __nv_fp8_storage_t sf8 = __nv_cvt_float_to_fp8(amax * (1.f / 6.f) * g.inv_global, __NV_SATFINITE, __NV_E4M3);
+              const float sf = __half2float(__half(__nv_cvt_fp8_to_halfraw(sf8, __NV_E4M3)));
+              const float inv = sf > 0.f ? g.inv_global / sf : 0.f;
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj) {
+                const uint32_t p2 = __nv_cvt_float2_to_fp4x2(make_float2(x[16 * blk + 2 * jj] * inv, x[16 * blk + 2 * jj + 1] * inv),
+                                                             __NV_E2M1, cudaRoundNearest);
+                packed[2 * blk + (jj >> 2)] |= (p2 & 0xffu) << (8 * (jj & 3));
+              }
+              sf_pair |= (uint32_t)sf8 << (8 * blk);
+            }
+            *reinterpret_cast<uint4*>(box + swz128(r, (uint32_t)(sub * 16))) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            // blocks 2 * sub and 2 * sub + 1 of the chunk's sixteen: MMA step sub / 2, factors (sub & 1) * 2 and + 1
+            *reinterpret_cast<uint16_t*>(sf_row + (sub >> 1) * 512 + (sub & 1) * 2) = (uint16_t)sf_pair;
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");
+          if (et == 0) {
+            tma_store_2d(&tmOut, smem_u32(box), nc * (BN / 2), row0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
         } else {
 #pragma unroll 1
@@ -886,6 +945,7 @@ struct MgbsMlp {
   int l1_pair_clusters = 0;             // the same for the layer-1 kernel
   bool head_pair = true;
   bool fused_l1 = true;
+  bool fused_quant = true;  // NVFP4: the layer-1 epilogue writes packed 4-bit activations itself
   bool profile = false;
   cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
 };
@@ -959,6 +1019,8 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
   l1_smem((const void*)mgbs::k_mlp_l1<1, 8, 0>);
   l1_smem((const void*)mgbs::k_mlp_l1<1, 4, 0>);
   l1_smem((const void*)mgbs::k_mlp_l1<1, 8, 1>);
+  l1_smem((const void*)mgbs::k_mlp_l1<1, 8, 0, 1>);
+  l1_smem((const void*)mgbs::k_mlp_l1<1, 8, 1, 1>);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_head_pair<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::PAIR_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_head_pair<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::PAIR_SMEM);
@@ -1010,6 +1072,10 @@ int mgbs_mlp_set_head_mode(MgbsMlp* m, int32_t pair) {
 
 int mgbs_mlp_set_l1_mode(MgbsMlp* m, int32_t fused) {
   if (!m) return MGBS_ERR_ARG;
+  if (m->cfg.dtype == 2) {  // NVFP4: fused = layer-1 epilogue quantises; 0 = e4m3 activations + a separate pass
+    m->fused_quant = fused != 0;
+    return 0;
+  }
   if (m->cfg.dtype != 0 && !fused) return MGBS_ERR_UNSUPPORTED;  // the e4m3 path has no separate one-hot matrix
   m->fused_l1 = fused != 0;
   return 0;
@@ -1072,6 +1138,7 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
     g.accumulate_q = 0;
     g.err = c.err;
     if (prof) cudaEventRecord(m->ev[1], st);
+    bool quant_in_l1 = false;
     if (m->fused_l1) {
       L1Args l;
       l.children = children;
@@ -1083,8 +1150,11 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
       l.bias = c.b1[i];
       l.col_scale = c.s1[i];
       l.out_inv_scale = c.act_inv_scale;
+      l.sf_out = c.sf_h1;
+      l.inv_global = c.act4_inv_global;
       l.err = c.err;
       const bool resident = m->k1_pad / (e4 ? BK8 : BK) <= L1_A_STAGES;
+      quant_in_l1 = f4 && m->fused_quant && resident;
       // bf16 builds six K-blocks per tile: eight producer warps are needed even with the resident tile (measured:
       // 0.69-0.76 ms with 4 epilogue + 8 producer warps against 0.82 ms with 8 + 4 on the 786 432-row case);
       // e4m3 builds three and gains from the wider epilogue
@@ -1103,10 +1173,12 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
         at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
         lc.attrs = at;
         lc.numAttrs = 1;
-        cudaError_t le = cudaLaunchKernelEx(&lc, k_mlp_l1<1, 8, 1>, m->tm_w1h[i], m->tm_h1, l);
+        cudaError_t le = quant_in_l1 ? cudaLaunchKernelEx(&lc, k_mlp_l1<1, 8, 1, 1>, m->tm_w1h[i], m->tm_h1q, l)
+                                     : cudaLaunchKernelEx(&lc, k_mlp_l1<1, 8, 1>, m->tm_w1h[i], m->tm_h1, l);
         if (le != cudaSuccess) return (int)le;
       } else if (e4 && resident) {
-        k_mlp_l1<1, 8, 0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
+        if (quant_in_l1) k_mlp_l1<1, 8, 0, 1><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1q, l);
+        else k_mlp_l1<1, 8, 0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
       } else if (e4) {
         k_mlp_l1<1, 4, 0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
       } else {
@@ -1124,7 +1196,9 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
     g.accumulate_q = i > 0 ? 1 : 0;
     g.col_scale = c.s2[i];
     if (f4) {
-      // e4m3 activations -> NVFP4 (packed elements + block factors), then the block-scaled 4-bit GEMM + head
+      // e4m3 activations -> NVFP4 (packed elements + block factors) unless the layer-1 epilogue wrote them already,
+      // then the block-scaled 4-bit GEMM + head
+      if (!quant_in_l1)
       MGBS_SC_TRY(launch_quant_h1_nvfp4(reinterpret_cast<const uint8_t*>(c.h1), count_dev, rows_cap, c.hidden,
                                         1.f / c.act_inv_scale, c.act4_inv_global, reinterpret_cast<uint8_t*>(c.h1q),
                                         c.sf_h1, m->sms, st));

@@ -192,9 +192,10 @@ def _dequantize_nvfp4_activations(sc, count):
     return out
 
 
+@pytest.mark.parametrize("fused", [True, False])
 @pytest.mark.parametrize("name,count,wscale", [("rand54", 20000, 1.0), ("rand96", 5000, 1.0), ("rand54", 77, 1.0),
                                                ("rand54", 3000, 6.0)])
-def test_nvfp4_scorer_within_tolerance(name, count, wscale):
+def test_nvfp4_scorer_within_tolerance(name, count, wscale, fused):
     """Second layer on the block-scaled 4-bit tensor-core path (E2M1 elements, E4M3 factor per 16, float32 tensor
     scale; first layer e4m3).  Three checks: (1) the stated bound, max-abs error of the network output <= 5e-2
     against the float32 network; (2) the tensor-core GEMM itself is exact: the device output equals a float32
@@ -213,6 +214,7 @@ def test_nvfp4_scorer_within_tolerance(name, count, wscale):
     w["b2"] = (rng.standard_normal(1024) * 0.05).astype(np.float32)
     w["b3"] = np.float32(0.1)
     sc = scorers.MLPValueScorer([w], pz.state_len, stride, pz.num_values, max_rows=count, dtype="nvfp4")
+    sc.set_l1_mode(fused)
     rows = children_of(pz, count, seed=count + 2)
     dev = torch.from_numpy(padded(rows, stride)).cuda()
     keys = sc.score(dev)
@@ -230,11 +232,11 @@ def test_nvfp4_scorer_within_tolerance(name, count, wscale):
     x = bo.one_hot(rows[:n_chk], pz.num_values)
     w1q, s1 = bo._e4m3_rows(w["w1"])
     h1 = np.maximum(x @ (w1q * s1[:, None]).T + w["b1"][None, :], 0.0).astype(np.float32)
-    h1q_model = bo.quantize_nvfp4(bo._e4m3_tensor(h1, sc.act_bound), bo.nvfp4_tensor_scale(sc.act_bound))
+    h1q_model = bo.quantize_nvfp4(h1 if fused else bo._e4m3_tensor(h1, sc.act_bound), bo.nvfp4_tensor_scale(sc.act_bound))
     differs = np.abs(h1q_dev - h1q_model) > 1e-6
     assert differs.mean() < 0.01, differs.mean()
     assert np.abs(h1q_dev - h1q_model).max() <= 0.26 * float(h1.max()), np.abs(h1q_dev - h1q_model).max()
-    q_model = bo.mlp_forward_nvfp4_model(rows, [w], pz.num_values, sc.act_bound)
+    q_model = bo.mlp_forward_nvfp4_model(rows, [w], pz.num_values, sc.act_bound, via_e4m3=not fused)
     assert np.abs(q_dev - q_model).max() <= 2e-2 * max(1.0, wscale ** 2)
     # (1) the stated bound
     if wscale == 1.0:
