@@ -697,7 +697,9 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
             }
             *reinterpret_cast<uint4*>(box + swz128(r, (uint32_t)(sub * 16))) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             // blocks 2 * sub and 2 * sub + 1 of the chunk's sixteen: MMA step sub / 2, factors (sub & 1) * 2 and + 1
-            *reinterpret_cast<uint16_t*>(sf_row + (sub >> 1) * 512 + (sub & 1) * 2) = (uint16_t)sf_pair;
+            // (the odd CTA of a pair also walks the tile after the last one when the tile count is odd: the TMA store
+            // clips it, these plain stores must not happen)
+            if (mt < num_mtiles) *reinterpret_cast<uint16_t*>(sf_row + (sub >> 1) * 512 + (sub & 1) * 2) = (uint16_t)sf_pair;
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");

@@ -234,7 +234,9 @@ def test_nvfp4_scorer_within_tolerance(name, count, wscale, fused):
     h1 = np.maximum(x @ (w1q * s1[:, None]).T + w["b1"][None, :], 0.0).astype(np.float32)
     h1q_model = bo.quantize_nvfp4(h1 if fused else bo._e4m3_tensor(h1, sc.act_bound), bo.nvfp4_tensor_scale(sc.act_bound))
     differs = np.abs(h1q_dev - h1q_model) > 1e-6
-    assert differs.mean() < 0.01, differs.mean()
+    # two-pass form: e4m3 values over an e4m3 factor often sit exactly on an E2M1 midpoint (2.5, 1.25, ...), where the
+    # device's x * (1 / step) and the model's x / step round to different neighbours; the fused form has no such ties
+    assert differs.mean() < (1e-4 if fused else 0.03), differs.mean()
     assert np.abs(h1q_dev - h1q_model).max() <= 0.26 * float(h1.max()), np.abs(h1q_dev - h1q_model).max()
     q_model = bo.mlp_forward_nvfp4_model(rows, [w], pz.num_values, sc.act_bound, via_e4m3=not fused)
     assert np.abs(q_dev - q_model).max() <= 2e-2 * max(1.0, wscale ** 2)
