@@ -368,7 +368,7 @@ typedef struct MgbsMlpConfig {
   /* dtype 2 (NVFP4: E2M1 elements, one E4M3 factor per 16 elements, one float32 scale per tensor): layer 1 runs as for
    * dtype 1 (w1, s1, h1, act_inv_scale as above) and its e4m3 activations are re-quantised to NVFP4; layer 2 runs on
    * the block-scaled 4-bit tensor-core path.  w2 then holds packed E2M1 [hidden, hidden / 2] bytes (even K in the low
-   * nibble), sf_w2 its block factors in tiles [column chunk of 256][K-block of 256][step of 64][half of 128 rows]
+   * nibble), sf_w2 its block factors in tiles [column chunk of 128][K-block of 256][step of 64]
    * [512 B: row r at (r % 32) * 16 + (r / 32) * 4 + block], s2[n] = (tensor scale of W2) * (tensor scale of the
    * activations); h1q / sf_h1 are the scorer's own buffers: packed activations [rows_pad, hidden / 2] and their
    * factors [rows_pad / 128][hidden / 256][4][512 B]; act4_inv_global = 1 / (tensor scale of the activations). */

@@ -13,15 +13,15 @@
 // its four factors at byte r0 * 16 + r1 * 4 (32 "lanes" of 16 bytes: what tcgen05.cp 32x128b.warpx4 copies from
 // shared into tensor memory, lane r0, 32-bit column r1, replicated over the four lane quadrants).  Global memory
 // holds them in the order the kernel consumes them, so that one bulk copy per pipeline stage brings a K-block's
-// factors: A: [row tile of 128][K-block][step 0..3][512 B]; B: [column chunk of 256][K-block][step][half 0..1][512 B].
+// factors: A: [row tile of 128][K-block][step 0..3][512 B]; B: [column chunk of 128][K-block][step 0..3][512 B].
 //
 // First-layer activations are produced in e4m3 by the fused layer-1 kernel and re-quantised to NVFP4 by
 // k_quant_h1_nvfp4 (block maximum -> E4M3 scale, elements -> E2M1, written in the layouts above).
 //
-// Tensor memory: one accumulator of 256 columns (the two-buffer scheme of the 8- and 16-bit kernels would need all
-// 512 columns and leave none for the factors), then per pipeline stage 16 columns for A's and 32 for B's factors.
-// With one accumulator the epilogue cannot overlap the next tile's MMAs, so it is spread over eight warps (two
-// per lane quadrant, 128 columns each).
+// Tensor memory: the factors need columns of their own, so two accumulators of 256 columns (the scheme of the 8- and
+// 16-bit kernels) do not fit the 512.  A single 256-column accumulator cannot overlap its epilogue with the next tile's
+// MMAs and measured 1.85 PFLOP/s; the kernel therefore works on 128 x 128 tiles: two accumulators of 128 columns
+// (256), then per pipeline stage 16 columns for A's and 16 for B's factors (6 stages: 192).
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
@@ -35,18 +35,20 @@ namespace mgbs {
 
 constexpr int F4_BK = 256;                   // elements per 128-byte K-block row
 constexpr int F4_STEPS = 4;                  // MMA steps (64 elements) per K-block
+constexpr int F4_BN = 128;                   // accumulator columns per tile
+constexpr int F4_B_BYTES = F4_BN * 128;      // 16 KB: 128 weight rows x one K-block
 constexpr int F4_SFA_BYTES = F4_STEPS * 512;             // 2 KB per stage
-constexpr int F4_SFB_BYTES = F4_STEPS * 2 * 512;         // 4 KB per stage
-constexpr int F4_STAGE_BYTES = A_BYTES + B_BYTES + F4_SFA_BYTES + F4_SFB_BYTES;  // 54 KB
-constexpr int F4_STAGES = 4;
-constexpr int F4_THREADS = 320;              // TMA warp, MMA warp, eight epilogue warps
-constexpr int F4_SMEM = F4_STAGES * F4_STAGE_BYTES + 1024 + 1024;
-constexpr uint32_t F4_SF_COLS = 48;          // tensor-memory columns of one stage's factors: 16 (A) + 32 (B)
-constexpr uint32_t F4_SF_BASE = BN;          // factors start after the accumulator
+constexpr int F4_SFB_BYTES = F4_STEPS * 512;             // 2 KB per stage
+constexpr int F4_STAGE_BYTES = A_BYTES + F4_B_BYTES + F4_SFA_BYTES + F4_SFB_BYTES;  // 36 KB
+constexpr int F4_STAGES = 6;
+constexpr int F4_THREADS = 192;              // TMA warp, MMA warp, four epilogue warps
+constexpr int F4_SMEM = F4_STAGES * F4_STAGE_BYTES + 1024 + 512;
+constexpr uint32_t F4_SF_COLS = 32;          // tensor-memory columns of one stage's factors: 16 (A) + 16 (B)
+constexpr uint32_t F4_SF_BASE = 2 * F4_BN;   // factors start after the two accumulators
 
 // Instruction descriptor of kind::mxf4nvf4: A and B format E2M1 (code 1, bits 7-9 / 10-12), both K-major, N >> 3 in
 // bits 17-22, scale format UE4M3 (bit 23 = 0), M >> 4 in bits 24-28, scale-factor ids 0, K = 64 (bit 31 = 0).
-constexpr uint32_t kIdescNvfp4 = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+constexpr uint32_t kIdescNvfp4 = (1u << 7) | (1u << 10) | ((uint32_t)(F4_BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
 __device__ __forceinline__ void tc_mma_nvfp4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t sfa_tmem,
                                              uint32_t sfb_tmem, uint32_t accumulate) {
@@ -80,15 +82,14 @@ k_mlp_head_nvfp4(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + F4_STAGES * F4_STAGE_BYTES);
-  // bars[0..S) full, [S..2S) empty, [2S] tmem_full, [2S+1] tmem_empty, [2S+2] drain, then the tmem base word
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * F4_STAGES + 3);
-  float* partial = reinterpret_cast<float*>(bars + 2 * F4_STAGES + 4);  // [128] row sums of the second column half
+  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty, [2S+4] drain, then the tmem base
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * F4_STAGES + 5);
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (F4_STAGES + s); };
-  const uint32_t tfull_bar = bar0 + 8u * (2 * F4_STAGES);
-  const uint32_t tempty_bar = bar0 + 8u * (2 * F4_STAGES + 1);
-  const uint32_t drain_bar = bar0 + 8u * (2 * F4_STAGES + 2);
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * F4_STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * F4_STAGES + 2 + b); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * F4_STAGES + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -96,13 +97,12 @@ k_mlp_head_nvfp4(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (rows > g.row_limit) rows = g.row_limit;
   if (rows < 0) rows = 0;
   const int num_mtiles = (int)((rows + BM - 1) / BM);
-  const int n_chunks = g.n_total / BN;
+  const int n_chunks = g.n_total / F4_BN;
   const int k_blocks = g.k_total / F4_BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < F4_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    mbar_init(tfull_bar, 1);
-    mbar_init(tempty_bar, 8);
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
     mbar_init(drain_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -128,9 +128,9 @@ k_mlp_head_nvfp4(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             const uint32_t sa = smem_u32(smem + stage * F4_STAGE_BYTES);
             mbar_expect_tx(full_bar(stage), F4_STAGE_BYTES);
             tma_load_2d(sa, &tmA, kb * 128, mt * BM, full_bar(stage));               // x in bytes: 128 per K-block
-            tma_load_2d(sa + A_BYTES, &tmB, kb * 128, nc * BN, full_bar(stage));
-            bulk_load(sa + A_BYTES + B_BYTES, g.sfa + ((int64_t)mt * k_blocks + kb) * F4_SFA_BYTES, F4_SFA_BYTES, full_bar(stage));
-            bulk_load(sa + A_BYTES + B_BYTES + F4_SFA_BYTES, g.sfb + ((int64_t)nc * k_blocks + kb) * F4_SFB_BYTES, F4_SFB_BYTES,
+            tma_load_2d(sa + A_BYTES, &tmB, kb * 128, nc * F4_BN, full_bar(stage));
+            bulk_load(sa + A_BYTES + F4_B_BYTES, g.sfa + ((int64_t)mt * k_blocks + kb) * F4_SFA_BYTES, F4_SFA_BYTES, full_bar(stage));
+            bulk_load(sa + A_BYTES + F4_B_BYTES + F4_SFA_BYTES, g.sfb + ((int64_t)nc * k_blocks + kb) * F4_SFB_BYTES, F4_SFB_BYTES,
                       full_bar(stage));
             if (++stage == F4_STAGES) { stage = 0; phase ^= 1u; }
           }
@@ -145,33 +145,33 @@ k_mlp_head_nvfp4(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
         for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
-          if (!mbar_wait(tempty_bar, (acc_it & 1u) ^ 1u, g.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          const uint32_t b = acc_it & 1u;
+          if (!mbar_wait(tempty_bar(b), ((acc_it >> 1) & 1u) ^ 1u, g.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base;
+          const uint32_t d_tmem = tmem_base + b * F4_BN;
           for (int kb = 0; kb < k_blocks; ++kb) {
             if (!mbar_wait(full_bar(stage), phase, g.err, ERR_WAIT_FULL)) { ok = false; break; }
             tc_fence_after();
             const uint32_t sa = smem_u32(smem + stage * F4_STAGE_BYTES);
-            const uint32_t sf_s = sa + A_BYTES + B_BYTES;
+            const uint32_t sf_s = sa + A_BYTES + F4_B_BYTES;
             const uint32_t sf_t = tmem_base + F4_SF_BASE + (uint32_t)stage * F4_SF_COLS;
-            // this stage's scale factors: 4 chunks for A (4 columns each), 8 for B
+            // this stage's scale factors: 4 chunks for A and 4 for B, 4 columns each
 #pragma unroll
             for (int k = 0; k < F4_STEPS; ++k) {
               tc_cp_sf(sf_t + 4u * k, make_desc_sf(sf_s + 512u * k));
-              tc_cp_sf(sf_t + 16u + 8u * k, make_desc_sf(sf_s + F4_SFA_BYTES + 1024u * k));
-              tc_cp_sf(sf_t + 16u + 8u * k + 4u, make_desc_sf(sf_s + F4_SFA_BYTES + 1024u * k + 512u));
+              tc_cp_sf(sf_t + 16u + 4u * k, make_desc_sf(sf_s + F4_SFA_BYTES + 512u * k));
             }
             const uint64_t adesc = make_desc_sw128(sa);
             const uint64_t bdesc = make_desc_sw128(sa + A_BYTES);
 #pragma unroll
             for (int k = 0; k < F4_STEPS; ++k) {
               // one step = 64 elements = 32 bytes inside the swizzle row: +2 in (address >> 4)
-              tc_mma_nvfp4(d_tmem, adesc + 2u * k, bdesc + 2u * k, sf_t + 4u * k, sf_t + 16u + 8u * k, (kb | k) != 0 ? 1u : 0u);
+              tc_mma_nvfp4(d_tmem, adesc + 2u * k, bdesc + 2u * k, sf_t + 4u * k, sf_t + 16u + 4u * k, (kb | k) != 0 ? 1u : 0u);
             }
             tc_commit(empty_bar(stage));
             if (++stage == F4_STAGES) { stage = 0; phase ^= 1u; }
           }
-          if (ok) tc_commit(tfull_bar);
+          if (ok) tc_commit(tfull_bar(b));
         }
       }
       tc_commit(drain_bar);
@@ -179,43 +179,42 @@ k_mlp_head_nvfp4(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else {
     const int quad = warp & 3;            // TMEM lane quadrant this warp may read
-    const int half = (warp - 2) >> 2;     // which 128 accumulator columns
     uint32_t acc_it = 0;
     bool ok = true;
     for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
-      const int r = quad * 32 + lane;
-      const int64_t row = (int64_t)mt * BM + r;
+      const int64_t row = (int64_t)mt * BM + quad * 32 + lane;
       const bool row_ok = row < rows;
       float rowsum = 0.f;
       for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
-        if (!mbar_wait(tfull_bar, acc_it & 1u, g.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+        const uint32_t b = acc_it & 1u;
+        if (!mbar_wait(tfull_bar(b), (acc_it >> 1) & 1u, g.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)half * 128u;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * F4_BN;
 #pragma unroll 1
-        for (int c0 = 0; c0 < 128; c0 += 32) {
+        for (int c0 = 0; c0 < F4_BN; c0 += 32) {
           uint32_t v[32];
           tc_ld32(taddr + c0, v);
           tc_wait_ld();
-          const int n0 = nc * BN + half * 128 + c0;
+          const int n0 = nc * F4_BN + c0;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float x = fmaxf(fmaf(__uint_as_float(v[j]), __ldg(g.col_scale + n0 + j), __ldg(g.bias + n0 + j)), 0.f);
-            rowsum = fmaf(x, __ldg(g.w_out + n0 + j), rowsum);
+          for (int j4 = 0; j4 < 8; ++j4) {
+            const float4 bq = __ldg(reinterpret_cast<const float4*>(g.bias + n0) + j4);
+            const float4 wq = __ldg(reinterpret_cast<const float4*>(g.w_out + n0) + j4);
+            const float4 cq = __ldg(reinterpret_cast<const float4*>(g.col_scale + n0) + j4);
+            rowsum = fmaf(fmaxf(fmaf(__uint_as_float(v[4 * j4]), cq.x, bq.x), 0.f), wq.x, rowsum);
+            rowsum = fmaf(fmaxf(fmaf(__uint_as_float(v[4 * j4 + 1]), cq.y, bq.y), 0.f), wq.y, rowsum);
+            rowsum = fmaf(fmaxf(fmaf(__uint_as_float(v[4 * j4 + 2]), cq.z, bq.z), 0.f), wq.z, rowsum);
+            rowsum = fmaf(fmaxf(fmaf(__uint_as_float(v[4 * j4 + 3]), cq.w, bq.w), 0.f), wq.w, rowsum);
           }
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar);
+        if (lane == 0) mbar_arrive(tempty_bar(b));
       }
-      // the two column halves of a row meet in shared memory (fixed order: deterministic sums)
-      if (half == 1) partial[r] = rowsum;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (half == 0 && row_ok && ok) {
-        const float total = rowsum + partial[r];
-        if (g.accumulate_q) g.out_q[row] += total;
-        else g.out_q[row] = total;
+      if (row_ok && ok) {
+        if (g.accumulate_q) g.out_q[row] += rowsum;
+        else g.out_q[row] = rowsum;
       }
-      asm volatile("bar.sync 1, 256;" ::: "memory");
     }
   }
   tc_fence_before();
@@ -284,7 +283,7 @@ int launch_quant_h1_nvfp4(const uint8_t* h1_e4m3, const uint32_t* count_dev, int
 }
 
 int launch_head_nvfp4(const CUtensorMap& tmA, const CUtensorMap& tmB, const Nvfp4HeadArgs& g, int sms, cudaStream_t st) {
-  if (g.k_total % F4_BK != 0 || g.n_total % BN != 0) return MGBS_ERR_UNSUPPORTED;
+  if (g.k_total % F4_BK != 0 || g.n_total % F4_BN != 0) return MGBS_ERR_UNSUPPORTED;
   k_mlp_head_nvfp4<<<sms, F4_THREADS, F4_SMEM, st>>>(tmA, tmB, g);
   return (int)cudaGetLastError();
 }

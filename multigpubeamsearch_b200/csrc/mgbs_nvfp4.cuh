@@ -12,7 +12,7 @@ struct Nvfp4HeadArgs {
   int32_t n_total;            // hidden units of layer 2 (multiple of 256)
   int32_t k_total;            // reduction length (multiple of 256)
   const uint8_t* sfa;         // block factors of the activations, [row tile][K-block][step][512 B]
-  const uint8_t* sfb;         // block factors of the weights, [column chunk][K-block][step][half][512 B]
+  const uint8_t* sfb;         // block factors of the weights, [column chunk of 128][K-block][step][512 B]
   const float* bias;          // [n_total]
   const float* col_scale;     // [n_total]: product of the two tensor scales (per output channel)
   const float* w_out;         // [n_total] weights of the scalar head

@@ -1003,7 +1003,7 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
     if (!rc) rc = make_map(&m->tm_w1h[i], c.w1[i], (uint64_t)c.hidden, (uint64_t)k1_pad, mgbs::BN / 2, eb);
     if (f4) {
       if (!rc && !c.sf_w2[i]) rc = MGBS_ERR_ARG;
-      if (!rc) rc = make_map(&m->tm_w2q[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden / 2, mgbs::BN, 1);
+      if (!rc) rc = make_map(&m->tm_w2q[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden / 2, 128, 1);
       continue;
     }
     if (!rc) rc = make_map(&m->tm_w2[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden, mgbs::BN, eb);
