@@ -20,8 +20,15 @@
 //
 // Tensor memory: the factors need columns of their own, so two accumulators of 256 columns (the scheme of the 8- and
 // 16-bit kernels) do not fit the 512.  A single 256-column accumulator cannot overlap its epilogue with the next tile's
-// MMAs and measured 1.85 PFLOP/s; the kernel therefore works on 128 x 128 tiles: two accumulators of 128 columns
-// (256), then per pipeline stage 16 columns for A's and 16 for B's factors (6 stages: 192).
+// MMAs and measured 1.85 PFLOP/s; the kernel therefore works on 128 x 128 tiles with two accumulators of 128 columns.
+//
+// What bounds these kernels is not the tensor core but operand traffic from L2: streaming both operands per 128 x 128
+// tile is 9 KB per million multiply-adds (the e4m3 CTA-pair kernel needs 8) and measured 0.8 ms for layer 2, no
+// faster than e4m3.  With 4-bit operands a whole row tile of A (128 rows x K = 1024: 64 KB, plus 8 KB of factors) fits
+// shared memory, so it is loaded ONCE per row tile and kept for all column chunks, double-buffered so that the next
+// row tile arrives while this one is multiplied; only the weights stream (16 KB + 2 KB of factors per stage).  A's
+// factors stay in tensor memory for the row tile as well.  Columns: 2 x 128 accumulators, 2 x 64 for A's factors,
+// 4 x 16 for the weight stages' factors.
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
@@ -36,15 +43,17 @@ namespace mgbs {
 constexpr int F4_BK = 256;                   // elements per 128-byte K-block row
 constexpr int F4_STEPS = 4;                  // MMA steps (64 elements) per K-block
 constexpr int F4_BN = 128;                   // accumulator columns per tile
+constexpr int F4_MAX_KB = 4;                 // K-blocks of a resident A tile (K <= 1024)
 constexpr int F4_B_BYTES = F4_BN * 128;      // 16 KB: 128 weight rows x one K-block
-constexpr int F4_SFA_BYTES = F4_STEPS * 512;             // 2 KB per stage
-constexpr int F4_SFB_BYTES = F4_STEPS * 512;             // 2 KB per stage
-constexpr int F4_STAGE_BYTES = A_BYTES + F4_B_BYTES + F4_SFA_BYTES + F4_SFB_BYTES;  // 36 KB
-constexpr int F4_STAGES = 6;
+constexpr int F4_SFA_BYTES = F4_STEPS * 512;             // 2 KB per K-block
+constexpr int F4_SFB_BYTES = F4_STEPS * 512;             // 2 KB per K-block
+constexpr int F4_A_BUF = F4_MAX_KB * (A_BYTES + F4_SFA_BYTES);  // 72 KB: data of all K-blocks, then their factors
+constexpr int F4_STAGE_BYTES = F4_B_BYTES + F4_SFB_BYTES;       // 18 KB
+constexpr int F4_STAGES = 4;
 constexpr int F4_THREADS = 192;              // TMA warp, MMA warp, four epilogue warps
-constexpr int F4_SMEM = F4_STAGES * F4_STAGE_BYTES + 1024 + 512;
-constexpr uint32_t F4_SF_COLS = 32;          // tensor-memory columns of one stage's factors: 16 (A) + 16 (B)
-constexpr uint32_t F4_SF_BASE = 2 * F4_BN;   // factors start after the two accumulators
+constexpr int F4_SMEM = 2 * F4_A_BUF + F4_STAGES * F4_STAGE_BYTES + 1024 + 512;
+constexpr uint32_t F4_SFA_BASE = 2 * F4_BN;                       // A's factors: 2 buffers x 64 columns
+constexpr uint32_t F4_SFB_BASE = F4_SFA_BASE + 2 * 16 * F4_MAX_KB; // weight stages' factors: 4 x 16 columns
 
 // Instruction descriptor of kind::mxf4nvf4: A and B format E2M1 (code 1, bits 7-9 / 10-12), both K-major, N >> 3 in
 // bits 17-22, scale format UE4M3 (bit 23 = 0), M >> 4 in bits 24-28, scale-factor ids 0, K = 64 (bit 31 = 0).
@@ -81,15 +90,19 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
 k_mlp_head_nvfp4(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Nvfp4HeadArgs g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + F4_STAGES * F4_STAGE_BYTES);
-  // bars[0..S) full, [S..2S) empty, [2S..2S+2) tmem_full, [2S+2..2S+4) tmem_empty, [2S+4] drain, then the tmem base
-  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * F4_STAGES + 5);
+  uint8_t* a_buf = smem;                         // 2 x 72 KB
+  uint8_t* b_ring = smem + 2 * F4_A_BUF;         // 4 x 18 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(b_ring + F4_STAGES * F4_STAGE_BYTES);
+  // bars: b_full[S], b_empty[S], a_full[2], a_empty[2], tmem_full[2], tmem_empty[2], drain; then the tmem base word
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + 2 * F4_STAGES + 9);
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (F4_STAGES + s); };
-  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * F4_STAGES + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * F4_STAGES + 2 + b); };
-  const uint32_t drain_bar = bar0 + 8u * (2 * F4_STAGES + 4);
+  auto afull_bar = [&](int b) { return bar0 + 8u * (2 * F4_STAGES + b); };
+  auto aempty_bar = [&](int b) { return bar0 + 8u * (2 * F4_STAGES + 2 + b); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * F4_STAGES + 4 + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * F4_STAGES + 6 + b); };
+  const uint32_t drain_bar = bar0 + 8u * (2 * F4_STAGES + 8);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -98,11 +111,14 @@ k_mlp_head_nvfp4(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (rows < 0) rows = 0;
   const int num_mtiles = (int)((rows + BM - 1) / BM);
   const int n_chunks = g.n_total / F4_BN;
-  const int k_blocks = g.k_total / F4_BK;
+  const int k_blocks = g.k_total / F4_BK;  // <= F4_MAX_KB (checked by the launcher)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < F4_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(afull_bar(b), 1); mbar_init(aempty_bar(b), 1);
+      mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4);
+    }
     mbar_init(drain_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -120,18 +136,32 @@ k_mlp_head_nvfp4(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t a_it = 0;   // row tiles whose A load has been issued
       bool ok = true;
+      // one row tile of A: K-blocks of 16 KB through the tensor map, then the tile's factors as one contiguous copy
+      auto load_a = [&](int mt) -> bool {
+        const uint32_t ab = a_it & 1u;
+        if (!mbar_wait(aempty_bar(ab), ((a_it >> 1) & 1u) ^ 1u, g.err, ERR_WAIT_EMPTY)) return false;
+        const uint32_t dst = smem_u32(a_buf + ab * F4_A_BUF);
+        mbar_expect_tx(afull_bar(ab), (uint32_t)k_blocks * (A_BYTES + F4_SFA_BYTES));
+        for (int kb = 0; kb < k_blocks; ++kb) tma_load_2d(dst + kb * A_BYTES, &tmA, kb * 128, mt * BM, afull_bar(ab));
+        bulk_load(dst + F4_MAX_KB * A_BYTES, g.sfa + (int64_t)mt * k_blocks * F4_SFA_BYTES, (uint32_t)k_blocks * F4_SFA_BYTES,
+                  afull_bar(ab));
+        ++a_it;
+        return true;
+      };
+      if ((int)blockIdx.x < num_mtiles) ok = load_a(blockIdx.x);
       for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
         for (int nc = 0; nc < n_chunks && ok; ++nc) {
-          for (int kb = 0; kb < k_blocks; ++kb) {
+          // the next row tile's A goes out once this tile's weights are on their way: by then the MMAs of the
+          // previous row tile have retired and released the buffer it takes, so this thread does not stall
+          if (nc == (n_chunks > 1 ? 1 : 0) && mt + (int)gridDim.x < num_mtiles) ok = load_a(mt + gridDim.x);
+          for (int kb = 0; kb < k_blocks && ok; ++kb) {
             if (!mbar_wait(empty_bar(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-            const uint32_t sa = smem_u32(smem + stage * F4_STAGE_BYTES);
+            const uint32_t sb = smem_u32(b_ring + stage * F4_STAGE_BYTES);
             mbar_expect_tx(full_bar(stage), F4_STAGE_BYTES);
-            tma_load_2d(sa, &tmA, kb * 128, mt * BM, full_bar(stage));               // x in bytes: 128 per K-block
-            tma_load_2d(sa + A_BYTES, &tmB, kb * 128, nc * F4_BN, full_bar(stage));
-            bulk_load(sa + A_BYTES + F4_B_BYTES, g.sfa + ((int64_t)mt * k_blocks + kb) * F4_SFA_BYTES, F4_SFA_BYTES, full_bar(stage));
-            bulk_load(sa + A_BYTES + F4_B_BYTES + F4_SFA_BYTES, g.sfb + ((int64_t)nc * k_blocks + kb) * F4_SFB_BYTES, F4_SFB_BYTES,
-                      full_bar(stage));
+            tma_load_2d(sb, &tmB, kb * 128, nc * F4_BN, full_bar(stage));   // x in bytes: 128 per K-block
+            bulk_load(sb + F4_B_BYTES, g.sfb + ((int64_t)nc * k_blocks + kb) * F4_SFB_BYTES, F4_SFB_BYTES, full_bar(stage));
             if (++stage == F4_STAGES) { stage = 0; phase ^= 1u; }
           }
         }
@@ -141,9 +171,19 @@ k_mlp_head_nvfp4(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      uint32_t acc_it = 0;
+      uint32_t acc_it = 0, a_it = 0;
       bool ok = true;
-      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x) {
+      for (int mt = blockIdx.x; mt < num_mtiles && ok; mt += gridDim.x, ++a_it) {
+        const uint32_t ab = a_it & 1u;
+        if (!mbar_wait(afull_bar(ab), (a_it >> 1) & 1u, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(a_buf + ab * F4_A_BUF);
+        const uint32_t sfa_t = tmem_base + F4_SFA_BASE + ab * (16u * F4_MAX_KB);
+        // A's factors for the whole row tile: 4 columns per MMA step
+        for (int kb = 0; kb < k_blocks; ++kb)
+#pragma unroll
+          for (int k = 0; k < F4_STEPS; ++k)
+            tc_cp_sf(sfa_t + 16u * kb + 4u * k, make_desc_sf(sa + F4_MAX_KB * A_BYTES + (uint32_t)(kb * F4_STEPS + k) * 512u));
         for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
           const uint32_t b = acc_it & 1u;
           if (!mbar_wait(tempty_bar(b), ((acc_it >> 1) & 1u) ^ 1u, g.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
@@ -152,27 +192,23 @@ k_mlp_head_nvfp4(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int kb = 0; kb < k_blocks; ++kb) {
             if (!mbar_wait(full_bar(stage), phase, g.err, ERR_WAIT_FULL)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t sa = smem_u32(smem + stage * F4_STAGE_BYTES);
-            const uint32_t sf_s = sa + A_BYTES + F4_B_BYTES;
-            const uint32_t sf_t = tmem_base + F4_SF_BASE + (uint32_t)stage * F4_SF_COLS;
-            // this stage's scale factors: 4 chunks for A and 4 for B, 4 columns each
+            const uint32_t sb = smem_u32(b_ring + stage * F4_STAGE_BYTES);
+            const uint32_t sfb_t = tmem_base + F4_SFB_BASE + (uint32_t)stage * 16u;
 #pragma unroll
-            for (int k = 0; k < F4_STEPS; ++k) {
-              tc_cp_sf(sf_t + 4u * k, make_desc_sf(sf_s + 512u * k));
-              tc_cp_sf(sf_t + 16u + 4u * k, make_desc_sf(sf_s + F4_SFA_BYTES + 512u * k));
-            }
-            const uint64_t adesc = make_desc_sw128(sa);
-            const uint64_t bdesc = make_desc_sw128(sa + A_BYTES);
+            for (int k = 0; k < F4_STEPS; ++k) tc_cp_sf(sfb_t + 4u * k, make_desc_sf(sb + F4_B_BYTES + 512u * k));
+            const uint64_t adesc = make_desc_sw128(sa + kb * A_BYTES);
+            const uint64_t bdesc = make_desc_sw128(sb);
 #pragma unroll
             for (int k = 0; k < F4_STEPS; ++k) {
               // one step = 64 elements = 32 bytes inside the swizzle row: +2 in (address >> 4)
-              tc_mma_nvfp4(d_tmem, adesc + 2u * k, bdesc + 2u * k, sf_t + 4u * k, sf_t + 16u + 4u * k, (kb | k) != 0 ? 1u : 0u);
+              tc_mma_nvfp4(d_tmem, adesc + 2u * k, bdesc + 2u * k, sfa_t + 16u * kb + 4u * k, sfb_t + 4u * k, (kb | k) != 0 ? 1u : 0u);
             }
             tc_commit(empty_bar(stage));
             if (++stage == F4_STAGES) { stage = 0; phase ^= 1u; }
           }
           if (ok) tc_commit(tfull_bar(b));
         }
+        if (ok) tc_commit(aempty_bar(ab));  // every MMA that read this A buffer has retired when this arrives
       }
       tc_commit(drain_bar);
       mbar_wait(drain_bar, 0, g.err, ERR_WAIT_DRAIN);
@@ -283,7 +319,7 @@ int launch_quant_h1_nvfp4(const uint8_t* h1_e4m3, const uint32_t* count_dev, int
 }
 
 int launch_head_nvfp4(const CUtensorMap& tmA, const CUtensorMap& tmB, const Nvfp4HeadArgs& g, int sms, cudaStream_t st) {
-  if (g.k_total % F4_BK != 0 || g.n_total % F4_BN != 0) return MGBS_ERR_UNSUPPORTED;
+  if (g.k_total % F4_BK != 0 || g.k_total / F4_BK > F4_MAX_KB || g.n_total % F4_BN != 0) return MGBS_ERR_UNSUPPORTED;
   k_mlp_head_nvfp4<<<sms, F4_THREADS, F4_SMEM, st>>>(tmA, tmB, g);
   return (int)cudaGetLastError();
 }
