@@ -318,3 +318,39 @@ def test_zobrist_hash_is_the_xor_of_table_entries_and_owner_rule():
     b = bo.depth_step([frontier], pz.generators, pz.solved, bo.hamming_scorer(pz.solved), 200,
                       hasher=lambda c: bo.hash128_zobrist(c, table))
     assert a.states.shape == b.states.shape and np.array_equal(np.sort(a.score), np.sort(b.score))
+
+
+def _residual_q_golden():
+    """Outputs of the reference's static_forward_q / static_forward_scores / _fold_bn_linear on seeded inputs
+    (tests/golden/make_residual_q_golden.py) and that script's seeded generators."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_residual_q_golden", GOLDEN / "make_residual_q_golden.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return json.loads((GOLDEN / "residual_q_reference.json").read_text()), mod
+
+
+def test_residual_q_network_matches_reference_static_forward():
+    data, mod = _residual_q_golden()
+    assert len(data["forward"]) == 3
+    for c in data["forward"]:
+        w = mod.residual_q_weights(c["seed"], c["state_size"], c["num_classes"], c["hidden1"], c["hidden2"], c["outputs"])
+        states = mod.residual_q_states(c["seed"] + 50, c["rows"], c["state_len"], c["value_range"])
+        q = bo.residual_q_forward(states, w)
+        want = np.asarray(c["q"], dtype=np.float32)
+        assert q.shape == want.shape
+        assert np.max(np.abs(q - want)) <= 2e-5 * max(1.0, float(np.max(np.abs(want))))  # float32 summation order
+        sc = bo.residual_q_scores_u16(want, w["action_perm"], w["score_scale"], w["score_bias"])
+        assert sc.tolist() == c["scores_i16"]  # the quantiser itself, on the reference's own q, is exact
+        assert np.max(np.abs(bo.residual_q_scores_u16(q, w["action_perm"]).astype(np.int64)
+                             - np.asarray(c["scores_i16"], dtype=np.int64))) <= 1  # the reference's own bound
+
+
+def test_batch_norm_folding_matches_reference():
+    data, mod = _residual_q_golden()
+    for c in data["fold_bn"]:
+        case = mod.bn_case(c["seed"], c["outs"], c["ins"])
+        fw, fb = bo.fold_bn_linear(case["weight"], case["bias"], case["bn_weight"], case["bn_bias"],
+                                   case["running_mean"], case["running_var"])
+        assert np.allclose(fw, np.asarray(c["weight"], dtype=np.float32), rtol=1e-6, atol=1e-7)
+        assert np.allclose(fb, np.asarray(c["bias"], dtype=np.float32), rtol=1e-6, atol=1e-6)
