@@ -339,7 +339,7 @@ def run_ours(args):
     job.saturate(start)
     sampler = ClockSampler([local_rank] if world == 1 else (list(range(world)) if rank == 0 else []))
     sampler.start()  # samples the pre-roll, the warm-up, the timed steps and the passes after
-    pre_steps, pre_s = job.preroll(PREROLL_SECONDS)
+    pre_steps, pre_s = job.preroll(args.preroll_s) if args.preroll_s > 0 else (0, 0.0)
     job.timed_steps(W, flush)  # warm-up with the flush in place
     res = job.measure(K, flush)
     clocks_main = sampler.stop()
@@ -701,6 +701,8 @@ def main():
     ap.add_argument("--no-c3", action="store_true", help="N > 1: skip the extra pass at global beam 262 144")
     ap.add_argument("--no-parity", action="store_true", help="skip the untimed oracle check")
     ap.add_argument("--no-cpu", action="store_true", help="N = 1: skip the CPU baseline leg")
+    ap.add_argument("--preroll-s", type=float, default=PREROLL_SECONDS,
+                    help="seconds of untimed steps before the warm-up (0 for a short run under a profiler)")
     ap.add_argument("--beam-per-gpu", type=int, default=0, help="cases c4/c5/c2q")
     ap.add_argument("--hash-mode", default="fnv", choices=["fnv", "zobrist128"], help="cases c4/c5/c2q")
     ap.add_argument("--rows", type=int, default=151552, help="case scorer")

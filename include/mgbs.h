@@ -31,6 +31,7 @@ extern "C" {
 #define MGBS_MAX_FANOUT 32
 #define MGBS_MAX_STATE_LEN 128
 #define MGBS_MAX_MODELS 4
+#define MGBS_MAX_RES_BLOCKS 4
 
 /* select modes */
 #define MGBS_SELECT_EXACT_K 0      /* keep the first beam entries of the (score, hash, fingerprint) order */
@@ -401,14 +402,17 @@ int mgbs_mlp_enqueue(void* mlp, const uint8_t* children, const uint32_t* count_d
  * move (scorers.py:1-57: uint8 [B, n] -> [B, fanout]; FullBeamNiceStaticBackend::forward, beam_engine.cpp:621-667:
  * embedding + ReLU, two hidden layers, output layer of width fanout).  Candidate parent*fanout + move takes
  * q[parent][move]; keys as for the value scorers.  Network: one-hot(state_len x num_values) -> hidden1 (ReLU) ->
- * hidden2 (ReLU) -> fanout, bf16 operands, float32 accumulation; hidden1 and hidden2 multiples of 256; ensemble
- * members are averaged.  All buffers are the caller's. */
+ * hidden2 (ReLU) -> [residual blocks] -> fanout, bf16 operands, float32 accumulation; hidden1 and hidden2 multiples
+ * of 256; ensemble members are averaged.  All buffers are the caller's. */
 typedef struct MgbsQmlpConfig {
   int32_t state_len, state_stride, num_values, fanout, hidden1, hidden2, num_models;
   int32_t k1_pad;        /* state_len*num_values rounded up to a multiple of 64 */
   int64_t max_parents;   /* capacity in parent rows; h1, h2, q hold max_parents rounded up to 128 rows */
   float score_offset;
-  int32_t pad0;
+  /* 0: key = uint32(clamp(q - score_offset, 0, 300) * 256 + 0.5) (kernel_fullbeamnice_q_to_score_key_ring,
+   * beam_kernels.cu:326-346).  1, 2: the 16-bit higher-is-better scores of QuantizedActionScorer (scorers.py:38-53),
+   * sigmoid_u16 and float_u16, as key = 65535 - score. */
+  int32_t key_mode;
   void* h1;              /* bf16 [rows_pad, hidden1] */
   void* h2;              /* bf16 [rows_pad, hidden2] */
   float* q;              /* f32 [rows_pad, fanout] */
@@ -419,6 +423,19 @@ typedef struct MgbsQmlpConfig {
   const float* b2[MGBS_MAX_MODELS];
   const void* w3[MGBS_MAX_MODELS];  /* bf16 [256, hidden2]: rows >= fanout are zero */
   const float* b3[MGBS_MAX_MODELS]; /* f32 [256]: entries >= fanout are zero */
+  /* Residual form (the reference's static network, scripts/static_fullbeamnice_inference.py:146-171 and
+   * FullBeamNiceStaticBackend::forward, beam_engine.cpp:621-667): after hidden2, num_res_blocks blocks of
+   * x = relu(relu(x Wa^T + ba) Wb^T + bb + x) with square hidden2 x hidden2 layers, then the output layer. */
+  int32_t num_res_blocks;           /* 0 .. MGBS_MAX_RES_BLOCKS */
+  /* 1: the first layer is an embedding sum over w1t (for vocabularies too wide for the one-hot contraction;
+   * kernel_fullbeamnice_embed_relu, beam_kernels.cu:208-237); w1 and k1_pad are then unused. */
+  int32_t embed_sum;
+  int32_t activation;               /* hidden layers: 0 ReLU, 1 GELU (MLPActionScorer, scorers.py:21-36; embed_sum only) */
+  int32_t pad1;
+  void* h3;                         /* bf16 [rows_pad, hidden2]: scratch of the residual blocks (num_res_blocks > 0) */
+  const void* w1t[MGBS_MAX_MODELS]; /* embed_sum: bf16 [state_len * num_values, hidden1], row = pos * num_values + value */
+  const void* wr[2 * MGBS_MAX_RES_BLOCKS][MGBS_MAX_MODELS];  /* bf16 [hidden2, hidden2]: block b uses 2b (first), 2b+1 */
+  const float* br[2 * MGBS_MAX_RES_BLOCKS][MGBS_MAX_MODELS]; /* f32 [hidden2] */
 } MgbsQmlpConfig;
 typedef struct MgbsQmlp MgbsQmlp;
 int mgbs_sizeof_qmlp_config(void);

@@ -515,7 +515,9 @@ class BeamEngine:
         weight dictionary (keys embed_w_t ... out_bias, action_perm; scripts/static_fullbeamnice_inference.py:59-185).
         See scorers.fullbeamnice_scorer_from_static_weights."""
         from . import scorers
-        sc = scorers.fullbeamnice_scorer_from_static_weights(weights, self.cfg, self._sizes)
+        sc = scorers.fullbeamnice_scorer_from_static_weights(
+            weights, int(self.cfg["state_len"]), int(self.cfg["state_size_bytes"]), int(self.cfg["fanout"]),
+            max_parents=int(self._sizes["n_local"]), score_offset=float(self.cfg.get("score_offset", 0.0)))
         self.set_scorer(sc)
 
     def enable_debug(self, verbose: bool = False, print_counters: bool = False, log_period: int = 0) -> None:

@@ -38,13 +38,15 @@ struct GemmArgs {
   const float* col_scale;     // fp8 only: [n_total] dequantisation factor of each output column
   const float* w_out;         // EPI 1: [n_total] weights of the scalar head
   __nv_bfloat16* out_bf16;    // EPI 0: [rows, n_total]
+  const __nv_bfloat16* resid = nullptr;  // EPI 0: [rows, n_total] added before the ReLU, or null (may alias out_bf16)
+  int32_t gelu = 0;           // EPI 0: GELU instead of ReLU
   float* out_q;               // EPI 1: [rows]
   int32_t accumulate_q;       // EPI 1, 2: add to out_q instead of overwriting (ensemble members after the first)
   int32_t q_cols;             // EPI 2: output columns kept (the fan-out); out_q is [rows, q_cols]
   int* err;
 };
 
-// EPI 0: out = bf16(relu(acc + bias)).  EPI 1: q[row] (+)= sum_n relu(acc + bias[n]) * w_out[n].
+// EPI 0: out = bf16(relu(acc + bias (+ resid))).  EPI 1: q[row] (+)= sum_n relu(acc + bias[n]) * w_out[n].
 // EPI 2: q[row, n] (+)= acc + bias[n] for n < q_cols (output layer of an action-value network: one value per move).
 template <int EPI, int F8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -163,10 +165,26 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
           const int n0 = nc * BN + c0;
           if (EPI == 0) {
             uint32_t packed[16];
+            if (g.resid != nullptr && row_ok) {  // each thread reads the 32 values it is about to overwrite
+              const uint4* src = reinterpret_cast<const uint4*>(g.resid + row * g.n_total + n0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 r4 = src[q];
+                const uint32_t rw[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rw[t]));
+                  v[8 * q + 2 * t] = __float_as_uint(__uint_as_float(v[8 * q + 2 * t]) + f.x);
+                  v[8 * q + 2 * t + 1] = __float_as_uint(__uint_as_float(v[8 * q + 2 * t + 1]) + f.y);
+                }
+              }
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const float x0 = fmaxf(__uint_as_float(v[2 * j]) + __ldg(g.bias + n0 + 2 * j), 0.f);
-              const float x1 = fmaxf(__uint_as_float(v[2 * j + 1]) + __ldg(g.bias + n0 + 2 * j + 1), 0.f);
+              const float a0 = __uint_as_float(v[2 * j]) + __ldg(g.bias + n0 + 2 * j);
+              const float a1 = __uint_as_float(v[2 * j + 1]) + __ldg(g.bias + n0 + 2 * j + 1);
+              const float x0 = g.gelu ? gelu_erf(a0) : fmaxf(a0, 0.f);
+              const float x1 = g.gelu ? gelu_erf(a1) : fmaxf(a1, 0.f);
               __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
               packed[j] = *reinterpret_cast<uint32_t*>(&h);
             }
@@ -424,6 +442,7 @@ struct L1Args {
   int32_t n, stride, V;
   int32_t n_total;           // hidden (multiple of BN)
   int32_t k_total;           // n*V rounded up to the K-block width (64 bf16 / 128 e4m3)
+  int32_t k_real;            // n*V: one-hot columns that can be non-zero; MMA steps entirely beyond it are skipped
   const float* bias;
   const float* col_scale;    // fp8 only: [n_total] dequantisation factor of each W1 output channel
   float out_inv_scale;       // fp8 only: activations are stored as e4m3(value * out_inv_scale)
@@ -555,16 +574,20 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
             tc_fence_after();
             const uint64_t adesc = make_desc_sw128(smem_u32(a_ring + sa * A_BYTES));
             const uint64_t bdesc = make_desc_sw128(smem_u32(b_ring + sb * BSB));
+            // the last K-block is mostly padding (324 one-hot columns in 384): its all-zero steps add nothing
+            constexpr int KSTEP = BKE / (BK / UMMA_K);  // one-hot columns per MMA step: 16 (bf16) or 32 (e4m3)
+            int ksteps = (g.k_real - kb * BKE + KSTEP - 1) / KSTEP;
+            ksteps = ksteps < 1 ? 1 : (ksteps > BK / UMMA_K ? BK / UMMA_K : ksteps);
             if (PAIR) {
 #pragma unroll
               for (int k = 0; k < BK / UMMA_K; ++k)
-                tc_mma_pair<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
+                if (k < ksteps) tc_mma_pair<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
               if (!resident || nc == n_chunks - 1) tc_commit_pair(a_empty(sa), (uint16_t)3);
               tc_commit_pair(b_empty(sb), (uint16_t)3);
             } else {
 #pragma unroll
               for (int k = 0; k < BK / UMMA_K; ++k)
-                tc_mma<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
+                if (k < ksteps) tc_mma<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
               if (!resident || nc == n_chunks - 1) tc_commit(a_empty(sa));
               tc_commit(b_empty(sb));
             }
@@ -903,6 +926,52 @@ __global__ void __launch_bounds__(256) k_onehot(const uint8_t* __restrict__ chil
   }
 }
 
+// First layer as an embedding sum, for vocabularies too wide for a one-hot contraction (the reference's 120 values
+// per position give K = 14400; kernel_fullbeamnice_embed_relu, beam_kernels.cu:208-237, is the same operation):
+//   out[row, h] = bf16(act(bias[h] + sum_pos table[(pos * V + state[pos]) * hidden + h])), float32 accumulation.
+// One thread owns 8 adjacent columns of one row, so the threads of a row read one contiguous table row per
+// position (16 bytes each); the table (n * V * hidden bf16: 44 MB at 120 x 120 x 1536) stays in L2.
+__global__ void __launch_bounds__(256) k_embed_relu(const uint8_t* __restrict__ states, const uint32_t* count_dev,
+                                                    int64_t row_limit, int n, int stride, int V, int hidden,
+                                                    const __nv_bfloat16* __restrict__ table,
+                                                    const float* __restrict__ bias, int gelu,
+                                                    __nv_bfloat16* __restrict__ out) {
+  int64_t rows = (int64_t)(*count_dev);
+  if (rows > row_limit) rows = row_limit;
+  const int chunks = hidden / 8;
+  const int64_t total = rows * chunks;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / chunks;
+    const int c0 = (int)(i - r * chunks) * 8;
+    const uint8_t* row = states + r * stride;
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = __ldg(bias + c0 + j);
+#pragma unroll 4
+    for (int pos = 0; pos < n; ++pos) {
+      int v = __ldg(row + pos);
+      v = v < V ? v : V - 1;  // a value outside the vocabulary must not read outside the table
+      const uint4 t4 = __ldg(reinterpret_cast<const uint4*>(table + ((int64_t)pos * V + v) * hidden + c0));
+      const uint32_t tw[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&tw[t]));
+        acc[2 * t] += f.x;
+        acc[2 * t + 1] += f.y;
+      }
+    }
+    uint32_t w[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float x0 = gelu ? gelu_erf(acc[2 * t]) : fmaxf(acc[2 * t], 0.f);
+      const float x1 = gelu ? gelu_erf(acc[2 * t + 1]) : fmaxf(acc[2 * t + 1], 0.f);
+      __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+      w[t] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(out + r * hidden + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 // q (mean over ensemble members) -> u32 key = uint32(clamp(q - offset, 0, 300) * 256 + 0.5)
 // (kernel_fullbeamnice_q_to_score_key_ring, beam_kernels.cu:341-344)
 __global__ void __launch_bounds__(256) k_q_to_key(const float* __restrict__ q, const uint32_t* count_dev, float inv_models,
@@ -917,13 +986,23 @@ __global__ void __launch_bounds__(256) k_q_to_key(const float* __restrict__ q, c
 
 // Action values [parents, fanout] (summed over ensemble members) -> score keys of the candidates; candidate
 // c = parent * fanout + move reads q[c], so the two arrays share one index.
+// key_mode 1, 2: the reference's 16-bit "higher is better" scores (QuantizedActionScorer, scorers.py:38-53:
+// sigmoid_u16 = round(sigmoid(y) * 65535), float_u16 = round(y), both clamped to 0..65535) turned into keys by
+// key = 65535 - score, so that the order of the legacy engine (larger score first) is kept.
 __global__ void __launch_bounds__(256) k_qa_to_key(const float* __restrict__ q, const int32_t* parents_dev, int fanout,
-                                                   float inv_models, float offset, uint32_t* __restrict__ keys) {
+                                                   float inv_models, float offset, int key_mode,
+                                                   uint32_t* __restrict__ keys) {
   const int64_t total = (int64_t)(*parents_dev) * fanout;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    float x = q[i] * inv_models - offset;
-    x = fminf(fmaxf(x, 0.f), 300.f);
-    keys[i] = (uint32_t)(x * 256.f + 0.5f);
+    float x = q[i] * inv_models;
+    if (key_mode == 0) {
+      x = fminf(fmaxf(x - offset, 0.f), 300.f);
+      keys[i] = (uint32_t)(x * 256.f + 0.5f);
+    } else {
+      if (key_mode == 1) x = 65535.f / (1.f + expf(-x));
+      x = fminf(fmaxf(rintf(x), 0.f), 65535.f);
+      keys[i] = 65535u - (uint32_t)x;
+    }
   }
 }
 
@@ -1149,6 +1228,7 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
       l.n = c.state_len; l.stride = c.state_stride; l.V = c.num_values;
       l.n_total = c.hidden;
       l.k_total = m->k1_pad;
+      l.k_real = c.state_len * c.num_values;
       l.bias = c.b1[i];
       l.col_scale = c.s1[i];
       l.out_inv_scale = c.act_inv_scale;
@@ -1261,8 +1341,9 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
 struct MgbsQmlp {
   MgbsQmlpConfig cfg;
   int sms = 148;
-  CUtensorMap tm_h1, tm_h1w, tm_h2;
+  CUtensorMap tm_h1, tm_h1w, tm_h2, tm_h3;
   CUtensorMap tm_w1[MGBS_MAX_MODELS], tm_w2[MGBS_MAX_MODELS], tm_w3[MGBS_MAX_MODELS];
+  CUtensorMap tm_wr[2 * MGBS_MAX_RES_BLOCKS][MGBS_MAX_MODELS];
 };
 
 extern "C" {
@@ -1278,9 +1359,13 @@ int mgbs_qmlp_create(const MgbsQmlpConfig* cfg, MgbsQmlp** out) {
   if (c.num_models < 1 || c.num_models > MGBS_MAX_MODELS || c.max_parents < 1) return MGBS_ERR_ARG;
   const int k1 = c.state_len * c.num_values;
   const int k1_pad = (k1 + mgbs::BK - 1) / mgbs::BK * mgbs::BK;
-  if (c.k1_pad != k1_pad || k1_pad / mgbs::BK > mgbs::L1_MAX_KBLOCKS) return MGBS_ERR_ARG;
+  if (c.embed_sum != 0 && c.embed_sum != 1) return MGBS_ERR_ARG;
+  if (c.key_mode < 0 || c.key_mode > 2 || c.activation < 0 || c.activation > 1) return MGBS_ERR_ARG;
+  if (c.activation == 1 && !c.embed_sum) return MGBS_ERR_UNSUPPORTED;  // the one-hot contraction kernel is ReLU only
+  if (!c.embed_sum && (c.k1_pad != k1_pad || k1_pad / mgbs::BK > mgbs::L1_MAX_KBLOCKS)) return MGBS_ERR_ARG;
   if (c.state_stride < c.state_len || c.state_stride % 16 != 0 || c.state_stride > MGBS_MAX_STATE_LEN) return MGBS_ERR_ARG;
   if (!c.h1 || !c.h2 || !c.q || !c.err) return MGBS_ERR_ARG;
+  if (c.num_res_blocks < 0 || c.num_res_blocks > MGBS_MAX_RES_BLOCKS || (c.num_res_blocks > 0 && !c.h3)) return MGBS_ERR_ARG;
   MgbsQmlp* m = new (std::nothrow) MgbsQmlp();
   if (!m) return MGBS_ERR_STATE;
   m->cfg = c;
@@ -1293,11 +1378,16 @@ int mgbs_qmlp_create(const MgbsQmlpConfig* cfg, MgbsQmlp** out) {
   int rc = make_map_bf16(&m->tm_h1, c.h1, rows_pad, (uint64_t)c.hidden1, mgbs::BM);
   if (!rc) rc = mgbs::make_map_box(&m->tm_h1w, c.h1, rows_pad, (uint64_t)c.hidden1, 32, 32, 2, 64);
   if (!rc) rc = make_map_bf16(&m->tm_h2, c.h2, rows_pad, (uint64_t)c.hidden2, mgbs::BM);
+  if (!rc && c.num_res_blocks > 0) rc = make_map_bf16(&m->tm_h3, c.h3, rows_pad, (uint64_t)c.hidden2, mgbs::BM);
   for (int i = 0; i < c.num_models && !rc; ++i) {
-    if (!c.w1[i] || !c.b1[i] || !c.w2[i] || !c.b2[i] || !c.w3[i] || !c.b3[i]) { rc = MGBS_ERR_ARG; break; }
-    rc = make_map_bf16(&m->tm_w1[i], c.w1[i], (uint64_t)c.hidden1, (uint64_t)k1_pad, mgbs::BN);
+    if (!(c.embed_sum ? c.w1t[i] : c.w1[i]) || !c.b1[i] || !c.w2[i] || !c.b2[i] || !c.w3[i] || !c.b3[i]) { rc = MGBS_ERR_ARG; break; }
+    if (!c.embed_sum) rc = make_map_bf16(&m->tm_w1[i], c.w1[i], (uint64_t)c.hidden1, (uint64_t)k1_pad, mgbs::BN);
     if (!rc) rc = make_map_bf16(&m->tm_w2[i], c.w2[i], (uint64_t)c.hidden2, (uint64_t)c.hidden1, mgbs::BN);
     if (!rc) rc = make_map_bf16(&m->tm_w3[i], c.w3[i], (uint64_t)mgbs::BN, (uint64_t)c.hidden2, mgbs::BN);
+    for (int l = 0; l < 2 * c.num_res_blocks && !rc; ++l) {
+      if (!c.wr[l][i] || !c.br[l][i]) { rc = MGBS_ERR_ARG; break; }
+      rc = make_map_bf16(&m->tm_wr[l][i], c.wr[l][i], (uint64_t)c.hidden2, (uint64_t)c.hidden2, mgbs::BN);
+    }
   }
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<2, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
@@ -1329,11 +1419,19 @@ int mgbs_qmlp_enqueue(void* user, const uint8_t* parents, const int32_t* parent_
     l.n = c.state_len; l.stride = c.state_stride; l.V = c.num_values;
     l.n_total = c.hidden1;
     l.k_total = c.k1_pad;
+    l.k_real = c.state_len * c.num_values;
     l.bias = c.b1[i];
     l.col_scale = nullptr;
     l.out_inv_scale = 1.f;
+    l.sf_out = nullptr;
+    l.inv_global = 0.f;
     l.err = c.err;
-    k_mlp_l1<0, 4, 0><<<grid, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
+    if (c.embed_sum)
+      k_embed_relu<<<m->sms * 8, 256, 0, st>>>(parents, count_dev, c.max_parents, c.state_len, c.state_stride, c.num_values,
+                                               c.hidden1, reinterpret_cast<const __nv_bfloat16*>(c.w1t[i]), c.b1[i],
+                                               c.activation, reinterpret_cast<__nv_bfloat16*>(c.h1));
+    else
+      k_mlp_l1<0, 4, 0><<<grid, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
     GemmArgs g;
     g.count_dev = count_dev;
     g.row_offset = 0;
@@ -1347,8 +1445,21 @@ int mgbs_qmlp_enqueue(void* user, const uint8_t* parents, const int32_t* parent_
     g.out_q = nullptr;
     g.accumulate_q = 0;
     g.q_cols = 0;
+    g.gelu = c.activation;
     g.err = c.err;
     k_mlp_gemm<0, 0><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h1, m->tm_w2[i], g);
+    for (int b = 0; b < c.num_res_blocks; ++b) {  // x (in h2) = relu(relu(x Wa^T + ba) Wb^T + bb + x), h3 in between
+      g.k_total = c.hidden2;
+      g.bias = c.br[2 * b][i];
+      g.out_bf16 = reinterpret_cast<__nv_bfloat16*>(c.h3);
+      g.resid = nullptr;
+      k_mlp_gemm<0, 0><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h2, m->tm_wr[2 * b][i], g);
+      g.bias = c.br[2 * b + 1][i];
+      g.out_bf16 = reinterpret_cast<__nv_bfloat16*>(c.h2);
+      g.resid = reinterpret_cast<const __nv_bfloat16*>(c.h2);  // in place: A is h3, each thread adds what it overwrites
+      k_mlp_gemm<0, 0><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h3, m->tm_wr[2 * b + 1][i], g);
+    }
+    g.resid = nullptr;
     g.n_total = BN;  // output layer padded to one 256-column chunk
     g.k_total = c.hidden2;
     g.bias = c.b3[i];
@@ -1359,7 +1470,7 @@ int mgbs_qmlp_enqueue(void* user, const uint8_t* parents, const int32_t* parent_
     k_mlp_gemm<2, 0><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_h2, m->tm_w3[i], g);
   }
   k_qa_to_key<<<m->sms * 4, 256, 0, st>>>(c.q, parent_count_dev, c.fanout, 1.f / (float)c.num_models, c.score_offset,
-                                          cand_scores);
+                                          c.key_mode, cand_scores);
   return (int)cudaGetLastError();
 }
 

@@ -9,7 +9,7 @@ by hand-written tcgen05 GEMM kernels inside libmgbs_b200.so; this module only pr
 from __future__ import annotations
 
 import ctypes as C
-from typing import Dict, List, Sequence, Union
+from typing import Any, Dict, List, Optional, Sequence, Union
 
 import numpy as np
 import torch
@@ -300,14 +300,22 @@ class MLPValueScorer:
 # ----------------------------------------------------------------------------------------------
 
 
+MAX_RES_BLOCKS = 4
+KEY_MODES = ("q", "sigmoid_u16", "float_u16")  # MgbsQmlpConfig.key_mode
+
+
 class MgbsQmlpConfig(C.Structure):
     _fields_ = [
         ("state_len", C.c_int32), ("state_stride", C.c_int32), ("num_values", C.c_int32), ("fanout", C.c_int32),
         ("hidden1", C.c_int32), ("hidden2", C.c_int32), ("num_models", C.c_int32), ("k1_pad", C.c_int32),
-        ("max_parents", C.c_int64), ("score_offset", C.c_float), ("pad0", C.c_int32),
+        ("max_parents", C.c_int64), ("score_offset", C.c_float), ("key_mode", C.c_int32),
         ("h1", C.c_void_p), ("h2", C.c_void_p), ("q", C.c_void_p), ("err", C.c_void_p),
         ("w1", C.c_void_p * MAX_MODELS), ("b1", C.c_void_p * MAX_MODELS), ("w2", C.c_void_p * MAX_MODELS),
         ("b2", C.c_void_p * MAX_MODELS), ("w3", C.c_void_p * MAX_MODELS), ("b3", C.c_void_p * MAX_MODELS),
+        ("num_res_blocks", C.c_int32), ("embed_sum", C.c_int32), ("activation", C.c_int32), ("pad1", C.c_int32),
+        ("h3", C.c_void_p),
+        ("w1t", C.c_void_p * MAX_MODELS),
+        ("wr", (C.c_void_p * MAX_MODELS) * (2 * MAX_RES_BLOCKS)), ("br", (C.c_void_p * MAX_MODELS) * (2 * MAX_RES_BLOCKS)),
     ]
 
 
@@ -326,12 +334,23 @@ class MLPActionValueScorer:
     scorer contract (scorers.MLPActionScorer, scorers.py:21-36: uint8 [B, n] in, [B, fanout] out; the static
     FullBeamNice backend has the same shape, beam_engine.cpp:621-667); it costs 1/fanout of the value scorers' forward
     passes.  Weights: dicts with w1 [H1, n*V], b1, w2 [H2, H1], b2, w3 [fanout, H2], b3 [fanout]; bf16 operands, float32
-    accumulation; members are averaged; keys as in the value scorers."""
+    accumulation; members are averaged; keys as in the value scorers.
+
+    Residual form (the reference's static network, scripts/static_fullbeamnice_inference.py:146-171): an optional
+    ``res`` entry in each dict, a list of (wa [H2, H2], ba, wb [H2, H2], bb) per block, inserts
+    x = relu(relu(x wa^T + ba) wb^T + bb + x) between hidden2 and the output layer.  ``embed_sum=True`` evaluates
+    the first layer as a sum of table rows (one per position) instead of a one-hot contraction: the form for wide
+    vocabularies (kernel_fullbeamnice_embed_relu, beam_kernels.cu:208-237); it is chosen automatically when the
+    one-hot width exceeds what the contraction kernel holds in shared memory.  ``activation="gelu"`` (embedding-sum
+    form only) and ``key_mode`` "sigmoid_u16" / "float_u16" serve the reference's MLPActionScorer /
+    QuantizedActionScorer (scorers.py:21-53); see action_scorer_to_device."""
 
     scores_parents = True
+    ONE_HOT_MAX_K = 1024  # widest one-hot first layer of the contraction kernel (16 K-blocks of 64)
 
     def __init__(self, weights, state_len: int, state_stride: int, num_values: int, fanout: int, max_parents: int,
-                 score_offset: float = -150.0, device=None):
+                 score_offset: float = -150.0, device=None, embed_sum: Optional[bool] = None,
+                 activation: str = "relu", key_mode: str = "q"):
         self.lib = _lib.load()
         for name, (res, args) in _Q_SIGS.items():
             fn = getattr(self.lib, name)
@@ -354,16 +373,42 @@ class MLPActionValueScorer:
         cfg.state_len, cfg.state_stride, cfg.num_values, cfg.fanout = state_len, state_stride, num_values, fanout
         cfg.hidden1, cfg.hidden2, cfg.num_models, cfg.k1_pad = h1, h2, len(weights), k1_pad
         cfg.max_parents, cfg.score_offset = int(max_parents), float(score_offset)
+        blocks = len(weights[0].get("res", ()))
+        if blocks > MAX_RES_BLOCKS or any(len(w.get("res", ())) != blocks for w in weights):
+            raise RuntimeError(f"0..{MAX_RES_BLOCKS} residual blocks, the same number in every ensemble member")
+        self.num_res_blocks = blocks
+        self.embed_sum = bool(k1_pad > self.ONE_HOT_MAX_K) if embed_sum is None else bool(embed_sum)
+        cfg.num_res_blocks, cfg.embed_sum = blocks, int(self.embed_sum)
+        if activation not in ("relu", "gelu") or key_mode not in KEY_MODES:
+            raise RuntimeError("activation is relu or gelu; key_mode is one of " + ", ".join(KEY_MODES))
+        if activation == "gelu" and not self.embed_sum:
+            raise RuntimeError("GELU layers need embed_sum=True (the one-hot contraction kernel applies ReLU)")
+        cfg.activation, cfg.key_mode = int(activation == "gelu"), KEY_MODES.index(key_mode)
+        self.activation, self.key_mode = activation, key_mode
 
         def keep(t):
             self._keep.append(t)
             return t.data_ptr()
 
+        def bf16(a):
+            return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dev).to(torch.bfloat16).contiguous()
+
+        def f32(a):
+            return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dev)
+
         for i, w in enumerate(weights):
             if w["w1"].shape != (h1, k1) or w["w2"].shape != (h2, h1) or w["w3"].shape != (fanout, h2):
                 raise RuntimeError("weight shapes do not match the puzzle")
-            w1 = torch.zeros((h1, k1_pad), dtype=torch.bfloat16, device=dev)
-            w1[:, :k1] = torch.from_numpy(np.ascontiguousarray(w["w1"], dtype=np.float32)).to(dev).to(torch.bfloat16)
+            for l, (wa, ba, wb, bb) in enumerate(w.get("res", ())):
+                if wa.shape != (h2, h2) or wb.shape != (h2, h2) or ba.shape != (h2,) or bb.shape != (h2,):
+                    raise RuntimeError("residual blocks must be square in hidden2")
+                cfg.wr[2 * l][i], cfg.br[2 * l][i] = keep(bf16(wa)), keep(f32(ba))
+                cfg.wr[2 * l + 1][i], cfg.br[2 * l + 1][i] = keep(bf16(wb)), keep(f32(bb))
+            if self.embed_sum:
+                cfg.w1t[i] = keep(bf16(np.ascontiguousarray(np.asarray(w["w1"], dtype=np.float32).T)))  # [n*V, H1]
+            w1 = torch.zeros((h1, k1_pad if not self.embed_sum else 64), dtype=torch.bfloat16, device=dev)
+            if not self.embed_sum:
+                w1[:, :k1] = bf16(w["w1"])
             w3 = torch.zeros((256, h2), dtype=torch.bfloat16, device=dev)
             w3[:fanout] = torch.from_numpy(np.ascontiguousarray(w["w3"], dtype=np.float32)).to(dev).to(torch.bfloat16)
             b3 = torch.zeros((256,), dtype=torch.float32, device=dev)
@@ -374,6 +419,9 @@ class MLPActionValueScorer:
             cfg.b2[i] = keep(torch.from_numpy(np.ascontiguousarray(w["b2"], dtype=np.float32)).to(dev))
         self.h1 = torch.zeros((rows_pad, h1), dtype=torch.bfloat16, device=dev)
         self.h2 = torch.zeros((rows_pad, h2), dtype=torch.bfloat16, device=dev)
+        if blocks:
+            self.h3 = torch.zeros((rows_pad, h2), dtype=torch.bfloat16, device=dev)
+            cfg.h3 = self.h3.data_ptr()
         self.q = torch.zeros((rows_pad, fanout), dtype=torch.float32, device=dev)
         self.err = torch.zeros((1,), dtype=torch.int32, device=dev)
         self._count = torch.zeros((1,), dtype=torch.int32, device=dev)
@@ -395,7 +443,9 @@ class MLPActionValueScorer:
     def flops_per_state(self) -> int:
         """Per CANDIDATE: one parent pass serves fanout candidates."""
         k1 = self.state_len * self.num_values
-        per_parent = 2 * (k1 * self.hidden1 + self.hidden1 * self.hidden2 + self.hidden2 * self.fanout)
+        first = self.state_len * self.hidden1 if self.embed_sum else 2 * k1 * self.hidden1  # adds only, as a sum
+        per_parent = first + 2 * (self.hidden1 * self.hidden2 + 2 * self.num_res_blocks * self.hidden2 * self.hidden2
+                                  + self.hidden2 * self.fanout)
         return self.num_models * per_parent // self.fanout
 
     def score(self, parents: torch.Tensor) -> torch.Tensor:
@@ -418,6 +468,176 @@ class MLPActionValueScorer:
 
     def error_code(self) -> int:
         return int(self.err.item())
+
+
+class MLPActionScorer(torch.nn.Module):
+    """The reference's trainable action scorer with the same constructor and contract (scorers.MLPActionScorer,
+    scorers.py:21-36): uint8 [B, input_dim] -> float [B, fanout]; the bytes are scaled by 1/value_scale (119 in the
+    reference, its largest state value), then Linear + GELU per hidden size and a Linear to fanout.  A torch module
+    for training and export; the engine runs it through action_scorer_to_device."""
+
+    def __init__(self, input_dim: int = 120, hidden_sizes: Sequence[int] = (1024, 256), fanout: int = 24,
+                 value_scale: float = 119.0):
+        super().__init__()
+        sizes = [int(input_dim)] + [int(h) for h in hidden_sizes]
+        self.linears = torch.nn.ModuleList(torch.nn.Linear(a, b) for a, b in zip(sizes[:-1], sizes[1:]))
+        self.out = torch.nn.Linear(sizes[-1], int(fanout))
+        self.value_scale = float(value_scale)
+
+    def forward(self, states_u8: torch.Tensor) -> torch.Tensor:
+        x = states_u8.to(torch.float32) / self.value_scale
+        for lin in self.linears:
+            x = torch.nn.functional.gelu(lin(x))
+        return self.out(x)
+
+
+class QuantizedActionScorer(torch.nn.Module):
+    """16-bit quantiser around a base scorer (scorers.QuantizedActionScorer, scorers.py:38-53): "sigmoid_u16" =
+    round(sigmoid(y) * 65535), "float_u16" = round(y), clamped to 0..65535 and returned as int16 by bit pattern
+    (values from 32768 come out negative).  Larger is better."""
+
+    def __init__(self, base: torch.nn.Module, score_mode: str = "sigmoid_u16"):
+        super().__init__()
+        if score_mode not in ("sigmoid_u16", "float_u16"):
+            raise RuntimeError("unsupported score_mode")
+        self.base, self.score_mode = base, score_mode
+
+    def forward(self, states_u8: torch.Tensor) -> torch.Tensor:
+        y = self.base(states_u8)
+        if self.score_mode == "sigmoid_u16":
+            y = torch.sigmoid(y) * 65535.0
+        q = torch.clamp(torch.round(y), 0.0, 65535.0).to(torch.int32)
+        return torch.where(q >= 32768, q - 65536, q).to(torch.int16)
+
+
+def make_default_mlp_scorer(hidden_sizes: Sequence[int] = (1024, 256), fanout: int = 24, input_dim: int = 120,
+                            value_scale: float = 119.0) -> torch.nn.Module:
+    """make_default_mlp_scorer (scorers.py:56-57): sigmoid-quantised MLPActionScorer."""
+    return QuantizedActionScorer(MLPActionScorer(input_dim, hidden_sizes, fanout, value_scale))
+
+
+def action_scorer_to_device(module: torch.nn.Module, state_len: int, state_stride: int, num_values: int,
+                            max_parents: int, device=None) -> "MLPActionValueScorer":
+    """Device scorer for an MLPActionScorer or a QuantizedActionScorer around one (two hidden layers, each a
+    multiple of 256 wide).  The dense first layer on bytes scaled by 1/value_scale is a sum of table rows
+    ``W1[:, pos] * value / value_scale`` - one per position - so it runs on the embedding-sum kernel; hidden layers
+    use GELU; a quantised wrapper selects the matching key mode (key = 65535 - its 16-bit score), a bare
+    MLPActionScorer gives keys uint32(clamp(y, 0, 300) * 256 + 0.5)."""
+    key_mode = "q"
+    base = module
+    if isinstance(module, QuantizedActionScorer):
+        key_mode, base = module.score_mode, module.base
+    if not isinstance(base, MLPActionScorer) or len(base.linears) != 2:
+        raise RuntimeError("action_scorer_to_device takes an MLPActionScorer with two hidden layers")
+    if base.linears[0].in_features != state_len:
+        raise RuntimeError(f"the scorer reads {base.linears[0].in_features} bytes per state, the puzzle has {state_len}")
+    w1 = _np(base.linears[0].weight)  # [H1, n]
+    values = (np.arange(num_values, dtype=np.float32) / np.float32(base.value_scale))
+    table = (w1.T[:, None, :] * values[None, :, None]).reshape(state_len * num_values, w1.shape[0])  # row = pos*V + v
+    w = {"w1": np.ascontiguousarray(table.T), "b1": _np(base.linears[0].bias),
+         "w2": _np(base.linears[1].weight), "b2": _np(base.linears[1].bias),
+         "w3": _np(base.out.weight), "b3": _np(base.out.bias)}
+    return MLPActionValueScorer(w, state_len, state_stride, num_values, base.out.out_features, max_parents,
+                                score_offset=0.0, device=device, embed_sum=True, activation="gelu", key_mode=key_mode)
+
+
+def _np(t) -> np.ndarray:
+    return t.detach().float().cpu().numpy() if isinstance(t, torch.Tensor) else np.asarray(t, dtype=np.float32)
+
+
+def fold_bn_linear(weight, bias, bn_weight, bn_bias, running_mean, running_var, eps: float = 1e-5):
+    """Inference-form batch norm folded into the linear layer before it (float32): W' = W * s per output row,
+    b' = (b - mean) * s + beta with s = gamma / sqrt(var + eps) (_fold_bn_linear,
+    scripts/static_fullbeamnice_inference.py:59-71)."""
+    scale = (_np(bn_weight) / np.sqrt(_np(running_var) + np.float32(eps))).astype(np.float32)
+    w = (_np(weight) * scale[:, None]).astype(np.float32)
+    b = ((_np(bias) - _np(running_mean)) * scale + _np(bn_bias)).astype(np.float32)
+    return w, b
+
+
+def static_weights_from_state_dict(sd: Dict[str, Any], num_res_blocks: int, state_len: int, num_classes: int,
+                                   state_size: Optional[int] = None, class_pad: Optional[int] = None,
+                                   action_perm: Optional[Sequence[int]] = None) -> Dict[str, Any]:
+    """The reference's static weight dictionary from a trained module's state dict (load_static_weights,
+    scripts/static_fullbeamnice_inference.py:74-143): batch norms folded into input_layer, hidden_layer and every
+    residual_blocks.{i}.fc{1,2}; matrices transposed to [in, out]; the embedding re-laid from ``num_classes`` rows
+    per position to ``class_pad`` rows per position over ``state_size`` positions (the reference pads 120 x 120 to
+    128 x 128), new rows zero."""
+    state_size = int(state_size or state_len)
+    class_pad = int(class_pad or num_classes)
+    embed = _np(sd["input_layer.weight"])
+    hd1 = _np(sd["input_layer.bias"]).shape[0]
+    if embed.shape[0] == hd1 and embed.shape[1] == state_len * num_classes:
+        embed = np.ascontiguousarray(embed.T)  # stored [out, in]
+    if embed.shape != (state_len * num_classes, hd1):
+        raise RuntimeError(f"input_layer.weight has shape {embed.shape}, expected {(state_len * num_classes, hd1)}")
+    table = np.zeros((state_size * class_pad, hd1), dtype=np.float32)
+    for pos in range(state_len):
+        table[pos * class_pad: pos * class_pad + num_classes] = embed[pos * num_classes: (pos + 1) * num_classes]
+    s1 = (_np(sd["bn1.weight"]) / np.sqrt(_np(sd["bn1.running_var"]) + np.float32(1e-5))).astype(np.float32)
+    out: Dict[str, Any] = {
+        "embed_w_t": table * s1[None, :],
+        "embed_bias": (_np(sd["input_layer.bias"]) - _np(sd["bn1.running_mean"])) * s1 + _np(sd["bn1.bias"]),
+    }
+    hw, hb = fold_bn_linear(sd["hidden_layer.weight"], sd["hidden_layer.bias"], sd["bn2.weight"], sd["bn2.bias"],
+                            sd["bn2.running_mean"], sd["bn2.running_var"])
+    out["hidden_w_t"], out["hidden_bias"] = np.ascontiguousarray(hw.T), hb
+    for b in range(int(num_res_blocks)):
+        pre = f"residual_blocks.{b}"
+        for fc, bn in (("fc1", "bn1"), ("fc2", "bn2")):
+            w, bias = fold_bn_linear(sd[f"{pre}.{fc}.weight"], sd[f"{pre}.{fc}.bias"], sd[f"{pre}.{bn}.weight"],
+                                     sd[f"{pre}.{bn}.bias"], sd[f"{pre}.{bn}.running_mean"], sd[f"{pre}.{bn}.running_var"])
+            out[f"res{b}_{fc}_w_t"], out[f"res{b}_{fc}_bias"] = np.ascontiguousarray(w.T), bias
+    out["out_w_t"] = np.ascontiguousarray(_np(sd["output_layer.weight"]).T)
+    out["out_bias"] = _np(sd["output_layer.bias"])
+    outputs = out["out_bias"].shape[0]
+    out["action_perm"] = np.asarray(action_perm if action_perm is not None else np.arange(outputs), dtype=np.int64)
+    out["state_size"], out["num_classes"] = state_size, class_pad
+    out["score_scale"], out["score_bias"] = 1024.0, 65535.0
+    return out
+
+
+def fullbeamnice_scorer_from_static_weights(weights: Dict[str, Any], state_len: int, state_stride: int, fanout: int,
+                                            max_parents: int, score_offset: float = 0.0, device=None,
+                                            embed_sum: Optional[bool] = None) -> "MLPActionValueScorer":
+    """Action-value scorer from the reference's static weight dictionary (keys embed_w_t, embed_bias, hidden_w_t,
+    hidden_bias, res{i}_fc{1,2}_w_t / _bias, out_w_t, out_bias, action_perm, state_size, num_classes;
+    StaticFullBeamNiceWeights, scripts/static_fullbeamnice_inference.py:36-56, consumed by
+    FullBeamNiceStaticBackend, beam_engine.cpp:556-619).
+
+    The dictionary's tables are [in, out]; they are transposed here.  Positions past ``state_len`` (the reference
+    stores 120-byte states in 128 positions, the extra ones holding value 0) contribute the constant row
+    ``embed_w_t[pos * num_classes]``, which is folded into the first bias.  The output columns are reordered by
+    ``action_perm`` (q_current = q[:, action_perm], static_forward_scores :174-178), so column m is move m of the
+    engine.  Keys are uint32(clamp(q - score_offset, 0, 300) * 256 + 0.5) as in
+    kernel_fullbeamnice_q_to_score_key_ring (beam_kernels.cu:326-346); the reference uses offset 0."""
+    size, classes = int(weights["state_size"]), int(weights["num_classes"])
+    if state_len > size:
+        raise RuntimeError(f"the weights cover {size} positions, the puzzle has {state_len}")
+    table = _np(weights["embed_w_t"])
+    h1 = table.shape[1]
+    if table.shape[0] != size * classes:
+        raise RuntimeError(f"embed_w_t has {table.shape[0]} rows, expected state_size * num_classes = {size * classes}")
+    b1 = _np(weights["embed_bias"]).astype(np.float32).copy()
+    for pos in range(state_len, size):
+        b1 += table[pos * classes]
+    perm = np.asarray(_np(weights["action_perm"]), dtype=np.int64)
+    if perm.shape[0] != fanout or sorted(perm.tolist()) != list(range(fanout)):
+        raise RuntimeError("action_perm must be a permutation of the engine's moves")
+    res = []
+    b = 0
+    while f"res{b}_fc1_w_t" in weights:
+        res.append((np.ascontiguousarray(_np(weights[f"res{b}_fc1_w_t"]).T), _np(weights[f"res{b}_fc1_bias"]),
+                    np.ascontiguousarray(_np(weights[f"res{b}_fc2_w_t"]).T), _np(weights[f"res{b}_fc2_bias"])))
+        b += 1
+    w = {
+        "w1": np.ascontiguousarray(table[: state_len * classes].T), "b1": b1,
+        "w2": np.ascontiguousarray(_np(weights["hidden_w_t"]).T), "b2": _np(weights["hidden_bias"]),
+        "w3": np.ascontiguousarray(_np(weights["out_w_t"]).T[perm]), "b3": _np(weights["out_bias"])[perm],
+        "res": res,
+    }
+    return MLPActionValueScorer(w, state_len, state_stride, classes, fanout, max_parents, score_offset=score_offset,
+                                device=device, embed_sum=embed_sum)
 
 
 # ----------------------------------------------------------------------------------------------

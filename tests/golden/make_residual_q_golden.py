@@ -5,7 +5,8 @@ Run in a container that has the reference checkout (it is imported, never copied
     python tests/golden/make_residual_q_golden.py /path/to/reference
 
 Calls the reference's ``static_forward_q``, ``static_forward_scores`` and ``_fold_bn_linear``
-(scripts/static_fullbeamnice_inference.py) on seeded random weights and states and records the outputs.  The
+(scripts/static_fullbeamnice_inference.py) and its ``MLPActionScorer`` / ``QuantizedActionScorer`` (scorers.py) on
+seeded random weights and states and records the outputs.  The
 tests rebuild weights and states from the recorded seeds with ``residual_q_weights`` / ``residual_q_states`` below, so
 only seeds, shapes and outputs are stored.
 """
@@ -45,6 +46,14 @@ def residual_q_weights(seed: int, state_size: int, num_classes: int, hidden1: in
 
 def residual_q_states(seed: int, rows: int, state_len: int, num_values: int) -> np.ndarray:
     return np.random.default_rng(seed).integers(0, num_values, size=(rows, state_len), dtype=np.uint8)
+
+
+def action_scorer_weights(seed: int, input_dim: int, hidden: tuple, fanout: int):
+    """Seeded float32 [out, in] matrices and biases of the reference's MLPActionScorer (Linear, GELU, ..., Linear)."""
+    rng = np.random.default_rng(seed)
+    sizes = [input_dim, *hidden, fanout]
+    return [((rng.standard_normal((b, a)) * (1.5 / np.sqrt(a))).astype(np.float32),
+             (rng.standard_normal(b) * 0.2).astype(np.float32)) for a, b in zip(sizes[:-1], sizes[1:])]
 
 
 def bn_case(seed: int, outs: int, ins: int):
@@ -95,6 +104,24 @@ def main() -> None:
         out["fold_bn"].append({"seed": seed, "outs": outs, "ins": ins,
                                "weight": [[float(x) for x in r] for r in fw.numpy()],
                                "bias": [float(x) for x in fb.numpy()]})
+    import scorers as ref_scorers  # the reference's scorers.py
+    out["action_scorer"] = []
+    for seed, hidden, rows in ((9701, (32, 16), 10), (9702, (48, 24), 6)):
+        layers = action_scorer_weights(seed, 120, hidden, 24)
+        base = ref_scorers.MLPActionScorer(120, hidden, 24)
+        sd = {}
+        for i, (wm, bv) in enumerate(layers):
+            sd[f"net.{2 * i}.weight"], sd[f"net.{2 * i}.bias"] = torch.from_numpy(wm), torch.from_numpy(bv)
+        base.load_state_dict(sd, strict=True)
+        states = residual_q_states(seed + 50, rows, 120, 120)
+        with torch.no_grad():
+            y = base(torch.from_numpy(states))
+            sig = ref_scorers.QuantizedActionScorer(base, "sigmoid_u16")(torch.from_numpy(states))
+            flt = ref_scorers.QuantizedActionScorer(base, "float_u16")(torch.from_numpy(states))
+        out["action_scorer"].append({"seed": seed, "hidden": list(hidden), "rows": rows,
+                                     "y": [[float(x) for x in r] for r in y.numpy()],
+                                     "sigmoid_u16": sig.numpy().astype(int).tolist(),
+                                     "float_u16": flt.numpy().astype(int).tolist()})
     dst = Path(__file__).resolve().parent / "residual_q_reference.json"
     dst.write_text(json.dumps(out, separators=(",", ":")))
     print(f"wrote {dst} ({dst.stat().st_size} bytes)")

@@ -103,3 +103,31 @@ def test_engine_create_rejects_bad_configs_without_a_gpu():
     offs = (C.c_int64 * 2)()
     assert lib.mgbs_sym_frontier_offsets(C.byref(c), offs) == 0
     assert offs[0] % 256 == 0 and offs[1] - offs[0] >= 500 * 64 and offs[1] + 500 * 64 <= nb.value
+
+
+def test_python_surface_has_the_reference_names():
+    """Every method the reference binds on BeamEngine (beam_engine.cpp:2114-2148), its module-level functions
+    (beam_engine.py) and the names of its scorers.py / production_v6_dispatcher.py exist here."""
+    from multigpubeamsearch_b200 import beam_engine as be
+    from multigpubeamsearch_b200 import production_v6_dispatcher as pd
+    from multigpubeamsearch_b200 import scorers
+    methods = ["init_nccl", "load_torchscript_ensemble", "load_fullbeamnice_static", "begin_uniform_score",
+               "set_uniform_score", "end_uniform_score", "warmup_inference", "benchmark_inference",
+               "set_action_permutation_table", "set_central_state", "reset_search", "clear_runtime_state",
+               "enable_cuda_graphs", "cuda_graph_captured", "enable_step_timers", "step_timing", "set_active_limit",
+               "set_next_limit", "clear_logical_limits", "enable_debug", "step", "step_current", "step_prepass_fast",
+               "set_prepass_light_solved_scan", "search", "status", "history_entry", "current_state_bytes", "sizes"]
+    missing = [m for m in methods if not callable(getattr(be.BeamEngine, m, None))]
+    assert not missing, missing
+    for name in ("build_extension", "configure_engine", "allocate_buffers", "make_default_config", "init_distributed_if_needed",
+                 "create_nccl_id", "make_shallow_scramble", "run_one_search"):
+        assert callable(getattr(be, name, None)), name
+    for name in ("MLPActionScorer", "QuantizedActionScorer", "make_default_mlp_scorer"):
+        assert callable(getattr(scorers, name, None)), name
+    assert callable(pd.ProductionV6Dispatcher.run_task)
+    fields = set(pd.ProductionV6Result.__dataclass_fields__)
+    assert {"task_id", "status", "path", "depth_rows", "solved_depth", "solved_rank", "solved_parent_idx",
+            "solved_move", "raw_solved_record_exists", "path_replay_valid", "path_failure_reason"} <= fields
+    for key in ("k_expand_tile", "score_ring_depth", "net_ring_depth", "inference_parallelism",
+                "histogram_period_micro", "beta", "hash_load_factor", "probe_limit", "global_beam_width"):
+        assert key in be.make_default_config(), key

@@ -564,3 +564,51 @@ def test_zobrist_hash_mode_matches_oracle(name, count, beam):
         engine.cfg["world_size"] = w
         assert engine.owner_of(frontier[0]) == int(bo.owner_from_hash128(hi0, lo0, w)[0])
     engine.cfg["world_size"] = 1
+
+
+@pytest.mark.parametrize("select_mode,hash_mode", [("v6_inclusive", "zobrist128"), ("exact_k", "hash64")])
+def test_production_v6_dispatcher_runs_tasks(select_mode, hash_mode):
+    """ProductionV6Dispatcher.run_task (production_v6_dispatcher.py:708-868): one object, several start states; the
+    result carries the reference's fields, a path that replays to the solved state, and one row per depth with the
+    reference's keys.  The start state itself and a state one move away are the reference's own known answers
+    (scripts/kaggle_correctness_check.py:154-179: depths 0, 1, 2)."""
+    from multigpubeamsearch_b200.production_v6_dispatcher import ProductionV6Dispatcher, replay_path_to_central
+    pz = puzzles.puzzle54()
+    disp = ProductionV6Dispatcher(0, 1, torch.device("cuda", 0), beam_width=2048, b_micro=8192, puzzle=pz,
+                                  max_depth=16, select_mode=select_mode, hash_mode=hash_mode)
+    try:
+        for task, moves in enumerate(([], [4], [4, 9], [2, 5, 8, 11, 0])):
+            start = be.make_shallow_scramble(pz, moves)
+            want = bo.search(start, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam=2048, max_depth=12)
+            res = disp.run_task(task, start, 12, 2048)
+            assert res.task_id == task and res.status == "solved", (moves, res)
+            # inclusive ties on the coarse Hamming scale can exceed the frontier rows (capacity bits, reported);
+            # no timeout bit in any mode, and no bit at all with exact top-K
+            assert res.status_bits & (64 | 128) == 0 and (select_mode != "exact_k" or res.status_bits == 0), res
+            assert res.solved_depth <= len(moves)
+            if select_mode == "exact_k":
+                assert res.solved_depth == want.depth
+            assert res.path_replay_valid and res.path_failure_reason == ""
+            names = res.path.split(".") if res.path else []
+            assert len(names) == res.solved_depth
+            if names:
+                assert replay_path_to_central(pz, disp.action_names, start, res.path) == (True, len(names), "")
+            assert len(res.depth_rows) == res.solved_depth
+            for d, row in enumerate(res.depth_rows):
+                assert row["task_id"] == task and row["depth"] == d
+                for key in ("frontier_size", "expanded_parent_count", "stream2_generated_candidate_count",
+                            "stream3_after_threshold_count", "stream3_unique_count", "stream4_clean_count",
+                            "next_frontier_size_after", "threshold_initialized", "current_threshold",
+                            "global_keep_count", "solved_count", "stop_flag", "elapsed_sec"):
+                    assert key in row, key
+                assert row["stream2_generated_candidate_count"] == row["frontier_size"] * pz.fanout
+            if res.depth_rows:
+                assert res.depth_rows[-1]["stop_flag"] == 1
+        far = pz.scramble(7, 40)
+        res = disp.run_task(99, far, 3, 2048)  # cannot be solved in three depths
+        assert res.status == "max_depth_reached" and res.path == "" and res.path_failure_reason == "no_solved_state"
+        assert len(res.depth_rows) == 3 and res.depth_rows[-1]["next_frontier_size_after"] > 0
+        with pytest.raises(RuntimeError, match="invalid_config"):
+            disp.run_task(100, far, 3, 4096)
+    finally:
+        disp.close()

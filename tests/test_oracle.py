@@ -354,3 +354,19 @@ def test_batch_norm_folding_matches_reference():
                                    case["running_mean"], case["running_var"])
         assert np.allclose(fw, np.asarray(c["weight"], dtype=np.float32), rtol=1e-6, atol=1e-7)
         assert np.allclose(fb, np.asarray(c["bias"], dtype=np.float32), rtol=1e-6, atol=1e-6)
+
+
+def test_action_scorer_and_quantiser_match_reference_modules():
+    """MLPActionScorer / QuantizedActionScorer of the reference's scorers.py on seeded weights."""
+    data, mod = _residual_q_golden()
+    assert len(data["action_scorer"]) == 2
+    for c in data["action_scorer"]:
+        layers = mod.action_scorer_weights(c["seed"], 120, tuple(c["hidden"]), 24)
+        states = mod.residual_q_states(c["seed"] + 50, c["rows"], 120, 120)
+        y = bo.action_scorer_forward(states, layers)
+        want = np.asarray(c["y"], dtype=np.float32)
+        assert np.max(np.abs(y - want)) <= 1e-5
+        for mode in ("sigmoid_u16", "float_u16"):
+            bits = np.asarray(c[mode], dtype=np.int64) & 0xFFFF  # int16 bit pattern -> unsigned score
+            got = bo.quantized_action_scores(want, mode).astype(np.int64)
+            assert np.max(np.abs(got - bits)) <= (1 if mode == "sigmoid_u16" else 0)  # last bit of exp()

@@ -296,6 +296,114 @@ def test_action_value_scorer_matches_fp32(name, count, models, h2):
                           bo.q_to_score_key(q_dev.reshape(-1).astype(np.float32), -150.0))
 
 
+def _golden_generators():
+    import importlib.util
+    from pathlib import Path
+    path = Path(__file__).resolve().parent / "golden" / "make_residual_q_golden.py"
+    spec = importlib.util.spec_from_file_location("make_residual_q_golden", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+@pytest.mark.parametrize("size,classes,state_len,h1,h2,outs,rows,embed_sum", [
+    (54, 6, 54, 512, 256, 12, 3000, False),     # one-hot contraction for the first layer
+    (54, 6, 54, 512, 256, 12, 3000, True),      # the same network through the embedding sum
+    (128, 128, 120, 512, 256, 24, 1500, None),  # the reference's own layout: 120-byte states in 128 x 128 storage
+    (54, 6, 54, 256, 512, 12, 1, True),
+])
+def test_residual_action_value_network_matches_fp32(size, classes, state_len, h1, h2, outs, rows, embed_sum):
+    """The reference's static network (embedding sum, hidden layer, two residual blocks, one value per move) from its
+    weight dictionary, against the float32 restatement of static_forward_q that the golden vectors pin."""
+    mod = _golden_generators()
+    w = mod.residual_q_weights(9700 + h1 + h2, size, classes, h1, h2, outs)
+    states = mod.residual_q_states(9800 + rows, rows, state_len, min(classes, 120))
+    stride = (state_len + 15) // 16 * 16
+    sc = scorers.fullbeamnice_scorer_from_static_weights(w, state_len, stride, outs, max_parents=rows,
+                                                         embed_sum=embed_sum)
+    assert sc.num_res_blocks == 2 and sc.embed_sum == (embed_sum if embed_sum is not None else True)
+    keys = sc.score(torch.from_numpy(padded(states, stride)).cuda())
+    torch.cuda.synchronize()
+    assert sc.error_code() == 0
+    q_ref = bo.residual_q_forward(states, w)[:, w["action_perm"]]  # column m = move m of the engine
+    q_dev = sc.last_q(rows).cpu().numpy()
+    assert q_dev.shape == q_ref.shape
+    # bf16 operands and bf16 activations across six layers, float32 accumulation: 2e-2 of the output range
+    span = float(q_ref.max() - q_ref.min()) if rows > 1 else float(np.abs(q_ref).max())
+    assert np.abs(q_dev - q_ref).max() <= 2e-2 * max(span, 1.0), (np.abs(q_dev - q_ref).max(), span)
+    assert np.array_equal(keys.cpu().numpy().astype(np.uint32), bo.q_to_score_key(q_dev.reshape(-1), 0.0))
+
+
+def test_embedding_sum_equals_one_hot_contraction():
+    """Both forms of the first layer on the same bf16 table: the sums differ only in float32 summation order."""
+    mod = _golden_generators()
+    w = mod.residual_q_weights(9901, 54, 6, 512, 256, 12)
+    states = mod.residual_q_states(9902, 2000, 54, 6)
+    dev = torch.from_numpy(padded(states, 64)).cuda()
+    qs = []
+    for form in (False, True):
+        sc = scorers.fullbeamnice_scorer_from_static_weights(w, 54, 64, 12, max_parents=2000, embed_sum=form)
+        sc.score(dev)
+        torch.cuda.synchronize()
+        assert sc.error_code() == 0
+        qs.append(sc.last_q(2000).cpu().numpy().copy())
+    assert np.abs(qs[0] - qs[1]).max() <= 5e-2  # one bf16 rounding step of a first-layer activation, propagated
+
+
+@pytest.mark.parametrize("mode", ["q", "sigmoid_u16", "float_u16"])
+def test_reference_action_scorer_module_on_the_device(mode):
+    """MLPActionScorer (dense layer on scaled bytes, GELU, two hidden layers) through the embedding-sum kernel, and the
+    16-bit quantiser modes as keys 65535 - score."""
+    mod = _golden_generators()
+    n, V, fanout, rows = 120, 120, 24, 2500
+    layers = mod.action_scorer_weights(9931, n, (512, 256), fanout)
+    if mode == "float_u16":  # spread the outputs over a useful range of the 16-bit scale
+        layers[-1] = (layers[-1][0] * 2000.0, layers[-1][1] * 2000.0 + 30000.0)
+    base = scorers.MLPActionScorer(n, (512, 256), fanout)
+    with torch.no_grad():
+        for lin, (wm, bv) in zip((*base.linears, base.out), layers):
+            lin.weight.copy_(torch.from_numpy(wm))
+            lin.bias.copy_(torch.from_numpy(bv))
+    module = base if mode == "q" else scorers.QuantizedActionScorer(base, mode)
+    sc = scorers.action_scorer_to_device(module, n, 128, V, max_parents=rows)
+    states = mod.residual_q_states(9932, rows, n, V)
+    keys = sc.score(torch.from_numpy(padded(states, 128)).cuda()).cpu().numpy().astype(np.uint32)
+    torch.cuda.synchronize()
+    assert sc.error_code() == 0
+    y_ref = bo.action_scorer_forward(states, layers)
+    y_dev = sc.last_q(rows).cpu().numpy()
+    span = float(y_ref.max() - y_ref.min())
+    assert np.abs(y_dev - y_ref).max() <= 2e-2 * max(span, 1.0), (np.abs(y_dev - y_ref).max(), span)
+    if mode == "q":
+        assert np.array_equal(keys, bo.q_to_score_key(y_dev.reshape(-1), 0.0))
+    else:  # exact on the device's own outputs up to the last bit of exp / rounding at .5
+        want = 65535 - bo.quantized_action_scores(y_dev.reshape(-1), mode).astype(np.int64)
+        assert np.abs(keys.astype(np.int64) - want).max() <= 1
+
+
+def test_engine_loads_the_static_network_and_steps():
+    """BeamEngine.load_fullbeamnice_static (beam_engine.cpp:887-891): the dictionary becomes the parent scorer; the
+    step then selects exactly on the keys the device computed."""
+    mod = _golden_generators()
+    pz = puzzles.puzzle54()
+    w = mod.residual_q_weights(9911, 54, 6, 512, 256, pz.fanout)
+    cfg = be.config_for_puzzle(pz, global_beam_width=500, max_depth=4, beta=1.2, hash_load_factor=0.45,
+                               probe_limit=256, band_rounds=8, inference_backend="mlp", score_offset=0.0)
+    _, cfg, buffers, engine = be.configure_engine(pz, cfg=cfg)
+    engine.load_fullbeamnice_static(w)
+    frontier = np.unique(children_of(pz, 300, seed=8), axis=0)
+    engine.load_frontier(frontier)
+    engine.step()
+    st = engine.status()
+    assert st["status_bits"] == 0
+    ncand = frontier.shape[0] * pz.fanout
+    dev_scores = buffers["cand_score"][:ncand].cpu().numpy().astype(np.uint32)
+    q_ref = bo.residual_q_forward(frontier, w)[:, w["action_perm"]].reshape(-1)
+    assert np.abs(dev_scores.astype(np.int64) - bo.q_to_score_key(q_ref, 0.0).astype(np.int64)).max() <= 16  # 0.06 in q
+    want = bo.depth_step([frontier], pz.generators, pz.solved, None, 500, score_override=[dev_scores])
+    assert np.array_equal(bo.sorted_rows(engine.frontier()), bo.sorted_rows(want.states))
+
+
 def test_engine_with_action_value_scorer_matches_oracle_on_device_scores():
     """Engine step with the parent scorer: candidate p*G + m takes q[p, m]; selection is exact given those keys."""
     pz = puzzles.puzzle54()
