@@ -345,7 +345,11 @@ int mgbs_launch_expand(const uint8_t* frontier, const int32_t* count_dev, int64_
  * and its activation buffers fb_act1..fb_out (beam_engine.py:223-231). */
 typedef struct MgbsMlpConfig {
   int32_t state_len, state_stride, num_values, hidden, num_models;
-  int32_t k1_pad;       /* state_len*num_values rounded up to a multiple of 64 (bf16) or 128 (fp8) */
+  /* One-hot column order of the first layer (w1's second axis, and x): column = value * P + position with
+   * P = state_len rounded up to a multiple of 8, so that eight adjacent columns are one byte-compare of the state row.
+   * k1_pad = num_values * P rounded up to a multiple of 64 (bf16) or 128 (fp8); columns of positions >= state_len and
+   * columns >= num_values * P must be zero in w1. */
+  int32_t k1_pad;
   int64_t max_rows;     /* capacity in child rows; x, h1 and q hold max_rows rounded up to 128 */
   float score_offset;   /* key = uint32(clamp(q - score_offset, 0, 300) * 256 + 0.5) (beam_kernels.cu:341-344) */
   float b3[MGBS_MAX_MODELS];
@@ -391,6 +395,10 @@ int mgbs_mlp_set_l1_mode(MgbsMlp* m, int32_t fused);
 /* Layer 2 + head implementation: 1 (default where the device can co-schedule CTA pairs) = thread-block clusters of
  * two sharing each weight block (tcgen05 cta_group::2); 0 = one CTA per 128-row tile (kept for comparison). */
 int mgbs_mlp_set_head_mode(MgbsMlp* m, int32_t pair);
+/* Layer-1 kernel variant for tuning: epilogue_warps 4 or 8 of the kernel's 12 worker warps (the others build the
+ * one-hot operand; 0 = default for the operand type), pair = thread-block clusters of two sharing the weight tiles
+ * (-1 = default).  Every variant computes the same values. */
+int mgbs_mlp_set_l1_variant(MgbsMlp* m, int32_t epilogue_warps, int32_t pair);
 /* Per-kernel timing for benchmarks (single-member scorers, eager launches only): when on, mgbs_mlp_enqueue records
  * CUDA events between its kernels; mgbs_mlp_profile_read returns the last call's milliseconds for
  * {one-hot, layer-1 GEMM, layer-2 GEMM + head, key}.  Mirrors benchmark_inference (beam_engine.cpp:931-977). */
@@ -406,7 +414,7 @@ int mgbs_mlp_enqueue(void* mlp, const uint8_t* children, const uint32_t* count_d
  * of 256; ensemble members are averaged.  All buffers are the caller's. */
 typedef struct MgbsQmlpConfig {
   int32_t state_len, state_stride, num_values, fanout, hidden1, hidden2, num_models;
-  int32_t k1_pad;        /* state_len*num_values rounded up to a multiple of 64 */
+  int32_t k1_pad;        /* as MgbsMlpConfig.k1_pad (bf16): num_values * P rounded up to a multiple of 64; same column order */
   int64_t max_parents;   /* capacity in parent rows; h1, h2, q hold max_parents rounded up to 128 rows */
   float score_offset;
   /* 0: key = uint32(clamp(q - score_offset, 0, 300) * 256 + 0.5) (kernel_fullbeamnice_q_to_score_key_ring,
@@ -521,7 +529,7 @@ int mgbs_tf_enqueue(void* tf, const uint8_t* children, const uint32_t* count_dev
 typedef struct MgbsMlpNoAllocArgs {
   int32_t state_len, state_stride, num_values, hidden;
   float score_offset, b3;
-  const void* w1;  /* bf16 [hidden, k1_pad], zero padded, k1_pad = state_len*num_values rounded up to 64 */
+  const void* w1;  /* bf16 [hidden, k1_pad], zero padded; k1_pad and the column order as in MgbsMlpConfig */
   const float* b1; /* [hidden] */
   const void* w2;  /* bf16 [hidden, hidden] */
   const float* b2; /* [hidden] */

@@ -252,8 +252,12 @@ k_mlp_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
 // counts the eight epilogue warps of the pair.
 // ------------------------------------------------------------------------------------------------
 
-constexpr int PAIR_STAGES = 6;
-constexpr int PAIR_STAGE_BYTES = 2 * A_BYTES;  // 128 x 128-byte rows of A + 128 x 128-byte rows of B
+// A stage holds PAIR_KPS consecutive K-blocks.  The thread that issues the MMAs pays a few hundred cycles per stage
+// for the barrier wait, the fence and the commit whatever the stage holds (measured ~600-700 cycles per iteration
+// against 512 cycles of tensor work for one K-block of four MMAs), so two K-blocks per stage halve that overhead.
+constexpr int PAIR_KPS = 2;
+constexpr int PAIR_STAGES = 3;
+constexpr int PAIR_STAGE_BYTES = PAIR_KPS * 2 * A_BYTES;  // per K-block: 128 x 128-byte rows of A + 128 rows of B
 constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
 
 template <int F8>
@@ -282,7 +286,7 @@ k_mlp_head_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const int num_ptiles = (int)((rows + 2 * BM - 1) / (2 * BM));  // tiles of 256 rows
   const int n_chunks = g.n_total / BN;
   constexpr int BKE = F8 ? BK8 : BK;
-  const int k_blocks = g.k_total / BKE;
+  const int k_blocks = g.k_total / (BKE * PAIR_KPS);  // stages per N-chunk (k_total is a multiple of 256)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < PAIR_STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -314,8 +318,12 @@ k_mlp_head_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             if (!mbar_wait(empty_bar(stage), phase ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
             const uint32_t sa = smem_u32(smem + stage * PAIR_STAGE_BYTES);
             if (crank == 0) mbar_expect_tx(full_bar(stage), 2 * PAIR_STAGE_BYTES);  // both CTAs' boxes
-            tma_load_2d_pair(sa, &tmA, kb * BKE, row0, full_bar(stage));
-            tma_load_2d_pair(sa + A_BYTES, &tmB, kb * BKE, nc * BN + (int)crank * (BN / 2), full_bar(stage));
+#pragma unroll
+            for (int j = 0; j < PAIR_KPS; ++j) {
+              const int kcol = (kb * PAIR_KPS + j) * BKE;
+              tma_load_2d_pair(sa + j * 2 * A_BYTES, &tmA, kcol, row0, full_bar(stage));
+              tma_load_2d_pair(sa + j * 2 * A_BYTES + A_BYTES, &tmB, kcol, nc * BN + (int)crank * (BN / 2), full_bar(stage));
+            }
             if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
           }
         }
@@ -337,11 +345,14 @@ k_mlp_head_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             if (!mbar_wait(full_bar(stage), phase, g.err, ERR_WAIT_FULL)) { ok = false; break; }
             tc_fence_after();
             const uint32_t sa = smem_u32(smem + stage * PAIR_STAGE_BYTES);
-            const uint64_t adesc = make_desc_sw128(sa);
-            const uint64_t bdesc = make_desc_sw128(sa + A_BYTES);
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k)
-              tc_mma_pair<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
+            for (int j = 0; j < PAIR_KPS; ++j) {
+              const uint64_t adesc = make_desc_sw128(sa + j * 2 * A_BYTES);
+              const uint64_t bdesc = make_desc_sw128(sa + j * 2 * A_BYTES + A_BYTES);
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k)
+                tc_mma_pair<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | j | k) != 0 ? 1u : 0u);
+            }
             tc_commit_pair(empty_bar(stage), (uint16_t)3);  // both CTAs may refill this stage
             if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
           }
@@ -442,7 +453,7 @@ struct L1Args {
   int32_t n, stride, V;
   int32_t n_total;           // hidden (multiple of BN)
   int32_t k_total;           // n*V rounded up to the K-block width (64 bf16 / 128 e4m3)
-  int32_t k_real;            // n*V: one-hot columns that can be non-zero; MMA steps entirely beyond it are skipped
+  int32_t k_real;            // onehot_columns(n, V): columns at or past it are padding; MMA steps entirely beyond are skipped
   const float* bias;
   const float* col_scale;    // fp8 only: [n_total] dequantisation factor of each W1 output channel
   float out_inv_scale;       // fp8 only: activations are stored as e4m3(value * out_inv_scale)
@@ -476,7 +487,6 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
   // barriers: a_full[4], a_empty[4], b_full[3], b_empty[3], tmem_full[2], tmem_empty[2], drain
   constexpr int NB = 2 * L1_A_STAGES + 2 * NBS + 5;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + NB);
-  int32_t* p_lo_tab = reinterpret_cast<int32_t*>(bars + NB + 1);  // first position of each K-block
   const uint32_t bar0 = smem_u32(bars);
   auto a_full = [&](int s) { return bar0 + 8u * s; };
   auto a_empty = [&](int s) { return bar0 + 8u * (L1_A_STAGES + s); };
@@ -507,7 +517,6 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
     for (int s = 0; s < NBS; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), (PAIR ? 2 : 1) * EW); }
     mbar_init(drain_bar, 1);
-    for (int kb = 0; kb < k_blocks && kb < L1_MAX_KBLOCKS; ++kb) p_lo_tab[kb] = (kb * BKE) / g.V;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -551,53 +560,71 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
     }
   } else if (warp == 1) {
     // ---- MMA issue ----
+    // One thread; every instruction of its loop is on the critical path (a lone warp issues dependent instructions
+    // several cycles apart, and a K-block of four MMAs keeps the tensor core busy for only ~450 cycles), so the loop
+    // carries as little as possible: descriptors are 32-bit adds on a precomputed base, ring positions advance
+    // incrementally, and the resident one-hot tile is waited for once per tile, not once per N-chunk.
     if (lane == 0 && crank == 0) {
+      constexpr int KSTEP = BKE / (BK / UMMA_K);  // one-hot columns per MMA step: 16 (bf16) or 32 (e4m3)
+      const uint32_t desc_hi = (uint32_t)(make_desc_sw128(0u) >> 32);
+      const uint32_t a_lo0 = (uint32_t)make_desc_sw128(smem_u32(a_ring));
+      const uint32_t b_lo0 = (uint32_t)make_desc_sw128(smem_u32(b_ring));
+      // the last K-block is mostly padding (336 one-hot columns in 384): its all-zero steps add nothing
+      int last_steps = (g.k_real - (k_blocks - 1) * BKE + KSTEP - 1) / KSTEP;
+      last_steps = last_steps < 1 ? 1 : (last_steps > BK / UMMA_K ? BK / UMMA_K : last_steps);
       int sb = 0;
-      uint32_t pb = 0, acc_it = 0, it_base = 0;
+      uint32_t pb = 0, acc_it = 0;
+      int sa_t = 0;          // A slot and parity of the current tile's first K-block (resident) / next K-block (ring)
+      uint32_t pa_t = 0;
       bool ok = true;
-      for (int mt = tile_first; mt < num_mtiles && ok; mt += tile_step, it_base += (uint32_t)blocks_per_tile) {
+      for (int mt = tile_first; mt < num_mtiles && ok; mt += tile_step) {
+        int sa = sa_t;
+        uint32_t pa = pa_t;
         for (int nc = 0; nc < n_chunks && ok; ++nc, ++acc_it) {
           const uint32_t b = acc_it & 1u;
           if (!mbar_wait(tempty_bar(b), ((acc_it >> 1) & 1u) ^ 1u, g.err, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + b * BN;
+          if (resident) { sa = sa_t; pa = pa_t; }  // every N-chunk walks the same K-blocks of the tile
           for (int kb = 0; kb < k_blocks; ++kb) {
-            const uint32_t it = it_base + (uint32_t)(resident ? kb : nc * k_blocks + kb);
-            const int sa = (int)(it % L1_A_STAGES);
-            // resident tile: N-chunks after the first find the phase already complete
-            if (PAIR) {
-              if (!mbar_wait_cluster(a_full(sa), (it / L1_A_STAGES) & 1u, g.err, ERR_WAIT_FULL)) { ok = false; break; }
-            } else {
-              if (!mbar_wait(a_full(sa), (it / L1_A_STAGES) & 1u, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+            if (!resident || nc == 0) {            // later N-chunks of a resident tile: already waited for
+              if (PAIR) {
+                if (!mbar_wait_cluster(a_full(sa), pa, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+              } else {
+                if (!mbar_wait(a_full(sa), pa, g.err, ERR_WAIT_FULL)) { ok = false; break; }
+              }
             }
             if (!mbar_wait(b_full(sb), pb, g.err, ERR_WAIT_FULL)) { ok = false; break; }
             tc_fence_after();
-            const uint64_t adesc = make_desc_sw128(smem_u32(a_ring + sa * A_BYTES));
-            const uint64_t bdesc = make_desc_sw128(smem_u32(b_ring + sb * BSB));
-            // the last K-block is mostly padding (324 one-hot columns in 384): its all-zero steps add nothing
-            constexpr int KSTEP = BKE / (BK / UMMA_K);  // one-hot columns per MMA step: 16 (bf16) or 32 (e4m3)
-            int ksteps = (g.k_real - kb * BKE + KSTEP - 1) / KSTEP;
-            ksteps = ksteps < 1 ? 1 : (ksteps > BK / UMMA_K ? BK / UMMA_K : ksteps);
-            if (PAIR) {
+            const uint32_t al = a_lo0 + (uint32_t)sa * (A_BYTES >> 4);
+            const uint32_t bl = b_lo0 + (uint32_t)sb * (BSB >> 4);
+            const int ksteps = kb == k_blocks - 1 ? last_steps : BK / UMMA_K;
 #pragma unroll
-              for (int k = 0; k < BK / UMMA_K; ++k)
-                if (k < ksteps) tc_mma_pair<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              if (k < ksteps) {
+                const uint64_t adesc = ((uint64_t)desc_hi << 32) | (al + 2u * k);
+                const uint64_t bdesc = ((uint64_t)desc_hi << 32) | (bl + 2u * k);
+                if (PAIR) tc_mma_pair<F8>(d_tmem, adesc, bdesc, (kb | k) != 0 ? 1u : 0u);
+                else tc_mma<F8>(d_tmem, adesc, bdesc, (kb | k) != 0 ? 1u : 0u);
+              }
+            }
+            if (PAIR) {
               if (!resident || nc == n_chunks - 1) tc_commit_pair(a_empty(sa), (uint16_t)3);
               tc_commit_pair(b_empty(sb), (uint16_t)3);
             } else {
-#pragma unroll
-              for (int k = 0; k < BK / UMMA_K; ++k)
-                if (k < ksteps) tc_mma<F8>(d_tmem, adesc + 2u * k, bdesc + 2u * k, (kb | k) != 0 ? 1u : 0u);
               if (!resident || nc == n_chunks - 1) tc_commit(a_empty(sa));
               tc_commit(b_empty(sb));
             }
             if (++sb == NBS) { sb = 0; pb ^= 1u; }
+            if (++sa == L1_A_STAGES) { sa = 0; pa ^= 1u; }
           }
           if (ok) {
             if (PAIR) tc_commit_pair(tfull_bar(b), (uint16_t)3);
             else tc_commit(tfull_bar(b));
           }
         }
+        sa_t = sa;  // resident: the tile's first slot advanced by k_blocks; ring: simply where the walk stopped
+        pa_t = pa;
       }
       if (PAIR) tc_commit_pair(drain_bar, (uint16_t)1);
       else tc_commit(drain_bar);
@@ -806,6 +833,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
     const int half = (warp - 2 - EW) % WPG;  // rows half*ROWS_W .. of the block
     const int pt = (warp - 2 - EW) * 32 + lane;  // threads 0..127 load the child tile
     const int V = g.V, n = g.n;
+    const int groups = (n + 7) >> 3;  // eight-position groups per value in the column order
     uint32_t it_base = 0;           // index of this tile's first K-block in the CTA's K-block sequence
     bool ok = true;
     for (int mt = tile_first; mt - (int)crank < num_mtiles; mt += tile_step, it_base += (uint32_t)blocks_per_tile) {
@@ -834,47 +862,47 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         const int slot = (int)(it % L1_A_STAGES);
         uint8_t* a_stage = a_ring + slot * A_BYTES;
         if (!mbar_wait(a_empty(slot), ((it / L1_A_STAGES) & 1u) ^ 1u, g.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-        // zero this warp's 64 rows (8 KB, contiguous): consecutive lanes write consecutive 16-byte chunks
-        uint4* a4 = reinterpret_cast<uint4*>(a_stage + half * (A_BYTES / WPG));
-#pragma unroll 8
-        for (int q = 0; q < A_BYTES / WPG / 16 / 32; ++q) a4[q * 32 + lane] = make_uint4(0u, 0u, 0u, 0u);
-        __syncwarp();
-        // ones: column pos*V + value inside [kb*64, kb*64+64); rows half*64 + lane and + 32
-        const int c_lo = kb * BKE;
-        const int p_lo = p_lo_tab[kb];
-        int p_hi = p_lo + (BKE + V - 1) / V;  // inclusive upper bound on positions that can reach this block
-        if (p_hi > n - 1) p_hi = n - 1;
-        // twelve positions at a time (a whole K-block for 64 one-hot columns of 6 values): their bytes sit in four
-        // aligned words of the child row, fetched with independent loads - one shared-memory latency per group;
-        // a load per position would be a chain of dependent loads, each queued behind the tensor cores' operand
-        // reads - then scattered
-#pragma unroll 1
-        for (int pg = p_lo; pg <= p_hi; pg += 12) {
-          const int w_lo = pg >> 2;
-          uint32_t cw[ROWS_W / 32][4];
+        // One-hot columns are ordered value-major in groups of eight positions (column = value * 8 * groups +
+        // position): a 16-byte chunk of a bf16 row is then "which of these eight positions hold value v", a byte
+        // compare of two words of the child row - no zeroing pass, no scattered stores.  (e4m3 rows hold two such
+        // groups per chunk.)  A quarter warp writes the eight chunks of one row and the four quarters take four
+        // consecutive rows, so every store instruction fills four whole 128-byte rows without bank conflicts.
+        const int chunk = lane & 7, rsub = lane >> 3;
+        constexpr int GPC = F8 ? 2 : 1;                      // position groups per 16-byte chunk
+        uint32_t vv[GPC], m0[GPC], m1[GPC];                  // value replicated into four bytes; valid-position masks
+        int boff[GPC];                                       // byte offset of the group in the child row
 #pragma unroll
-          for (int rr = 0; rr < ROWS_W / 32; ++rr) {
-            const uint32_t* crow = reinterpret_cast<const uint32_t*>(child_s + (half * ROWS_W + lane + 32 * rr) * L1_CHILD_PITCH);
+        for (int s = 0; s < GPC; ++s) {
+          const int c8 = (kb * 8 + chunk) * GPC + s;         // group index in the column order
+          const int v = c8 / groups, gidx = c8 - v * groups;
+          const int valid = v < V ? (n - 8 * gidx > 8 ? 8 : n - 8 * gidx) : 0;  // positions of the group that exist
+          vv[s] = (uint32_t)v * 0x01010101u;
+          m0[s] = valid >= 4 ? 0xffffffffu : (valid > 0 ? (1u << (8 * valid)) - 1u : 0u);
+          m1[s] = valid >= 8 ? 0xffffffffu : (valid > 4 ? (1u << (8 * (valid - 4))) - 1u : 0u);
+          boff[s] = valid > 0 ? 8 * gidx : 0;
+        }
+#pragma unroll 4
+        for (int rb = 0; rb < ROWS_W; rb += 4) {
+          const uint32_t row = (uint32_t)(half * ROWS_W + rb + rsub);
+          const uint8_t* crow = child_s + row * L1_CHILD_PITCH;
+          uint32_t o[4];
 #pragma unroll
-            for (int w = 0; w < 4; ++w) cw[rr][w] = crow[w_lo + w];  // may run past the state bytes: those are not used
-          }
-#pragma unroll
-          for (int t = 0; t < 12; ++t) {
-            const int pos = pg + t;
-            if (pos > p_hi) break;
-            const int cbase = pos * V - c_lo;
-            const int byte = pos - 4 * w_lo;  // 0..14
-#pragma unroll
-            for (int rr = 0; rr < ROWS_W / 32; ++rr) {
-              const uint32_t row = (uint32_t)(half * ROWS_W + lane + 32 * rr);
-              const uint32_t word = (byte >> 2) == 0 ? cw[rr][0] : (byte >> 2) == 1 ? cw[rr][1] : (byte >> 2) == 2 ? cw[rr][2] : cw[rr][3];
-              const int col = cbase + (int)((word >> (8 * (byte & 3))) & 0xffu);
-              if (col >= 0 && col < BKE) {
-                if (F8) a_stage[swz128(row, (uint32_t)col)] = 0x38;  // e4m3 1.0
-                else *reinterpret_cast<uint16_t*>(a_stage + swz128(row, (uint32_t)col * 2u)) = 0x3f80;  // bf16 1.0
-              }
+          for (int s = 0; s < GPC; ++s) {
+            const uint32_t w0 = *reinterpret_cast<const uint32_t*>(crow + boff[s]);
+            const uint32_t w1 = *reinterpret_cast<const uint32_t*>(crow + boff[s] + 4);
+            const uint32_t e0 = __vcmpeq4(w0, vv[s]) & m0[s];  // 0xff in the bytes whose position holds the value
+            const uint32_t e1 = __vcmpeq4(w1, vv[s]) & m1[s];
+            if (F8) {                                          // e4m3 1.0 = 0x38 per column
+              o[2 * s] = e0 & 0x38383838u;
+              o[2 * s + 1] = e1 & 0x38383838u;
+            } else {                                           // bf16 1.0 = 0x3f80 per column: each byte doubled
+              o[0] = __byte_perm(e0, 0u, 0x1100) & 0x3f803f80u;
+              o[1] = __byte_perm(e0, 0u, 0x3322) & 0x3f803f80u;
+              o[2] = __byte_perm(e1, 0u, 0x1100) & 0x3f803f80u;
+              o[3] = __byte_perm(e1, 0u, 0x3322) & 0x3f803f80u;
             }
           }
+          *reinterpret_cast<uint4*>(a_stage + swz128(row, (uint32_t)chunk * 16u)) = make_uint4(o[0], o[1], o[2], o[3]);
         }
         if (PAIR) asm volatile("fence.proxy.async;" ::: "memory");
         else asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -896,17 +924,20 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
   }
 }
 
-// children [rows, stride] u8 -> one-hot [rows, k_pad] bf16, column = pos * V + value; 8 columns (16 bytes) per thread
+// children [rows, stride] u8 -> one-hot [rows, k_pad] bf16 in the column order of the layer-1 kernels:
+// column = value * 8 * groups + position, groups = ceil(n / 8); 8 columns (one position group of one value) per thread
 __global__ void __launch_bounds__(256) k_onehot(const uint8_t* __restrict__ children, const uint32_t* count_dev,
                                                 int64_t row_offset, int64_t row_limit, int n, int stride, int V,
                                                 int k_pad, __nv_bfloat16* __restrict__ x) {
   int64_t rows = (int64_t)(*count_dev) - row_offset;
   if (rows > row_limit) rows = row_limit;
   const int chunks = k_pad / 8;
+  const int groups = (n + 7) >> 3;
   const int64_t total = rows * chunks;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / chunks;
-    const int c0 = (int)(i - r * chunks) * 8;
+    const int c8 = (int)(i - r * chunks);
+    const int val = c8 / groups, p0 = (c8 - val * groups) * 8;
     const uint8_t* row = children + (row_offset + r) * stride;
     uint32_t w[4];
 #pragma unroll
@@ -914,15 +945,13 @@ __global__ void __launch_bounds__(256) k_onehot(const uint8_t* __restrict__ chil
       uint32_t acc = 0;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int col = c0 + 2 * j + h;
-        const int pos = col / V;
-        const int val = col - pos * V;
-        const bool on = pos < n && __ldg(row + pos) == val;
+        const int pos = p0 + 2 * j + h;
+        const bool on = val < V && pos < n && __ldg(row + pos) == val;
         acc |= (on ? 0x3f80u : 0u) << (16 * h);  // bf16 1.0
       }
       w[j] = acc;
     }
-    *reinterpret_cast<uint4*>(x + (row_offset + r) * k_pad + c0) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(x + (row_offset + r) * k_pad + c8 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
@@ -1027,11 +1056,24 @@ struct MgbsMlp {
   bool head_pair = true;
   bool fused_l1 = true;
   bool fused_quant = true;  // NVFP4: the layer-1 epilogue writes packed 4-bit activations itself
+  int l1_ew = 0, l1_pair = -1;  // layer-1 kernel variant: 0 / -1 = chosen by operand type
   bool profile = false;
   cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 using mgbs::make_map;
+
+// Address of the layer-1 kernel instance for (e4m3 operands, epilogue warps, CTA pairs, NVFP4 output).
+static const void* l1_variant(int f8, int ew, int pair, int out4) {
+  using namespace mgbs;
+  if (out4) return pair ? (const void*)k_mlp_l1<1, 8, 1, 1> : (const void*)k_mlp_l1<1, 8, 0, 1>;
+#define MGBS_L1_CASE(F, E, P) \
+  if (f8 == F && ew == E && pair == P) return (const void*)k_mlp_l1<F, E, P, 0>;
+  MGBS_L1_CASE(0, 4, 0) MGBS_L1_CASE(0, 4, 1) MGBS_L1_CASE(0, 8, 0) MGBS_L1_CASE(0, 8, 1)
+  MGBS_L1_CASE(1, 4, 0) MGBS_L1_CASE(1, 4, 1) MGBS_L1_CASE(1, 8, 0) MGBS_L1_CASE(1, 8, 1)
+#undef MGBS_L1_CASE
+  return nullptr;
+}
 using mgbs::make_map_bf16;
 
 #define MGBS_SC_TRY(expr)       \
@@ -1050,7 +1092,7 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
   if (c.state_len < 1 || c.state_len > MGBS_MAX_STATE_LEN || c.num_values < 1 || c.num_values > 256) return MGBS_ERR_ARG;
   if (c.hidden < mgbs::BN || c.hidden % mgbs::BN != 0) return MGBS_ERR_UNSUPPORTED;
   if (c.num_models < 1 || c.num_models > MGBS_MAX_MODELS || c.max_rows < 1) return MGBS_ERR_ARG;
-  const int k1 = c.state_len * c.num_values;
+  const int k1 = mgbs::onehot_columns(c.state_len, c.num_values);
   if (c.dtype != 0 && c.dtype != 1 && c.dtype != 2) return MGBS_ERR_ARG;
   const int f4 = c.dtype == 2;
   const int f8 = c.dtype == 1 || f4;  // NVFP4 runs layer 1 on the e4m3 path
@@ -1096,12 +1138,9 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
   auto l1_smem = [&](const void* fn) {
     if (!rc) rc = (int)cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::L1_SMEM);
   };
-  l1_smem((const void*)mgbs::k_mlp_l1<0, 4, 0>);
-  l1_smem((const void*)mgbs::k_mlp_l1<1, 8, 0>);
-  l1_smem((const void*)mgbs::k_mlp_l1<1, 4, 0>);
-  l1_smem((const void*)mgbs::k_mlp_l1<1, 8, 1>);
-  l1_smem((const void*)mgbs::k_mlp_l1<1, 8, 0, 1>);
-  l1_smem((const void*)mgbs::k_mlp_l1<1, 8, 1, 1>);
+  for (int v = 0; v < 8; ++v) l1_smem(l1_variant(v & 1, v & 2 ? 8 : 4, (v >> 2) & 1, 0));
+  l1_smem(l1_variant(1, 8, 0, 1));
+  l1_smem(l1_variant(1, 8, 1, 1));
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_head_pair<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::PAIR_SMEM);
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_head_pair<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::PAIR_SMEM);
@@ -1126,7 +1165,7 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
     lc.blockDim = dim3(mgbs::L1_THREADS);
     lc.dynamicSmemBytes = mgbs::L1_SMEM;
     nclusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&nclusters, mgbs::k_mlp_l1<1, 8, 1>, &lc) == cudaSuccess && nclusters > 0)
+    if (cudaOccupancyMaxActiveClusters(&nclusters, (const void*)mgbs::k_mlp_l1<1, 8, 1>, &lc) == cudaSuccess && nclusters > 0)
       m->l1_pair_clusters = nclusters < m->sms / 2 ? nclusters : m->sms / 2;
     else
       (void)cudaGetLastError();
@@ -1159,6 +1198,14 @@ int mgbs_mlp_set_l1_mode(MgbsMlp* m, int32_t fused) {
   }
   if (m->cfg.dtype != 0 && !fused) return MGBS_ERR_UNSUPPORTED;  // the e4m3 path has no separate one-hot matrix
   m->fused_l1 = fused != 0;
+  return 0;
+}
+
+int mgbs_mlp_set_l1_variant(MgbsMlp* m, int32_t epilogue_warps, int32_t pair) {
+  if (!m) return MGBS_ERR_ARG;
+  if ((epilogue_warps != 0 && epilogue_warps != 4 && epilogue_warps != 8) || pair < -1 || pair > 1) return MGBS_ERR_ARG;
+  m->l1_ew = epilogue_warps;
+  m->l1_pair = pair;
   return 0;
 }
 
@@ -1228,7 +1275,7 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
       l.n = c.state_len; l.stride = c.state_stride; l.V = c.num_values;
       l.n_total = c.hidden;
       l.k_total = m->k1_pad;
-      l.k_real = c.state_len * c.num_values;
+      l.k_real = onehot_columns(c.state_len, c.num_values);
       l.bias = c.b1[i];
       l.col_scale = c.s1[i];
       l.out_inv_scale = c.act_inv_scale;
@@ -1237,35 +1284,32 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
       l.err = c.err;
       const bool resident = m->k1_pad / (e4 ? BK8 : BK) <= L1_A_STAGES;
       quant_in_l1 = f4 && m->fused_quant && resident;
-      // bf16 builds six K-blocks per tile: eight producer warps are needed even with the resident tile (measured:
-      // 0.69-0.76 ms with 4 epilogue + 8 producer warps against 0.82 ms with 8 + 4 on the 786 432-row case);
-      // e4m3 builds three and gains from the wider epilogue
-      // CTA pairs for layer 1 only where they were measured faster: e4m3 operands with the resident tile (1.09 ms
-      // against 1.11 ms for the whole scorer on 786 432 rows).  With bf16 the pair was 0.05 ms slower than single
-      // CTAs: the even CTA's MMAs then wait for the slower of two sets of one-hot producers.
-      if (m->head_pair && m->l1_pair_clusters > 0 && e4 && resident) {
-        cudaLaunchConfig_t lc;
-        memset(&lc, 0, sizeof(lc));
-        lc.gridDim = dim3(2 * m->l1_pair_clusters);
-        lc.blockDim = dim3(L1_THREADS);
-        lc.dynamicSmemBytes = L1_SMEM;
-        lc.stream = st;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeClusterDimension;
-        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-        lc.attrs = at;
-        lc.numAttrs = 1;
-        cudaError_t le = quant_in_l1 ? cudaLaunchKernelEx(&lc, k_mlp_l1<1, 8, 1, 1>, m->tm_w1h[i], m->tm_h1q, l)
-                                     : cudaLaunchKernelEx(&lc, k_mlp_l1<1, 8, 1>, m->tm_w1h[i], m->tm_h1, l);
-        if (le != cudaSuccess) return (int)le;
-      } else if (e4 && resident) {
-        if (quant_in_l1) k_mlp_l1<1, 8, 0, 1><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1q, l);
-        else k_mlp_l1<1, 8, 0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1, l);
-      } else if (e4) {
-        k_mlp_l1<1, 4, 0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
-      } else {
-        k_mlp_l1<0, 4, 0><<<grid_gemm, L1_THREADS, L1_SMEM, st>>>(m->tm_w1[i], m->tm_h1w, l);
-      }
+      // Variant: epilogue warps (the other producer warps build the one-hot operand) and CTA pairs.
+      // Defaults by operand type; mgbs_mlp_set_l1_variant overrides them.  The ring form (K > 384) needs the eight
+      // producer warps; CTA pairs need a device that can co-schedule them.
+      int ew = m->l1_ew ? m->l1_ew : (e4 && resident ? 8 : 4);
+      int pair = m->l1_pair >= 0 ? m->l1_pair : (e4 && resident ? 1 : 0);
+      if (!resident) ew = 4;
+      if (!(m->head_pair && m->l1_pair_clusters > 0 && resident)) pair = 0;
+      if (quant_in_l1) ew = 8;
+      const void* fn = l1_variant(e4 ? 1 : 0, ew, pair, quant_in_l1 ? 1 : 0);
+      if (!fn) return MGBS_ERR_STATE;
+      const CUtensorMap* tm_b = pair ? &m->tm_w1h[i] : &m->tm_w1[i];
+      const CUtensorMap* tm_o = quant_in_l1 ? &m->tm_h1q : (ew == 4 ? &m->tm_h1w : &m->tm_h1);
+      void* kargs[3] = {(void*)tm_b, (void*)tm_o, (void*)&l};
+      cudaLaunchConfig_t lc;
+      memset(&lc, 0, sizeof(lc));
+      lc.gridDim = dim3(pair ? 2 * m->l1_pair_clusters : grid_gemm);
+      lc.blockDim = dim3(L1_THREADS);
+      lc.dynamicSmemBytes = L1_SMEM;
+      lc.stream = st;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = pair ? 2 : 1; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      lc.attrs = at;
+      lc.numAttrs = 1;
+      cudaError_t le = cudaLaunchKernelExC(&lc, fn, kargs);
+      if (le != cudaSuccess) return (int)le;
     } else {
       k_mlp_gemm<0, 0><<<grid_gemm, GEMM_THREADS, GEMM_SMEM, st>>>(m->tm_x, m->tm_w1[i], g);
     }
@@ -1357,7 +1401,7 @@ int mgbs_qmlp_create(const MgbsQmlpConfig* cfg, MgbsQmlp** out) {
   if (c.fanout < 1 || c.fanout > MGBS_MAX_FANOUT) return MGBS_ERR_ARG;
   if (c.hidden1 < mgbs::BN || c.hidden1 % mgbs::BN != 0 || c.hidden2 < mgbs::BN || c.hidden2 % mgbs::BN != 0) return MGBS_ERR_UNSUPPORTED;
   if (c.num_models < 1 || c.num_models > MGBS_MAX_MODELS || c.max_parents < 1) return MGBS_ERR_ARG;
-  const int k1 = c.state_len * c.num_values;
+  const int k1 = mgbs::onehot_columns(c.state_len, c.num_values);
   const int k1_pad = (k1 + mgbs::BK - 1) / mgbs::BK * mgbs::BK;
   if (c.embed_sum != 0 && c.embed_sum != 1) return MGBS_ERR_ARG;
   if (c.key_mode < 0 || c.key_mode > 2 || c.activation < 0 || c.activation > 1) return MGBS_ERR_ARG;
@@ -1419,7 +1463,7 @@ int mgbs_qmlp_enqueue(void* user, const uint8_t* parents, const int32_t* parent_
     l.n = c.state_len; l.stride = c.state_stride; l.V = c.num_values;
     l.n_total = c.hidden1;
     l.k_total = c.k1_pad;
-    l.k_real = c.state_len * c.num_values;
+    l.k_real = onehot_columns(c.state_len, c.num_values);
     l.bias = c.b1[i];
     l.col_scale = nullptr;
     l.out_inv_scale = 1.f;
@@ -1522,7 +1566,7 @@ extern "C" int mgbs_mlp_score_noalloc(const MgbsMlpNoAllocArgs* a, const uint8_t
   if (!a->w1 || !a->b1 || !a->w2 || !a->b2 || !a->w3) return MGBS_ERR_ARG;
   if (a->state_len < 1 || a->state_len > MGBS_MAX_STATE_LEN || a->num_values < 1 || a->num_values > 256) return MGBS_ERR_ARG;
   if (a->state_stride < a->state_len || a->state_stride % 16 != 0) return MGBS_ERR_ARG;
-  const int k1_pad = (a->state_len * a->num_values + BK - 1) / BK * BK;
+  const int k1_pad = (onehot_columns(a->state_len, a->num_values) + BK - 1) / BK * BK;
   if (a->hidden < BN || a->hidden % BN != 0) return MGBS_ERR_UNSUPPORTED;
   // sizes beyond the static scratch are refused, never truncated
   if (rows > kNoAllocMaxRows || k1_pad > kNoAllocMaxK1 || a->hidden > kNoAllocMaxHidden) return MGBS_ERR_TOO_LARGE;

@@ -24,6 +24,10 @@ constexpr int GEMM_THREADS = 192;
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr uint32_t TMEM_COLS = 512;
 
+// Width of the one-hot first-layer operand: columns are ordered value-major in groups of eight positions
+// (column = value * 8 * ceil(n / 8) + position), so that eight adjacent columns are one byte-compare of the state row.
+inline __host__ __device__ int onehot_columns(int state_len, int num_values) { return num_values * ((state_len + 7) / 8 * 8); }
+
 constexpr int ERR_WAIT_EMPTY = 1, ERR_WAIT_FULL = 2, ERR_WAIT_TMEM_EMPTY = 3, ERR_WAIT_TMEM_FULL = 4, ERR_WAIT_DRAIN = 5;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -60,22 +64,24 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* err, int code) {
+// Bounded waits: about 1-2 s of polling at most, then report and give up.  The common case - the phase is already
+// complete, or completes within the instruction's own wait - is one try_wait and a branch; the polling loop with its
+// counter lives out of line so that the callers' loops stay short.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, int* err, int code, int cluster) {
   for (uint32_t it = 0; it < (1u << 24); ++it) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (cluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     if (it > 1024) __nanosleep(64);
   }
   if (err) atomicCAS(err, 0, code);
   return false;
 }
-// Bounded wait: about 1-2 s of polling at most, then report and give up.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* err, int code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, err, code, 1);
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
-  for (uint32_t it = 0; it < (1u << 24); ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (it > 1024) __nanosleep(64);
-  }
-  if (err) atomicCAS(err, 0, code);
-  return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, err, code, 0);
 }
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {

@@ -70,6 +70,24 @@ def nvfp4_quantize_weights(w: np.ndarray):
     return np.ascontiguousarray(packed), sfb.reshape(-1).copy(), float(tscale)
 
 
+def onehot_columns(state_len: int, num_values: int) -> int:
+    """Width of the one-hot operand in the column order of the layer-1 kernels: column = value * P + position with
+    P = state_len rounded up to 8 (eight adjacent columns = one byte-compare of the state row)."""
+    return num_values * ((state_len + 7) // 8 * 8)
+
+
+def onehot_relayout(w1: np.ndarray, state_len: int, num_values: int, k1_pad: int) -> np.ndarray:
+    """[H, state_len * num_values] with column position * V + value (the layout of Linear weights on a flattened
+    one-hot, scorers.py:21-36) -> [H, k1_pad] float32 in the kernels' column order, zero padded."""
+    w1 = np.asarray(w1, dtype=np.float32)
+    h = w1.shape[0]
+    p = (state_len + 7) // 8 * 8
+    out = np.zeros((h, k1_pad), dtype=np.float32)
+    src = w1.reshape(h, state_len, num_values)
+    out[:, : num_values * p].reshape(h, num_values, p)[:, :, :state_len] = src.transpose(0, 2, 1)
+    return out
+
+
 class MgbsMlpNoAllocArgs(C.Structure):
     _fields_ = [
         ("state_len", C.c_int32), ("state_stride", C.c_int32), ("num_values", C.c_int32), ("hidden", C.c_int32),
@@ -89,6 +107,7 @@ _SIGS = {
     "mgbs_mlp_profile": (C.c_int, [C.c_void_p, C.c_int32]),
     "mgbs_mlp_set_l1_mode": (C.c_int, [C.c_void_p, C.c_int32]),
     "mgbs_mlp_set_head_mode": (C.c_int, [C.c_void_p, C.c_int32]),
+    "mgbs_mlp_set_l1_variant": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32]),
     "mgbs_mlp_profile_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
     "mgbs_mlp_enqueue": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
@@ -132,7 +151,7 @@ class MLPValueScorer:
             raise RuntimeError("NVFP4 needs a hidden width that is a multiple of 256")
         self.dtype = dtype
         kblk = 128 if f8 else 64
-        k1_pad = (k1 + kblk - 1) // kblk * kblk
+        k1_pad = (onehot_columns(state_len, num_values) + kblk - 1) // kblk * kblk
         rows_pad = (int(max_rows) + 127) // 128 * 128
         self.state_len, self.state_stride, self.num_values = state_len, state_stride, num_values
         self.hidden, self.k1_pad, self.max_rows = hidden, k1_pad, int(max_rows)
@@ -149,13 +168,13 @@ class MLPValueScorer:
         for i, w in enumerate(weights):
             if w["w1"].shape != (hidden, k1) or w["w2"].shape != (hidden, hidden) or w["w3"].shape != (hidden,):
                 raise RuntimeError("weight shapes must be w1 [H, n*V], w2 [H, H], w3 [H]")
-            w1_f = torch.from_numpy(np.ascontiguousarray(w["w1"], dtype=np.float32)).to(dev)
+            # first-layer weights in the kernels' one-hot column order (value-major, positions padded to eight)
+            w1_f = torch.from_numpy(onehot_relayout(w["w1"], state_len, num_values, k1_pad)).to(dev)
             w2_f = torch.from_numpy(np.ascontiguousarray(w["w2"], dtype=np.float32)).to(dev)
             if f8:
                 s1 = (w1_f.abs().amax(dim=1) / 448.0).clamp_min(1e-12)
                 s2w = (w2_f.abs().amax(dim=1) / 448.0).clamp_min(1e-12)
-                w1 = torch.zeros((hidden, k1_pad), dtype=torch.uint8, device=dev)
-                w1[:, :k1] = (w1_f / s1[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
+                w1 = (w1_f / s1[:, None]).to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
                 self.t["w1"].append(w1)
                 self.t["s1"].append(s1.contiguous())
                 if f4:
@@ -171,9 +190,7 @@ class MLPValueScorer:
                 cfg.s1[i] = self.t["s1"][i].data_ptr()
                 cfg.s2[i] = self.t["s2"][i].data_ptr()
             else:
-                w1 = torch.zeros((hidden, k1_pad), dtype=torch.bfloat16, device=dev)
-                w1[:, :k1] = w1_f.to(torch.bfloat16)
-                self.t["w1"].append(w1)
+                self.t["w1"].append(w1_f.to(torch.bfloat16).contiguous())
                 self.t["w2"].append(w2_f.to(torch.bfloat16).contiguous())
             for k in ("b1", "b2", "w3"):
                 self.t[k].append(torch.from_numpy(np.ascontiguousarray(w[k], dtype=np.float32)).to(dev))
@@ -248,6 +265,11 @@ class MLPValueScorer:
     def set_head_mode(self, pair: bool) -> None:
         """Layer 2 + head on CTA pairs sharing each weight block (default) or on single CTAs (for comparison)."""
         _lib.check(self.lib.mgbs_mlp_set_head_mode(self._h, int(bool(pair))), "set_head_mode")
+
+    def set_l1_variant(self, epilogue_warps: int = 0, pair: int = -1) -> None:
+        """Layer-1 kernel variant (tuning; all variants compute the same values): 4 or 8 epilogue warps (0 = default),
+        CTA pairs (-1 = default)."""
+        _lib.check(self.lib.mgbs_mlp_set_l1_variant(self._h, int(epilogue_warps), int(pair)), "set_l1_variant")
 
     def profile(self, on: bool) -> None:
         """Record CUDA events between the scorer's kernels (eager launches only)."""
@@ -363,7 +385,7 @@ class MLPActionValueScorer:
             raise RuntimeError(f"1..{MAX_MODELS} ensemble members supported")
         dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         k1 = state_len * num_values
-        k1_pad = (k1 + 63) // 64 * 64
+        k1_pad = (onehot_columns(state_len, num_values) + 63) // 64 * 64
         h1, h2 = int(weights[0]["w1"].shape[0]), int(weights[0]["w2"].shape[0])
         rows_pad = (int(max_parents) + 127) // 128 * 128
         self.state_len, self.state_stride, self.num_values, self.fanout = state_len, state_stride, num_values, fanout
@@ -406,9 +428,10 @@ class MLPActionValueScorer:
                 cfg.wr[2 * l + 1][i], cfg.br[2 * l + 1][i] = keep(bf16(wb)), keep(f32(bb))
             if self.embed_sum:
                 cfg.w1t[i] = keep(bf16(np.ascontiguousarray(np.asarray(w["w1"], dtype=np.float32).T)))  # [n*V, H1]
-            w1 = torch.zeros((h1, k1_pad if not self.embed_sum else 64), dtype=torch.bfloat16, device=dev)
-            if not self.embed_sum:
-                w1[:, :k1] = bf16(w["w1"])
+            if self.embed_sum:
+                w1 = torch.zeros((h1, 64), dtype=torch.bfloat16, device=dev)  # unused by the embedding-sum form
+            else:
+                w1 = bf16(onehot_relayout(w["w1"], state_len, num_values, k1_pad))
             w3 = torch.zeros((256, h2), dtype=torch.bfloat16, device=dev)
             w3[:fanout] = torch.from_numpy(np.ascontiguousarray(w["w3"], dtype=np.float32)).to(dev).to(torch.bfloat16)
             b3 = torch.zeros((256,), dtype=torch.float32, device=dev)

@@ -566,7 +566,7 @@ def test_zobrist_hash_mode_matches_oracle(name, count, beam):
     engine.cfg["world_size"] = 1
 
 
-@pytest.mark.parametrize("select_mode,hash_mode", [("v6_inclusive", "zobrist128"), ("exact_k", "hash64")])
+@pytest.mark.parametrize("select_mode,hash_mode", [("v6_inclusive", "zobrist128"), ("exact_k", "fnv")])
 def test_production_v6_dispatcher_runs_tasks(select_mode, hash_mode):
     """ProductionV6Dispatcher.run_task (production_v6_dispatcher.py:708-868): one object, several start states; the
     result carries the reference's fields, a path that replays to the solved state, and one row per depth with the
