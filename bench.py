@@ -570,7 +570,7 @@ def run_case(args):
         per_gpu = args.beam_per_gpu or (max(65536 // world, 1) if args.case == "c4" else 65536)
     beam = per_gpu * world
     prep = 10
-    depths = prep + args.warmup + args.steps + 4
+    depths = prep + max(args.warmup, 3) + args.steps + 8
     cfg = be.config_for_puzzle(pz, world_size=world, rank=rank, global_beam_width=beam, max_depth=depths,
                                history_rows=min(depths, 64), beta=1.2, gamma=1.05, hash_load_factor=0.45,
                                probe_limit=256, band_rounds=3, band_levels=3, inference_backend="mlp",
@@ -627,6 +627,16 @@ def run_case(args):
     barrier()
     clocks = sampler.stop()
     st = engine.status()
+    # per-stage times of the same steps, eager with CUDA events between the launches (every rank steps; rank 0 reports)
+    engine.enable_step_timers(True)
+    acc, n_prof = {}, 3
+    for _ in range(n_prof):
+        engine.step()
+        for k, v in engine.step_timing().items():
+            if k.endswith("_ms") and isinstance(v, float):
+                acc[k] = acc.get(k, 0.0) + v / n_prof
+    engine.enable_step_timers(False)
+    acc["select_ms"] = acc.get("bands_ms", 0.0) + acc.get("final_ms", 0.0)
     t = torch.tensor([sum(ms), float(st["total_candidates"] - c0), float(st["status_bits"]), float(sc.error_code())],
                      device=dev, dtype=torch.float64)
     tmax = t.clone()
@@ -643,6 +653,8 @@ def run_case(args):
             "scorer_tflops": sc.flops_per_state() * cands / (total_ms * 1e-3) / 1e12,
             "status_bits": int(t[2].item()), "scorer_err": int(t[3].item()),
             "unique_per_step": st["counters"][3], "band_rounds_used": st["counters"][5], "clocks": clocks,
+            "stage_ms": {k: round(v, 4) for k, v in acc.items()},
+            "hash_capacity_slots": sizes["hash_capacity"], "table_mb": round(sizes["hash_capacity"] * 32 / 1e6, 1),
         }))
     engine.close()
     if world > 1:

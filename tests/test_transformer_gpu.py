@@ -83,6 +83,28 @@ def test_transformer_scorer_fp8(count, encoders, micro):
     assert np.abs(keys.cpu().numpy().astype(np.int64) - rekey).max() <= 1
 
 
+def test_transformer_fp8_on_the_benchmark_initialisation():
+    """The benchmark's own transformer (2 encoders, Gaussian weights of std 0.02, unit LayerNorm gains, zero biases)
+    with e4m3 GEMM operands against the unrounded float32 model: the stated bound for FP8 is a maximum absolute
+    error of 2e-2 of the float32 output.  (The perturbed weights of the test above, with LayerNorm gains and biases
+    drawn at random, are a harder case and keep their own, wider bound.)"""
+    pz = puzzles.puzzle54()
+    ws = [puzzles.transformer_weights(54, 6, model_idx=i) for i in range(2)]
+    count = 600
+    sc = scorers.TransformerValueScorer(ws, 54, 64, 6, max_rows=count, micro_batch=512, dtype="fp8")
+    rows = _states(pz, count, seed=77)
+    sc.score(torch.from_numpy(_pad(rows, 64)).cuda())
+    torch.cuda.synchronize()
+    assert sc.error_code() == 0
+    q_dev = (sc.last_q(count).cpu().numpy() + sum(float(w["b_head"]) for w in ws)) / 2
+    q_ref = bo.transformer_forward(rows, ws)
+    err = float(np.abs(q_dev - q_ref).max())
+    span = float(q_ref.max() - q_ref.min())
+    print("fp8 transformer, benchmark initialisation: max abs error", err, "output span", span,
+          "max |q|", float(np.abs(q_ref).max()))
+    assert err <= 2e-2, err
+
+
 def test_engine_with_transformer_scorer():
     pz = puzzles.puzzle54()
     beam = 512
