@@ -346,7 +346,11 @@ def run_ours(args):
     ms = res["ms"]
     total_ms, total_cands, st = res["total_ms"], res["cands"], res["status"]
     rank_means = [sum(ms) / len(ms)]
+    rank_rows = [int(st["current_size"])]  # frontier rows each rank holds (hash-owner placement: how even it is)
     if world > 1:
+        rows_all = [None] * world
+        dist.all_gather_object(rows_all, rank_rows[0])
+        rank_rows = [int(x) for x in rows_all]
         gathered = [None] * world
         dist.all_gather_object(gathered, sum(ms) / len(ms))
         rank_means = [float(x) for x in gathered]
@@ -518,7 +522,7 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": total_ms / K, "p50_ms_per_step": statistics.median(ms),
             "p90_ms_per_step": sorted(ms)[min(len(ms) - 1, int(0.9 * len(ms)))], "max_ms_per_step": max(ms),
-            "rank_ms_per_step": rank_means,
+            "rank_ms_per_step": rank_means, "frontier_rows_per_rank": rank_rows,
             "ms_x_sm_mhz": (total_ms / K) * sm_mhz if sm_mhz else None,
             "slow_steps": sum(1 for x in ms if x > 1.5 * statistics.median(ms)), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",

@@ -612,3 +612,26 @@ def test_production_v6_dispatcher_runs_tasks(select_mode, hash_mode):
             disp.run_task(100, far, 3, 4096)
     finally:
         disp.close()
+
+
+def test_solve_rate_on_the_benchmark_puzzle_matches_oracle():
+    """"Solve rate unchanged" on the benchmark's own state space (54 positions, 12 moves): 24 seeded scrambles of 7 to
+    12 moves, Hamming scorer, beam 4096, depth limit 14.  The depth loop must report found / not found and the depth
+    exactly as the oracle does for every scramble (bit-exact selection makes this an equality, not a rate), and every
+    found path must replay to the solved state."""
+    pz = puzzles.puzzle54()
+    engine = make_engine(pz, global_beam_width=4096, max_depth=16)
+    engine.enable_cuda_graphs(True)
+    outcomes = []
+    for j in range(24):
+        start = pz.scramble(2000 + j, 7 + j % 6)
+        want = bo.search(start, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam=4096, max_depth=14)
+        res = be.run_one_search(engine, start, 14)
+        assert res["status"]["status_bits"] == 0, (j, res["status_names"])
+        assert (bool(res["found"]), res["depth"]) == (bool(want.found), want.depth), (j, res["found"], res["depth"], want.depth)
+        if want.found:
+            path = engine.reconstruct_path()
+            assert np.array_equal(bo.replay(start, pz.generators, path), pz.solved), j
+        outcomes.append(bool(want.found))
+    assert any(outcomes)
+    print("solve rate", sum(outcomes), "of", len(outcomes))

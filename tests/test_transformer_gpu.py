@@ -78,7 +78,7 @@ def test_transformer_scorer_fp8(count, encoders, micro):
     print("fp8 transformer: vs rounded-operand model", err_model, "vs float32", err_ref)
     # bf16 q/k/v between the GEMMs and values that sit on an e4m3 rounding boundary leave ~1e-3
     assert err_model <= 2e-2, err_model
-    assert err_ref <= 6e-2, err_ref
+    assert err_ref <= 3e-2, err_ref  # measured 2.2e-2 and 2.5e-2
     rekey = bo.q_to_score_key(q_dev.astype(np.float32), -150.0).astype(np.int64)
     assert np.abs(keys.cpu().numpy().astype(np.int64) - rekey).max() <= 1
 
