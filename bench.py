@@ -481,7 +481,7 @@ def run_ours(args):
         fp8 = {"value": r8["cands"] / (r8["total_ms"] * 1e-3), "unit": UNIT, "ms_per_step": r8["total_ms"] / k8,
                "steps": k8, "status_bits": r8["status_bits"], "scorer_err": r8["scorer_err"],
                "dtype": "fp8 e4m3 operands, fp32 accumulation",
-               "kernel_ms": {"k_mlp_l1<1,8,1>": statistics.mean(g1), "k_mlp_head_pair<1>": statistics.mean(g2)}}
+               "kernel_ms": {"k_mlp_l1<1,8,0>": statistics.mean(g1), "k_mlp_head_pair<1>": statistics.mean(g2)}}
         j8.close()
         del j8
         torch.cuda.empty_cache()

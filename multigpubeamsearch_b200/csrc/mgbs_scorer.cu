@@ -441,7 +441,7 @@ constexpr int L1_THREADS = 448;
 constexpr int L1_A_STAGES = 6;                           // 6 x 16 KB: a whole 128 x 384 one-hot tile when K <= 384
 constexpr int L1_B_STAGES = 3;
 constexpr int L1_PAIRS = 4;                              // producer warp pairs
-constexpr int L1_STAGING = A_BYTES;                      // one 128-row x 128-byte output box
+constexpr int L1_STAGING = A_BYTES;                      // 16 KB of private 2 KB output boxes of the epilogue warps
 constexpr int L1_CHILD_PITCH = MGBS_MAX_STATE_LEN + 4;   // bytes; odd word pitch -> conflict-free row reads
 constexpr int L1_MAX_KBLOCKS = 16;
 constexpr int L1_SMEM = L1_A_STAGES * A_BYTES + L1_B_STAGES * B_BYTES + L1_STAGING + BM * L1_CHILD_PITCH + 1024 + 512;
@@ -634,7 +634,6 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
     // ---- epilogue: TMEM -> bias, ReLU, bf16 -> swizzled staging box -> TMA store ----
     const int quad = warp & 3;
     const int sg = EW == 4 ? 0 : (warp - 2) >> 2;     // sub-group: which 32-column groups of a box this warp takes
-    const int et = (warp - 2) * 32 + lane;            // index among the epilogue threads
     const uint32_t r = (uint32_t)(quad * 32 + lane);  // tile row owned by this thread
     uint32_t acc_it = 0, box_it = 0;
     bool ok = true;
@@ -645,17 +644,24 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         if (!mbar_wait(tfull_bar(b), (acc_it >> 1) & 1u, g.err, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
         tc_fence_after();
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + b * BN;
-        if constexpr (EW == 4) {
-          // private staging: each warp owns two boxes of 32 rows x 64 bytes (64-byte swizzle) for its TMEM lane
-          // quadrant and alternates between them, so filling one overlaps the TMA store reading the other and
-          // no barrier between warps is needed.  (Storing straight from registers, 32 bytes per thread and row,
-          // measured 8 % slower for the whole scorer than these TMA stores of full rows.)
+        if constexpr (OUT4 == 0) {
+          // private staging: each warp owns boxes of 32 rows x 64 bytes (64-byte swizzle) for its TMEM lane quadrant,
+          // so no barrier between warps is needed and every warp has its own TMA stores in flight.  Four epilogue
+          // warps own two boxes each and alternate (filling one overlaps the store reading the other); eight
+          // warps own one each and take every other box of the chunk.  A TMA store holds its box for well over a
+          // thousand cycles, so what counts is the number of boxes in flight: one 16 KB box shared by eight warps
+          // behind two block barriers (the earlier form of the eight-warp epilogue) turned around every 2 300 cycles.
+          // (Storing straight from registers with plain global stores measured slower than these TMA stores.)
           constexpr int SUBC = F8 ? 64 : 32;  // output columns per 64-byte box row
-          uint8_t* mybuf = staging + (warp - 2) * 4096;
+          constexpr int NBOX = EW == 4 ? 2 : 1;
+          uint8_t* mybuf = staging + (warp - 2) * (NBOX * 2048);
 #pragma unroll 1
-          for (int gcol = 0; gcol < BN; gcol += SUBC, ++box_it) {
-            uint8_t* box = mybuf + (box_it & 1u) * 2048;
-            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          for (int gcol = sg * SUBC; gcol < BN; gcol += SUBC * (EW / 4), ++box_it) {
+            uint8_t* box = mybuf + (NBOX == 2 ? (box_it & 1u) * 2048 : 0u);
+            if (lane == 0) {
+              if (NBOX == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+              else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            }
             __syncwarp();
             uint32_t packed[16];
             if (F8) {
@@ -704,15 +710,16 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
           }
-        } else if constexpr (OUT4 != 0) {
-          // one box = the chunk's 256 columns, 128 bytes per row
-          uint8_t* box = staging;
-          if (et == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");
+        } else {
+          // NVFP4 output: 32 columns become 16 bytes, so a warp's half of the chunk (128 columns) is one private
+          // box of 32 rows x 64 bytes; the block factors go straight to global memory
+          uint8_t* box = staging + (warp - 2) * 2048;
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+          __syncwarp();
           uint8_t* sf_row = g.sf_out + (((int64_t)mt * n_chunks + nc) * 4) * 512 + (r & 31u) * 16u + (r >> 5) * 4u;
 #pragma unroll
-          for (int sub0 = 0; sub0 < BN / 32; sub0 += EW / 4) {
-            const int sub = sub0 + sg;
+          for (int i = 0; i < 4; ++i) {
+            const int sub = sg * 4 + i;
             uint32_t v[32];
             tc_ld32(taddr + sub * 32, v);
             tc_wait_ld();
@@ -745,75 +752,20 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
               }
               sf_pair |= (uint32_t)sf8 << (8 * blk);
             }
-            *reinterpret_cast<uint4*>(box + swz128(r, (uint32_t)(sub * 16))) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            // 64-byte swizzle: 16-byte chunk index ^= (row / 2) mod 4 inside 512-byte atoms
+            const uint32_t off = (uint32_t)lane * 64u + (((uint32_t)i ^ (((uint32_t)lane >> 1) & 3u)) << 4);
+            *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             // blocks 2 * sub and 2 * sub + 1 of the chunk's sixteen: MMA step sub / 2, factors (sub & 1) * 2 and + 1
             // (the odd CTA of a pair also walks the tile after the last one when the tile count is odd: the TMA store
             // clips it, these plain stores must not happen)
             if (mt < num_mtiles) *reinterpret_cast<uint16_t*>(sf_row + (sub >> 1) * 512 + (sub & 1) * 2) = (uint16_t)sf_pair;
           }
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");
-          if (et == 0) {
-            tma_store_2d(&tmOut, smem_u32(box), nc * (BN / 2), row0);
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmOut, smem_u32(box), nc * (BN / 2) + sg * 64, row0 + quad * 32);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           }
-        } else {
-#pragma unroll 1
-        for (int gcol = 0; gcol < BN; gcol += BKE, ++box_it) {  // one box = 128 bytes per row
-          uint8_t* box = staging;
-          // the TMA store that last read the box must be done before it is overwritten
-          if (et == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-          asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");
-#pragma unroll
-          for (int sub0 = 0; sub0 < BKE / 32; sub0 += EW / 4) {   // constant trip count: unrolls completely
-            const int sub = sub0 + sg;
-            uint32_t v[32];
-            tc_ld32(taddr + gcol + sub * 32, v);
-            tc_wait_ld();
-            const int n0 = nc * BN + gcol + sub * 32;
-            if (F8) {
-              uint32_t packed[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float4 cq = __ldg(reinterpret_cast<const float4*>(g.col_scale + n0) + j);
-                const float4 bq = __ldg(reinterpret_cast<const float4*>(g.bias + n0) + j);
-                float x[4];
-                x[0] = fmaxf(fmaf(__uint_as_float(v[4 * j]), cq.x, bq.x), 0.f) * g.out_inv_scale;
-                x[1] = fmaxf(fmaf(__uint_as_float(v[4 * j + 1]), cq.y, bq.y), 0.f) * g.out_inv_scale;
-                x[2] = fmaxf(fmaf(__uint_as_float(v[4 * j + 2]), cq.z, bq.z), 0.f) * g.out_inv_scale;
-                x[3] = fmaxf(fmaf(__uint_as_float(v[4 * j + 3]), cq.w, bq.w), 0.f) * g.out_inv_scale;
-                const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(x[0], x[1]), __NV_SATFINITE, __NV_E4M3);
-                const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(x[2], x[3]), __NV_SATFINITE, __NV_E4M3);
-                packed[j] = lo | (hi << 16);
-              }
-#pragma unroll
-              for (int q = 0; q < 2; ++q) {
-                const uint32_t off = swz128(r, (uint32_t)(sub * 32 + q * 16));
-                *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-              }
-            } else {
-              uint32_t packed[16];
-#pragma unroll
-              for (int j4 = 0; j4 < 8; ++j4) {
-                // four columns per bias load; ReLU rides in the packing conversion
-                const float4 bq = __ldg(reinterpret_cast<const float4*>(g.bias + n0) + j4);
-                packed[2 * j4] = pack_relu_bf16(__uint_as_float(v[4 * j4]) + bq.x, __uint_as_float(v[4 * j4 + 1]) + bq.y);
-                packed[2 * j4 + 1] = pack_relu_bf16(__uint_as_float(v[4 * j4 + 2]) + bq.z, __uint_as_float(v[4 * j4 + 3]) + bq.w);
-              }
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const uint32_t off = swz128(r, (uint32_t)(sub * 64 + q * 16));
-                *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-              }
-            }
-          }
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          asm volatile("bar.sync 1, %0;" ::"n"(EW * 32) : "memory");
-          if (et == 0) {
-            tma_store_2d(&tmOut, smem_u32(box), nc * BN + gcol, row0);
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          }
-        }
         }
         tc_fence_before();
         __syncwarp();
@@ -823,7 +775,7 @@ k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtens
         }
       }
     }
-    if (EW == 4 ? lane == 0 : et == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   } else {
     // ---- one-hot producers: warp pw owns A stage pw and builds K-blocks pw, pw+4, pw+8, ... of the sequence ----
     constexpr int PROD_W = 12 - EW;          // producer warps
@@ -1051,6 +1003,7 @@ struct MgbsMlp {
   CUtensorMap tm_w2h[MGBS_MAX_MODELS];  // W2 in boxes of 128 rows: the half of a chunk one CTA of a pair loads
   CUtensorMap tm_w1h[MGBS_MAX_MODELS];  // W1 likewise
   CUtensorMap tm_h1q, tm_w2q[MGBS_MAX_MODELS];  // NVFP4: packed activations and weights as byte tensors
+  CUtensorMap tm_h1qw;                          // packed activations, store boxes of one warp: 32 rows x 64 bytes
   int pair_clusters = 0;                // CTA pairs that can be resident at once (0: pairs unavailable)
   int l1_pair_clusters = 0;             // the same for the layer-1 kernel
   bool head_pair = true;
@@ -1131,6 +1084,7 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
     if (!rc) rc = make_map(&m->tm_w2h[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden, mgbs::BN / 2, eb);
   }
   if (f4 && !rc) rc = make_map(&m->tm_h1q, c.h1q, rows_pad, (uint64_t)c.hidden / 2, mgbs::BM, 1);
+  if (f4 && !rc) rc = mgbs::make_map_box(&m->tm_h1qw, c.h1q, rows_pad, (uint64_t)c.hidden / 2, 32, 64, 1, 64);
   if (f4 && !rc) rc = mgbs::nvfp4_prepare();
   if (f8) m->fused_l1 = true;
   if (!rc) rc = (int)cudaFuncSetAttribute(mgbs::k_mlp_gemm<0, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, mgbs::GEMM_SMEM);
@@ -1288,14 +1242,14 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
       // Defaults by operand type; mgbs_mlp_set_l1_variant overrides them.  The ring form (K > 384) needs the eight
       // producer warps; CTA pairs need a device that can co-schedule them.
       int ew = m->l1_ew ? m->l1_ew : (e4 && resident ? 8 : 4);
-      int pair = m->l1_pair >= 0 ? m->l1_pair : (e4 && resident ? 1 : 0);
+      int pair = m->l1_pair >= 0 ? m->l1_pair : 0;  // measured: 0.39 vs 0.41 ms (e4m3), 0.55 vs 0.59-0.63 ms (bf16)
       if (!resident) ew = 4;
       if (!(m->head_pair && m->l1_pair_clusters > 0 && resident)) pair = 0;
       if (quant_in_l1) ew = 8;
       const void* fn = l1_variant(e4 ? 1 : 0, ew, pair, quant_in_l1 ? 1 : 0);
       if (!fn) return MGBS_ERR_STATE;
       const CUtensorMap* tm_b = pair ? &m->tm_w1h[i] : &m->tm_w1[i];
-      const CUtensorMap* tm_o = quant_in_l1 ? &m->tm_h1q : (ew == 4 ? &m->tm_h1w : &m->tm_h1);
+      const CUtensorMap* tm_o = quant_in_l1 ? &m->tm_h1qw : &m->tm_h1w;  // boxes of one warp: 32 rows x 64 bytes
       void* kargs[3] = {(void*)tm_b, (void*)tm_o, (void*)&l};
       cudaLaunchConfig_t lc;
       memset(&lc, 0, sizeof(lc));

@@ -69,7 +69,9 @@ def bn_case(seed: int, outs: int, ins: int):
 
 
 def main() -> None:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_residual_q_golden.py /path/to/reference")
+    ref = Path(sys.argv[1])
     sys.dont_write_bytecode = True
     sys.path.insert(0, str(ref))
     sys.path.insert(0, str(ref / "scripts"))

@@ -266,6 +266,31 @@ def test_nvfp4_ensemble_within_tolerance():
     assert np.abs(q_dev - bo.mlp_forward(rows, ws, pz.num_values)).max() <= 5e-2
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp8"])
+def test_layer1_kernel_variants_agree(dtype):
+    """Four or eight epilogue warps, single CTAs or CTA pairs: the same activations and keys, bit for bit."""
+    pz = puzzles.by_name("rand54")
+    count = 20000 + 77  # a ragged last tile, and an odd number of tiles for the pairs
+    w = puzzles.mlp_weights(pz.state_len * pz.num_values, 1024)
+    w["b1"] = (np.random.default_rng(3).standard_normal(1024) * 0.05).astype(np.float32)
+    sc = scorers.MLPValueScorer(w, pz.state_len, 64, pz.num_values, max_rows=count, dtype=dtype)
+    dev = torch.from_numpy(padded(children_of(pz, count, seed=21), 64)).cuda()
+    base = None
+    for ew in (4, 8):
+        for pair in (0, 1):
+            sc.set_l1_variant(ew, pair)
+            sc.h1.zero_()
+            keys = sc.score(dev)
+            torch.cuda.synchronize()
+            assert sc.error_code() == 0, (ew, pair)
+            got = (sc.h1[:count].view(torch.uint8).clone(), keys.clone())
+            if base is None:
+                base = got
+            else:
+                assert torch.equal(got[0], base[0]) and torch.equal(got[1], base[1]), (ew, pair)
+    sc.set_l1_variant(0, -1)
+
+
 def _q_weights(pz, models, h1=1024, h2=512):
     ws = [puzzles.q_mlp_weights(pz.state_len * pz.num_values, pz.fanout, h1, h2, model_idx=i) for i in range(models)]
     rng = np.random.default_rng(17)
