@@ -373,7 +373,7 @@ typedef struct MgbsMlpConfig {
   /* dtype 2 (NVFP4: E2M1 elements, one E4M3 factor per 16 elements, one float32 scale per tensor): layer 1 runs as for
    * dtype 1 (w1, s1, h1, act_inv_scale as above) and its e4m3 activations are re-quantised to NVFP4; layer 2 runs on
    * the block-scaled 4-bit tensor-core path.  w2 then holds packed E2M1 [hidden, hidden / 2] bytes (even K in the low
-   * nibble), sf_w2 its block factors in tiles [column chunk of 128][K-block of 256][step of 64]
+   * nibble), sf_w2 its block factors in tiles [chunk of 256 rows][K-block of 256][group of 128 rows][step of 64]
    * [512 B: row r at (r % 32) * 16 + (r / 32) * 4 + block], s2[n] = (tensor scale of W2) * (tensor scale of the
    * activations); h1q / sf_h1 are the scorer's own buffers: packed activations [rows_pad, hidden / 2] and their
    * factors [rows_pad / 128][hidden / 256][4][512 B]; act4_inv_global = 1 / (tensor scale of the activations). */
@@ -393,7 +393,9 @@ int mgbs_mlp_destroy(MgbsMlp* m);
  * activations; 0 = separate one-hot kernel + plain GEMM with per-thread stores (kept for comparison). */
 int mgbs_mlp_set_l1_mode(MgbsMlp* m, int32_t fused);
 /* Layer 2 + head implementation: 1 (default where the device can co-schedule CTA pairs) = thread-block clusters of
- * two sharing each weight block (tcgen05 cta_group::2); 0 = one CTA per 128-row tile (kept for comparison). */
+ * two sharing each weight block (tcgen05 cta_group::2); 0 = one CTA per 128-row tile (kept for comparison).
+ * NVFP4 (dtype 2): 1 (default) = 256-column accumulator tiles with the block-factor copies on a thread of their own;
+ * 0 = 128-column tiles with two accumulators. */
 int mgbs_mlp_set_head_mode(MgbsMlp* m, int32_t pair);
 /* Layer-1 kernel variant for tuning: epilogue_warps 4 or 8 of the kernel's 12 worker warps (the others build the
  * one-hot operand; 0 = default for the operand type), pair = thread-block clusters of two sharing the weight tiles

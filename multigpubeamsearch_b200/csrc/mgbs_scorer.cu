@@ -417,14 +417,14 @@ k_mlp_head_pair(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 // Layer 1 with the one-hot operand built in shared memory.
 //
 // out[row, :] = bf16(relu(onehot(child[row]) * W1^T + b1)).  The A operand is never materialised in global
-// memory.  Eight producer warps build the 128 x 64 bf16 K-blocks of the one-hot matrix straight into the
-// 128-byte-swizzled A slots the tensor core reads.  When the whole one-hot tile fits the six A slots (K <= 384) each
-// K-block is built once per M-tile and reused by the four N-chunks; otherwise the slots form a ring and blocks are
-// rebuilt per N-chunk.  Each of four producer warp pairs works on every fourth block by itself (each warp zeroes its 64 rows = 8 KB with conflict-free 16-byte stores,
-// then sets the ones of two rows per lane with independent predicated stores), so four K-blocks are in production at any time and
-// the latency of one block is hidden behind the others.  W1 K-blocks stream by TMA through a separate 3-stage
-// ring.  The epilogue packs the activated tile to bf16 in a swizzled staging box and writes it with TMA stores
-// (full 128-byte rows instead of per-thread row segments).
+// memory.  The producer warps build the 128 x 64 bf16 K-blocks of the one-hot matrix straight into the
+// 128-byte-swizzled A slots the tensor core reads: with the value-major column order every 16-byte chunk is a byte
+// compare of two words of the child row, written with conflict-free 16-byte stores.  When the whole one-hot tile
+// fits the six A slots (K <= 384) each K-block is built once per M-tile and reused by the four N-chunks; otherwise
+// the slots form a ring and blocks are rebuilt per N-chunk.  Four producer groups each work on every fourth block,
+// so four K-blocks are in production at any time and the latency of one block is hidden behind the others.  W1
+// K-blocks stream by TMA through a separate 3-stage ring.  The epilogue packs the activated tile to bf16 in
+// swizzled staging boxes private to each warp and writes them with TMA stores.
 //
 // Warps: 0 = TMA (W1), 1 = MMA + TMEM owner, then EW epilogue warps, then 12 - EW one-hot producer warps.
 // ------------------------------------------------------------------------------------------------
@@ -477,14 +477,14 @@ __global__ void __launch_bounds__(L1_THREADS, 1)
 k_mlp_l1(const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmOut, L1Args g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint8_t* a_ring = smem;                                   // 4 x 16 KB, 1024-aligned
+  uint8_t* a_ring = smem;                                   // 6 x 16 KB, 1024-aligned
   uint8_t* b_ring = a_ring + L1_A_STAGES * A_BYTES;         // 3 x 32 KB, or 6 x 16 KB for CTA pairs
   constexpr int NBS = PAIR ? 2 * L1_B_STAGES : L1_B_STAGES; // stages of the weight ring
   constexpr int BSB = PAIR ? B_BYTES / 2 : B_BYTES;         // bytes per stage
-  uint8_t* staging = b_ring + L1_B_STAGES * B_BYTES;        // 2 x 16 KB
+  uint8_t* staging = b_ring + L1_B_STAGES * B_BYTES;        // 16 KB: the epilogue warps' private boxes
   uint8_t* child_s = staging + L1_STAGING;
   uint64_t* bars = reinterpret_cast<uint64_t*>(((uintptr_t)(child_s + BM * L1_CHILD_PITCH) + 7) & ~(uintptr_t)7);
-  // barriers: a_full[4], a_empty[4], b_full[3], b_empty[3], tmem_full[2], tmem_empty[2], drain
+  // barriers: a_full[A], a_empty[A], b_full[NBS], b_empty[NBS], tmem_full[2], tmem_empty[2], drain (A = L1_A_STAGES)
   constexpr int NB = 2 * L1_A_STAGES + 2 * NBS + 5;
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(bars + NB);
   const uint32_t bar0 = smem_u32(bars);
@@ -1004,12 +1004,14 @@ struct MgbsMlp {
   CUtensorMap tm_w1h[MGBS_MAX_MODELS];  // W1 likewise
   CUtensorMap tm_h1q, tm_w2q[MGBS_MAX_MODELS];  // NVFP4: packed activations and weights as byte tensors
   CUtensorMap tm_h1qw;                          // packed activations, store boxes of one warp: 32 rows x 64 bytes
+  CUtensorMap tm_w2qw[MGBS_MAX_MODELS];         // packed weights in boxes of 256 rows (the wide head kernel)
   int pair_clusters = 0;                // CTA pairs that can be resident at once (0: pairs unavailable)
   int l1_pair_clusters = 0;             // the same for the layer-1 kernel
   bool head_pair = true;
   bool fused_l1 = true;
   bool fused_quant = true;  // NVFP4: the layer-1 epilogue writes packed 4-bit activations itself
   int l1_ew = 0, l1_pair = -1;  // layer-1 kernel variant: 0 / -1 = chosen by operand type
+  bool f4_wide = true;          // NVFP4 head: 256-column tiles (see mgbs_nvfp4.cu)
   bool profile = false;
   cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
 };
@@ -1078,6 +1080,7 @@ int mgbs_mlp_create(const MgbsMlpConfig* cfg, MgbsMlp** out) {
     if (f4) {
       if (!rc && !c.sf_w2[i]) rc = MGBS_ERR_ARG;
       if (!rc) rc = make_map(&m->tm_w2q[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden / 2, 128, 1);
+      if (!rc) rc = make_map(&m->tm_w2qw[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden / 2, 256, 1);
       continue;
     }
     if (!rc) rc = make_map(&m->tm_w2[i], c.w2[i], (uint64_t)c.hidden, (uint64_t)c.hidden, mgbs::BN, eb);
@@ -1139,6 +1142,10 @@ int mgbs_mlp_destroy(MgbsMlp* m) {
 
 int mgbs_mlp_set_head_mode(MgbsMlp* m, int32_t pair) {
   if (!m) return MGBS_ERR_ARG;
+  if (m->cfg.dtype == 2) {  // NVFP4: 1 = the head with 256-column tiles, 0 = 128-column tiles and two accumulators
+    m->f4_wide = pair != 0;
+    return 0;
+  }
   if (pair && m->pair_clusters < 1) return MGBS_ERR_UNSUPPORTED;
   m->head_pair = pair != 0;
   return 0;
@@ -1295,7 +1302,7 @@ int mgbs_mlp_enqueue(void* user, const uint8_t* children, const uint32_t* count_
       h.out_q = c.q;
       h.accumulate_q = i > 0 ? 1 : 0;
       h.err = c.err;
-      MGBS_SC_TRY(launch_head_nvfp4(m->tm_h1q, m->tm_w2q[i], h, m->sms, st));
+      MGBS_SC_TRY(launch_head_nvfp4(m->tm_h1q, m->tm_w2q[i], m->tm_w2qw[i], h, m->sms, st, m->f4_wide ? 1 : 0));
     } else if (m->head_pair && m->pair_clusters > 0) {
       cudaLaunchConfig_t lc;
       memset(&lc, 0, sizeof(lc));

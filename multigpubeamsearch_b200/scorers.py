@@ -50,7 +50,7 @@ def e2m1_codes(x: np.ndarray) -> np.ndarray:
 def nvfp4_quantize_weights(w: np.ndarray):
     """NVFP4 form of a weight matrix [N, K] (N a multiple of 256, K of 256) for the block-scaled tensor-core path:
     (packed E2M1 bytes [N, K/2] with even K in the low nibble, block factors as bytes in the kernel's tile order
-    [N/128][K/256][4 steps][512], tensor scale)."""
+    [N/256][K/256][2 groups of 128 rows][4 steps][512], tensor scale)."""
     w = np.ascontiguousarray(w, dtype=np.float32)
     n, k = w.shape
     if n % 256 or k % 256:
@@ -64,9 +64,11 @@ def nvfp4_quantize_weights(w: np.ndarray):
     scaled = np.where(step > 0, blocks / np.where(step > 0, step, 1.0), 0.0)
     codes = e2m1_codes(scaled).reshape(n, k)
     packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).astype(np.uint8)
-    # factors: row r of chunk c (128 rows), K-block kb, step st, block j -> tile (c, kb, st) byte (r % 32) * 16 + (r // 32) * 4 + j
-    sfb = sf8.view(torch.uint8).numpy().reshape(n // 128, 4, 32, k // 256, 4, 4)  # [c, r1, r0, kb, st, j]
-    sfb = np.ascontiguousarray(sfb.transpose(0, 3, 4, 2, 1, 5))                    # [c, kb, st, r0, r1, j]
+    # factors: row r of group g (128 rows) of chunk c (256 rows), K-block kb, step st, block j ->
+    # tile (c, kb, g, st) byte (r % 32) * 16 + (r // 32) * 4 + j
+    # the two 128-row groups of a 256-row chunk sit side by side, so one K-block of a 256-column tile is one 4 KB run
+    sfb = sf8.view(torch.uint8).numpy().reshape(n // 256, 2, 4, 32, k // 256, 4, 4)  # [c, g, r1, r0, kb, st, j]
+    sfb = np.ascontiguousarray(sfb.transpose(0, 4, 1, 5, 3, 2, 6))                    # [c, kb, g, st, r0, r1, j]
     return np.ascontiguousarray(packed), sfb.reshape(-1).copy(), float(tscale)
 
 

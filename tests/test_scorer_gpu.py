@@ -253,6 +253,26 @@ def test_nvfp4_scorer_within_tolerance(name, count, wscale, fused):
     assert np.array_equal(keys.cpu().numpy()[perm], keys2.cpu().numpy())
 
 
+def test_nvfp4_head_variants_agree():
+    """The two forms of the block-scaled head (256-column tiles with one accumulator, 128-column tiles with two) read
+    the same quantised operands: their outputs differ only by float32 summation order in the epilogue."""
+    pz = puzzles.by_name("rand54")
+    count = 30000 + 55
+    w = puzzles.mlp_weights(pz.state_len * pz.num_values, 1024)
+    sc = scorers.MLPValueScorer(w, pz.state_len, 64, pz.num_values, max_rows=count, dtype="nvfp4")
+    dev = torch.from_numpy(padded(children_of(pz, count, seed=31), 64)).cuda()
+    qs = []
+    for wide in (True, False):
+        sc.set_head_mode(wide)
+        sc.score(dev)
+        torch.cuda.synchronize()
+        assert sc.error_code() == 0, wide
+        qs.append(sc.last_q(count).cpu().numpy().copy())
+    sc.set_head_mode(True)
+    scale = float(np.abs(qs[1]).max())
+    assert np.abs(qs[0] - qs[1]).max() <= 1e-5 * max(scale, 1.0), (np.abs(qs[0] - qs[1]).max(), scale)
+
+
 def test_nvfp4_ensemble_within_tolerance():
     """Three members (the large-frontier configuration's scorer): the members' head outputs add up in one buffer."""
     pz = puzzles.puzzle96()
