@@ -15,6 +15,7 @@ resident in HBM (CUDA events around each step, max over ranks, L2 flushed betwee
 of at least a second of steps so that every N is measured at its sustained clocks.  ``e2e`` = the same metric
 through the host-facing calls load_frontier -> step -> frontier with pinned host buffers inside the timed region.
 ``parity_check`` = an untimed Hamming-scored depth of the same N-rank engine compared with the CPU oracle.
+``fp8`` / ``nvfp4`` = short extra passes of the same steps with the scorer in E4M3 and in NVFP4.
 ``--impl reference`` times the PyTorch-CPU restatement of the step on the host cores on the same frontier size.
 
 Other cases (one JSON line each, no contract keys): c4 transformer ensemble, c5 large frontier with three MLPs,
@@ -459,32 +460,37 @@ def run_ours(args):
     del engine, sc, job
     torch.cuda.empty_cache()
 
-    # ---- the same steps with the scorer in FP8 (E4M3 operands, per-channel scales): short extra pass ----
-    fp8 = None
-    if args.dtype == "bf16" and not args.no_fp8:
-        j8 = Job(pz, world, rank, local_rank, beam, 64, scorer_dtype="fp8")
-        j8.saturate(start)
-        j8.timed_steps(W, flush)
-        k8 = max(3, min(K, 20))
-        r8 = j8.measure(k8, flush)
-        j8.scorer.profile(True)
-        j8.engine.enable_step_timers(True)
+    # ---- the same steps with the scorer in FP8 (E4M3 operands, per-channel scales) and NVFP4: short extra passes ----
+    def quantised_pass(dtype, label, kernels):
+        jq = Job(pz, world, rank, local_rank, beam, 64, scorer_dtype=dtype)
+        jq.saturate(start)
+        jq.timed_steps(W, flush)
+        kq = max(3, min(K, 20))
+        rq = jq.measure(kq, flush)
+        jq.scorer.profile(True)
+        jq.engine.enable_step_timers(True)
         g1, g2 = [], []
         for _ in range(5):
-            j8.engine.step()
-            j8.engine.step_timing()
-            t8 = j8.scorer.profile_read()
-            g1.append(t8["gemm1_ms"])
-            g2.append(t8["gemm2_ms"])
-        j8.scorer.profile(False)
-        j8.engine.enable_step_timers(False)
-        fp8 = {"value": r8["cands"] / (r8["total_ms"] * 1e-3), "unit": UNIT, "ms_per_step": r8["total_ms"] / k8,
-               "steps": k8, "status_bits": r8["status_bits"], "scorer_err": r8["scorer_err"],
-               "dtype": "fp8 e4m3 operands, fp32 accumulation",
-               "kernel_ms": {"k_mlp_l1<1,8,0>": statistics.mean(g1), "k_mlp_head_pair<1>": statistics.mean(g2)}}
-        j8.close()
-        del j8
+            jq.engine.step()
+            jq.engine.step_timing()
+            tq = jq.scorer.profile_read()
+            g1.append(tq["gemm1_ms"])
+            g2.append(tq["gemm2_ms"])
+        jq.scorer.profile(False)
+        jq.engine.enable_step_timers(False)
+        out = {"value": rq["cands"] / (rq["total_ms"] * 1e-3), "unit": UNIT, "ms_per_step": rq["total_ms"] / kq,
+               "steps": kq, "status_bits": rq["status_bits"], "scorer_err": rq["scorer_err"], "dtype": label,
+               "kernel_ms": {kernels[0]: statistics.mean(g1), kernels[1]: statistics.mean(g2)}}
+        jq.close()
+        del jq
         torch.cuda.empty_cache()
+        return out
+
+    fp8 = nvfp4 = None
+    if args.dtype == "bf16" and not args.no_fp8:
+        fp8 = quantised_pass("fp8", "fp8 e4m3 operands, fp32 accumulation", ("k_mlp_l1<1,8,0>", "k_mlp_head_pair<1>"))
+        nvfp4 = quantised_pass("nvfp4", "layer 1 e4m3 operands with NVFP4 output; layer 2 NVFP4 (E2M1, E4M3 block-16 factors)",
+                               ("k_mlp_l1<1,8,0,1>", "k_mlp_head_nvfp4_wide"))
 
     # ---- N > 1: the sharded reference configuration itself (global beam 262 144 on these N ranks) ----
     c3 = None
@@ -540,6 +546,7 @@ def run_ours(args):
                     "steps": e2e_steps},
             "parity_check": parity,
             "fp8": fp8,
+            "nvfp4": nvfp4,
             "c3": c3,
             "gpu_launches": launches_per_step * K,
             "clocks": clocks_main,
@@ -713,7 +720,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default="c2", choices=["c2", "c4", "c5", "c2q", "scorer"])
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8", "nvfp4"], help="scorer operand type of the headline run")
-    ap.add_argument("--no-fp8", action="store_true", help="skip the short extra FP8 pass")
+    ap.add_argument("--no-fp8", action="store_true", help="skip the short extra FP8 and NVFP4 passes")
     ap.add_argument("--no-c3", action="store_true", help="N > 1: skip the extra pass at global beam 262 144")
     ap.add_argument("--no-parity", action="store_true", help="skip the untimed oracle check")
     ap.add_argument("--no-cpu", action="store_true", help="N = 1: skip the CPU baseline leg")
