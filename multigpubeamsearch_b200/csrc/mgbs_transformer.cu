@@ -27,7 +27,7 @@ namespace mgbs {
 // per output tile the epilogue (bias, GELU, bf16 packing) costs more instructions than the tensor core needs cycles.
 constexpr int TF_THREADS = 320;
 constexpr int TF_STAGES = 3;
-constexpr int TF_STAGING = 4 * A_BYTES;  // two 128 x 64 bf16 boxes per column half
+constexpr int TF_STAGING = 4 * A_BYTES;  // eight epilogue warps x two private boxes of 32 rows x 128 bytes
 constexpr int TF_SMEM = TF_STAGES * STAGE_BYTES + TF_STAGING + 1024 + 256;
 
 enum { TF_EPI_STORE = 0, TF_EPI_STORE_GELU = 1, TF_EPI_RESID = 2 };
@@ -50,7 +50,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // C = A * W^T (+ bias) with A [rows, K] and W [N, K] bf16, K-major, both by TMA.
-// TF_EPI_STORE / _GELU: bf16 output through a swizzled staging box and TMA stores (tmOut: [rows, N] bf16).
+// TF_EPI_STORE / _GELU: bf16 output through swizzled staging boxes and TMA stores (tmOut: [rows, N] bf16, boxes of 32 rows).
 // TF_EPI_RESID: resid[row, n] += acc + bias[n] in float32 through TMA reduce-add (tmOut: [rows, N] float32).
 // F8 = 1: both operands e4m3 (kind::f8f6f4, 128-element K-blocks), accumulators multiplied by col_scale; the GELU
 // variant then also writes e4m3 (one 128-column box per epilogue half), the plain store variant still writes bf16.
@@ -146,7 +146,11 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
   } else {
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;              // which 128 columns of the accumulator
-    const int et = ((warp - 2) & 3) * 32 + lane;   // 0..127 inside this half's group
+    // Each warp stages its 32 rows in two private 4 KB boxes (32 rows x 128 bytes) and alternates between them: no
+    // barrier between warps, sixteen TMA operations in flight per CTA.  (A TMA store or reduce holds its box for
+    // well over a thousand cycles; with four 16 KB boxes shared by the warps of a column half, behind two barriers
+    // per box, the epilogue was what these GEMMs waited for.)
+    uint8_t* mybox = staging + (warp - 2) * 8192;
     const uint32_t r = (uint32_t)(quad * 32 + lane);
     uint32_t acc_it = 0, box_it = 0;
     bool ok = true;
@@ -165,9 +169,9 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           // 128-byte rows, instead of as 16-byte accesses to 32 different rows per warp instruction
 #pragma unroll 1
           for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32, ++box_it) {
-            uint8_t* box = staging + (half * 2 + (box_it & 1u)) * A_BYTES;
-            if (et == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-            asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+            uint8_t* box = mybox + (box_it & 1u) * 4096;
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
             uint32_t v[32];
             tc_ld32(taddr + c0, v);
             tc_wait_ld();
@@ -182,12 +186,12 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
               x.y = row_ok ? fmaf(__uint_as_float(v[4 * q + 1]), cq.y, bq.y) : 0.f;
               x.z = row_ok ? fmaf(__uint_as_float(v[4 * q + 2]), cq.z, bq.z) : 0.f;
               x.w = row_ok ? fmaf(__uint_as_float(v[4 * q + 3]), cq.w, bq.w) : 0.f;
-              *reinterpret_cast<float4*>(box + swz128(r, (uint32_t)(q * 16))) = x;
+              *reinterpret_cast<float4*>(box + swz128((uint32_t)lane, (uint32_t)(q * 16))) = x;
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
-            if (et == 0) {
-              tma_reduce_add_2d(&tmOut, smem_u32(box), n0, row0);
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_2d(&tmOut, smem_u32(box), n0, row0 + quad * 32);
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
           }
@@ -196,9 +200,9 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
           constexpr int BOXC = OUT8 ? 128 : 64;                   // columns per 128-byte box row
 #pragma unroll 1
           for (int gcol = half * (BN / 2); gcol < (half + 1) * (BN / 2); gcol += BOXC, ++box_it) {
-            uint8_t* box = staging + (half * 2 + (box_it & 1u)) * A_BYTES;
-            if (et == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-            asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
+            uint8_t* box = mybox + (box_it & 1u) * 4096;
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
 #pragma unroll
             for (int sub = 0; sub < BOXC / 32; ++sub) {
               uint32_t v[32];
@@ -230,7 +234,7 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 }
 #pragma unroll
                 for (int q = 0; q < 2; ++q) {
-                  const uint32_t off = swz128(r, (uint32_t)(sub * 32 + q * 16));
+                  const uint32_t off = swz128((uint32_t)lane, (uint32_t)(sub * 32 + q * 16));
                   *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
                 }
               } else {
@@ -242,15 +246,15 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
                 }
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                  const uint32_t off = swz128(r, (uint32_t)(sub * 64 + q * 16));
+                  const uint32_t off = swz128((uint32_t)lane, (uint32_t)(sub * 64 + q * 16));
                   *reinterpret_cast<uint4*>(box + off) = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
                 }
               }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            asm volatile("bar.sync %0, 128;" ::"r"(1 + half) : "memory");
-            if (et == 0) {
-              tma_store_2d(&tmOut, smem_u32(box), nc * BN + gcol, row0);
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmOut, smem_u32(box), nc * BN + gcol, row0 + quad * 32);
               asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             }
           }
@@ -260,7 +264,7 @@ k_tf_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUten
         if (lane == 0) mbar_arrive(tempty_bar(b));
       }
     }
-    if (et == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
@@ -580,7 +584,8 @@ struct MgbsTf {
   int64_t mb_rows_pad = 0;  // rounded up to 128
   int n_micro = 0;
   CUtensorMap tm_y, tm_qkv, tm_att, tm_hid;  // activations (load as A operand / store as output)
-  CUtensorMap tm_x;                          // float32 residual stream (reduce-add target)
+  CUtensorMap tm_qkv_st, tm_hid_st;          // qkv and hid as store targets: boxes of 32 rows (one warp's rows)
+  CUtensorMap tm_x_st;                       // float32 residual stream (reduce-add target), boxes of 32 rows
   CUtensorMap tm_wqkv[MGBS_TF_MAX_ENCODERS][MGBS_TF_MAX_LAYERS], tm_wo[MGBS_TF_MAX_ENCODERS][MGBS_TF_MAX_LAYERS],
       tm_w1[MGBS_TF_MAX_ENCODERS][MGBS_TF_MAX_LAYERS], tm_w2[MGBS_TF_MAX_ENCODERS][MGBS_TF_MAX_LAYERS];
 };
@@ -614,9 +619,11 @@ int mgbs_tf_create(const MgbsTfConfig* cfg, MgbsTf** out) {
   const int eb = c.dtype == 1 ? 1 : 2;  // bytes per GEMM operand element
   int rc = mgbs::make_map(&t->tm_y, c.y, R, 256, mgbs::BM, eb);
   if (!rc) rc = mgbs::make_map_bf16(&t->tm_qkv, c.qkv, R, 768, mgbs::BM);
-  if (!rc) rc = mgbs::make_map(&t->tm_x, c.x, R, 256, mgbs::BM, 4);
   if (!rc) rc = mgbs::make_map(&t->tm_att, c.att, R, 256, mgbs::BM, eb);
   if (!rc) rc = mgbs::make_map(&t->tm_hid, c.hid, R, (uint64_t)c.ffn, mgbs::BM, eb);
+  if (!rc) rc = mgbs::make_map_bf16(&t->tm_qkv_st, c.qkv, R, 768, 32);
+  if (!rc) rc = mgbs::make_map(&t->tm_hid_st, c.hid, R, (uint64_t)c.ffn, 32, eb);
+  if (!rc) rc = mgbs::make_map(&t->tm_x_st, c.x, R, 256, 32, 4);
   for (int e = 0; e < c.encoders && !rc; ++e) {
     if (!c.tok_emb[e] || !c.pos_emb[e] || !c.lnf_g[e] || !c.lnf_b[e] || !c.w_head[e]) rc = MGBS_ERR_ARG;
     for (int l = 0; l < c.layers && !rc; ++l) {
@@ -682,35 +689,35 @@ int mgbs_tf_enqueue(void* user, const uint8_t* children, const uint32_t* count_d
         if (f8) {
           k_tf_layernorm<1><<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln1_g, L.ln1_b, c.y, L.inv_y1);
           g.col_scale = L.cs_qkv;
-          k_tf_gemm<TF_EPI_STORE, 1><<<gg, gb, TF_SMEM, st>>>(t->tm_y, t->tm_wqkv[e][l], t->tm_qkv, g);
+          k_tf_gemm<TF_EPI_STORE, 1><<<gg, gb, TF_SMEM, st>>>(t->tm_y, t->tm_wqkv[e][l], t->tm_qkv_st, g);
           k_tf_attention<1><<<t->sms * 2, TF_ATT_WARPS * 32, TF_ATT_SMEM, st>>>(qkv, count_dev, T, off, t->mb_rows, c.att, L.inv_att);
         } else {
           k_tf_layernorm<0><<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln1_g, L.ln1_b, c.y, 1.f);
-          k_tf_gemm<TF_EPI_STORE, 0><<<gg, gb, TF_SMEM, st>>>(t->tm_y, t->tm_wqkv[e][l], t->tm_qkv, g);
+          k_tf_gemm<TF_EPI_STORE, 0><<<gg, gb, TF_SMEM, st>>>(t->tm_y, t->tm_wqkv[e][l], t->tm_qkv_st, g);
           k_tf_attention<0><<<t->sms * 2, TF_ATT_WARPS * 32, TF_ATT_SMEM, st>>>(qkv, count_dev, T, off, t->mb_rows, c.att, 1.f);
         }
         g.n_total = 256; g.k_total = 256; g.bias = L.bo;
         if (f8) {
           g.col_scale = L.cs_o;
-          k_tf_gemm<TF_EPI_RESID, 1><<<gg, gb, TF_SMEM, st>>>(t->tm_att, t->tm_wo[e][l], t->tm_x, g);
+          k_tf_gemm<TF_EPI_RESID, 1><<<gg, gb, TF_SMEM, st>>>(t->tm_att, t->tm_wo[e][l], t->tm_x_st, g);
           k_tf_layernorm<1><<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln2_g, L.ln2_b, c.y, L.inv_y2);
         } else {
-          k_tf_gemm<TF_EPI_RESID, 0><<<gg, gb, TF_SMEM, st>>>(t->tm_att, t->tm_wo[e][l], t->tm_x, g);
+          k_tf_gemm<TF_EPI_RESID, 0><<<gg, gb, TF_SMEM, st>>>(t->tm_att, t->tm_wo[e][l], t->tm_x_st, g);
           k_tf_layernorm<0><<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, L.ln2_g, L.ln2_b, c.y, 1.f);
         }
         g.n_total = c.ffn; g.k_total = 256; g.bias = L.b1;
         if (f8) {
           g.col_scale = L.cs_1; g.out_inv_scale = L.inv_hid;
-          k_tf_gemm<TF_EPI_STORE_GELU, 1><<<gg, gb, TF_SMEM, st>>>(t->tm_y, t->tm_w1[e][l], t->tm_hid, g);
+          k_tf_gemm<TF_EPI_STORE_GELU, 1><<<gg, gb, TF_SMEM, st>>>(t->tm_y, t->tm_w1[e][l], t->tm_hid_st, g);
         } else {
-          k_tf_gemm<TF_EPI_STORE_GELU, 0><<<gg, gb, TF_SMEM, st>>>(t->tm_y, t->tm_w1[e][l], t->tm_hid, g);
+          k_tf_gemm<TF_EPI_STORE_GELU, 0><<<gg, gb, TF_SMEM, st>>>(t->tm_y, t->tm_w1[e][l], t->tm_hid_st, g);
         }
         g.n_total = 256; g.k_total = c.ffn; g.bias = L.b2;
         if (f8) {
           g.col_scale = L.cs_2;
-          k_tf_gemm<TF_EPI_RESID, 1><<<gg, gb, TF_SMEM, st>>>(t->tm_hid, t->tm_w2[e][l], t->tm_x, g);
+          k_tf_gemm<TF_EPI_RESID, 1><<<gg, gb, TF_SMEM, st>>>(t->tm_hid, t->tm_w2[e][l], t->tm_x_st, g);
         } else {
-          k_tf_gemm<TF_EPI_RESID, 0><<<gg, gb, TF_SMEM, st>>>(t->tm_hid, t->tm_w2[e][l], t->tm_x, g);
+          k_tf_gemm<TF_EPI_RESID, 0><<<gg, gb, TF_SMEM, st>>>(t->tm_hid, t->tm_w2[e][l], t->tm_x_st, g);
         }
       }
       k_tf_pool_head<<<ew_grid, 256, 0, st>>>(c.x, count_dev, T, off, t->mb_rows, c.lnf_g[e], c.lnf_b[e], c.w_head[e],
