@@ -70,6 +70,11 @@ def make_default_config() -> Dict[str, Any]:
         # world > 1: "peer" = candidates stored straight into the owner's buckets over NVLink peer mappings and
         # histograms reduced in-kernel; "nccl" = grouped send/recv + all-reduce (the reference's scheme)
         "exchange": os.environ.get("MGBS_EXCHANGE", "peer"),
+        # where the survivors of a depth live: "owner" = on the rank that owns their hash (no extra traffic; uniform
+        # hashes keep the ranks within a fraction of a percent of each other), "balanced" = the reference's final
+        # placement (production_v6_dispatcher.py:584-588): rows are moved after every depth so that every rank holds
+        # exactly its share
+        "placement": os.environ.get("MGBS_PLACEMENT", "owner"),
         # Knobs of the reference's tile pipeline (beam_engine.py:44-58, 68-109).  They are accepted so that a
         # reference configuration loads unchanged; this engine has no expand tiles, score ring or net ring (one
         # depth is one fixed-shape launch sequence), so they do not change what runs:
@@ -315,6 +320,9 @@ class BeamEngine:
             c.sym_bytes = int(b["sym"].numel())
             c.tickets = p("tickets")
         c.peer_poll_limit = int(cfg.get("peer_poll_limit", 0) or 0)
+        if str(cfg.get("placement", "owner")) not in ("owner", "balanced"):
+            raise RuntimeError("placement must be 'owner' or 'balanced'")
+        self._balanced = str(cfg.get("placement", "owner")) == "balanced" and int(cfg["world_size"]) > 1
         pipeline = str(cfg.get("select_pipeline", "persistent"))
         if pipeline not in ("persistent", "staged"):
             raise RuntimeError("select_pipeline must be 'persistent' or 'staged'")
@@ -606,6 +614,59 @@ class BeamEngine:
             self._timing = {"total_cuda_event_ms": self._events[0].elapsed_time(self._events[1])}
         self._ctrl.depth += 1  # host shadow; status() refreshes it from the device
 
+    def rebalance_frontier(self) -> List[int]:
+        """Even out the current frontier across the ranks and return the rows each rank holds afterwards.
+
+        The reference's final placement (production_v6_dispatcher.py:584-588): with the survivors numbered g = 0..K-1
+        in rank-major order, row g goes to rank min(g * W // K, W - 1) at local index g - ceil(K * rank / W); its
+        kernels (beam_kernels_final.cu:18-55) ship requests and rows in two all-to-alls with host regrouping between
+        them.  Here the rows, their scores and their back-pointers (the history entries of the depth that made
+        them, so that paths still reconstruct) move in three ``all_to_all_single`` calls; the order is kept, so a
+        rank's rows are one contiguous run of the global order.  Collective and synchronous: every rank calls it
+        between steps.  Off the hot path by design: hash-owner placement already keeps the ranks within a fraction
+        of a percent of each other."""
+        world, rank = int(self.cfg["world_size"]), int(self.cfg["rank"])
+        c = self._read_ctrl()
+        parity = c.depth & 1
+        n = int(c.frontier_count[parity])
+        if world == 1:
+            return [n]
+        dev = self.buffers["ctrl"].device
+        torch.cuda.synchronize(dev)
+        counts_t = torch.zeros((world,), dtype=torch.int64, device=dev)
+        mine = torch.tensor([n], dtype=torch.int64, device=dev)
+        dist.all_gather_into_tensor(counts_t, mine)
+        counts = [int(x) for x in counts_t.tolist()]
+        total = sum(counts)
+        base = [sum(counts[:q]) for q in range(world + 1)]
+        lo = [-(-total * q // world) for q in range(world + 1)]  # ceil(K q / W): first global index of rank q
+
+        def overlap(a0, a1, b0, b1):
+            return max(0, min(a1, b1) - max(a0, b0))
+
+        send = [overlap(base[rank], base[rank + 1], lo[q], lo[q + 1]) for q in range(world)]
+        recv = [overlap(base[q], base[q + 1], lo[rank], lo[rank + 1]) for q in range(world)]
+        new_n = sum(recv)
+        if new_n > int(self._sizes["k_work"]):
+            raise RuntimeError("rebalance_frontier: the balanced share exceeds the frontier capacity")
+        rows = self._frontier_tensor(parity)
+        scores = self.buffers["score_current" if parity == 0 else "score_next"]
+        hist = self.buffers["history_payload"]
+        layer = hist[(c.depth - 1) % hist.shape[0]] if c.depth >= 1 else None
+        moved = []
+        for t in (rows, scores) + ((layer,) if layer is not None else ()):
+            out = torch.empty((new_n,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev)
+            dist.all_to_all_single(out, t[:n].contiguous(), output_split_sizes=recv, input_split_sizes=send)
+            moved.append((t, out))
+        for t, out in moved:
+            t[:new_n].copy_(out)
+        off = _lib.MgbsCtrl.frontier_count.offset + 4 * parity
+        self.buffers["ctrl"][off:off + 4].copy_(torch.tensor([new_n], dtype=torch.int32, device=dev).view(torch.uint8))
+        torch.cuda.synchronize(dev)
+        dist.barrier()  # nobody steps (and reads a peer's frontier) before every rank holds its new rows
+        self._read_ctrl()
+        return [lo[q + 1] - lo[q] for q in range(world)]
+
     def step_current(self, histogram_period_micro: int = 8) -> None:
         """Eager step without the graph (beam_engine.cpp:1118-1134)."""
         parity = self._ctrl.depth & 1
@@ -615,7 +676,20 @@ class BeamEngine:
     def search(self, max_depth: int, histogram_period_micro: int = 8) -> Dict[str, Any]:
         """Depth loop until found / max_depth / empty frontier (beam_engine.cpp:1147-1171)."""
         rows = int(self.buffers["history_payload"].shape[0])
-        rc = self.lib.mgbs_engine_search(self._h, int(max_depth), int(self._use_graph), C.byref(self._ctrl), self._sp())
+        if self._balanced:
+            # balanced placement moves rows between depths with host-side collectives: a depth loop on the host
+            rc = 0
+            while True:
+                st = self.status()
+                if st["found"] or st["depth"] >= int(max_depth) or (st["status_bits"] & (64 | 128)):
+                    break
+                self.step()
+                if sum(self.rebalance_frontier()) == 0:
+                    break
+            if self.status()["status_bits"] & (64 | 128):
+                rc = -6
+        else:
+            rc = self.lib.mgbs_engine_search(self._h, int(max_depth), int(self._use_graph), C.byref(self._ctrl), self._sp())
         self._graph_used = self._graph_used or self._use_graph
         if rc == -6:
             # every rank's loop has returned (each wait is bounded and a rank that gives up tells the others): the

@@ -142,6 +142,64 @@ def run_scale_case(beam, exchange, pipeline="persistent"):
     del engine, buffers
 
 
+def run_balance_case():
+    """Balanced placement (the reference's final balance, production_v6_dispatcher.py:584-588): after a step the
+    survivors sit on their hash owners, unevenly; rebalance_frontier must leave rank q with exactly the rows
+    ceil(K q / W) .. ceil(K (q + 1) / W) of the rank-major order (the oracle's balance_targets), rows, scores and
+    back-pointers moved together; and a search under placement="balanced" must give the oracle's answer with a path
+    that replays."""
+    world, rank = dist.get_world_size(), dist.get_rank()
+    pz = puzzles.puzzle54()
+    beam = 3000 + 7 * world
+    _, cfg, buffers, engine = be.configure_engine(pz, world_size=world, rank=rank, global_beam_width=beam, max_depth=16,
+                                                  beta=1.2, gamma=1.25, hash_load_factor=0.45, probe_limit=256,
+                                                  placement="balanced")
+    start = pz.scramble(3, 30)
+    owner = engine.owner_of(start)
+    engine.reset_search(bytes(start), active_on_this_rank=(owner == rank))
+    for _ in range(5):
+        engine.step()  # plain steps: survivors stay on their owners
+
+    def snapshot():
+        mine = (engine.frontier(), engine.frontier_scores(), engine.frontier_payloads())
+        parts = gather_rows(mine)
+        return parts
+
+    before = snapshot()
+    shares = engine.rebalance_frontier()
+    after = snapshot()
+    total = sum(p[0].shape[0] for p in before)
+    t_rank, t_local = bo.balance_targets(total, world)
+    want_counts = [int((t_rank == q).sum()) for q in range(world)]
+    assert shares == want_counts and [p[0].shape[0] for p in after] == want_counts, (shares, want_counts)
+    for k in range(3):  # rows, scores, back-pointers: the global rank-major sequence is unchanged
+        a = np.concatenate([p[k] for p in before], axis=0)
+        b = np.concatenate([p[k] for p in after], axis=0)
+        assert np.array_equal(a, b), k
+    assert len({p[0].shape[0] for p in before}) > 1 or world == 1  # the case was uneven to begin with
+    # the step after a rebalance still matches the oracle (parents are fetched from their new places)
+    fronts = [p[0] for p in after]
+    engine.step()
+    got = gather_rows(engine.frontier())
+    want = bo.depth_step(fronts, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam)
+    assert np.array_equal(bo.sorted_rows(np.concatenate(got, axis=0)), bo.sorted_rows(want.states))
+    # whole searches with the rows rebalanced after every depth
+    for j in (1, 21, 22):
+        s = pz.scramble(j, 6)
+        res = be.run_one_search(engine, s, 10)
+        w = bo.search(s, pz.generators, pz.solved, bo.hamming_scorer(pz.solved), beam=beam, max_depth=10)
+        assert (bool(res["found"]), res["depth"]) == (bool(w.found), w.depth), (j, res["found"], res["depth"], w.found, w.depth)
+        if w.found:
+            from multigpubeamsearch_b200.solver import reconstruct_path
+            path = reconstruct_path(engine)  # collective walk-back over the ranks' history entries
+            assert path is not None and len(path) == w.depth, (j, path)
+            assert np.array_equal(bo.replay(s, pz.generators, path), pz.solved), j
+    if rank == 0:
+        print(f"BALANCE_OK world={world} rows before {[p[0].shape[0] for p in before]} after {want_counts}", flush=True)
+    engine.close()
+    dist.barrier()
+
+
 def run_late_rank_case():
     """Failure detection without any GPU fault: the last rank is late on the HOST (it sleeps before it starts its
     depth loop) and the poll limit is short, so the other ranks' waits run out.  Every rank must come back from
@@ -215,6 +273,7 @@ def main():
     engine.close()
     dist.barrier()
     del engine, buffers
+    run_balance_case()
     run_late_rank_case()
     dist.barrier()
     dist.destroy_process_group()

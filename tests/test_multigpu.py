@@ -24,3 +24,4 @@ def test_sharded_search_matches_oracle(world):
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert out.stdout.count("CASE_OK") == 10 and "SEARCH_OK" in out.stdout, out.stdout[-2000:]
     assert out.stdout.count("SCALE_OK") == 2 and "LATE_RANK_OK" in out.stdout, out.stdout[-2000:]
+    assert "BALANCE_OK" in out.stdout, out.stdout[-2000:]
