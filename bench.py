@@ -593,8 +593,10 @@ def run_case(args):
     if args.case == "c4":
         sc = scorers.TransformerValueScorer([puzzles.transformer_weights(54, 6, model_idx=i) for i in range(2)],
                                             pz.state_len, cfg["state_size_bytes"], pz.num_values,
-                                            max_rows=sizes["cand_cap"], micro_batch=32768, dtype=args.dtype)
-        scorer_name = f"transformer 2x(4 layers, d256, 8 heads, ffn 1024) {args.dtype}"
+                                            max_rows=sizes["cand_cap"], micro_batch=32768,
+                                            dtype="nvfp4_weights" if args.dtype == "nvfp4" else args.dtype)
+        scorer_name = f"transformer 2x(4 layers, d256, 8 heads, ffn 1024) {args.dtype}" + (
+            " weights on bf16 GEMMs" if args.dtype == "nvfp4" else "")
     elif args.case == "c2q":
         sc = scorers.MLPActionValueScorer(puzzles.q_mlp_weights(k1, pz.fanout, 1024, 1024), pz.state_len,
                                           cfg["state_size_bytes"], pz.num_values, pz.fanout, max_parents=sizes["k_work"])

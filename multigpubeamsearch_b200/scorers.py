@@ -90,6 +90,29 @@ def onehot_relayout(w1: np.ndarray, state_len: int, num_values: int, k1_pad: int
     return out
 
 
+_E2M1_VALUES = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], dtype=np.float32)
+
+
+def nvfp4_round_weights(w: np.ndarray) -> np.ndarray:
+    """A weight matrix [N, K] (K a multiple of 16) rounded to the NVFP4 grid and returned as float32: per block of 16
+    consecutive K elements one E4M3 factor e4m3(blockmax / 6 / tensor scale), elements E2M1, tensor scale
+    max|w| / (6 * 448).  The values the block-scaled tensor-core path would multiply with (nvfp4_quantize_weights
+    packs the same numbers)."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    n, k = w.shape
+    if k % 16:
+        raise RuntimeError("NVFP4 blocks need K to be a multiple of 16")
+    tscale = np.float32(max(float(np.abs(w).max()), 1e-30) / (6.0 * 448.0))
+    blocks = w.reshape(n, k // 16, 16)
+    amax = np.abs(blocks).max(axis=2)
+    sf = torch.from_numpy((amax / np.float32(6.0) / tscale).astype(np.float32)).to(torch.float8_e4m3fn).to(torch.float32).numpy()
+    step = (sf * tscale)[:, :, None]
+    scaled = np.where(step > 0, blocks / np.where(step > 0, step, 1.0), 0.0)
+    codes = e2m1_codes(scaled)
+    vals = np.where(codes & 8, -1.0, 1.0).astype(np.float32) * _E2M1_VALUES[codes & 7]
+    return (vals * step).reshape(n, k).astype(np.float32)
+
+
 class MgbsMlpNoAllocArgs(C.Structure):
     _fields_ = [
         ("state_len", C.c_int32), ("state_stride", C.c_int32), ("num_values", C.c_int32), ("hidden", C.c_int32),
@@ -716,7 +739,7 @@ class TransformerValueScorer:
     e4m3 activations (LayerNorm output, attention output, GELU output) with one scale per tensor.  The activation
     scales come from bounds that hold for every input (a LayerNorm row has L2 norm 16 before its gain, so
     |row . w| <= (16 max|gain| + |shift|) |w|), not from calibration data; q, k, v stay bf16 for the attention
-    kernel."""
+    kernel.  ``dtype="nvfp4_weights"`` rounds the same matrices to the NVFP4 grid and runs them on the bf16 path."""
 
     def __init__(self, encoders: Sequence[Dict], state_len: int, state_stride: int, num_values: int, max_rows: int,
                  micro_batch: int = 32768, score_offset: float = -150.0, device=None, dtype: str = "bf16"):
@@ -751,10 +774,16 @@ class TransformerValueScorer:
             self._keep.append(t)
             return t.data_ptr()
 
-        if dtype not in ("bf16", "fp8"):
-            raise RuntimeError("dtype must be 'bf16' or 'fp8'")
+        if dtype not in ("bf16", "fp8", "nvfp4_weights"):
+            raise RuntimeError("dtype must be 'bf16', 'fp8' or 'nvfp4_weights'")
         self.dtype = dtype
         fp8 = dtype == "fp8"
+        if dtype == "nvfp4_weights":
+            # the four matrices of every layer rounded to the NVFP4 grid (E2M1 elements, E4M3 block-16 factors, one
+            # tensor scale) and fed to the bf16 GEMMs: these kernels are bound by activation bytes (K = 256), so the
+            # weights' storage format does not change their time; what this gives is the numerics of NVFP4 weights
+            encoders = [dict(w, layers=[dict(L, **{k: nvfp4_round_weights(L[k]) for k in _LAYER_BF16}) for L in w["layers"]])
+                        for w in encoders]
 
         def e4m3(w, act_scale):
             """Rows of w as e4m3 with per-row scales; returns (weights ptr, column-scale ptr)."""

@@ -98,3 +98,16 @@ def test_action_scorer_modules_keep_the_reference_contract():
         raise AssertionError("an unknown score_mode must be refused")
     except RuntimeError as e:
         assert "unsupported score_mode" in str(e)
+
+
+def test_nvfp4_weight_rounding_equals_the_oracle_model():
+    """scorers.nvfp4_round_weights (what the transformer's NVFP4-weight mode feeds its GEMMs) against the oracle's
+    NVFP4 model of the same matrix, bit for bit."""
+    rng = np.random.default_rng(12)
+    for shape, scale in (((64, 256), 0.02), ((24, 1024), 1.0), ((8, 16), 5.0)):
+        w = (rng.standard_normal(shape) * scale).astype(np.float32)
+        w[0, :16] = 0.0  # an all-zero block keeps factor 0
+        got = scorers.nvfp4_round_weights(w)
+        want = bo.quantize_nvfp4(w, bo.nvfp4_tensor_scale(float(np.abs(w).max())))
+        assert np.array_equal(got, want)
+        assert np.abs(got - w).max() <= 0.26 * np.abs(w).max()  # E2M1 steps are at most a quarter of the block maximum

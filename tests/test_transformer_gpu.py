@@ -105,6 +105,35 @@ def test_transformer_fp8_on_the_benchmark_initialisation():
     assert err <= 2e-2, err
 
 
+def test_transformer_with_nvfp4_weights():
+    """The four matrices of every layer rounded to the NVFP4 grid (E2M1, E4M3 block-16 factors): tightly against a
+    float32 evaluation with the same rounded weights (the bf16 path's own tolerance), and within the stated NVFP4
+    bound (5e-2) of the unrounded float32 model, on the benchmark's initialisation."""
+    pz = puzzles.puzzle54()
+    ws = [puzzles.transformer_weights(54, 6, model_idx=i) for i in range(2)]
+    count = 500
+    sc = scorers.TransformerValueScorer(ws, 54, 64, 6, max_rows=count, micro_batch=256, dtype="nvfp4_weights")
+    rows = _states(pz, count, seed=78)
+    sc.score(torch.from_numpy(_pad(rows, 64)).cuda())
+    torch.cuda.synchronize()
+    assert sc.error_code() == 0
+    q_dev = (sc.last_q(count).cpu().numpy() + sum(float(w["b_head"]) for w in ws)) / 2
+    ws_q = []
+    for w in ws:
+        layers = []
+        for L in w["layers"]:
+            Lq = dict(L)
+            for k in ("wqkv", "wo", "w1", "w2"):
+                Lq[k] = bo.quantize_nvfp4(L[k], bo.nvfp4_tensor_scale(float(np.abs(L[k]).max())))
+            layers.append(Lq)
+        ws_q.append(dict(w, layers=layers))
+    err_model = float(np.abs(q_dev - bo.transformer_forward(rows, ws_q)).max())
+    err_ref = float(np.abs(q_dev - bo.transformer_forward(rows, ws)).max())
+    print("transformer with NVFP4 weights: vs the same rounded weights in float32", err_model, "vs float32", err_ref)
+    assert err_model <= 1e-2, err_model
+    assert err_ref <= 5e-2, err_ref
+
+
 def test_engine_with_transformer_scorer():
     pz = puzzles.puzzle54()
     beam = 512
