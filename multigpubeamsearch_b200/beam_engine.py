@@ -637,15 +637,7 @@ class BeamEngine:
         mine = torch.tensor([n], dtype=torch.int64, device=dev)
         dist.all_gather_into_tensor(counts_t, mine)
         counts = [int(x) for x in counts_t.tolist()]
-        total = sum(counts)
-        base = [sum(counts[:q]) for q in range(world + 1)]
-        lo = [-(-total * q // world) for q in range(world + 1)]  # ceil(K q / W): first global index of rank q
-
-        def overlap(a0, a1, b0, b1):
-            return max(0, min(a1, b1) - max(a0, b0))
-
-        send = [overlap(base[rank], base[rank + 1], lo[q], lo[q + 1]) for q in range(world)]
-        recv = [overlap(base[q], base[q + 1], lo[rank], lo[rank + 1]) for q in range(world)]
+        send, recv, shares = balanced_exchange_plan(counts, rank)
         new_n = sum(recv)
         if new_n > int(self._sizes["k_work"]):
             raise RuntimeError("rebalance_frontier: the balanced share exceeds the frontier capacity")
@@ -665,7 +657,7 @@ class BeamEngine:
         torch.cuda.synchronize(dev)
         dist.barrier()  # nobody steps (and reads a peer's frontier) before every rank holds its new rows
         self._read_ctrl()
-        return [lo[q + 1] - lo[q] for q in range(world)]
+        return shares
 
     def step_current(self, histogram_period_micro: int = 8) -> None:
         """Eager step without the graph (beam_engine.cpp:1118-1134)."""
@@ -820,6 +812,25 @@ class BeamEngine:
             moves.append(int(mm))
             idx = int(pp)
         return moves[::-1]
+
+
+def balanced_exchange_plan(counts: List[int], rank: int):
+    """Who sends how many rows to whom when a frontier held as ``counts[q]`` rows on rank q (numbered g = 0..K-1 in
+    rank-major order) is rebalanced so that row g lives on rank min(g * W // K, W - 1), i.e. rank q holds the run
+    ceil(K q / W) .. ceil(K (q + 1) / W) (production_v6_dispatcher.py:584-588).  Returns for ``rank``: rows it sends
+    to each rank, rows it receives from each rank (both in rank order, which is also global order), and every rank's
+    share afterwards."""
+    world = len(counts)
+    total = sum(counts)
+    base = [sum(counts[:q]) for q in range(world + 1)]
+    lo = [-(-total * q // world) for q in range(world + 1)]  # ceil(K q / W): first global index of rank q
+
+    def overlap(a0, a1, b0, b1):
+        return max(0, min(a1, b1) - max(a0, b0))
+
+    send = [overlap(base[rank], base[rank + 1], lo[q], lo[q + 1]) for q in range(world)]
+    recv = [overlap(base[q], base[q + 1], lo[rank], lo[rank + 1]) for q in range(world)]
+    return send, recv, [lo[q + 1] - lo[q] for q in range(world)]
 
 
 def create_nccl_id(ext: _Ext, cfg: Dict[str, Any]) -> bytes:

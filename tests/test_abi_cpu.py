@@ -131,3 +131,31 @@ def test_python_surface_has_the_reference_names():
     for key in ("k_expand_tile", "score_ring_depth", "net_ring_depth", "inference_parallelism",
                 "histogram_period_micro", "beta", "hash_load_factor", "probe_limit", "global_beam_width"):
         assert key in be.make_default_config(), key
+
+
+def test_balanced_exchange_plan_matches_the_reference_placement():
+    """Host arithmetic of the balanced placement against the oracle's balance_targets
+    (production_v6_dispatcher.py:584-588) on ragged, empty and tiny frontiers."""
+    from multigpubeamsearch_b200 import beam_engine as be
+    from oracle import beam_oracle as bo
+    rng = np.random.default_rng(4)
+    cases = [[5, 0, 9, 2], [0, 0, 0], [1], [0, 7], [3, 3, 3, 3, 3, 3, 3, 4]]
+    cases += [rng.integers(0, 50, size=int(w)).tolist() for w in rng.integers(1, 9, size=40)]
+    for counts in cases:
+        world, total = len(counts), sum(counts)
+        t_rank, t_local = bo.balance_targets(total, world)
+        owner_before = np.repeat(np.arange(world), counts)  # rank holding global row g before
+        plans = [be.balanced_exchange_plan(counts, r) for r in range(world)]
+        want_shares = [int((t_rank == q).sum()) for q in range(world)]
+        for r, (send, recv, shares) in enumerate(plans):
+            assert shares == want_shares
+            assert sum(send) == counts[r] and sum(recv) == want_shares[r]
+            for q in range(world):
+                # rows that sit on r and belong on q, counted straight from the reference formula
+                assert send[q] == int(((owner_before == r) & (t_rank == q)).sum()), (counts, r, q)
+                assert recv[q] == plans[q][0][r]
+        # local index after the move = position in the receiver's run
+        for g in range(total):
+            q = int(t_rank[g])
+            first = -(-total * q // world)
+            assert int(t_local[g]) == g - first
