@@ -10,14 +10,24 @@ Every function cites the reference file:line it follows.  Where the reference
 fixes a shape at compile time (state length 120, fan-out 24) the restatement
 takes the shape from its arguments; nothing else is generalised.
 
-Parity pin: ``hash64`` is checked against outputs of the reference's own
-``data_loader.hash_state_cpu`` (fixtures under tests/golden/, generated by
-tests/golden/make_golden.py), the dedup/tie-break rules against the known
-answers of the reference's stream3/stream4 smoke tests, and the threshold
-rules against the reference's ``histogram_threshold`` / ``threshold_update``
-examples.  The scorer numerics have no golden outputs in the reference
-(weights blob absent): for those, parity is unpinned and tests use a stated
-tolerance against a float32 evaluation.
+Parity pin (fixtures under tests/golden/, each with the script that made it):
+``hash64`` against outputs of the reference's ``data_loader.hash_state_cpu``
+(make_golden.py); ``mix64``, ``hash_state_120``, ``fingerprint_state_120``,
+``tie16``, ``make_best_key``, the expansion, the Hamming score, the goal
+tests, the v6 128-bit Zobrist hash and owner rule, ``candidate_better``,
+``pack_route``, ``q_to_score_key`` and the monotone ``threshold_update``
+against the reference's own scalar device and host functions compiled as host
+C++ (oracle/Makefile, make_scalar_golden.py); the residual action-value
+network, the batch-norm folding, ``MLPActionScorer`` and
+``QuantizedActionScorer`` against the reference's Python functions
+(make_residual_q_golden.py); the dedup/tie-break rules against the known
+answers of the reference's stream3/stream4 smoke tests; the threshold rules
+against the reference's ``histogram_threshold`` / ``threshold_update``
+examples.  Unpinned: which set survives a whole depth (the reference's own
+result depends on the arrival order of its atomics, so it has no single
+answer) and the numerics of the value scorers (its weights blob is absent):
+for those, parity is unpinned and tests use the deterministic rule stated
+here, respectively a stated tolerance against a float32 evaluation.
 """
 
 from __future__ import annotations
